@@ -1,0 +1,56 @@
+// C ABI of the velogb10_b200 kernel library (loaded from Python through ctypes).
+// All pointers are device pointers unless stated otherwise; every function enqueues work on `stream`
+// and returns 0 on success (a negative value for a rejected argument, a positive cudaError_t otherwise).
+#pragma once
+#include <cuda_runtime.h>
+
+// weight formats
+#define VG_WF_NVFP4 0   // e2m1 codes + e4m3 scale per 16 along K
+#define VG_WF_FP8 1     // e4m3 codes, fp32 scale per row
+#define VG_WF_F16 2     // tile-major f16 (tensor-core GEMM input made from bf16 weights)
+#define VG_WF_BF16 3    // canonical row-major bf16 (CUDA-core GEMV, embedding)
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int vg_gemm_tc(const void* wt, const float* row_scale, const void* x_f16, int x_rows, int ldx, void* out, int out_f32,
+               int M, int K, int N, int ldo, int wfmt, int splitk, int* err, cudaStream_t stream);
+int vg_gemm_tc_resident_ctas(int wfmt);
+int vg_gemm_simt(const void* wq, const void* scales, const float* row_scale, const void* x_f16, void* out, int out_f32,
+                 int M, int K, int N, int ldx, int ldo, int wfmt, cudaStream_t stream);
+
+int vg_add_rmsnorm(void* res, const void* delta, const float* w, void* out_f16, void* out_bf16, int N, int h, float eps,
+                   int plus_one, int ld_res, int ld_delta, cudaStream_t stream);
+int vg_attn_prep(const void* qkv, int ld_qkv, const float* q_norm, const float* k_norm, const int* pos, const int* slot,
+                 const int* kv_row, void* q_out, void* kc, void* vc, int N, int nh, int nkv, int hd, int rdim,
+                 int max_seq, float eps, float theta, int gated, cudaStream_t stream);
+int vg_swiglu(const void* gu, void* out_f16, int N, int I, int ld, cudaStream_t stream);
+int vg_cast_f16(const void* in, int in_is_f32, void* out_f16, long long total, cudaStream_t stream);
+int vg_embed_gather(const void* table, const void* scales, const float* row_scale, const int* tok, void* out, int N,
+                    int h, int wfmt, cudaStream_t stream);
+
+int vg_attn_decode(const void* q, const void* kc, const void* vc, const int* lens, const int* slots, const int* base,
+                   const int* path, int path_ld, float* part, int N, int nh, int nkv, int hd, int max_seq, int ns_grid,
+                   int direct, const void* gate, int ld_gate, void* out, cudaStream_t stream);
+long long vg_attn_scratch_floats(int N, int nh, int hd, int ns_grid);
+
+int vg_gdn_conv(const void* x, int ldx, float* state, const float* w, const int* in_slot, const int* parent,
+                const int* out_slot, float* out, int N, int conv_dim, int ck, int phase, cudaStream_t stream);
+int vg_gdn_step(const float* qkv, const void* proj, int ldp, int off_z, int off_b, int off_a, float* S,
+                const float* A_log, const float* dt_bias, const float* norm_w, const int* chain_start,
+                const int* chain_len, int n_chains, const int* in_slot, const int* parent, const int* out_slot,
+                void* out_f16, int nk, int nv, int kd, int vd, float eps, cudaStream_t stream);
+
+int vg_argmax(const float* logits, int N, int V, int ld, int* out, float* out_val, int idx_offset, cudaStream_t stream);
+int vg_penalty(float* logits, int N, int V, int ld, const int* toks, const int* counts, const int* n_toks, int max_toks,
+               const float* rep, const float* pres, const float* freq, cudaStream_t stream);
+int vg_nucleus(const float* logits, int N, int V, int ld, const float* temp, const int* top_k, const float* top_p,
+               const unsigned* seed, int* out_tok, int* ids, float* probs, int* n_keep, cudaStream_t stream);
+int vg_nll(const float* logits, int N, int V, int ld, const int* target, float* out, cudaStream_t stream);
+
+const char* vg_build_id(void);
+
+#ifdef __cplusplus
+}
+#endif

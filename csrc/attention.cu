@@ -1,0 +1,222 @@
+// GQA attention over the slotted KV cache: flash-decoding style split-K kernel + fixed-order merge.
+//
+// One CTA serves (column, kv head, query sub-group, split). Its 8 warps walk the split's keys in a
+// fixed interleave (warp w takes keys k0+w, k0+w+8, ...), each lane owning hd/32 dims, with an online
+// softmax per query head in fp32; the warps' (m, l, acc) are merged in warp order. The number of
+// splits is a pure function of the column's own key count, ns = clamp(len/256, 1, 32), so a column is
+// computed the same way whether it runs alone or beside 15 others (reference:
+// kernels/gpu_batch.cu:1443-1477, :1491-1606, :2151-2186). Keys at or beyond `base[col]` are addressed
+// through a per-column row list (tree / forest verify); before it, key t is cache row t.
+// The merge kernel combines the splits in index order, normalises, applies the sigmoid output gate
+// and emits the f16 input of o_proj. Prefill uses the same kernel with one split per column and the
+// gate applied directly (it is outside the batch-invariance contract).
+//
+// The partial buffer (m, l, acc[hd]) per (column, head, split) is scratch memory owned by the caller.
+#include "common.cuh"
+#include "api.h"
+
+namespace {
+using namespace vg;
+
+constexpr int NW = 8;   // warps per CTA
+
+__device__ __forceinline__ int splits_for(int len) {
+  int ns = len / 256;
+  return ns < 1 ? 1 : (ns > 32 ? 32 : ns);
+}
+
+template <int HD, int GT>
+__global__ void __launch_bounds__(NW * 32) attn_split_kernel(
+    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
+    const int* __restrict__ lens, const int* __restrict__ slots, const int* __restrict__ base,
+    const int* __restrict__ path, int path_ld, float* __restrict__ part, int nh, int nkv, int max_seq, int ns_grid,
+    float scale, int direct, const __nv_bfloat16* __restrict__ gate, int ld_gate, int gate_off, __half* __restrict__ out) {
+  constexpr int DPL = HD / 32;              // dims per lane
+  const int col = blockIdx.x;
+  const int G = nh / nkv;
+  const int nsub = G / GT;
+  const int kvh = blockIdx.y / nsub, sub = blockIdx.y % nsub;
+  const int split = blockIdx.z;
+  const int len = lens[col];
+  const int ns = direct ? 1 : splits_for(len);
+  if (split >= ns) return;
+  const int chunk = (len + ns - 1) / ns;
+  const int k0 = split * chunk;
+  const int k1 = min(len, k0 + chunk);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slot = slots[col];
+  const int kbase = base ? base[col] : len;
+  const int h0 = kvh * G + sub * GT;        // first query head of this CTA
+
+  float qf[GT][DPL];
+#pragma unroll
+  for (int g = 0; g < GT; ++g) {
+    const __nv_bfloat16* qp = q + ((size_t)col * nh + h0 + g) * HD + lane * DPL;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) qf[g][i] = __bfloat162float(qp[i]) * scale;
+  }
+  float m[GT], l[GT], acc[GT][DPL];
+#pragma unroll
+  for (int g = 0; g < GT; ++g) {
+    m[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[g][i] = 0.f;
+  }
+  const __nv_bfloat16* kslot = kc + ((size_t)slot * nkv + kvh) * (size_t)max_seq * HD;
+  const __nv_bfloat16* vslot = vc + ((size_t)slot * nkv + kvh) * (size_t)max_seq * HD;
+
+  for (int t = k0 + warp; t < k1; t += NW) {
+    const int row = t < kbase ? t : path[(size_t)col * path_ld + (t - kbase)];
+    float kf[DPL], vf[DPL];
+    if (DPL == 8) {
+      const uint4 kv4 = *reinterpret_cast<const uint4*>(kslot + (size_t)row * HD + lane * 8);
+      const uint4 vv4 = *reinterpret_cast<const uint4*>(vslot + (size_t)row * HD + lane * 8);
+      const __nv_bfloat162* kp = reinterpret_cast<const __nv_bfloat162*>(&kv4);
+      const __nv_bfloat162* vp = reinterpret_cast<const __nv_bfloat162*>(&vv4);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 a = __bfloat1622float2(kp[i]), b = __bfloat1622float2(vp[i]);
+        kf[2 * i] = a.x; kf[2 * i + 1] = a.y; vf[2 * i] = b.x; vf[2 * i + 1] = b.y;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) {
+        kf[i] = __bfloat162float(kslot[(size_t)row * HD + lane * DPL + i]);
+        vf[i] = __bfloat162float(vslot[(size_t)row * HD + lane * DPL + i]);
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < GT; ++g) {
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) s = fmaf(qf[g][i], kf[i], s);
+      s = warp_sum(s);
+      const float mn = fmaxf(m[g], s);
+      const float corr = __expf(m[g] - mn);
+      const float p = __expf(s - mn);
+      l[g] = l[g] * corr + p;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) acc[g][i] = fmaf(p, vf[i], acc[g][i] * corr);
+      m[g] = mn;
+    }
+  }
+
+  // merge the warps in warp order through shared memory
+  __shared__ float sm_m[NW][GT], sm_l[NW][GT];
+  __shared__ float sm_acc[NW][GT][HD];
+#pragma unroll
+  for (int g = 0; g < GT; ++g) {
+    if (lane == 0) { sm_m[warp][g] = m[g]; sm_l[warp][g] = l[g]; }
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) sm_acc[warp][g][lane * DPL + i] = acc[g][i];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < GT * HD; idx += blockDim.x) {
+    const int g = idx / HD, d = idx % HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) M = fmaxf(M, sm_m[w][g]);
+    float L = 0.f, A = 0.f;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+      const float e = sm_m[w][g] == -INFINITY ? 0.f : __expf(sm_m[w][g] - M);
+      L += sm_l[w][g] * e;
+      A += sm_acc[w][g][d] * e;
+    }
+    const int head = h0 + g;
+    if (direct) {
+      float o = L > 0.f ? A / L : 0.f;
+      if (gate) o *= sigmoidf(__bfloat162float(gate[(size_t)col * ld_gate + (size_t)head * gate_off * 2 + gate_off + d]));
+      out[((size_t)col * nh + head) * HD + d] = f32_to_f16_sat(o);
+    } else {
+      float* pp = part + (((size_t)col * nh + head) * ns_grid + split) * (HD + 2);
+      if (d == 0) { pp[0] = M; pp[1] = L; }
+      pp[2 + d] = A;
+    }
+  }
+}
+
+template <int HD>
+__global__ void attn_merge_kernel(const float* __restrict__ part, const int* __restrict__ lens, int nh, int ns_grid,
+                                  const __nv_bfloat16* __restrict__ gate, int ld_gate, __half* __restrict__ out) {
+  const int col = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
+  const int ns = splits_for(lens[col]);
+  const float* pp = part + ((size_t)col * nh + head) * ns_grid * (HD + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < ns; ++s) M = fmaxf(M, pp[(size_t)s * (HD + 2)]);
+  float L = 0.f, A = 0.f;
+  for (int s = 0; s < ns; ++s) {
+    const float ms = pp[(size_t)s * (HD + 2)];
+    const float e = ms == -INFINITY ? 0.f : __expf(ms - M);
+    L += pp[(size_t)s * (HD + 2) + 1] * e;
+    A += pp[(size_t)s * (HD + 2) + 2 + d] * e;
+  }
+  float o = L > 0.f ? A / L : 0.f;
+  // gate layout inside the fused qkv row: head h occupies [h*2hd, h*2hd+hd) = q, [.. + hd, .. + 2hd) = gate
+  if (gate) o *= sigmoidf(__bfloat162float(gate[(size_t)col * ld_gate + (size_t)head * 2 * HD + HD + d]));
+  out[((size_t)col * nh + head) * HD + d] = f32_to_f16_sat(o);
+}
+
+template <int HD, int GT>
+int launch_split(const void* q, const void* kc, const void* vc, const int* lens, const int* slots, const int* base,
+                 const int* path, int path_ld, float* part, int N, int nh, int nkv, int max_seq, int ns_grid, int direct,
+                 const void* gate, int ld_gate, void* out, cudaStream_t st) {
+  const int G = nh / nkv;
+  dim3 grid(N, nkv * (G / GT), direct ? 1 : ns_grid);
+  attn_split_kernel<HD, GT><<<grid, NW * 32, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(kc),
+      static_cast<const __nv_bfloat16*>(vc), lens, slots, base, path, path_ld, part, nh, nkv, max_seq, ns_grid,
+      rsqrtf((float)HD), direct, static_cast<const __nv_bfloat16*>(gate), ld_gate, HD, static_cast<__half*>(out));
+  return (int)cudaGetLastError();
+}
+
+template <int HD>
+int dispatch_gt(int G, const void* q, const void* kc, const void* vc, const int* lens, const int* slots, const int* base,
+                const int* path, int path_ld, float* part, int N, int nh, int nkv, int max_seq, int ns_grid, int direct,
+                const void* gate, int ld_gate, void* out, cudaStream_t st) {
+#define VG_ARGS q, kc, vc, lens, slots, base, path, path_ld, part, N, nh, nkv, max_seq, ns_grid, direct, gate, ld_gate, out, st
+  if (HD == 256) {
+    if (G % 4 == 0) return launch_split<HD, 4>(VG_ARGS);
+    if (G % 3 == 0) return launch_split<HD, 3>(VG_ARGS);
+    if (G % 2 == 0) return launch_split<HD, 2>(VG_ARGS);
+    return launch_split<HD, 1>(VG_ARGS);
+  }
+  if (G % 4 == 0) return launch_split<HD, 4>(VG_ARGS);
+  if (G % 3 == 0) return launch_split<HD, 3>(VG_ARGS);
+  if (G % 2 == 0) return launch_split<HD, 2>(VG_ARGS);
+  return launch_split<HD, 1>(VG_ARGS);
+#undef VG_ARGS
+}
+
+}  // namespace
+
+// q [N, nh, hd] bf16; kc/vc [slots, nkv, max_seq, hd] bf16; lens[N] keys per column; slots[N];
+// base[N]/path[N, path_ld] optional row indirection; part: scratch of vg_attn_scratch_floats() floats;
+// gate: fused qkv buffer (bf16, row stride ld_gate) or null; out [N, nh*hd] f16.
+extern "C" int vg_attn_decode(const void* q, const void* kc, const void* vc, const int* lens, const int* slots,
+                              const int* base, const int* path, int path_ld, float* part, int N, int nh, int nkv, int hd,
+                              int max_seq, int ns_grid, int direct, const void* gate, int ld_gate, void* out,
+                              cudaStream_t st) {
+  if (N <= 0) return 0;
+  if (nh % nkv) return -2;
+  const int G = nh / nkv;
+  int rc;
+  switch (hd) {
+    case 64: rc = dispatch_gt<64>(G, q, kc, vc, lens, slots, base, path, path_ld, part, N, nh, nkv, max_seq, ns_grid, direct, gate, ld_gate, out, st); break;
+    case 128: rc = dispatch_gt<128>(G, q, kc, vc, lens, slots, base, path, path_ld, part, N, nh, nkv, max_seq, ns_grid, direct, gate, ld_gate, out, st); break;
+    case 256: rc = dispatch_gt<256>(G, q, kc, vc, lens, slots, base, path, path_ld, part, N, nh, nkv, max_seq, ns_grid, direct, gate, ld_gate, out, st); break;
+    default: return -3;
+  }
+  if (rc || direct) return rc;
+  dim3 grid(N, nh);
+  switch (hd) {
+    case 64: attn_merge_kernel<64><<<grid, 64, 0, st>>>(part, lens, nh, ns_grid, static_cast<const __nv_bfloat16*>(gate), ld_gate, static_cast<__half*>(out)); break;
+    case 128: attn_merge_kernel<128><<<grid, 128, 0, st>>>(part, lens, nh, ns_grid, static_cast<const __nv_bfloat16*>(gate), ld_gate, static_cast<__half*>(out)); break;
+    case 256: attn_merge_kernel<256><<<grid, 256, 0, st>>>(part, lens, nh, ns_grid, static_cast<const __nv_bfloat16*>(gate), ld_gate, static_cast<__half*>(out)); break;
+  }
+  return (int)cudaGetLastError();
+}
+
+extern "C" long long vg_attn_scratch_floats(int N, int nh, int hd, int ns_grid) {
+  return (long long)N * nh * ns_grid * (hd + 2);
+}

@@ -1,0 +1,165 @@
+// GatedDeltaNet kernels: depthwise causal conv (k <= 8) + SiLU, and the gated delta-rule recurrence
+// with the gated RMSNorm fused in. Decode, width-N verify (chain, tree, multi-lane forest) and prefill
+// all run the SAME per-token arithmetic in the SAME order, so verify(N) is bit-identical to N decodes
+// (reference: kernels/gpu_batch.cu:405-418, :439-660, :1326-1440 get this the same way, with separate
+// decode and prefill kernels that share the scalar recurrence).
+//
+// Column bookkeeping (device int arrays, one entry per token column):
+//   in_slot[t]   state slot holding the lane's state before its first column
+//   parent[t]    column whose output state this column continues from, or -1 (start from in_slot[t])
+//   out_slot[t]  state slot that receives the state after this column, or -1
+// Decode: parent = -1, out_slot = in_slot. Chain verify: parent = t-1, out_slot = checkpoint slots.
+// Prefill: parent = t-1, out_slot = -1 except the last column.
+//
+// Recurrence kernel: one CTA per (value head, chain); thread j owns column j of the head's state
+// S[kd, vd] in registers, so the three kd-long dot products are thread-local sequential sums and need
+// no cross-thread reduction. State layout [slot][nv][kd][vd] fp32; conv state [slot][conv_dim][ck] fp32
+// with the newest sample last.
+#include "common.cuh"
+#include "api.h"
+
+namespace {
+using namespace vg;
+
+constexpr int MAX_CK = 8;
+
+__global__ void gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, float* __restrict__ state,
+                                const float* __restrict__ w, const int* __restrict__ in_slot,
+                                const int* __restrict__ parent, const int* __restrict__ out_slot,
+                                float* __restrict__ out, int N, int conv_dim, int ck, int phase) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)N * conv_dim) return;
+  const int t = (int)(idx / conv_dim), c = (int)(idx % conv_dim);
+  const int os = out_slot[t];
+  if (!(phase & 1) && os < 0) return;
+  float win[MAX_CK];
+  int cur = t, j = ck - 1;
+  for (; j >= 0 && cur >= 0; --j) {
+    win[j] = __bfloat162float(x[(size_t)cur * ldx + c]);
+    cur = parent[cur];
+  }
+  const int d = ck - 1 - j;                 // samples taken from the columns
+  const float* st = state + ((size_t)in_slot[t] * conv_dim + c) * ck;
+  for (int jj = j; jj >= 0; --jj) win[jj] = st[jj + d];
+  if (phase & 1) {
+    float acc = 0.f;
+    for (int i = 0; i < ck; ++i) acc = fmaf(w[(size_t)c * ck + i], win[i], acc);
+    out[(size_t)t * conv_dim + c] = silu(acc);
+  }
+  if ((phase & 2) && os >= 0) {
+    float* dst = state + ((size_t)os * conv_dim + c) * ck;
+    for (int i = 0; i < ck; ++i) dst[i] = win[i];
+  }
+}
+
+template <int KD, int VD>
+__global__ void __launch_bounds__(VD) gdn_step_kernel(
+    const float* __restrict__ qkv, const __nv_bfloat16* __restrict__ proj, int ldp, int off_z, int off_b, int off_a,
+    float* __restrict__ S, const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+    const float* __restrict__ norm_w, const int* __restrict__ chain_start, const int* __restrict__ chain_len,
+    const int* __restrict__ in_slot, const int* __restrict__ parent, const int* __restrict__ out_slot,
+    __half* __restrict__ out, int nk, int nv, float eps) {
+  __shared__ float red[32];
+  __shared__ __align__(16) float ks[KD];
+  __shared__ __align__(16) float qs[KD];
+  const int vh = blockIdx.x, chain = blockIdx.y, j = threadIdx.x;
+  const int kh = vh * nk / nv;
+  const int key_dim = nk * KD, conv_dim = 2 * key_dim + nv * VD;
+  const int t0 = chain_start[chain], tn = chain_len[chain];
+  const float a_coef = -__expf(A_log[vh]);
+  const float dtb = dt_bias[vh];
+  const float nw = norm_w[j];
+  float s[KD];
+  int loaded_from = -2;      // column whose output state is in registers (-2: nothing)
+  for (int t = t0; t < t0 + tn; ++t) {
+    const int par = parent[t];
+    if (t == t0 || par != loaded_from) {
+      const int src = par < 0 ? in_slot[t] : out_slot[par];
+      const float* sp = S + (((size_t)src * nv + vh) * KD) * VD + j;
+#pragma unroll
+      for (int a = 0; a < KD; ++a) s[a] = sp[(size_t)a * VD];
+    }
+    // q, k of the key head: l2-normalise (eps 1e-6), q also scaled by 1/sqrt(kd)
+    const float* row = qkv + (size_t)t * conv_dim;
+    float qv = 0.f, kv = 0.f;
+    for (int i = j; i < KD; i += VD) {
+      qs[i] = row[kh * KD + i];
+      ks[i] = row[key_dim + kh * KD + i];
+    }
+    __syncthreads();
+    for (int i = j; i < KD; i += VD) { qv += qs[i] * qs[i]; kv += ks[i] * ks[i]; }
+    const float qn = block_sum(qv, red);
+    const float kn = block_sum(kv, red);
+    const float qsc = rsqrtf(qn + 1e-6f) * rsqrtf((float)KD);
+    const float ksc = rsqrtf(kn + 1e-6f);
+    const float v = row[2 * key_dim + vh * VD + j];
+    const float bb = __bfloat162float(proj[(size_t)t * ldp + off_b + vh]);
+    const float aa = __bfloat162float(proj[(size_t)t * ldp + off_a + vh]) + dtb;
+    const float beta = sigmoidf(bb);
+    const float sp_ = aa > 20.f ? aa : log1pf(__expf(aa));
+    const float g = __expf(a_coef * sp_);
+    // decay + kv_mem (four interleaved partial sums in a fixed order)
+    float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
+#pragma unroll
+    for (int a = 0; a < KD; a += 4) {
+      const float4 k4 = *reinterpret_cast<const float4*>(&ks[a]);
+      s[a] *= g; s[a + 1] *= g; s[a + 2] *= g; s[a + 3] *= g;
+      m0 = fmaf(s[a], k4.x, m0); m1 = fmaf(s[a + 1], k4.y, m1);
+      m2 = fmaf(s[a + 2], k4.z, m2); m3 = fmaf(s[a + 3], k4.w, m3);
+    }
+    const float kv_mem = ((m0 + m1) + (m2 + m3)) * ksc;
+    const float delta = (v - kv_mem) * beta;
+    const float dk = delta * ksc;
+    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+    for (int a = 0; a < KD; a += 4) {
+      const float4 k4 = *reinterpret_cast<const float4*>(&ks[a]);
+      const float4 q4 = *reinterpret_cast<const float4*>(&qs[a]);
+      s[a] = fmaf(k4.x, dk, s[a]); s[a + 1] = fmaf(k4.y, dk, s[a + 1]);
+      s[a + 2] = fmaf(k4.z, dk, s[a + 2]); s[a + 3] = fmaf(k4.w, dk, s[a + 3]);
+      o0 = fmaf(s[a], q4.x, o0); o1 = fmaf(s[a + 1], q4.y, o1);
+      o2 = fmaf(s[a + 2], q4.z, o2); o3 = fmaf(s[a + 3], q4.w, o3);
+    }
+    const float o = ((o0 + o1) + (o2 + o3)) * qsc;
+    const float ss = block_sum(o * o, red);
+    const float z = __bfloat162float(proj[(size_t)t * ldp + off_z + vh * VD + j]);
+    out[((size_t)t * nv + vh) * VD + j] = f32_to_f16_sat(o * rsqrtf(ss / (float)VD + eps) * nw * silu(z));
+    const int os = out_slot[t];
+    if (os >= 0) {
+      float* dp = S + (((size_t)os * nv + vh) * KD) * VD + j;
+#pragma unroll
+      for (int a = 0; a < KD; ++a) dp[(size_t)a * VD] = s[a];
+    }
+    loaded_from = t;
+    __syncthreads();   // qs/ks are rewritten by the next column
+  }
+}
+
+}  // namespace
+
+extern "C" int vg_gdn_conv(const void* x, int ldx, float* state, const float* w, const int* in_slot, const int* parent,
+                           const int* out_slot, float* out, int N, int conv_dim, int ck, int phase, cudaStream_t st) {
+  if (N <= 0) return 0;
+  if (ck > MAX_CK) return -2;
+  const size_t total = (size_t)N * conv_dim;
+  gdn_conv_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), ldx, state, w,
+                                                                   in_slot, parent, out_slot, out, N, conv_dim, ck, phase);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int vg_gdn_step(const float* qkv, const void* proj, int ldp, int off_z, int off_b, int off_a, float* S,
+                           const float* A_log, const float* dt_bias, const float* norm_w, const int* chain_start,
+                           const int* chain_len, int n_chains, const int* in_slot, const int* parent, const int* out_slot,
+                           void* out_f16, int nk, int nv, int kd, int vd, float eps, cudaStream_t st) {
+  if (n_chains <= 0) return 0;
+  dim3 grid(nv, n_chains);
+  const __nv_bfloat16* pj = static_cast<const __nv_bfloat16*>(proj);
+  __half* o = static_cast<__half*>(out_f16);
+  if (kd == 128 && vd == 128)
+    gdn_step_kernel<128, 128><<<grid, 128, 0, st>>>(qkv, pj, ldp, off_z, off_b, off_a, S, A_log, dt_bias, norm_w, chain_start, chain_len, in_slot, parent, out_slot, o, nk, nv, eps);
+  else if (kd == 64 && vd == 64)
+    gdn_step_kernel<64, 64><<<grid, 64, 0, st>>>(qkv, pj, ldp, off_z, off_b, off_a, S, A_log, dt_bias, norm_w, chain_start, chain_len, in_slot, parent, out_slot, o, nk, nv, eps);
+  else
+    return -3;
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,178 @@
+// Normalisation, RoPE and small element-wise kernels (one CTA per token column, fp32 math, fixed
+// reduction trees so results do not depend on the batch width):
+//   vg_add_rmsnorm      residual += delta; normed = rmsnorm(residual) * (1 + w)     -> f16 GEMM input
+//   vg_attn_prep        split fused qkv, per-head q/k RMSNorm, partial rotate-half RoPE, KV-cache write
+//   vg_swiglu           silu(gate) * up                                            -> f16 GEMM input
+//   vg_embed_gather     embedding rows from a bf16 / FP8 / NVFP4 table             -> bf16 residual
+//   vg_cast_f16         bf16/f32 -> saturating f16
+// They stand in for the reference's rmsnorm_b / fused_res_rmsnorm_b / rmsnorm_perhead_b / rope_b /
+// split_qkv_b / split_qgate_b / write_kv_b / silu_mul_b / embed_gather_* (reference:
+// kernels/gpu_batch.cu:34-110, :338-405, :821-880, :3011-3100), fused into fewer launches.
+#include "common.cuh"
+#include "api.h"
+
+namespace {
+using namespace vg;
+
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(__nv_bfloat16* res, const __nv_bfloat16* delta, const float* w,
+                                                           __half* out16, __nv_bfloat16* out_bf, int h, float eps,
+                                                           int plus_one, int ld_res, int ld_delta) {
+  __shared__ float red[32];
+  extern __shared__ float row[];
+  const int n = blockIdx.x;
+  __nv_bfloat16* r = res + (size_t)n * ld_res;
+  const __nv_bfloat16* d = delta ? delta + (size_t)n * ld_delta : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < h; i += blockDim.x) {
+    float v = __bfloat162float(r[i]);
+    if (d) {
+      v += __bfloat162float(d[i]);
+      const __nv_bfloat16 rb = __float2bfloat16_rn(v);
+      r[i] = rb;
+      v = __bfloat162float(rb);
+    }
+    row[i] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)h + eps);
+  for (int i = threadIdx.x; i < h; i += blockDim.x) {
+    const float v = row[i] * inv * (plus_one ? 1.0f + w[i] : w[i]);
+    if (out16) out16[(size_t)n * h + i] = f32_to_f16_sat(v);
+    if (out_bf) out_bf[(size_t)n * h + i] = __float2bfloat16_rn(v);
+  }
+}
+
+// One CTA per (column, head slot). Head slots: [0, nh) query heads, [nh, nh+nkv) key heads,
+// [nh+nkv, nh+2nkv) value heads. blockDim.x == hd.
+__global__ void attn_prep_kernel(const __nv_bfloat16* qkv, int ld_qkv, const float* q_norm, const float* k_norm,
+                                 const int* pos, const int* slot, const int* kv_row, __nv_bfloat16* q_out,
+                                 __nv_bfloat16* kc, __nv_bfloat16* vc, int nh, int nkv, int hd, int rdim, int max_seq,
+                                 float eps, float log2_theta, int gated) {
+  __shared__ float red[32];
+  extern __shared__ float xs[];
+  const int n = blockIdx.x, hs = blockIdx.y, d = threadIdx.x;
+  const int qw = gated ? 2 * hd : hd;
+  const __nv_bfloat16* src;
+  const float* nw = nullptr;
+  if (hs < nh) { src = qkv + (size_t)n * ld_qkv + hs * qw; nw = q_norm; }
+  else if (hs < nh + nkv) { src = qkv + (size_t)n * ld_qkv + nh * qw + (hs - nh) * hd; nw = k_norm; }
+  else { src = qkv + (size_t)n * ld_qkv + nh * qw + nkv * hd + (hs - nh - nkv) * hd; }
+  float v = __bfloat162float(src[d]);
+  if (hs >= nh + nkv) {
+    const int s = slot[n], row = kv_row[n];
+    vc[(((size_t)s * nkv + (hs - nh - nkv)) * max_seq + row) * hd + d] = __float2bfloat16_rn(v);
+    return;
+  }
+  float ss = block_sum(v * v, red);
+  v = v * rsqrtf(ss / (float)hd + eps) * (1.0f + nw[d]);
+  xs[d] = v;
+  __syncthreads();
+  if (d < rdim) {
+    const int half = rdim / 2;
+    const int i = d < half ? d : d - half;
+    // inv_freq = theta^(-2i/rdim)
+    const float inv_freq = exp2f(-log2_theta * (2.0f * (float)i / (float)rdim));
+    float sn, cs;
+    sincosf((float)pos[n] * inv_freq, &sn, &cs);
+    const float x1 = xs[i], x2 = xs[i + half];
+    v = d < half ? x1 * cs - x2 * sn : x2 * cs + x1 * sn;
+  }
+  if (hs < nh) {
+    q_out[((size_t)n * nh + hs) * hd + d] = __float2bfloat16_rn(v);
+  } else {
+    const int s = slot[n], row = kv_row[n];
+    kc[(((size_t)s * nkv + (hs - nh)) * max_seq + row) * hd + d] = __float2bfloat16_rn(v);
+  }
+}
+
+__global__ void swiglu_kernel(const __nv_bfloat16* gu, __half* out, int I, int ld, size_t total) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t n = i / I, c = i % I;
+  const float g = __bfloat162float(gu[n * ld + c]);
+  const float u = __bfloat162float(gu[n * ld + I + c]);
+  out[i] = f32_to_f16_sat(silu(g) * u);
+}
+
+template <typename T>
+__global__ void cast_f16_kernel(const T* in, __half* out, size_t total) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < total) out[i] = f32_to_f16_sat((float)in[i]);
+}
+
+__global__ void embed_gather_kernel(const void* table, const uint8_t* scales, const float* row_scale, const int* tok,
+                                    __nv_bfloat16* out, int h, int wfmt) {
+  const int n = blockIdx.x;
+  const size_t t = (size_t)tok[n];
+  for (int i = threadIdx.x; i < h; i += blockDim.x) {
+    float v;
+    if (wfmt == VG_WF_BF16) {
+      v = __bfloat162float(static_cast<const __nv_bfloat16*>(table)[t * h + i]);
+    } else if (wfmt == VG_WF_FP8) {
+      uint32_t s2;
+      asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(s2) : "h"((uint16_t)static_cast<const uint8_t*>(table)[t * h + i]));
+      v = __half22float2(*reinterpret_cast<__half2*>(&s2)).x * row_scale[t];
+    } else {
+      const uint8_t b = static_cast<const uint8_t*>(table)[t * (h / 2) + i / 2];
+      const int code = (i & 1) ? (b >> 4) : (b & 0xF);
+      const float mag = (code & 4) ? ((code & 2) ? ((code & 1) ? 6.f : 4.f) : ((code & 1) ? 3.f : 2.f))
+                                   : ((code & 2) ? ((code & 1) ? 1.5f : 1.f) : ((code & 1) ? .5f : 0.f));
+      uint32_t s2;
+      asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(s2) : "h"((uint16_t)scales[t * (h / 16) + i / 16]));
+      // value = code * (block scale * tensor scale), the order the canonical dequantisation uses.
+      v = ((code & 8) ? -mag : mag) * (__half22float2(*reinterpret_cast<__half2*>(&s2)).x * row_scale[t]);
+    }
+    out[(size_t)n * h + i] = __float2bfloat16_rn(v);
+  }
+}
+
+}  // namespace
+
+extern "C" int vg_add_rmsnorm(void* res, const void* delta, const float* w, void* out_f16, void* out_bf16, int N, int h,
+                              float eps, int plus_one, int ld_res, int ld_delta, cudaStream_t st) {
+  if (N <= 0) return 0;
+  add_rmsnorm_kernel<<<N, 256, h * sizeof(float), st>>>(static_cast<__nv_bfloat16*>(res),
+                                                       static_cast<const __nv_bfloat16*>(delta), w,
+                                                       static_cast<__half*>(out_f16),
+                                                       static_cast<__nv_bfloat16*>(out_bf16), h, eps, plus_one, ld_res,
+                                                       ld_delta);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int vg_attn_prep(const void* qkv, int ld_qkv, const float* q_norm, const float* k_norm, const int* pos,
+                            const int* slot, const int* kv_row, void* q_out, void* kc, void* vc, int N, int nh, int nkv,
+                            int hd, int rdim, int max_seq, float eps, float theta, int gated, cudaStream_t st) {
+  if (N <= 0) return 0;
+  if (hd > 1024 || (hd & 31)) return -2;
+  dim3 grid(N, nh + 2 * nkv);
+  attn_prep_kernel<<<grid, hd, hd * sizeof(float), st>>>(
+      static_cast<const __nv_bfloat16*>(qkv), ld_qkv, q_norm, k_norm, pos, slot, kv_row,
+      static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(kc), static_cast<__nv_bfloat16*>(vc), nh, nkv, hd,
+      rdim, max_seq, eps, log2f(theta), gated);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int vg_swiglu(const void* gu, void* out_f16, int N, int I, int ld, cudaStream_t st) {
+  const size_t total = (size_t)N * I;
+  if (!total) return 0;
+  swiglu_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(gu),
+                                                                 static_cast<__half*>(out_f16), I, ld, total);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int vg_cast_f16(const void* in, int in_is_f32, void* out_f16, long long total, cudaStream_t st) {
+  if (total <= 0) return 0;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (in_is_f32) cast_f16_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(in), static_cast<__half*>(out_f16), (size_t)total);
+  else cast_f16_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(in), static_cast<__half*>(out_f16), (size_t)total);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int vg_embed_gather(const void* table, const void* scales, const float* row_scale, const int* tok, void* out,
+                               int N, int h, int wfmt, cudaStream_t st) {
+  if (N <= 0) return 0;
+  embed_gather_kernel<<<N, 256, 0, st>>>(table, static_cast<const uint8_t*>(scales), row_scale, tok,
+                                         static_cast<__nv_bfloat16*>(out), h, wfmt);
+  return (int)cudaGetLastError();
+}

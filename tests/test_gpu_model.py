@@ -1,0 +1,100 @@
+"""Tiny hybrid model on the GPU runtime against the fp32 CPU oracle, plus the bitwise
+batch-invariance / verify == sequential-decode gates."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _build(recipe="all", std=0.05, moe=False):
+    from velogb10_b200.config import tiny_hybrid, tiny_moe
+    from velogb10_b200.checkpoint.synthetic import SyntheticSource
+    from velogb10_b200.models.weights import ModelBuilder
+    cfg = tiny_moe() if moe else tiny_hybrid()
+    w = ModelBuilder(cfg, SyntheticSource(cfg, 0, "cuda", std=std), recipe=recipe, device="cuda").build()
+    return cfg, w
+
+
+def _oracle(cfg, w):
+    from velogb10_b200.models.oracle import OracleModel
+    from velogb10_b200.checkpoint.synthetic import SyntheticSource
+    from velogb10_b200.models.weights import ModelBuilder
+    wc = ModelBuilder(cfg, SyntheticSource(cfg, 0, "cuda", std=0.05), recipe=w.recipe, device="cuda").build()
+    return OracleModel(wc)
+
+
+@pytest.mark.parametrize("recipe", ["all", "all,gdn:fp8", "off"])
+def test_prefill_and_decode_match_oracle(recipe):
+    from velogb10_b200.models.runtime import GpuModel
+    cfg, w = _build(recipe)
+    orc = _oracle(cfg, w)
+    gm = GpuModel(w, keep_canonical=True)
+    gm.alloc_state(4, 4 + 17, 256)
+    orc.alloc_state(4, 4 + 17, 256)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, cfg.vocab_size, (16,), generator=g).tolist()
+    lg, _ = gm.prefill(1, prompt)
+    lo, _ = orc.prefill(1, prompt)
+    lg = lg.float().cpu()
+    rel = (lg - lo).norm() / lo.norm()
+    assert rel < 0.05, rel
+    tok = int(lo.argmax())
+    for i in range(4):
+        lgd, _ = gm.decode([tok], [16 + i], [1])
+        lod, _ = orc.decode([tok], [16 + i], [1])
+        rel = (lgd[0].float().cpu() - lod[0]).norm() / lod[0].norm()
+        assert rel < 0.05, (i, rel)
+        tok = int(lod[0].argmax())
+
+
+def test_batch_and_verify_are_bitwise_sequential():
+    """Batch-4 decode == four single decodes; width-4 verify == 4 sequential decodes; checkpoints restore."""
+    from velogb10_b200.models.runtime import GpuModel
+    cfg, w = _build("all")
+    gm = GpuModel(w, keep_canonical=True)
+    gm.alloc_state(4, 4 + 17, 512)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (16, 23, 300, 260)]
+    firsts = []
+    for s, p in enumerate(prompts):
+        lg, _ = gm.prefill(s, p)
+        firsts.append(int(lg.argmax()))
+    # snapshot state after prefill
+    S0, C0, K0, V0 = gm.S.clone(), gm.conv.clone(), gm.kc.clone(), gm.vc.clone()
+    pos = [len(p) for p in prompts]
+    lb, _ = gm.decode(firsts, pos, [0, 1, 2, 3])
+    lb = lb.clone()
+    Sb = gm.S.clone()
+    gm.S.copy_(S0); gm.conv.copy_(C0); gm.kc.copy_(K0); gm.vc.copy_(V0)
+    for s in range(4):
+        l1, _ = gm.decode([firsts[s]], [pos[s]], [s])
+        assert torch.equal(l1[0], lb[s]), s
+    assert torch.equal(gm.S, Sb)
+    # chain verify on lane 2 (straddles the 256-key split boundary region) vs sequential decodes
+    gm.S.copy_(S0); gm.conv.copy_(C0); gm.kc.copy_(K0); gm.vc.copy_(V0)
+    toks = [firsts[2], 5, 7, 11]
+    lv, _ = gm.verify(2, toks, pos[2], ckpt_base=4)
+    lv = lv.clone()
+    ck = [gm.S[:, 4 + t].clone() for t in range(4)]
+    gm.S.copy_(S0); gm.conv.copy_(C0); gm.kc.copy_(K0); gm.vc.copy_(V0)
+    for t in range(4):
+        l1, _ = gm.decode([toks[t]], [pos[2] + t], [2])
+        assert torch.equal(l1[0], lv[t]), t
+        assert torch.equal(gm.S[:, 2], ck[t]), t
+
+
+def test_graph_replay_matches_eager():
+    from velogb10_b200.models.runtime import GpuModel
+    cfg, w = _build("all")
+    gm = GpuModel(w, keep_canonical=True)
+    gm.alloc_state(2, 2 + 17, 128)
+    gm.prefill(0, list(range(10, 30)))
+    gm.prefill(1, list(range(40, 70)))
+    S0, C0 = gm.S.clone(), gm.conv.clone()
+    le, _ = gm.decode([3, 4], [20, 30], [0, 1])
+    want = le.argmax(-1).int().clone()
+    gm.S.copy_(S0); gm.conv.copy_(C0)
+    got = gm.replay_decode([3, 4], [20, 30], [0, 1]).clone()
+    gm.S.copy_(S0); gm.conv.copy_(C0)
+    got2 = gm.replay_decode([3, 4], [20, 30], [0, 1]).clone()
+    assert torch.equal(got, want) and torch.equal(got2, want)

@@ -118,4 +118,5 @@ class SyntheticSource(TensorSource):
 def synthetic_state_dict(cfg: ModelConfig, seed: int = 0, device="cpu") -> Dict[str, torch.Tensor]:
     """The full bf16 model as a prefixed state dict (small configs only)."""
     src = SyntheticSource(cfg, seed, device)
-    return {PREFIX + n: src.get(n) for n in src.names()}
+    # MTP tensors are stored unprefixed (``mtp.fc.weight``), everything else under the language-model prefix
+    return {(n if n.startswith("mtp.") else PREFIX + n): src.get(n) for n in src.names()}

@@ -1,0 +1,435 @@
+"""GPU model runtime: weights on device, slotted KV / GDN-state store, and the layer loop that drives
+the sm_100a kernels for decode, width-N verify and prefill, with CUDA-graph capture of the decode step.
+
+It plays the role of the reference's ``GpuModel`` (reference: src/gpu.rs:3635-3698 layer loop,
+:3451-3597 mixers, :3143-3163 FFN, :4132-4259 state, :3987-4081 graphs) with a different shape:
+token-major activations, one fused residual+norm kernel between GEMMs, f16 GEMM inputs produced by the
+preceding kernel, and a single column-metadata plan (slot / parent / checkpoint arrays) shared by
+decode, chain, tree and forest verify and prefill.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..config import ModelConfig
+from ..ops import gemm as G
+from ..ops import kernels as K
+from ..ops import lib as _lib
+from .weights import LayerW, ModelWeights, MoeW, MtpW, QLinear
+
+MAX_PATH = 16
+
+
+@dataclass
+class Plan:
+    """Host-side description of the columns of one forward call."""
+    tok: List[int]
+    pos: List[int]                      # RoPE position of each column
+    kv_slot: List[int]
+    kv_row: List[int]                   # cache row the column's K/V are written to
+    lens: List[int]                     # number of keys the column attends to
+    base: List[int]                     # keys below base[c] are rows 0..base-1; the rest come from path
+    path: List[List[int]]               # extra rows per column (tree / forest), at most MAX_PATH
+    st_in: List[int]
+    parent: List[int]
+    st_out: List[int]
+    chains: List[Tuple[int, int]]       # (start, length) of sequentially dependent column runs
+    direct_attn: bool = False           # prefill: single split, merge fused
+
+    @property
+    def n(self) -> int:
+        return len(self.tok)
+
+    # ---- constructors
+    @staticmethod
+    def decode(tokens, pos, slots) -> "Plan":
+        n = len(tokens)
+        return Plan(list(tokens), list(pos), list(slots), list(pos), [p + 1 for p in pos], [p + 1 for p in pos],
+                    [[] for _ in range(n)], list(slots), [-1] * n, list(slots), [(i, 1) for i in range(n)])
+
+    @staticmethod
+    def chain(slot, tokens, pos_start, ckpt_base: Optional[int], final_to_slot: bool = False,
+              direct_attn: bool = False) -> "Plan":
+        n = len(tokens)
+        pos = [pos_start + t for t in range(n)]
+        st_out = [(-1 if ckpt_base is None else ckpt_base + t) for t in range(n)]
+        if final_to_slot:
+            st_out[-1] = slot
+        return Plan(list(tokens), pos, [slot] * n, pos, [p + 1 for p in pos], [p + 1 for p in pos],
+                    [[] for _ in range(n)], [slot] * n, [t - 1 for t in range(n)], st_out, [(0, n)], direct_attn)
+
+    @staticmethod
+    def tree(slot, tokens, pos_start, ckpt_base, parent) -> "Plan":
+        n = len(tokens)
+        depth, paths = [0] * n, []
+        for t in range(n):
+            p = parent[t]
+            paths.append(([] if p < 0 else paths[p]) + [pos_start + t])
+            depth[t] = 0 if p < 0 else depth[p] + 1
+        return Plan(list(tokens), [pos_start + d for d in depth], [slot] * n, [pos_start + t for t in range(n)],
+                    [pos_start + len(paths[t]) for t in range(n)], [pos_start] * n, paths, [slot] * n,
+                    list(parent), [ckpt_base + t for t in range(n)], [(0, n)])
+
+    @staticmethod
+    def concat(plans: Sequence["Plan"]) -> "Plan":
+        """Pack several lanes' plans into one forward (forest verify)."""
+        out = Plan([], [], [], [], [], [], [], [], [], [], [])
+        for p in plans:
+            off = out.n
+            out.chains += [(s + off, l) for s, l in p.chains]
+            out.parent += [(-1 if q < 0 else q + off) for q in p.parent]
+            out.tok += p.tok; out.pos += p.pos; out.kv_slot += p.kv_slot; out.kv_row += p.kv_row
+            out.lens += p.lens; out.base += p.base; out.path += p.path
+            out.st_in += p.st_in; out.st_out += p.st_out
+        return out
+
+
+class Workspace:
+    """Persistent device buffers for up to ``cap`` columns (fixed addresses, so forwards over them can be
+    captured in a CUDA graph)."""
+
+    def __init__(self, cfg: ModelConfig, w: ModelWeights, cap: int, device, logits_rows: int):
+        c = cfg
+        self.cap = cap
+        rows = max(cap, 16)
+        dev = device
+        i32 = lambda *s: torch.zeros(s, dtype=torch.int32, device=dev)
+        bf = lambda *s: torch.zeros(s, dtype=torch.bfloat16, device=dev)
+        f16 = lambda *s: torch.zeros(s, dtype=torch.float16, device=dev)
+        f32 = lambda *s: torch.zeros(s, dtype=torch.float32, device=dev)
+        self.tok, self.pos, self.kv_slot, self.kv_row = i32(rows), i32(rows), i32(rows), i32(rows)
+        self.lens, self.base, self.path = i32(rows), i32(rows), i32(rows, MAX_PATH)
+        self.st_in, self.parent, self.st_out = i32(rows), i32(rows), i32(rows)
+        self.chain_start, self.chain_len = i32(rows), i32(rows)
+        h = c.hidden_size
+        self.x = bf(rows, h)
+        self.xn16 = f16(rows, h)
+        self.delta = bf(rows, h)
+        widths = [1]
+        for L in list(w.layers) + ([w.mtp.layer] if w.mtp else []):
+            if L.attn:
+                widths.append(L.attn.qkv.m)
+            if L.gdn:
+                widths.append(L.gdn.in_proj.m)
+            if L.mlp:
+                widths.append(L.mlp.gate_up.m)
+            if L.moe and L.moe.shared:
+                widths.append(L.moe.shared.gate_up.m)
+        self.wide = bf(rows, max(widths))                 # qkv / in_proj / gate_up outputs
+        self._a16 = {}                                    # contiguous f16 GEMM-input buffers by width
+        self._rows, self._dev = rows, dev
+        nh_max = max([L.attn.nh for L in list(w.layers) + ([w.mtp.layer] if w.mtp else []) if L.attn] or [1])
+        self.q = bf(rows, nh_max * c.head_dim)
+        conv_max = max([L.gdn.conv_w.shape[0] for L in w.layers if L.gdn] or [1])
+        self.conv_out = f32(rows, conv_max)
+        self.logits = f32(max(logits_rows, 1), w.lm_head.m)
+        self.out_tok = i32(rows)
+        self.out_val = f32(rows)
+        self.hidden_keep = bf(rows, h)
+        if w.mtp is not None:
+            self.cat16 = f16(rows, 2 * h)
+            self.mtp_e = bf(rows, h)
+        self.n_uploaded = 0
+
+    def a16(self, width: int) -> torch.Tensor:
+        """Contiguous f16 ``[rows, width]`` buffer that receives attention / GDN / SwiGLU outputs."""
+        t = self._a16.get(width)
+        if t is None:
+            t = torch.zeros((self._rows, width), dtype=torch.float16, device=self._dev)
+            self._a16[width] = t
+        return t
+
+
+class GpuModel:
+    def __init__(self, weights: ModelWeights, device="cuda", max_cols: int = 16, prefill_chunk: int = 4096,
+                 comm=None, keep_canonical: bool = False):
+        self.w = weights
+        self.cfg = weights.cfg
+        self.dev = torch.device(device)
+        self.comm = comm
+        self.max_cols = max_cols
+        self.prefill_chunk = prefill_chunk
+        _lib.lib()
+        with torch.cuda.device(self.dev):
+            for name, q in weights.linears():
+                if q.packed is None and q.codes is None and q.w is None:
+                    continue
+                small = q.m < 128 or name.endswith(("router", "shared_gate"))
+                if name == "embed":
+                    if weights.lm_head is weights.embed:
+                        G.prepare(q, keep_canonical=True)
+                    continue
+                if small or q.experts > 1:
+                    continue
+                G.prepare(q, keep_canonical=keep_canonical)
+        self.ws = Workspace(self.cfg, weights, max_cols, self.dev, max_cols)
+        self.ws_prefill: Optional[Workspace] = None
+        self.state_ready = False
+        self.graphs: Dict[Tuple[str, int], torch.cuda.CUDAGraph] = {}
+        self.ns_grid = 32
+
+    # ---------------------------------------------------------------- state
+    def alloc_state(self, n_slots: int, n_state_slots: int, max_seq: int):
+        c = self.cfg
+        dev = self.dev
+        self.n_slots, self.n_state_slots, self.max_seq = n_slots, n_state_slots, max_seq
+        attn_layers = [i for i, L in enumerate(self.w.layers) if L.attn]
+        gdn_layers = [i for i, L in enumerate(self.w.layers) if L.gdn]
+        self.attn_index = {li: j for j, li in enumerate(attn_layers)}
+        self.gdn_index = {li: j for j, li in enumerate(gdn_layers)}
+        nkv = self.w.layers[attn_layers[0]].attn.nkv if attn_layers else 1
+        self.kc = torch.zeros((len(attn_layers), n_slots, nkv, max_seq, c.head_dim), dtype=torch.bfloat16, device=dev)
+        self.vc = torch.zeros_like(self.kc)
+        if gdn_layers:
+            g0 = self.w.layers[gdn_layers[0]].gdn
+            self.S = torch.zeros((len(gdn_layers), n_state_slots, g0.nv, c.lin_k_dim, c.lin_v_dim),
+                                 dtype=torch.float32, device=dev)
+            self.conv = torch.zeros((len(gdn_layers), n_state_slots, g0.conv_w.shape[0], c.conv_kernel),
+                                    dtype=torch.float32, device=dev)
+        else:
+            self.S = self.conv = None
+        if self.w.mtp is not None:
+            mn = self.w.mtp.layer.attn.nkv
+            self.mtp_kc = torch.zeros((n_slots, mn, max_seq, c.head_dim), dtype=torch.bfloat16, device=dev)
+            self.mtp_vc = torch.zeros_like(self.mtp_kc)
+        nh = max([L.attn.nh for L in self.w.layers if L.attn] + ([self.w.mtp.layer.attn.nh] if self.w.mtp else []) or [1])
+        self.attn_part = torch.zeros(K.attn_scratch_floats(max(self.max_cols, 16), nh, c.head_dim, self.ns_grid),
+                                     dtype=torch.float32, device=dev)
+        self.state_ready = True
+        self.graphs.clear()
+
+    def copy_state(self, src: int, dst: int):
+        if self.S is not None:
+            self.S[:, dst].copy_(self.S[:, src])
+            self.conv[:, dst].copy_(self.conv[:, src])
+
+    def zero_slot(self, slot: int, zero_kv: bool = False):
+        if self.S is not None:
+            self.S[:, slot].zero_()
+            self.conv[:, slot].zero_()
+        if zero_kv:
+            self.kc[:, slot].zero_()
+            self.vc[:, slot].zero_()
+
+    def compact_kv(self, slot: int, pos_start: int, cols: Sequence[int]):
+        """Move KV rows of accepted tree columns to contiguous positions (reference: src/gpu.rs:5325-5414)."""
+        src = torch.tensor([pos_start + c_ for c_ in cols], device=self.dev)
+        dst = torch.arange(pos_start, pos_start + len(cols), device=self.dev)
+        for cache in (self.kc, self.vc):
+            rows = cache[:, slot].index_select(2, src)
+            cache[:, slot].index_copy_(2, dst, rows)
+
+    # ---------------------------------------------------------------- plan upload
+    def _upload(self, ws: Workspace, p: Plan):
+        n = p.n
+        assert n <= ws.cap, (n, ws.cap)
+        path = [row + [0] * (MAX_PATH - len(row)) for row in p.path]
+        cs = [s for s, _ in p.chains] + [0] * (n - len(p.chains))
+        cl = [l for _, l in p.chains] + [0] * (n - len(p.chains))
+        host = torch.tensor([p.tok, p.pos, p.kv_slot, p.kv_row, p.lens, p.base, p.st_in, p.parent, p.st_out, cs, cl],
+                            dtype=torch.int32).pin_memory()
+        dst = [ws.tok, ws.pos, ws.kv_slot, ws.kv_row, ws.lens, ws.base, ws.st_in, ws.parent, ws.st_out,
+               ws.chain_start, ws.chain_len]
+        for i, d in enumerate(dst):
+            d[:n].copy_(host[i], non_blocking=True)
+        if any(p.path):
+            ws.path[:n].copy_(torch.tensor(path, dtype=torch.int32), non_blocking=True)
+        ws.n_uploaded = n
+
+    # ---------------------------------------------------------------- layers
+    def _reduce(self, t: torch.Tensor, n: int):
+        if self.comm is not None and self.comm.world > 1:
+            self.comm.all_reduce_rows(t, n)
+
+    def _attn(self, ws: Workspace, L: LayerW, n: int, kc, vc, plan_direct: bool, use_path: bool):
+        c, A = self.cfg, L.attn
+        qkv = ws.wide[:, :A.qkv.m]
+        G.linear(A.qkv, ws.xn16, n, out=qkv)
+        K.attn_prep(qkv, A.q_norm, A.k_norm, ws.pos, ws.kv_slot, ws.kv_row, ws.q, kc, vc, n, A.nh, A.nkv,
+                    c.head_dim, c.rotary_dim, c.rms_eps, c.rope_theta, c.attn_out_gate)
+        a16 = ws.a16(A.o.k)
+        K.attn_decode(ws.q, kc, vc, ws.lens, ws.kv_slot, self.attn_part, a16, n, A.nh, A.nkv, c.head_dim,
+                      gate=qkv if c.attn_out_gate else None, base=ws.base if use_path else None,
+                      path=ws.path if use_path else None, ns_grid=self.ns_grid, direct=plan_direct)
+        G.linear(A.o, a16, n, out=ws.delta)
+        self._reduce(ws.delta, n)
+
+    def _gdn(self, ws: Workspace, L: LayerW, li: int, n: int, n_chains: int, seq_mode: bool):
+        c, Gd = self.cfg, L.gdn
+        gi = self.gdn_index[li]
+        proj = ws.wide[:, :Gd.in_proj.m]
+        G.linear(Gd.in_proj, ws.xn16, n, out=proj)
+        conv_dim = Gd.conv_w.shape[0]
+        value_dim = Gd.nv * c.lin_v_dim
+        if seq_mode:
+            K.gdn_conv(proj, self.conv[gi], Gd.conv_w, ws.st_in, ws.parent, ws.st_out, ws.conv_out, n, conv_dim,
+                       c.conv_kernel, phase=1)
+            K.gdn_conv(proj, self.conv[gi], Gd.conv_w, ws.st_in, ws.parent, ws.st_out, ws.conv_out, n, conv_dim,
+                       c.conv_kernel, phase=2)
+        else:
+            K.gdn_conv(proj, self.conv[gi], Gd.conv_w, ws.st_in, ws.parent, ws.st_out, ws.conv_out, n, conv_dim,
+                       c.conv_kernel, phase=3)
+        g16 = ws.a16(Gd.out.k)
+        K.gdn_step(ws.conv_out, proj, conv_dim, conv_dim + value_dim, conv_dim + value_dim + Gd.nv, self.S[gi],
+                   Gd.A_log, Gd.dt_bias, Gd.norm, ws.chain_start, ws.chain_len, n_chains, ws.st_in, ws.parent,
+                   ws.st_out, g16, Gd.nk, Gd.nv, c.lin_k_dim, c.lin_v_dim, c.rms_eps)
+        G.linear(Gd.out, g16, n, out=ws.delta)
+        self._reduce(ws.delta, n)
+
+    def _mlp(self, ws: Workspace, M, n: int, out: torch.Tensor, reduce: bool = True):
+        gu = ws.wide[:, :M.gate_up.m]
+        G.linear(M.gate_up, ws.xn16, n, out=gu)
+        a16 = ws.a16(M.down.k)
+        K.swiglu(gu, a16, n, M.inter)
+        G.linear(M.down, a16, n, out=out)
+        if reduce:
+            self._reduce(out, n)
+
+    def _moe(self, ws: Workspace, M: MoeW, n: int):
+        from . import moe_runtime
+        moe_runtime.moe_forward(self, ws, M, n)
+
+    def _layer(self, ws, L: LayerW, li, n, n_chains, seq_mode, direct, use_path, kc, vc, first_delta):
+        c = self.cfg
+        K.add_rmsnorm(ws.x, first_delta, L.input_norm, c.rms_eps, n, out16=ws.xn16)
+        if L.attn is not None:
+            self._attn(ws, L, n, kc, vc, direct, use_path)
+        else:
+            self._gdn(ws, L, li, n, n_chains, seq_mode)
+        K.add_rmsnorm(ws.x, ws.delta, L.post_norm, c.rms_eps, n, out16=ws.xn16)
+        if L.moe is not None:
+            self._moe(ws, L.moe, n)
+        else:
+            self._mlp(ws, L.mlp, n, ws.delta)
+
+    def _backbone(self, ws: Workspace, n: int, n_chains: int, seq_mode: bool, direct: bool, use_path: bool,
+                  logits_rows: Optional[Tuple[int, int]] = None):
+        """Embedding -> layers -> final norm -> LM head over rows [r0, r1) (default: all n).
+        Leaves the pre-final-norm hidden in ws.x and fp32 logits in ws.logits[: r1 - r0]."""
+        c = self.cfg
+        K.embed_gather(self.w.embed, ws.tok, ws.x, n)
+        delta = None
+        for li, L in enumerate(self.w.layers):
+            kc = vc = None
+            if L.attn is not None:
+                ai = self.attn_index[li]
+                kc, vc = self.kc[ai], self.vc[ai]
+            self._layer(ws, L, li, n, n_chains, seq_mode, direct, use_path, kc, vc, delta)
+            delta = ws.delta
+        K.add_rmsnorm(ws.x, delta, self.w.final_norm, c.rms_eps, n, out16=ws.xn16)
+        r0, r1 = (0, n) if logits_rows is None else logits_rows
+        if r1 > r0:
+            if r0 != 0:
+                # the LM head always reads from the start of the buffer (one cached tensor map)
+                assert r0 >= r1 - r0
+                ws.xn16[:r1 - r0].copy_(ws.xn16[r0:r1])
+            G.linear(self.w.lm_head, ws.xn16, r1 - r0, out=ws.logits, out_f32=True)
+
+    # ---------------------------------------------------------------- public forwards
+    def forward(self, plan: Plan, want_logits: bool = True) -> Tuple[Optional[torch.Tensor], torch.Tensor]:
+        """Generic forward over the small workspace. Returns (logits [n, V_local] fp32 view, hidden [n, h] bf16 view)."""
+        ws = self.ws
+        self._upload(ws, plan)
+        n = plan.n
+        seq_mode = any(l > 1 for _, l in plan.chains)
+        self._backbone(ws, n, len(plan.chains), seq_mode, plan.direct_attn, any(plan.path),
+                       None if want_logits else (0, 0))
+        return (ws.logits[:n] if want_logits else None), ws.x[:n]
+
+    def decode(self, tokens, pos, slots):
+        return self.forward(Plan.decode(tokens, pos, slots))
+
+    def verify(self, slot, tokens, pos_start, ckpt_base=None, parent=None):
+        if parent is None:
+            return self.forward(Plan.chain(slot, tokens, pos_start, ckpt_base))
+        return self.forward(Plan.tree(slot, tokens, pos_start, ckpt_base, parent))
+
+    def prefill(self, slot: int, tokens: Sequence[int], pos_start: int = 0, want_hidden: bool = True):
+        """Chunked prefill of one lane; state carried in the lane's slot. Returns (logits of the last
+        token [V_local] fp32, hidden [N, h] bf16 or None)."""
+        N = len(tokens)
+        chunk = min(self.prefill_chunk, max(N, 16))
+        if self.ws_prefill is None or self.ws_prefill.cap < chunk:
+            self.ws_prefill = Workspace(self.cfg, self.w, chunk, self.dev, 1)
+            need = K.attn_scratch_floats(16, 1, self.cfg.head_dim, 1)
+            assert self.attn_part.numel() >= need
+        ws = self.ws_prefill
+        hs = []
+        logits = None
+        for o in range(0, N, chunk):
+            toks = tokens[o:o + chunk]
+            n = len(toks)
+            last = o + n >= N
+            plan = Plan.chain(slot, toks, pos_start + o, None, final_to_slot=True, direct_attn=True)
+            self._upload(ws, plan)
+            self._backbone(ws, n, 1, True, True, False, (n - 1, n) if last else (0, 0))
+            if want_hidden:
+                hs.append(ws.x[:n].clone())
+            if last:
+                logits = ws.logits[0]
+        return logits, (torch.cat(hs, 0) if want_hidden else None)
+
+    # ---------------------------------------------------------------- MTP head
+    def mtp_forward(self, slot: int, tokens: Sequence[int], hidden: torch.Tensor, pos: Sequence[int]):
+        """Draft head over N (hidden_t, token_{t+1}) pairs of one lane (replicated on every rank).
+        Returns (logits [N, V_local] fp32, head hidden [N, h] bf16)."""
+        m, c, ws = self.w.mtp, self.cfg, self.ws
+        n = len(tokens)
+        plan = Plan.chain(slot, tokens, 0, None)
+        plan.pos = list(pos); plan.kv_row = list(pos)
+        plan.lens = [p + 1 for p in pos]; plan.base = list(plan.lens)
+        self._upload(ws, plan)
+        h = c.hidden_size
+        K.embed_gather(self.w.embed, ws.tok, ws.mtp_e, n)
+        K.add_rmsnorm(ws.mtp_e, None, m.norm_embed, c.rms_eps, n, out_bf=ws.x)
+        ws.cat16[:n, :h].copy_(ws.x[:n])
+        ws.hidden_keep[:n].copy_(hidden[:n])
+        K.add_rmsnorm(ws.hidden_keep, None, m.norm_hidden, c.rms_eps, n, out_bf=ws.x)
+        ws.cat16[:n, h:].copy_(ws.x[:n])
+        G.linear(m.fc, ws.cat16, n, out=ws.x)
+        comm, self.comm = self.comm, None          # the draft head is unsharded: no reductions
+        try:
+            self._layer(ws, m.layer, -1, n, 1, True, False, False, self.mtp_kc, self.mtp_vc, None)
+        finally:
+            self.comm = comm
+        K.add_rmsnorm(ws.x, ws.delta, m.norm, c.rms_eps, n, out16=ws.xn16)
+        G.linear(self.w.lm_head, ws.xn16, n, out=ws.logits, out_f32=True)
+        return ws.logits[:n], ws.x[:n]
+
+    # ---------------------------------------------------------------- CUDA graphs
+    def capture_decode(self, b: int):
+        """Capture the greedy decode step for batch size ``b``: inputs are read from the workspace's
+        device arrays, the arg-max token ids land in ``ws.out_tok``."""
+        ws = self.ws
+        plan = Plan.decode([0] * b, [0] * b, list(range(b)))
+        self._upload(ws, plan)
+        # the attention launch grid covers every possible split, so a graph captured here is valid at any position
+        torch.cuda.synchronize(self.dev)
+        s = torch.cuda.Stream(device=self.dev)
+        s.wait_stream(torch.cuda.current_stream(self.dev))
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                self._backbone(ws, b, b, False, False, False)
+                K.argmax(ws.logits, b, ws.out_tok, ws.out_val)
+        torch.cuda.current_stream(self.dev).wait_stream(s)
+        torch.cuda.synchronize(self.dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._backbone(ws, b, b, False, False, False)
+            K.argmax(ws.logits, b, ws.out_tok, ws.out_val)
+        self.graphs[("decode", b)] = g
+        return g
+
+    def replay_decode(self, tokens, pos, slots) -> torch.Tensor:
+        """Graph replay of a greedy decode step; returns the device tensor of token ids."""
+        b = len(tokens)
+        g = self.graphs.get(("decode", b))
+        if g is None:
+            g = self.capture_decode(b)
+        self._upload(self.ws, Plan.decode(tokens, pos, slots))
+        g.replay()
+        return self.ws.out_tok[:b]

@@ -1,0 +1,161 @@
+"""Linear layers on the GPU: weight re-tiling for the tensor-core GEMM and the call wrappers.
+
+``prepare`` turns a canonical ``QLinear`` into the tile-major layout ``gemm_tc.cu`` streams with 1-D
+bulk copies: ``[M/128][K/128]`` tiles of 128 rows x 128 k, each tile contiguous, with the 16-byte
+chunks of a row pre-swizzled so the dequantising warps read shared memory without bank conflicts.
+This load-time transform is the counterpart of the reference's MMA-fragment repack
+(reference: src/quant.rs:424-537); it is internal to the engine and not part of the file format.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from ..models.weights import QLinear
+from . import lib as _lib
+from .lib import c_float, c_int, c_void_p, ptr, stream
+
+WF_NVFP4, WF_FP8, WF_F16, WF_BF16 = 0, 1, 2, 3
+_FMT_CODE = {"nvfp4": WF_NVFP4, "fp8": WF_FP8, "bf16": WF_BF16}
+
+
+@dataclass
+class TcWeight:
+    wt: torch.Tensor               # uint8, tile-major
+    row_scale: Optional[torch.Tensor]
+    m: int
+    k: int
+    fmt: int
+    splitk: int
+
+
+def _pad2(t: torch.Tensor, rows: int, cols: int) -> torch.Tensor:
+    if t.shape[0] == rows and t.shape[1] == cols:
+        return t
+    out = torch.zeros((rows, cols), dtype=t.dtype, device=t.device)
+    out[:t.shape[0], :t.shape[1]] = t
+    return out
+
+
+def _swizzle_chunks(t: torch.Tensor, fn) -> torch.Tensor:
+    """t [..., 128 rows, C chunks, B bytes]: physical chunk c of row r takes logical chunk c ^ fn(r)."""
+    C = t.shape[-2]
+    r = torch.arange(128, device=t.device)
+    idx = torch.arange(C, device=t.device)[None, :] ^ fn(r)[:, None]          # [128, C]
+    idx = idx.reshape((1,) * (t.dim() - 3) + (128, C, 1)).expand(t.shape)
+    return torch.gather(t, -2, idx)
+
+
+def tile_nvfp4(packed: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    m, kh = packed.shape
+    k = kh * 2
+    mt, ks = (m + 127) // 128, (k + 127) // 128
+    p = _pad2(packed, mt * 128, ks * 64).view(mt, 128, ks, 4, 16).permute(0, 2, 1, 3, 4)
+    p = _swizzle_chunks(p, lambda r: (r >> 1) & 3).reshape(mt, ks, 8192)
+    s = _pad2(scales, mt * 128, ks * 8).view(mt, 128, ks, 8).permute(0, 2, 1, 3).reshape(mt, ks, 1024)
+    return torch.cat([p, s], dim=-1).contiguous()
+
+
+def tile_fp8(codes: torch.Tensor) -> torch.Tensor:
+    m, k = codes.shape
+    mt, ks = (m + 127) // 128, (k + 127) // 128
+    p = _pad2(codes, mt * 128, ks * 128).view(mt, 128, ks, 8, 16).permute(0, 2, 1, 3, 4)
+    return _swizzle_chunks(p, lambda r: r & 7).reshape(mt, ks, 16384).contiguous()
+
+
+def tile_f16(w: torch.Tensor) -> torch.Tensor:
+    """bf16/f32 weights -> f16 UMMA tiles: per (m-tile, k-slab) two [128 x 64] K-major sub-tiles with
+    the 128-byte swizzle already applied."""
+    m, k = w.shape
+    mt, ks = (m + 127) // 128, (k + 127) // 128
+    h = _pad2(w.to(torch.float16), mt * 128, ks * 128).view(mt, 128, ks, 2, 8, 8).permute(0, 2, 3, 1, 4, 5)
+    h = h.contiguous().view(torch.uint8).reshape(mt, ks, 2, 128, 8, 16)
+    return _swizzle_chunks(h, lambda r: r & 7).reshape(mt, ks, 32768).contiguous()
+
+
+_resident = {}
+
+
+def _resident_ctas(fmt: int) -> int:
+    if fmt not in _resident:
+        _resident[fmt] = max(1, int(_lib.lib().vg_gemm_tc_resident_ctas(c_int(WF_NVFP4))))
+    return _resident[fmt]
+
+
+def choose_splitk(m: int, k: int, fmt: int) -> int:
+    """Split-K factor for the decode shape: a pure function of (M, K, format), never of the batch
+    width, so that every width <= 16 runs the same reduction tree."""
+    tiles = (m + 127) // 128
+    ks = (k + 127) // 128
+    slots = _resident_ctas(fmt)
+    best, best_eff = 1, 0.0
+    for s in range(1, 9):
+        if s > 1 and ks // s < 4:
+            break
+        waves = -(-tiles * s // slots)
+        eff = tiles * s / (waves * slots)
+        # prefer fewer waves of work per CTA only when the fill is clearly better
+        score = eff / waves ** 0.25
+        if score > best_eff * 1.02:
+            best, best_eff = s, score
+    return best
+
+
+def prepare(q: QLinear, keep_canonical: bool = True, splitk: Optional[int] = None) -> TcWeight:
+    """Build (once) the tensor-core layout of a linear that lives on a CUDA device."""
+    if q.kernel is not None:
+        return q.kernel
+    if q.fmt == "nvfp4":
+        wt, fmt, rs = tile_nvfp4(q.packed, q.scales), WF_NVFP4, q.row_scale
+    elif q.fmt == "fp8":
+        wt, fmt, rs = tile_fp8(q.codes), WF_FP8, q.row_scale
+    else:
+        wt, fmt, rs = tile_f16(q.w), WF_F16, None
+    mt = (q.m + 127) // 128
+    if rs is not None and rs.numel() < mt * 128:
+        rs = torch.cat([rs, torch.zeros(mt * 128 - rs.numel(), dtype=rs.dtype, device=rs.device)])
+    sk = splitk if splitk is not None else choose_splitk(q.m, q.k, fmt)
+    q.kernel = TcWeight(wt, rs, q.m, q.k, fmt, sk)
+    if not keep_canonical:
+        q.packed = q.scales = q.codes = q.w = None
+    return q.kernel
+
+
+def linear(q: QLinear, x16: torch.Tensor, n: Optional[int] = None, out: Optional[torch.Tensor] = None,
+           out_f32: bool = False) -> torch.Tensor:
+    """``out[n, m] = sum_k W[m, k] x[n, k]`` on the tensor cores. ``x16`` is f16 ``[rows >= n, K]``."""
+    tw = prepare(q)
+    assert x16.dtype == torch.float16 and x16.stride(1) == 1 and x16.shape[1] == tw.k
+    n = x16.shape[0] if n is None else n
+    if out is None:
+        out = torch.empty((n, tw.m), dtype=torch.float32 if out_f32 else torch.bfloat16, device=x16.device)
+    L = _lib.lib()
+    rc = L.vg_gemm_tc(ptr(tw.wt), ptr(tw.row_scale), ptr(x16), c_int(x16.shape[0]), c_int(x16.stride(0)), ptr(out),
+                      c_int(1 if out.dtype == torch.float32 else 0), c_int(tw.m), c_int(tw.k), c_int(n),
+                      c_int(out.stride(0)), c_int(tw.fmt), c_int(tw.splitk), ptr(_lib.err_word(x16.device)), stream())
+    _lib.check(rc, "vg_gemm_tc")
+    return out
+
+
+def linear_simt(q: QLinear, x16: torch.Tensor, n: Optional[int] = None, out: Optional[torch.Tensor] = None,
+                out_f32: bool = False) -> torch.Tensor:
+    """Same contract as ``linear`` on CUDA cores over the canonical layout (small matrices, cross-checks)."""
+    n = x16.shape[0] if n is None else n
+    if out is None:
+        out = torch.empty((n, q.m), dtype=torch.float32 if out_f32 else torch.bfloat16, device=x16.device)
+    if q.fmt == "nvfp4":
+        w, sc = q.packed, q.scales
+    elif q.fmt == "fp8":
+        w, sc = q.codes, None
+    else:
+        w, sc = q.w, None
+    if w is None:
+        raise _lib.KernelError("canonical weights were released; use linear()")
+    L = _lib.lib()
+    rc = L.vg_gemm_simt(ptr(w), ptr(sc), ptr(q.row_scale), ptr(x16), ptr(out),
+                        c_int(1 if out.dtype == torch.float32 else 0), c_int(q.m), c_int(q.k), c_int(n),
+                        c_int(x16.stride(0)), c_int(out.stride(0)), c_int(_FMT_CODE[q.fmt]), stream())
+    _lib.check(rc, "vg_gemm_simt")
+    return out

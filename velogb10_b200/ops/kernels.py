@@ -1,0 +1,118 @@
+"""Thin Python wrappers over the non-GEMM kernels (norms, RoPE/KV write, attention, GatedDeltaNet,
+embedding, sampling). Each wrapper validates shapes/dtypes, enqueues on the current stream and
+returns the output tensor; none of them allocates unless the caller omits ``out``."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..models.weights import QLinear
+from . import lib as _lib
+from .gemm import _FMT_CODE
+from .lib import c_float, c_int, c_ll, ptr, stream
+
+
+def add_rmsnorm(res: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor, eps: float, n: int,
+                out16: Optional[torch.Tensor] = None, out_bf: Optional[torch.Tensor] = None, plus_one: bool = True):
+    """``res[:n] += delta[:n]`` (when delta is given), then RMSNorm of the updated rows into ``out16``
+    (f16) and/or ``out_bf`` (bf16). ``res`` is bf16 [rows, h] and is updated in place."""
+    h = res.shape[1]
+    assert res.dtype == torch.bfloat16 and w.dtype == torch.float32
+    rc = _lib.lib().vg_add_rmsnorm(ptr(res), ptr(delta), ptr(w), ptr(out16), ptr(out_bf), c_int(n), c_int(h),
+                                   c_float(eps), c_int(1 if plus_one else 0), c_int(res.stride(0)),
+                                   c_int(delta.stride(0) if delta is not None else 0), stream())
+    _lib.check(rc, "vg_add_rmsnorm")
+
+
+def attn_prep(qkv, q_norm, k_norm, pos, slot, kv_row, q_out, kc, vc, n, nh, nkv, hd, rdim, eps, theta, gated=True):
+    max_seq = kc.shape[2]
+    rc = _lib.lib().vg_attn_prep(ptr(qkv), c_int(qkv.stride(0)), ptr(q_norm), ptr(k_norm), ptr(pos), ptr(slot),
+                                 ptr(kv_row), ptr(q_out), ptr(kc), ptr(vc), c_int(n), c_int(nh), c_int(nkv), c_int(hd),
+                                 c_int(rdim), c_int(max_seq), c_float(eps), c_float(theta), c_int(1 if gated else 0),
+                                 stream())
+    _lib.check(rc, "vg_attn_prep")
+
+
+def swiglu(gu: torch.Tensor, out16: torch.Tensor, n: int, inter: int):
+    rc = _lib.lib().vg_swiglu(ptr(gu), ptr(out16), c_int(n), c_int(inter), c_int(gu.stride(0)), stream())
+    _lib.check(rc, "vg_swiglu")
+
+
+def cast_f16(x: torch.Tensor, out16: Optional[torch.Tensor] = None) -> torch.Tensor:
+    assert x.is_contiguous() and x.dtype in (torch.float32, torch.bfloat16)
+    if out16 is None:
+        out16 = torch.empty(x.shape, dtype=torch.float16, device=x.device)
+    rc = _lib.lib().vg_cast_f16(ptr(x), c_int(1 if x.dtype == torch.float32 else 0), ptr(out16), c_ll(x.numel()), stream())
+    _lib.check(rc, "vg_cast_f16")
+    return out16
+
+
+def embed_gather(e: QLinear, tok: torch.Tensor, out: torch.Tensor, n: int):
+    if e.fmt == "nvfp4":
+        table, sc = e.packed, e.scales
+    elif e.fmt == "fp8":
+        table, sc = e.codes, None
+    else:
+        table, sc = e.w, None
+    rc = _lib.lib().vg_embed_gather(ptr(table), ptr(sc), ptr(e.row_scale), ptr(tok), ptr(out), c_int(n), c_int(e.k),
+                                    c_int(_FMT_CODE[e.fmt]), stream())
+    _lib.check(rc, "vg_embed_gather")
+
+
+def attn_scratch_floats(n: int, nh: int, hd: int, ns_grid: int = 32) -> int:
+    return int(_lib.lib().vg_attn_scratch_floats(c_int(n), c_int(nh), c_int(hd), c_int(ns_grid)))
+
+
+def attn_decode(q, kc, vc, lens, slots, part, out16, n, nh, nkv, hd, gate=None, base=None, path=None,
+                ns_grid: int = 32, direct: bool = False):
+    """Split-K GQA attention of ``n`` columns over the slotted cache. ``lens[c]`` keys are attended by
+    column c; ``part`` is the fp32 partial buffer (scratch, ``attn_scratch_floats`` elements)."""
+    max_seq = kc.shape[2]
+    rc = _lib.lib().vg_attn_decode(ptr(q), ptr(kc), ptr(vc), ptr(lens), ptr(slots), ptr(base), ptr(path),
+                                   c_int(path.stride(0) if path is not None else 0), ptr(part), c_int(n), c_int(nh),
+                                   c_int(nkv), c_int(hd), c_int(max_seq), c_int(ns_grid), c_int(1 if direct else 0),
+                                   ptr(gate), c_int(gate.stride(0) if gate is not None else 0), ptr(out16), stream())
+    _lib.check(rc, "vg_attn_decode")
+
+
+def gdn_conv(x, state, w, in_slot, parent, out_slot, out, n, conv_dim, ck, phase: int = 3):
+    rc = _lib.lib().vg_gdn_conv(ptr(x), c_int(x.stride(0)), ptr(state), ptr(w), ptr(in_slot), ptr(parent),
+                                ptr(out_slot), ptr(out), c_int(n), c_int(conv_dim), c_int(ck), c_int(phase), stream())
+    _lib.check(rc, "vg_gdn_conv")
+
+
+def gdn_step(qkv, proj, off_z, off_b, off_a, S, A_log, dt_bias, norm_w, chain_start, chain_len, n_chains,
+             in_slot, parent, out_slot, out16, nk, nv, kd, vd, eps):
+    rc = _lib.lib().vg_gdn_step(ptr(qkv), ptr(proj), c_int(proj.stride(0)), c_int(off_z), c_int(off_b), c_int(off_a),
+                                ptr(S), ptr(A_log), ptr(dt_bias), ptr(norm_w), ptr(chain_start), ptr(chain_len),
+                                c_int(n_chains), ptr(in_slot), ptr(parent), ptr(out_slot), ptr(out16), c_int(nk),
+                                c_int(nv), c_int(kd), c_int(vd), c_float(eps), stream())
+    _lib.check(rc, "vg_gdn_step")
+
+
+def argmax(logits: torch.Tensor, n: int, out: torch.Tensor, out_val: Optional[torch.Tensor] = None,
+           idx_offset: int = 0):
+    assert logits.dtype == torch.float32
+    rc = _lib.lib().vg_argmax(ptr(logits), c_int(n), c_int(logits.shape[1]), c_int(logits.stride(0)), ptr(out),
+                              ptr(out_val), c_int(idx_offset), stream())
+    _lib.check(rc, "vg_argmax")
+
+
+def penalty(logits, n, toks, counts, n_toks, rep, pres, freq):
+    rc = _lib.lib().vg_penalty(ptr(logits), c_int(n), c_int(logits.shape[1]), c_int(logits.stride(0)), ptr(toks),
+                               ptr(counts), ptr(n_toks), c_int(toks.shape[1]), ptr(rep), ptr(pres), ptr(freq), stream())
+    _lib.check(rc, "vg_penalty")
+
+
+def nucleus(logits, n, temp, top_k, top_p, seed, out_tok=None, ids=None, probs=None, n_keep=None):
+    rc = _lib.lib().vg_nucleus(ptr(logits), c_int(n), c_int(logits.shape[1]), c_int(logits.stride(0)), ptr(temp),
+                               ptr(top_k), ptr(top_p), ptr(seed), ptr(out_tok), ptr(ids), ptr(probs), ptr(n_keep),
+                               stream())
+    _lib.check(rc, "vg_nucleus")
+
+
+def nll(logits, n, target, out):
+    rc = _lib.lib().vg_nll(ptr(logits), c_int(n), c_int(logits.shape[1]), c_int(logits.stride(0)), ptr(target),
+                           ptr(out), stream())
+    _lib.check(rc, "vg_nll")
