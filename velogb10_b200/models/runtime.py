@@ -101,10 +101,12 @@ class Workspace:
         bf = lambda *s: torch.zeros(s, dtype=torch.bfloat16, device=dev)
         f16 = lambda *s: torch.zeros(s, dtype=torch.float16, device=dev)
         f32 = lambda *s: torch.zeros(s, dtype=torch.float32, device=dev)
-        self.tok, self.pos, self.kv_slot, self.kv_row = i32(rows), i32(rows), i32(rows), i32(rows)
-        self.lens, self.base, self.path = i32(rows), i32(rows), i32(rows, MAX_PATH)
-        self.st_in, self.parent, self.st_out = i32(rows), i32(rows), i32(rows)
-        self.chain_start, self.chain_len = i32(rows), i32(rows)
+        # all per-column int32 metadata lives in one buffer so a step needs a single host->device copy
+        self.meta = i32(11, rows)
+        self.meta_host = torch.zeros((11, rows), dtype=torch.int32).pin_memory()
+        (self.tok, self.pos, self.kv_slot, self.kv_row, self.lens, self.base, self.st_in, self.parent, self.st_out,
+         self.chain_start, self.chain_len) = [self.meta[i] for i in range(11)]
+        self.path = i32(rows, MAX_PATH)
         h = c.hidden_size
         self.x = bf(rows, h)
         self.xn16 = f16(rows, h)
@@ -134,6 +136,7 @@ class Workspace:
             self.cat16 = f16(rows, 2 * h)
             self.mtp_e = bf(rows, h)
         self.n_uploaded = 0
+        self.upload_done = None
 
     def a16(self, width: int) -> torch.Tensor:
         """Contiguous f16 ``[rows, width]`` buffer that receives attention / GDN / SwiGLU outputs."""
@@ -230,14 +233,20 @@ class GpuModel:
         path = [row + [0] * (MAX_PATH - len(row)) for row in p.path]
         cs = [s for s, _ in p.chains] + [0] * (n - len(p.chains))
         cl = [l for _, l in p.chains] + [0] * (n - len(p.chains))
-        host = torch.tensor([p.tok, p.pos, p.kv_slot, p.kv_row, p.lens, p.base, p.st_in, p.parent, p.st_out, cs, cl],
-                            dtype=torch.int32).pin_memory()
-        dst = [ws.tok, ws.pos, ws.kv_slot, ws.kv_row, ws.lens, ws.base, ws.st_in, ws.parent, ws.st_out,
-               ws.chain_start, ws.chain_len]
-        for i, d in enumerate(dst):
-            d[:n].copy_(host[i], non_blocking=True)
+        mh = ws.meta_host
+        if ws.upload_done is not None:
+            ws.upload_done.synchronize()        # the previous copy must have left the pinned buffer
+        for i, row in enumerate((p.tok, p.pos, p.kv_slot, p.kv_row, p.lens, p.base, p.st_in, p.parent, p.st_out, cs, cl)):
+            mh[i, :n] = torch.tensor(row, dtype=torch.int32)
+        if mh.shape[1] <= 64:
+            ws.meta.copy_(mh, non_blocking=True)
+        else:
+            ws.meta[:, :n].copy_(mh[:, :n], non_blocking=True)
         if any(p.path):
             ws.path[:n].copy_(torch.tensor(path, dtype=torch.int32), non_blocking=True)
+        if ws.upload_done is None:
+            ws.upload_done = torch.cuda.Event()
+        ws.upload_done.record()
         ws.n_uploaded = n
 
     # ---------------------------------------------------------------- layers
@@ -407,6 +416,9 @@ class GpuModel:
         ws = self.ws
         plan = Plan.decode([0] * b, [0] * b, list(range(b)))
         self._upload(ws, plan)
+        # warm-up and capture run real steps on slots 0..b-1 at position 0: save what they touch
+        saved = [(t, t[:, :b].clone()) for t in (self.S, self.conv) if t is not None]
+        saved += [(t, t[:, :b, :, :1].clone()) for t in (self.kc, self.vc)]
         # the attention launch grid covers every possible split, so a graph captured here is valid at any position
         torch.cuda.synchronize(self.dev)
         s = torch.cuda.Stream(device=self.dev)
@@ -421,8 +433,34 @@ class GpuModel:
         with torch.cuda.graph(g):
             self._backbone(ws, b, b, False, False, False)
             K.argmax(ws.logits, b, ws.out_tok, ws.out_val)
+        for t, keep in saved:
+            if t is self.kc or t is self.vc:
+                t[:, :b, :, :1].copy_(keep)
+            else:
+                t[:, :b].copy_(keep)
         self.graphs[("decode", b)] = g
         return g
+
+    def time_decode_steps(self, tok: int, pos: int, slot: int, steps: int) -> float:
+        """Device time (ms) of ``steps`` consecutive batch-1 greedy decode steps with the sampled token fed
+        back on the device: graph replays separated only by the tiny device-side updates of the step inputs."""
+        ws = self.ws
+        if ("decode", 1) not in self.graphs:
+            self.capture_decode(1)
+        g = self.graphs[("decode", 1)]
+        self._upload(ws, Plan.decode([tok], [pos], [slot]))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        adv = ws.meta[1:6, :1]          # pos, kv_slot(unchanged, +0), kv_row, lens, base
+        inc = torch.tensor([[1], [0], [1], [1], [1]], dtype=torch.int32, device=self.dev)
+        torch.cuda.synchronize(self.dev)
+        e0.record()
+        for _ in range(steps):
+            g.replay()
+            ws.tok[:1].copy_(ws.out_tok[:1])
+            adv.add_(inc)
+        e1.record()
+        torch.cuda.synchronize(self.dev)
+        return e0.elapsed_time(e1)
 
     def replay_decode(self, tokens, pos, slots) -> torch.Tensor:
         """Graph replay of a greedy decode step; returns the device tensor of token ids."""

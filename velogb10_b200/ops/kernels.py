@@ -73,7 +73,7 @@ def attn_decode(q, kc, vc, lens, slots, part, out16, n, nh, nkv, hd, gate=None, 
                                    c_int(path.stride(0) if path is not None else 0), ptr(part), c_int(n), c_int(nh),
                                    c_int(nkv), c_int(hd), c_int(max_seq), c_int(ns_grid), c_int(1 if direct else 0),
                                    ptr(gate), c_int(gate.stride(0) if gate is not None else 0), ptr(out16), stream())
-    _lib.check(rc, "vg_attn_decode")
+    _lib.check(rc, "vg_attn_decode", 1 if direct else 2)
 
 
 def gdn_conv(x, state, w, in_slot, parent, out_slot, out, n, conv_dim, ck, phase: int = 3):

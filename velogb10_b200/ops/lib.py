@@ -54,9 +54,21 @@ def stream() -> c_void_p:
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def check(rc: int, what: str):
+launches = 0        # kernels enqueued through this module since import (each wrapper reports its count)
+
+
+def check(rc: int, what: str, kernels: int = 1):
+    global launches
     if rc != 0:
         raise KernelError(f"{what} failed with code {rc}")
+    launches += kernels
+
+
+def count_launches(fn) -> int:
+    """Number of kernels ``fn()`` enqueues through this library."""
+    before = launches
+    fn()
+    return launches - before
 
 
 _err_words = {}
