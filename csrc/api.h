@@ -17,6 +17,8 @@ extern "C" {
 int vg_gemm_tc(const void* wt, const float* row_scale, const void* x_f16, int x_rows, int ldx, void* out, int out_f32,
                int M, int K, int N, int ldo, int wfmt, int splitk, int* err, cudaStream_t stream);
 int vg_gemm_tc_resident_ctas(int wfmt);
+void vg_gemm_tc_set_variant(int variant, int dbg);
+void vg_gemm_tc_set_trace(long long* buf);
 int vg_gemm_simt(const void* wq, const void* scales, const float* row_scale, const void* x_f16, void* out, int out_f32,
                  int M, int K, int N, int ldx, int ldo, int wfmt, cudaStream_t stream);
 

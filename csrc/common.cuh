@@ -59,12 +59,25 @@ VG_DEVINL bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait. Returns false when the budget ran out (the caller reports and unwinds).
-VG_DEVINL bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t max_polls = (1u << 22)) {
-  for (uint32_t i = 0; i < max_polls; ++i) {
+VG_DEVINL uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: gives up after `budget_ns` of wall time (default 200 ms). Returns false when the budget
+// ran out (the caller reports and unwinds).
+VG_DEVINL bool mbar_wait(uint64_t* bar, uint32_t parity, uint64_t budget_ns = 200ull * 1000 * 1000) {
+  for (int i = 0; i < 64; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
   }
-  return false;
+  const uint64_t t0 = global_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (global_ns() - t0 > budget_ns) return false;
+  }
 }
 
 // ------------------------------------------------------------------ TMA

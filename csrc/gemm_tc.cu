@@ -10,12 +10,16 @@
 // dequantize-then-library-GEMM prefill path (reference: kernels/gpu_batch.cu:2846-2996,
 // src/gpu.rs:2080-2185).
 //
-// Pipeline per CTA (320 threads):
-//   warp 0      TMA producer: 1-D bulk copies of pre-tiled packed weight slabs (128 rows x 128 k) and
-//               tiled tensor copies of the activation slab (128-byte swizzle), no multicast.
-//   warps 2-9   dequantize a packed slab from shared memory into an f16 K-major swizzled UMMA tile
-//               (e2m1 -> f16 with cvt, times the e4m3 block scale; exact in f16), then run the epilogue.
-//   warp 1      allocates TMEM, issues tcgen05.mma (M=128, N=BN, K=16) and commits to mbarriers.
+// Pipeline per CTA (352 threads):
+//   warp 0      weight producer: 1-D bulk copies of pre-tiled packed weight slabs (128 rows x 128 k).
+//   warp 10     activation producer: tiled tensor copies of the X slab (128-byte swizzle), no multicast.
+//   warps 2-9   dequantizers: thread = weight row; e2m1 -> f16 with cvt, times the e4m3 block scale
+//               (exact in f16), written with tcgen05.st straight into TMEM as the A operand, so the
+//               expanded weights never touch shared memory. They also run the epilogue.
+//   warp 1      allocates TMEM, issues tcgen05.mma (A from TMEM, B from shared memory; M=128, N=BN,
+//               K=16) and commits to mbarriers.
+// Unquantized (f16-tiled) weights skip the dequantizers: their tiles are bulk-copied into shared memory
+// already in UMMA layout and used as a shared-memory A operand.
 // Split-K runs as a thread-block cluster along z: partial tiles are summed through distributed
 // shared memory in cluster-rank order by the rank-0 CTA, so no global scratch or atomics are needed.
 // All mbarrier waits are bounded; on expiry an error code is stored to the status word and the CTA
@@ -34,13 +38,15 @@ using namespace vg;
 
 constexpr int BM = 128;
 constexpr int BK = 128;
-constexpr int A_BYTES = BM * BK * 2;       // one dequantized f16 weight slab
+constexpr int A_BYTES = BM * BK * 2;       // one f16 weight slab in shared memory (f16-tiled weights only)
 constexpr int SUB_BYTES = BM * 128;        // one 64-wide K sub-tile of it
+constexpr int A_COLS = BK / 2;             // TMEM columns of one dequantized slab (two f16 per column)
+constexpr int NTHREADS = 384;
 
 template <int WFMT> struct PackBytes;
 template <> struct PackBytes<VG_WF_NVFP4> { static constexpr int v = 128 * 64 + 128 * 8; };
 template <> struct PackBytes<VG_WF_FP8> { static constexpr int v = 128 * 128; };
-template <> struct PackBytes<VG_WF_F16> { static constexpr int v = 0; };
+template <> struct PackBytes<VG_WF_F16> { static constexpr int v = A_BYTES; };
 
 struct GemmParams {
   const uint8_t* wt;
@@ -50,17 +56,28 @@ struct GemmParams {
   int ks_total;
   int out_f32;
   int* err;
+  int dbg;     // diagnostics: bit 0 skips the dequantisation math, bit 1 skips the MMA issue
+  long long* trace;   // optional [9][64] cycle stamps of CTA (0,0,0): per-role pipeline events per slab
 };
 
-template <int WFMT, int BN, int NP, int NA, int NB>
-struct SmemLayout {
+constexpr uint32_t pow2_cols(uint32_t c) { return c <= 32 ? 32 : c <= 64 ? 64 : c <= 128 ? 128 : c <= 256 ? 256 : 512; }
+
+// NP: weight stages in shared memory; NA: slabs in flight between dequantizers / activation producer and
+// the MMA issuers (TMEM A buffers and activation stages are released together by one commit).
+template <int WFMT, int BN, int NP, int NA>
+struct Cfg {
+  static constexpr bool quant = WFMT != VG_WF_F16;
+  static constexpr int pack = PackBytes<WFMT>::v;
   static constexpr int b_bytes = BN * BK * 2;
-  static constexpr int a_off = 0;
-  static constexpr int b_off = a_off + NA * A_BYTES;
-  static constexpr int p_off = b_off + NB * b_bytes;
-  static constexpr int bar_off = p_off + NP * PackBytes<WFMT>::v;
-  static constexpr int n_bars = 2 * NP + 2 * NA + 2 * NB + 1;
-  static constexpr int total = bar_off + n_bars * 8 + 16 + 1024;   // + tmem slot/abort + alignment slack
+  static constexpr int b_off = 0;
+  static constexpr int p_off = b_off + NA * b_bytes;              // multiple of 1024 for every BN >= 8
+  static constexpr int bar_off = p_off + NP * pack;
+  static constexpr int n_bars = 2 * NP + 3 * NA + 1;
+  static constexpr int smem_total = bar_off + n_bars * 8 + 16 + 1024;
+  static constexpr uint32_t acc_w = BN;                            // columns of one accumulator
+  static constexpr uint32_t acc_cols = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators (one per MMA issuer)
+  static constexpr uint32_t tmem_cols = pow2_cols(acc_cols + (quant ? NA * A_COLS : 0));
+  static_assert(NP * pack >= BN * BM * 4 || BN > 64, "split-K staging must fit in the weight stages");
 };
 
 __device__ __forceinline__ uint32_t cvt_e4m3x2_f16x2(uint16_t v) {
@@ -69,8 +86,8 @@ __device__ __forceinline__ uint32_t cvt_e4m3x2_f16x2(uint16_t v) {
   return r;
 }
 
-// 8 e2m1 codes (one 32-bit word, low nibble first) times a block scale -> 8 f16 in a uint4.
-__device__ __forceinline__ uint4 dequant8_fp4(uint32_t w, __half2 s2) {
+// 8 e2m1 codes (one 32-bit word, low nibble first) times a block scale -> 8 f16 in 4 registers.
+__device__ __forceinline__ void dequant8_fp4(uint32_t w, __half2 s2, uint32_t* o) {
   uint32_t h0, h1, h2, h3;
   asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
       "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
@@ -84,12 +101,38 @@ __device__ __forceinline__ uint4 dequant8_fp4(uint32_t w, __half2 s2) {
   __half2 b = __hmul2(*reinterpret_cast<__half2*>(&h1), s2);
   __half2 c = __hmul2(*reinterpret_cast<__half2*>(&h2), s2);
   __half2 d = __hmul2(*reinterpret_cast<__half2*>(&h3), s2);
-  uint4 o;
-  o.x = *reinterpret_cast<uint32_t*>(&a);
-  o.y = *reinterpret_cast<uint32_t*>(&b);
-  o.z = *reinterpret_cast<uint32_t*>(&c);
-  o.w = *reinterpret_cast<uint32_t*>(&d);
-  return o;
+  o[0] = *reinterpret_cast<uint32_t*>(&a);
+  o[1] = *reinterpret_cast<uint32_t*>(&b);
+  o[2] = *reinterpret_cast<uint32_t*>(&c);
+  o[3] = *reinterpret_cast<uint32_t*>(&d);
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// A operand from TMEM, B operand from shared memory.
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+enum { TR_PROD = 0, TR_PACK_FULL, TR_MATH, TR_A_EMPTY, TR_ST_DONE, TR_MMA_A, TR_MMA_B, TR_MMA_DONE, TR_BPROD };
+__device__ __forceinline__ void stamp(const GemmParams& p, int role, int slab) {
+  if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && slab < 64) p.trace[role * 64 + slab] = clock64();
 }
 
 __device__ __forceinline__ void report(int* err, int code, volatile int* abort_flag) {
@@ -97,26 +140,23 @@ __device__ __forceinline__ void report(int* err, int code, volatile int* abort_f
   *abort_flag = 1;
 }
 
-template <int WFMT, int BN, int NP_, int NA, int NB>
-__global__ void __launch_bounds__(320, 1)
+template <int WFMT, int BN, int NP, int NA>
+__global__ void __launch_bounds__(NTHREADS, 1)
 gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
-  using L = SmemLayout<WFMT, BN, NP_, NA, NB>;
-  constexpr int NP = NP_ > 0 ? NP_ : 1;   // ring size used in index math (no pack ring for f16 weights)
-  constexpr int PACK = PackBytes<WFMT>::v;
-  constexpr uint32_t NCOLS = BN < 32 ? 32 : BN;
+  using C = Cfg<WFMT, BN, NP, NA>;
+  constexpr int PACK = C::pack;
+  constexpr bool QUANT = C::quant;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sA = smem + L::a_off;
-  uint8_t* sB = smem + L::b_off;
-  uint8_t* sP = smem + L::p_off;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::bar_off);
+  uint8_t* sB = smem + C::b_off;
+  uint8_t* sP = smem + C::p_off;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::bar_off);
   uint64_t* pack_full = bars;
-  uint64_t* pack_empty = pack_full + NP_;
-  uint64_t* a_full = pack_empty + NP_;
-  uint64_t* a_empty = a_full + NA;
-  uint64_t* b_full = a_empty + NA;
-  uint64_t* b_empty = b_full + NB;
-  uint64_t* acc_full = b_empty + NB;
+  uint64_t* pack_empty = pack_full + NP;
+  uint64_t* a_full = pack_empty + NP;       // dequantized slab is in TMEM
+  uint64_t* b_full = a_full + NA;           // activation slab is in shared memory
+  uint64_t* ab_empty = b_full + NA;         // the MMAs that read both have completed
+  uint64_t* acc_full = ab_empty + NA;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -126,132 +166,153 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
   const int ks0 = (int)(((long long)z * p.ks_total) / S);
   const int ks1 = (int)(((long long)(z + 1) * p.ks_total) / S);
   const int nks = ks1 - ks0;
+  // Each row tile walks its K range from a different starting slab (wrapping around), so the CTAs of a
+  // wave do not all ask L2 for the same activation lines at the same moment. The order is a function of
+  // the tile index only, hence identical for every batch width.
+  const int rot = nks > 0 ? (int)(((unsigned)mt * 7u + (unsigned)z * 3u) % (unsigned)nks) : 0;
+  auto slab_of = [&](int i) { int k = i + rot; return ks0 + (k >= nks ? k - nks : k); };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NP_; ++i) { mbar_init(&pack_full[i], 1); mbar_init(&pack_empty[i], 8); }
-    for (int i = 0; i < NA; ++i) { mbar_init(&a_full[i], WFMT == VG_WF_F16 ? 1 : 8); mbar_init(&a_empty[i], 1); }
-    for (int i = 0; i < NB; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
-    mbar_init(acc_full, 1);
+    // quantized: pack_empty is released by the 8 dequantizer warps; f16 tiles: by the MMA commit
+    for (int i = 0; i < NP; ++i) { mbar_init(&pack_full[i], 1); mbar_init(&pack_empty[i], QUANT ? 8 : 1); }
+    for (int i = 0; i < NA; ++i) { mbar_init(&a_full[i], 8); mbar_init(&b_full[i], 1); mbar_init(&ab_empty[i], 1); }
+    mbar_init(acc_full, 2);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmap_x);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, NCOLS);
+    tmem_alloc(tmem_slot, C::tmem_cols);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_a0 = tmem_base + C::acc_cols;
 
   if (warp == 0) {
-    // ------------------------------------------------ TMA producer
+    // ------------------------------------------------ weight producer
     if (lane == 0) {
       for (int i = 0; i < nks && !*abort_flag; ++i) {
-        const int ks = ks0 + i;
-        if (WFMT != VG_WF_F16) {
-          const int s = i % NP;
-          if (!mbar_wait(&pack_empty[s], ((i / NP) & 1) ^ 1)) { report(p.err, VG_ERR_EMPTY_WAIT, abort_flag); break; }
-          mbar_arrive_expect_tx(&pack_full[s], PACK);
-          tma_bulk_g2s(sP + (size_t)s * PACK, p.wt + ((size_t)mt * p.ks_total + ks) * PACK, PACK, &pack_full[s]);
-        } else {
-          const int a = i % NA;
-          if (!mbar_wait(&a_empty[a], ((i / NA) & 1) ^ 1)) { report(p.err, VG_ERR_EMPTY_WAIT, abort_flag); break; }
-          mbar_arrive_expect_tx(&a_full[a], A_BYTES);
-          tma_bulk_g2s(sA + (size_t)a * A_BYTES, p.wt + ((size_t)mt * p.ks_total + ks) * A_BYTES, A_BYTES, &a_full[a]);
-        }
-        const int b = i % NB;
-        if (!mbar_wait(&b_empty[b], ((i / NB) & 1) ^ 1)) { report(p.err, VG_ERR_EMPTY_WAIT, abort_flag); break; }
-        mbar_arrive_expect_tx(&b_full[b], L::b_bytes);
-        uint8_t* bdst = sB + (size_t)b * L::b_bytes;
+        const int s = i % NP;
+        if (!mbar_wait(&pack_empty[s], ((i / NP) & 1) ^ 1)) { report(p.err, VG_ERR_EMPTY_WAIT, abort_flag); break; }
+        stamp(p, TR_PROD, i);
+        mbar_arrive_expect_tx(&pack_full[s], PACK);
+        tma_bulk_g2s(sP + (size_t)s * PACK, p.wt + ((size_t)mt * p.ks_total + slab_of(i)) * PACK, PACK, &pack_full[s]);
+      }
+    }
+  } else if (warp == 10) {
+    // ------------------------------------------------ activation producer
+    if (lane == 0) {
+      for (int i = 0; i < nks && !*abort_flag; ++i) {
+        const int b = i % NA;
+        if (!mbar_wait(&ab_empty[b], ((i / NA) & 1) ^ 1)) { report(p.err, VG_ERR_EMPTY_WAIT, abort_flag); break; }
+        stamp(p, TR_BPROD, i);
+        mbar_arrive_expect_tx(&b_full[b], C::b_bytes);
+        uint8_t* bdst = sB + (size_t)b * C::b_bytes;
+        const int ks = slab_of(i);
         tma_tensor2d_g2s(bdst, &tmap_x, ks * BK, nt * BN, &b_full[b]);
         tma_tensor2d_g2s(bdst + BN * 128, &tmap_x, ks * BK + 64, nt * BN, &b_full[b]);
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------ MMA issuer
+  } else if (warp == 1 || warp == 11) {
+    // ------------------------------------------------ MMA issuers: even slabs -> accumulator 0 (warp 1),
+    // odd slabs -> accumulator 1 (warp 11). The epilogue adds the two in a fixed order.
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_f16(BM, BN, 0, 0);
+      const int me = warp == 1 ? 0 : 1;
+      const uint32_t tmem_acc = tmem_base + (uint32_t)me * C::acc_w;
       bool ok = true;
-      for (int i = 0; i < nks && !*abort_flag; ++i) {
-        const int a = i % NA, b = i % NB;
-        if (!mbar_wait(&a_full[a], (i / NA) & 1)) { report(p.err, VG_ERR_DEQ_WAIT, abort_flag); ok = false; break; }
-        if (!mbar_wait(&b_full[b], (i / NB) & 1)) { report(p.err, VG_ERR_TMA_WAIT, abort_flag); ok = false; break; }
+      for (int i = me; i < nks && !*abort_flag; i += 2) {
+        const int a = i % NA;
+        const int sp = i % NP;
+        if (QUANT) {
+          if (!mbar_wait(&a_full[a], (i / NA) & 1)) { report(p.err, VG_ERR_DEQ_WAIT, abort_flag); ok = false; break; }
+        } else {
+          if (!mbar_wait(&pack_full[sp], (i / NP) & 1)) { report(p.err, VG_ERR_TMA_WAIT, abort_flag); ok = false; break; }
+        }
+        stamp(p, TR_MMA_A, i);
+        if (!mbar_wait(&b_full[a], (i / NA) & 1)) { report(p.err, VG_ERR_TMA_WAIT, abort_flag); ok = false; break; }
+        stamp(p, TR_MMA_B, i);
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(sA + (size_t)a * A_BYTES);
-        const uint32_t b_addr = smem_u32(sB + (size_t)b * L::b_bytes);
+        const uint32_t b_addr = smem_u32(sB + (size_t)a * C::b_bytes);
+        if (!(p.dbg & 2)) {
 #pragma unroll
-        for (int sub = 0; sub < 2; ++sub) {
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            const uint64_t ad = umma_desc_sw128(a_addr + sub * SUB_BYTES + kk * 32);
-            const uint64_t bd = umma_desc_sw128(b_addr + sub * (BN * 128) + kk * 32);
-            umma_f16(tmem_base, ad, bd, idesc, (i | sub | kk) != 0 ? 1u : 0u);
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint64_t bd = umma_desc_sw128(b_addr + (kk >> 2) * (BN * 128) + (kk & 3) * 32);
+            const uint32_t acc_flag = (i >= 2 || kk != 0) ? 1u : 0u;
+            if (QUANT) {
+              umma_f16_ts(tmem_acc, tmem_a0 + (uint32_t)(a * A_COLS + kk * 8), bd, idesc, acc_flag);
+            } else {
+              const uint32_t a_addr = smem_u32(sP + (size_t)sp * PACK);
+              umma_f16(tmem_acc, umma_desc_sw128(a_addr + (kk >> 2) * SUB_BYTES + (kk & 3) * 32), bd, idesc, acc_flag);
+            }
           }
         }
-        umma_commit(&a_empty[a]);
-        umma_commit(&b_empty[b]);
+        umma_commit(&ab_empty[a]);
+        if (!QUANT) umma_commit(&pack_empty[sp]);
+        stamp(p, TR_MMA_DONE, i);
       }
       if (ok) umma_commit(acc_full);
     }
-  } else {
-    // ------------------------------------------------ dequantizers
-    if (WFMT != VG_WF_F16) {
-      const int dt = threadIdx.x - 64;
-      const int dw = dt >> 5;
-      const int r = dw * 16 + (lane & 7) + ((lane >> 4) << 3);
-      const int half = (lane >> 3) & 1;
-      const int rs = r & 7;
-      for (int i = 0; i < nks && !*abort_flag; ++i) {
-        const int s = i % NP, a = i % NA;
-        if (!mbar_wait(&pack_full[s], (i / NP) & 1)) { report(p.err, VG_ERR_TMA_WAIT, abort_flag); break; }
-        if (!mbar_wait(&a_empty[a], ((i / NA) & 1) ^ 1)) { report(p.err, VG_ERR_EMPTY_WAIT, abort_flag); break; }
-        const uint8_t* pk = sP + (size_t)s * PACK;
-        uint8_t* arow = sA + (size_t)a * A_BYTES + half * SUB_BYTES + r * 128;
-        if (WFMT == VG_WF_NVFP4) {
-          const int sw = (r >> 1) & 3;
-          const uint4 p0 = *reinterpret_cast<const uint4*>(pk + r * 64 + (((2 * half) ^ sw) << 4));
-          const uint4 p1 = *reinterpret_cast<const uint4*>(pk + r * 64 + (((2 * half + 1) ^ sw) << 4));
-          const uint32_t sc = *reinterpret_cast<const uint32_t*>(pk + 8192 + r * 8 + half * 4);
-          uint32_t s01 = cvt_e4m3x2_f16x2((uint16_t)(sc & 0xffff));
-          uint32_t s23 = cvt_e4m3x2_f16x2((uint16_t)(sc >> 16));
-          const __half2 h01 = *reinterpret_cast<__half2*>(&s01);
-          const __half2 h23 = *reinterpret_cast<__half2*>(&s23);
-          const __half2 sc0 = __low2half2(h01), sc1 = __high2half2(h01);
-          const __half2 sc2 = __low2half2(h23), sc3 = __high2half2(h23);
-          *reinterpret_cast<uint4*>(arow + ((0 ^ rs) << 4)) = dequant8_fp4(p0.x, sc0);
-          *reinterpret_cast<uint4*>(arow + ((1 ^ rs) << 4)) = dequant8_fp4(p0.y, sc0);
-          *reinterpret_cast<uint4*>(arow + ((2 ^ rs) << 4)) = dequant8_fp4(p0.z, sc1);
-          *reinterpret_cast<uint4*>(arow + ((3 ^ rs) << 4)) = dequant8_fp4(p0.w, sc1);
-          *reinterpret_cast<uint4*>(arow + ((4 ^ rs) << 4)) = dequant8_fp4(p1.x, sc2);
-          *reinterpret_cast<uint4*>(arow + ((5 ^ rs) << 4)) = dequant8_fp4(p1.y, sc2);
-          *reinterpret_cast<uint4*>(arow + ((6 ^ rs) << 4)) = dequant8_fp4(p1.z, sc3);
-          *reinterpret_cast<uint4*>(arow + ((7 ^ rs) << 4)) = dequant8_fp4(p1.w, sc3);
-        } else {
-          // FP8: row r holds 128 code bytes in eight 16-byte chunks stored at chunk ^ (r & 7).
+  } else if (QUANT) {
+    // ------------------------------------------------ dequantizers (warps 2..9): thread = weight row
+    const int q = warp & 3;                      // TMEM lane quarter this warp owns
+    const int half = (warp - 2) >> 2;            // which 64-wide half of the slab's K range
+    const int r = q * 32 + lane;
+    const int rs = r & 7;
+    for (int i = 0; i < nks && !*abort_flag; ++i) {
+      const int s = i % NP, a = i % NA;
+      if (!mbar_wait(&pack_full[s], (i / NP) & 1)) { report(p.err, VG_ERR_TMA_WAIT, abort_flag); break; }
+      if (warp == 2 && lane == 0) stamp(p, TR_PACK_FULL, i);
+      const uint8_t* pk = sP + (size_t)s * PACK;
+      uint32_t v[32];
+      if (p.dbg & 1) {
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const int j = half * 4 + c;     // source chunk: k = j*16 .. j*16+15
-            const uint4 q = *reinterpret_cast<const uint4*>(pk + r * 128 + ((j ^ rs) << 4));
-            uint4 lo, hi;
-            lo.x = cvt_e4m3x2_f16x2((uint16_t)(q.x & 0xffff)); lo.y = cvt_e4m3x2_f16x2((uint16_t)(q.x >> 16));
-            lo.z = cvt_e4m3x2_f16x2((uint16_t)(q.y & 0xffff)); lo.w = cvt_e4m3x2_f16x2((uint16_t)(q.y >> 16));
-            hi.x = cvt_e4m3x2_f16x2((uint16_t)(q.z & 0xffff)); hi.y = cvt_e4m3x2_f16x2((uint16_t)(q.z >> 16));
-            hi.z = cvt_e4m3x2_f16x2((uint16_t)(q.w & 0xffff)); hi.w = cvt_e4m3x2_f16x2((uint16_t)(q.w >> 16));
-            *reinterpret_cast<uint4*>(arow + (((2 * c) ^ rs) << 4)) = lo;
-            *reinterpret_cast<uint4*>(arow + (((2 * c + 1) ^ rs) << 4)) = hi;
-          }
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(&a_full[a]);
-          mbar_arrive(&pack_empty[s]);
+        for (int j = 0; j < 32; ++j) v[j] = 0;
+      } else if (WFMT == VG_WF_NVFP4) {
+        const int sw = (r >> 1) & 3;
+        const uint4 p0 = *reinterpret_cast<const uint4*>(pk + r * 64 + (((2 * half) ^ sw) << 4));
+        const uint4 p1 = *reinterpret_cast<const uint4*>(pk + r * 64 + (((2 * half + 1) ^ sw) << 4));
+        const uint32_t sc = *reinterpret_cast<const uint32_t*>(pk + 8192 + r * 8 + half * 4);
+        uint32_t s01 = cvt_e4m3x2_f16x2((uint16_t)(sc & 0xffff));
+        uint32_t s23 = cvt_e4m3x2_f16x2((uint16_t)(sc >> 16));
+        const __half2 h01 = *reinterpret_cast<__half2*>(&s01);
+        const __half2 h23 = *reinterpret_cast<__half2*>(&s23);
+        const __half2 sc0 = __low2half2(h01), sc1 = __high2half2(h01);
+        const __half2 sc2 = __low2half2(h23), sc3 = __high2half2(h23);
+        dequant8_fp4(p0.x, sc0, v + 0);  dequant8_fp4(p0.y, sc0, v + 4);
+        dequant8_fp4(p0.z, sc1, v + 8);  dequant8_fp4(p0.w, sc1, v + 12);
+        dequant8_fp4(p1.x, sc2, v + 16); dequant8_fp4(p1.y, sc2, v + 20);
+        dequant8_fp4(p1.z, sc3, v + 24); dequant8_fp4(p1.w, sc3, v + 28);
+      } else {
+        // FP8: row r holds 128 code bytes in eight 16-byte chunks stored at chunk ^ (r & 7).
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint4 qv = *reinterpret_cast<const uint4*>(pk + r * 128 + (((half * 4 + c) ^ rs) << 4));
+          v[c * 8 + 0] = cvt_e4m3x2_f16x2((uint16_t)(qv.x & 0xffff)); v[c * 8 + 1] = cvt_e4m3x2_f16x2((uint16_t)(qv.x >> 16));
+          v[c * 8 + 2] = cvt_e4m3x2_f16x2((uint16_t)(qv.y & 0xffff)); v[c * 8 + 3] = cvt_e4m3x2_f16x2((uint16_t)(qv.y >> 16));
+          v[c * 8 + 4] = cvt_e4m3x2_f16x2((uint16_t)(qv.z & 0xffff)); v[c * 8 + 5] = cvt_e4m3x2_f16x2((uint16_t)(qv.z >> 16));
+          v[c * 8 + 6] = cvt_e4m3x2_f16x2((uint16_t)(qv.w & 0xffff)); v[c * 8 + 7] = cvt_e4m3x2_f16x2((uint16_t)(qv.w >> 16));
         }
       }
+      // the packed stage is consumed: hand it back before waiting for a free TMEM slab
+      __syncwarp();
+      if (warp == 2 && lane == 0) stamp(p, TR_MATH, i);
+      if (lane == 0) mbar_arrive(&pack_empty[s]);
+      if (!mbar_wait(&ab_empty[a], ((i / NA) & 1) ^ 1)) { report(p.err, VG_ERR_EMPTY_WAIT, abort_flag); break; }
+      if (warp == 2 && lane == 0) stamp(p, TR_A_EMPTY, i);
+      tc_fence_after();
+      tmem_st32(tmem_a0 + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * A_COLS + half * 32), v);
+      tmem_st_wait();
+      if (warp == 2 && lane == 0) stamp(p, TR_ST_DONE, i);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&a_full[a]);
     }
   }
+  __syncwarp();
 
   // ---------------------------------------------------- epilogue (warps 2..9)
   constexpr int CPW = BN / 2;            // accumulator columns handled by one warp
@@ -260,16 +321,19 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
   const int q = warp & 3;                // TMEM lane quarter this warp may read
   const int grp = warp >= 6 ? 1 : 0;     // which half of the columns
   const int m_local = q * 32 + lane;
-  if (warp >= 2) {
+  const bool epi = warp >= 2 && warp <= 9;
+  if (epi) {
     if (mbar_wait(acc_full, 0)) {
       tc_fence_after();
 #pragma unroll
       for (int c = 0; c < CPW; c += 8) {
-        uint32_t v[8];
-        tmem_ld8(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(grp * CPW + c), v);
+        uint32_t v0[8], v1[8];
+        tmem_ld8(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(grp * CPW + c), v0);
+        tmem_ld8(tmem_base + ((uint32_t)(q * 32) << 16) + C::acc_w + (uint32_t)(grp * CPW + c), v1);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[c + j] = __uint_as_float(v[j]);
+        for (int j = 0; j < 8; ++j)
+          acc[c + j] = nks >= 2 ? __uint_as_float(v0[j]) + __uint_as_float(v1[j]) : __uint_as_float(v0[j]);
       }
       have_acc = true;
     } else {
@@ -278,13 +342,14 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
   }
   if (S > 1) {
     // Partial tiles go through distributed shared memory; cluster rank 0 sums them in rank order.
-    float* red = reinterpret_cast<float*>(sA);
-    if (warp >= 2 && have_acc) {
+    // The weight stages are idle by now (every MMA has completed) and serve as the staging buffer.
+    float* red = reinterpret_cast<float*>(sP);
+    if (epi && have_acc) {
 #pragma unroll
       for (int c = 0; c < CPW; ++c) red[(grp * CPW + c) * BM + m_local] = acc[c];
     }
     cluster_sync_all();
-    if (z == 0 && warp >= 2 && have_acc) {
+    if (z == 0 && epi && have_acc) {
       const uint32_t red_addr = smem_u32(red);
       for (int s = 1; s < S; ++s) {
         const uint32_t remote = dsmem_map(red_addr, (uint32_t)s);
@@ -294,7 +359,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
     }
     cluster_sync_all();
   }
-  if (warp >= 2 && have_acc && z == 0) {
+  if (epi && have_acc && z == 0) {
     const int m = mt * BM + m_local;
     if (m < p.M) {
       const float rsc = p.row_scale ? p.row_scale[m] : 1.0f;
@@ -315,7 +380,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, NCOLS);
+  if (warp == 1) tmem_dealloc(tmem_base, C::tmem_cols);
 }
 
 // ------------------------------------------------------------------ host side
@@ -343,10 +408,14 @@ struct TmapKey {
     return std::tie(ptr, rows, k, bn, ldx) < std::tie(o.ptr, o.rows, o.k, o.bn, o.ldx);
   }
 };
+int g_variant = 0;
+int g_dbg = 0;
+long long* g_trace = nullptr;
 std::map<TmapKey, CUtensorMap> g_tmaps;
 std::mutex g_tmap_mu;
 
-// Tensor map over X [rows, K] f16, row stride ldx elements; box = 64 k-elements x BN rows, 128-byte swizzle.
+// Tensor map over X [rows, K] f16, row stride ldx elements; box = 64 k-elements x BN rows, 128-byte
+// swizzle. Rows beyond `rows` and k beyond K are zero-filled by the copy engine without touching memory.
 int get_tmap_x(const void* x, int rows, int K, int bn, int ldx, CUtensorMap* out) {
   std::lock_guard<std::mutex> lk(g_tmap_mu);
   TmapKey key{x, rows, K, bn, ldx};
@@ -369,21 +438,20 @@ int get_tmap_x(const void* x, int rows, int K, int bn, int ldx, CUtensorMap* out
   return 0;
 }
 
-template <int WFMT, int BN, int NP, int NA, int NB>
+template <int WFMT, int BN, int NP, int NA>
 int launch(const GemmParams& p, const CUtensorMap& tm, int splitk, cudaStream_t st) {
-  using L = SmemLayout<WFMT, BN, NP, NA, NB>;
-  auto kern = gemm_tc_kernel<WFMT, BN, NP, NA, NB>;
+  using C = Cfg<WFMT, BN, NP, NA>;
+  auto kern = gemm_tc_kernel<WFMT, BN, NP, NA>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_total);
     if (e != cudaSuccess) return (int)e;
-    cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     configured = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((p.M + BM - 1) / BM, (p.N + BN - 1) / BN, splitk);
-  cfg.blockDim = dim3(320);
-  cfg.dynamicSmemBytes = L::total;
+  cfg.blockDim = dim3(NTHREADS);
+  cfg.dynamicSmemBytes = C::smem_total;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -395,18 +463,29 @@ int launch(const GemmParams& p, const CUtensorMap& tm, int splitk, cudaStream_t 
   return (int)cudaLaunchKernelEx(&cfg, kern, p, tm);
 }
 
+// Stage counts: NVFP4 decode keeps 8 x 9 KB weight stages in flight per CTA and fits two CTAs per SM.
+template <int WFMT, int BN> struct Stages;
+template <int BN> struct Stages<VG_WF_NVFP4, BN> { static constexpr int np = BN <= 64 ? 8 : 6, na = 3; };
+template <int BN> struct Stages<VG_WF_FP8, BN> { static constexpr int np = BN <= 32 ? 5 : 4, na = 3; };
+template <int BN> struct Stages<VG_WF_F16, BN> { static constexpr int np = 3, na = 3; };
+
+template <int WFMT, int BN>
+int launch_bn(const GemmParams& p, const CUtensorMap& tm, int splitk, cudaStream_t st) {
+  using S = Stages<WFMT, BN>;
+  return launch<WFMT, BN, S::np, S::na>(p, tm, splitk, st);
+}
+
 template <int WFMT>
-int dispatch_bn(const GemmParams& p, const void* x, int x_rows, int ldx, int splitk, cudaStream_t st) {
+int dispatch_bn(const GemmParams& p, const void* x, int ldx, int splitk, cudaStream_t st) {
   CUtensorMap tm;
   int bn = p.N <= 16 ? 16 : (p.N <= 32 ? 32 : (p.N <= 64 ? 64 : 128));
-  int rc = get_tmap_x(x, x_rows, p.K, bn, ldx, &tm);
+  int rc = get_tmap_x(x, p.N, p.K, bn, ldx, &tm);
   if (rc) return rc;
-  constexpr bool F16 = WFMT == VG_WF_F16;
   switch (bn) {
-    case 16: return launch<WFMT, 16, F16 ? 0 : 3, F16 ? 3 : 2, 3>(p, tm, splitk, st);
-    case 32: return launch<WFMT, 32, F16 ? 0 : 3, F16 ? 3 : 2, 3>(p, tm, splitk, st);
-    case 64: return launch<WFMT, 64, F16 ? 0 : 3, F16 ? 3 : 2, 3>(p, tm, splitk, st);
-    default: return launch<WFMT, 128, F16 ? 0 : 3, F16 ? 3 : 2, 3>(p, tm, splitk, st);
+    case 16: return launch_bn<WFMT, 16>(p, tm, splitk, st);
+    case 32: return launch_bn<WFMT, 32>(p, tm, splitk, st);
+    case 64: return launch_bn<WFMT, 64>(p, tm, splitk, st);
+    default: return launch_bn<WFMT, 128>(p, tm, splitk, st);
   }
 }
 
@@ -415,7 +494,7 @@ int dispatch_bn(const GemmParams& p, const void* x, int x_rows, int ldx, int spl
 extern "C" int vg_gemm_tc(const void* wt, const float* row_scale, const void* x_f16, int x_rows, int ldx, void* out,
                           int out_f32, int M, int K, int N, int ldo, int wfmt, int splitk, int* err,
                           cudaStream_t stream) {
-  if (M <= 0 || K <= 0 || N <= 0 || (K % 16) != 0 || splitk < 1 || splitk > 8) return -2;
+  if (M <= 0 || K <= 0 || N <= 0 || (K % 16) != 0 || splitk < 1 || splitk > 8 || x_rows < N) return -2;
   if (ldx < K || (ldx % 8) != 0 || (reinterpret_cast<uintptr_t>(x_f16) & 15) != 0) return -4;
   GemmParams p;
   p.wt = static_cast<const uint8_t*>(wt);
@@ -425,27 +504,35 @@ extern "C" int vg_gemm_tc(const void* wt, const float* row_scale, const void* x_
   p.ks_total = (K + BK - 1) / BK;
   p.out_f32 = out_f32;
   p.err = err;
+  p.dbg = g_dbg;
+  p.trace = g_trace;
   if (splitk > p.ks_total) splitk = p.ks_total;
   if (N > 64) splitk = 1;
   switch (wfmt) {
-    case VG_WF_NVFP4: return dispatch_bn<VG_WF_NVFP4>(p, x_f16, x_rows, ldx, splitk, stream);
-    case VG_WF_FP8: return dispatch_bn<VG_WF_FP8>(p, x_f16, x_rows, ldx, splitk, stream);
-    case VG_WF_F16: return dispatch_bn<VG_WF_F16>(p, x_f16, x_rows, ldx, splitk, stream);
+    case VG_WF_NVFP4: return dispatch_bn<VG_WF_NVFP4>(p, x_f16, ldx, splitk, stream);
+    case VG_WF_FP8: return dispatch_bn<VG_WF_FP8>(p, x_f16, ldx, splitk, stream);
+    case VG_WF_F16: return dispatch_bn<VG_WF_F16>(p, x_f16, ldx, splitk, stream);
   }
   return -3;
 }
 
-// Occupancy-derived number of CTAs of the decode configuration that can be resident at once (used by
-// the host heuristic that picks the split-K factor).
+// Experiment hooks used by the micro-benchmark: diagnostic flags (see GemmParams::dbg).
+extern "C" void vg_gemm_tc_set_variant(int variant, int dbg) { g_variant = variant; g_dbg = dbg; }
+// Device buffer of 9 x 64 int64 that receives cycle stamps of CTA (0,0,0)'s pipeline events (null = off).
+extern "C" void vg_gemm_tc_set_trace(long long* buf) { g_trace = buf; }
+
+// Number of CTAs of the decode configuration that can be resident at once (used by the host
+// heuristic that picks the split-K factor).
 extern "C" int vg_gemm_tc_resident_ctas(int wfmt) {
   int dev = 0, sms = 0, per_sm = 1;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (wfmt == VG_WF_NVFP4) {
-    using L = SmemLayout<VG_WF_NVFP4, 16, 3, 2, 3>;
-    auto kern = gemm_tc_kernel<VG_WF_NVFP4, 16, 3, 2, 3>;
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 320, L::total);
+    using S = Stages<VG_WF_NVFP4, 16>;
+    using C = Cfg<VG_WF_NVFP4, 16, S::np, S::na>;
+    auto kern = gemm_tc_kernel<VG_WF_NVFP4, 16, S::np, S::na>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_total);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, NTHREADS, C::smem_total);
   }
   return sms * (per_sm > 0 ? per_sm : 1);
 }

@@ -14,32 +14,71 @@
 namespace {
 using namespace vg;
 
-__global__ void __launch_bounds__(256) add_rmsnorm_kernel(__nv_bfloat16* res, const __nv_bfloat16* delta, const float* w,
-                                                           __half* out16, __nv_bfloat16* out_bf, int h, float eps,
-                                                           int plus_one, int ld_res, int ld_delta) {
+// Vectorised: every thread owns up to MAXC chunks of 8 consecutive elements (16-byte loads/stores), all
+// loads are issued before the first use, and the row stays in registers between the two passes.
+constexpr int NORM_MAXC = 4;
+__global__ void __launch_bounds__(1024) add_rmsnorm_kernel(__nv_bfloat16* res, const __nv_bfloat16* delta, const float* w,
+                                                            __half* out16, __nv_bfloat16* out_bf, int h, float eps,
+                                                            int plus_one, int ld_res, int ld_delta) {
   __shared__ float red[32];
-  extern __shared__ float row[];
   const int n = blockIdx.x;
   __nv_bfloat16* r = res + (size_t)n * ld_res;
   const __nv_bfloat16* d = delta ? delta + (size_t)n * ld_delta : nullptr;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < h; i += blockDim.x) {
-    float v = __bfloat162float(r[i]);
-    if (d) {
-      v += __bfloat162float(d[i]);
-      const __nv_bfloat16 rb = __float2bfloat16_rn(v);
-      r[i] = rb;
-      v = __bfloat162float(rb);
+  const int nchunks = h >> 3;
+  uint4 rv[NORM_MAXC], dv[NORM_MAXC];
+#pragma unroll
+  for (int c = 0; c < NORM_MAXC; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    if (ch < nchunks) {
+      rv[c] = *reinterpret_cast<const uint4*>(r + ch * 8);
+      if (d) dv[c] = *reinterpret_cast<const uint4*>(d + ch * 8);
     }
-    row[i] = v;
-    ss += v * v;
+  }
+  float v[NORM_MAXC][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < NORM_MAXC; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    if (ch < nchunks) {
+      const __nv_bfloat16* rp = reinterpret_cast<const __nv_bfloat16*>(&rv[c]);
+      const __nv_bfloat16* dp = reinterpret_cast<const __nv_bfloat16*>(&dv[c]);
+      uint4 upd;
+      __nv_bfloat16* up = reinterpret_cast<__nv_bfloat16*>(&upd);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float x = __bfloat162float(rp[i]);
+        if (d) {
+          x += __bfloat162float(dp[i]);
+          up[i] = __float2bfloat16_rn(x);
+          x = __bfloat162float(up[i]);
+        }
+        v[c][i] = x;
+        ss += x * x;
+      }
+      if (d) *reinterpret_cast<uint4*>(r + ch * 8) = upd;
+    }
   }
   ss = block_sum(ss, red);
   const float inv = rsqrtf(ss / (float)h + eps);
-  for (int i = threadIdx.x; i < h; i += blockDim.x) {
-    const float v = row[i] * inv * (plus_one ? 1.0f + w[i] : w[i]);
-    if (out16) out16[(size_t)n * h + i] = f32_to_f16_sat(v);
-    if (out_bf) out_bf[(size_t)n * h + i] = __float2bfloat16_rn(v);
+#pragma unroll
+  for (int c = 0; c < NORM_MAXC; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    if (ch < nchunks) {
+      const float4 w0 = *reinterpret_cast<const float4*>(w + ch * 8);
+      const float4 w1 = *reinterpret_cast<const float4*>(w + ch * 8 + 4);
+      const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      uint4 o16, obf;
+      __half* hp = reinterpret_cast<__half*>(&o16);
+      __nv_bfloat16* bp = reinterpret_cast<__nv_bfloat16*>(&obf);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float y = v[c][i] * inv * (plus_one ? 1.0f + ww[i] : ww[i]);
+        hp[i] = f32_to_f16_sat(y);
+        bp[i] = __float2bfloat16_rn(y);
+      }
+      if (out16) *reinterpret_cast<uint4*>(out16 + (size_t)n * h + ch * 8) = o16;
+      if (out_bf) *reinterpret_cast<uint4*>(out_bf + (size_t)n * h + ch * 8) = obf;
+    }
   }
 }
 
@@ -132,7 +171,10 @@ __global__ void embed_gather_kernel(const void* table, const uint8_t* scales, co
 extern "C" int vg_add_rmsnorm(void* res, const void* delta, const float* w, void* out_f16, void* out_bf16, int N, int h,
                               float eps, int plus_one, int ld_res, int ld_delta, cudaStream_t st) {
   if (N <= 0) return 0;
-  add_rmsnorm_kernel<<<N, 256, h * sizeof(float), st>>>(static_cast<__nv_bfloat16*>(res),
+  if ((h & 7) || (ld_res & 7) || (ld_delta & 7) || h > 8 * 1024 * NORM_MAXC) return -2;
+  int threads = ((h >> 3) + 31) / 32 * 32;
+  if (threads > 1024) threads = ((((h >> 3) + NORM_MAXC - 1) / NORM_MAXC) + 31) / 32 * 32;
+  add_rmsnorm_kernel<<<N, threads, 0, st>>>(static_cast<__nv_bfloat16*>(res),
                                                        static_cast<const __nv_bfloat16*>(delta), w,
                                                        static_cast<__half*>(out_f16),
                                                        static_cast<__nv_bfloat16*>(out_bf16), h, eps, plus_one, ld_res,

@@ -70,3 +70,21 @@ def test_splitk_choice_is_width_independent():
     from velogb10_b200.ops import gemm as G
     assert 1 <= G.choose_splitk(5120, 17408, 0) <= 8
     assert G.choose_splitk(5120, 17408, 0) == G.choose_splitk(5120, 17408, 0)
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "fp8", "bf16"])
+@pytest.mark.parametrize("m,k", [(5120, 5120), (640, 1664)])
+def test_gemm_tc_every_splitk(fmt, m, k):
+    """Every cluster split-K factor gives the reference result (odd and even slab counts per CTA)."""
+    from velogb10_b200.ops import gemm as G, lib
+    q = _mk(fmt, m, k)
+    G.prepare(q)
+    x = torch.randn(16, k, device="cuda").to(torch.float16)
+    ref = _ref(q, x)
+    for s in range(1, 9):
+        q.kernel.splitk = s
+        out = G.linear(q, x, 16, out_f32=True)
+        torch.cuda.synchronize()
+        lib.check_err_word()
+        err = (out - ref).abs().max().item()
+        assert err <= 2e-3 * ref.abs().max().item() + 1e-4, (s, err)

@@ -90,17 +90,9 @@ def choose_splitk(m: int, k: int, fmt: int) -> int:
     tiles = (m + 127) // 128
     ks = (k + 127) // 128
     slots = _resident_ctas(fmt)
-    best, best_eff = 1, 0.0
-    for s in range(1, 9):
-        if s > 1 and ks // s < 4:
-            break
-        waves = -(-tiles * s // slots)
-        eff = tiles * s / (waves * slots)
-        # prefer fewer waves of work per CTA only when the fill is clearly better
-        score = eff / waves ** 0.25
-        if score > best_eff * 1.02:
-            best, best_eff = s, score
-    return best
+    # fill the resident CTA slots of one wave (two CTAs per SM for the NVFP4 decode tile), at most 6-way
+    # (wider clusters schedule poorly), keeping at least 4 slabs of K per CTA
+    return max(1, min(6, slots // max(tiles, 1), ks // 4))
 
 
 def prepare(q: QLinear, keep_canonical: bool = True, splitk: Optional[int] = None) -> TcWeight:

@@ -1,0 +1,74 @@
+"""Runs a few eager steps of a (possibly depth-reduced) preset model between cudaProfilerStart/Stop, so a
+profiler attached with ``--profile-from-start off`` sees only those steps.
+
+  python -m velogb10_b200.utils.profile_step --model 27b --layers 8 --mode decode --steps 1
+  ncu --metrics gpu__time_duration.sum --clock-control none --profile-from-start off --csv \
+      --log-file launches.csv python -m velogb10_b200.utils.profile_step --model 27b --layers 8
+
+Without a profiler it prints CUDA-event timings of the same steps. ``--layers`` keeps the per-layer
+shapes and the 3:1 layer pattern of the preset, so per-kernel times are those of the full model.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="27b")
+    ap.add_argument("--layers", type=int, default=8)
+    ap.add_argument("--mode", default="decode", choices=["decode", "verify", "prefill"])
+    ap.add_argument("--steps", type=int, default=1)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--width", type=int, default=4)
+    ap.add_argument("--ctx", type=int, default=512)
+    ap.add_argument("--prompt", type=int, default=1024)
+    ap.add_argument("--recipe", default="all")
+    args = ap.parse_args()
+
+    from ..config import preset
+    from ..engine.llm import LLM
+    from ..models.runtime import Plan
+    from ..ops import lib as vlib
+
+    cfg = preset(args.model, mtp=False)
+    if args.layers and args.layers < cfg.num_layers:
+        cfg.num_layers = args.layers
+        cfg.layer_types = cfg.layer_types[:args.layers]
+    llm = LLM.synthetic(cfg, recipe=args.recipe, max_batch=max(4, args.batch), max_seq=max(args.ctx, args.prompt) + 64)
+    gm = llm.model
+    g = torch.Generator().manual_seed(1)
+    toks = torch.randint(0, cfg.vocab_size, (max(args.ctx, args.prompt),), generator=g).tolist()
+    for s in range(args.batch):
+        gm.prefill(s, toks[:args.ctx], 0, want_hidden=False)
+
+    def step(i):
+        if args.mode == "decode":
+            gm.decode([1 + i] * args.batch, [args.ctx + i] * args.batch, list(range(args.batch)))
+        elif args.mode == "verify":
+            gm.verify(0, list(range(1, 1 + args.width)), args.ctx, ckpt_base=args.batch)
+        else:
+            gm.prefill(1 % max(args.batch, 2), toks[:args.prompt], 0, want_hidden=False)
+
+    step(0)
+    torch.cuda.synchronize()
+    n_launch = vlib.count_launches(lambda: step(1))
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.profiler.start()
+    e0.record()
+    for i in range(args.steps):
+        step(2 + i)
+    e1.record()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    vlib.check_err_word()
+    print(json.dumps({"mode": args.mode, "layers": cfg.num_layers, "steps": args.steps,
+                      "ms_per_step_eager": e0.elapsed_time(e1) / args.steps, "launches_per_step": n_launch}))
+
+
+if __name__ == "__main__":
+    main()
