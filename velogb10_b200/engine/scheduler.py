@@ -1,0 +1,518 @@
+"""Continuous-batching scheduler with slot indirection, per-slot prefix cache (live and prompt
+checkpoints), chunked prefill, and MTP speculative decoding (greedy chain, stochastic chain, n-gram fork
+tree, multi-lane forest).
+
+Behavioural spec (reference: src/batch.rs:400-531 state, :750-771 loop, :954-1153 admission,
+:1160-1285 decode step, :1390-1523 tree, :1534-1698 forest, :1743-1949 greedy chain, :1959-2147
+stochastic chain, :2153-2267 batched decode):
+
+* lanes are front-packed logical positions; each holds a physical slot into the KV / recurrent-state store;
+  finishing a lane returns the slot without copying state, and the slot keeps its token list for reuse;
+* admission picks, among free slots, the longest cached sequence (live state or prompt checkpoint) that is
+  a strict prefix of the prompt, prefills the remainder in windows with a forced boundary at the chat
+  template's checkpoint position, primes the draft head, and emits the first token immediately;
+* a decode step runs phase A (speculation: one lane, or a packed forest of greedy lanes) then phase B
+  (one batched decode over the remaining lanes);
+* greedy speculation is exactly lossless because a width-N verify is bit-identical to N decodes.
+
+The scheduler drives any *runner* exposing ``prefill / decode / verify / verify_forest / mtp_forward /
+copy_state / zero_slot / compact_kv`` (the CUDA runtime or the fp32 CPU oracle).
+"""
+from __future__ import annotations
+
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Callable, Deque, Dict, List, Optional, Sequence, Set, Tuple
+
+import torch
+
+from . import sampling as S
+from .mtp import MtpPolicy
+from .sampling import SamplingParams
+
+PREFILL_WINDOW = 8192
+MTP_PRIME_CHUNK = 2048
+VERIFY_CKPTS = 17            # 16 verify columns + 1 scratch (tree root)
+MAX_FOREST_LANES = 5
+MAX_VERIFY_COLS = 16
+
+
+@dataclass
+class Request:
+    prompt: List[int]
+    max_new_tokens: int = 256
+    params: SamplingParams = field(default_factory=SamplingParams)
+    stop_ids: Set[int] = field(default_factory=set)
+    ckpt_at: Optional[int] = None                     # prompt position of the chat-template boundary
+    on_token: Optional[Callable[[int], None]] = None
+    on_finish: Optional[Callable[[str, dict], None]] = None
+    id: int = 0
+    cancelled: bool = False
+    # filled by the scheduler
+    t_submit: float = 0.0
+    t_first: float = 0.0
+    prefix_hit: int = 0
+
+
+@dataclass
+class Lane:
+    req: Request
+    slot: int
+    pos: int                     # tokens whose state lives in the slot == next feed position
+    last_tok: int                # emitted but not yet fed
+    generated: int
+    history: List[int]
+    key: int                     # RNG state, advances once per step
+    h_prev: Optional[torch.Tensor] = None      # backbone hidden that predicted last_tok (draft head input)
+    mtp_ok: bool = False
+    done: Optional[str] = None
+
+
+class Scheduler:
+    def __init__(self, runner, max_batch: int, max_seq: int, eos_ids: Sequence[int] = (), policy: Optional[MtpPolicy] = None,
+                 prefix_cache: bool = True, ngram_draft: int = 0, tree_draft: bool = False, mtp_lanes: bool = False,
+                 prefill_window: int = PREFILL_WINDOW, zero_kv: bool = False, use_graphs: bool = True,
+                 alloc: bool = True):
+        self.r = runner
+        self.max_batch, self.max_seq = max_batch, max_seq
+        self.eos = set(int(e) for e in eos_ids)
+        self.has_mtp = getattr(runner, "w", None) is not None and runner.w.mtp is not None
+        self.policy = policy or MtpPolicy("auto" if self.has_mtp else "off", has_head=self.has_mtp)
+        self.prefix_cache = prefix_cache
+        self.ngram, self.tree, self.mtp_lanes = ngram_draft, tree_draft, mtp_lanes
+        self.window = prefill_window
+        self.zero_kv = zero_kv
+        self.use_graphs = use_graphs and hasattr(runner, "replay_decode")
+        # state-slot map: [0, B) lanes | [B, B+17) verify checkpoints | [B+17, 2B+17) prompt checkpoints
+        self.ckpt_base = max_batch
+        self.prompt_ckpt_base = max_batch + VERIFY_CKPTS
+        if alloc:
+            runner.alloc_state(max_batch, 2 * max_batch + VERIFY_CKPTS, max_seq)
+        self.free_slots: List[int] = list(range(max_batch))
+        self.slot_cache: List[List[int]] = [[] for _ in range(max_batch)]
+        self.slot_ckpt_seq: List[List[int]] = [[] for _ in range(max_batch)]
+        self.lanes: List[Lane] = []
+        self.queue: Deque[Request] = deque()
+        self.next_id = 1
+        self.stats = {"admitted": 0, "prefix_live": 0, "prefix_ckpt": 0, "prefix_miss": 0, "decode_steps": 0,
+                      "mtp_steps": 0, "forest_steps": 0, "tree_steps": 0, "tokens": 0, "prefill_tokens": 0}
+        self.log: List[str] = []
+
+    # ------------------------------------------------------------------ public
+    def submit(self, req: Request) -> int:
+        req.id = self.next_id
+        self.next_id += 1
+        req.t_submit = time.time()
+        self.queue.append(req)
+        return req.id
+
+    def idle(self) -> bool:
+        return not self.lanes and not self.queue
+
+    def run_until_idle(self, max_steps: int = 1 << 30):
+        n = 0
+        while not self.idle() and n < max_steps:
+            self.step()
+            n += 1
+
+    def step(self) -> bool:
+        """Admit what fits, then run one decode step. Returns False when there was nothing to do."""
+        while self.queue and self.free_slots and len(self.lanes) < self.max_batch:
+            self._admit(self.queue.popleft())
+        if not self.lanes:
+            return False
+        self._decode_step()
+        return True
+
+    # ------------------------------------------------------------------ admission
+    def _pick_slot(self, prompt: List[int]) -> Tuple[int, int, str]:
+        """(slot, reused_len, kind) with kind in live / ckpt / miss."""
+        best = (-1, 0, "miss")
+        if self.prefix_cache:
+            for s in self.free_slots:
+                for kind, seq in (("live", self.slot_cache[s]), ("ckpt", self.slot_ckpt_seq[s])):
+                    n = len(seq)
+                    if 0 < n < len(prompt) and n > best[1] and prompt[:n] == seq:
+                        best = (s, n, kind)
+        if best[0] < 0:
+            # prefer a slot without cached state so cached prefixes survive longer
+            empty = [s for s in self.free_slots if not self.slot_cache[s] and not self.slot_ckpt_seq[s]]
+            return (empty[0] if empty else self.free_slots[0]), 0, "miss"
+        return best
+
+    def _finish_req(self, req: Request, reason: str, prompt_tokens: int, completion: int):
+        if req.on_finish:
+            now = time.time()
+            req.on_finish(reason, {"prompt_tokens": prompt_tokens, "completion_tokens": completion,
+                                   "prefix_hit": req.prefix_hit, "t_submit": req.t_submit, "t_first": req.t_first,
+                                   "t_done": now})
+
+    def _admit(self, req: Request):
+        prompt = list(req.prompt)
+        plen = len(prompt)
+        if req.cancelled:
+            return
+        if plen == 0 or plen >= self.max_seq:
+            self._finish_req(req, "context_length_exceeded", plen, 0)
+            return
+        slot, reuse, kind = self._pick_slot(prompt)
+        self.free_slots.remove(slot)
+        max_new = max(1, min(req.max_new_tokens, self.max_seq - plen))
+        r = self.r
+        if kind == "ckpt":
+            r.copy_state(self.prompt_ckpt_base + slot, slot)
+            self.stats["prefix_ckpt"] += 1
+        elif kind == "live":
+            self.stats["prefix_live"] += 1
+        else:
+            r.zero_slot(slot, self.zero_kv)
+            self.slot_ckpt_seq[slot] = []
+            self.stats["prefix_miss"] += 1
+        req.prefix_hit = reuse
+        self.log.append(f"[req] {req.id} slot {slot} prompt {plen} prefix {kind} {reuse}")
+        # prefill the suffix in windows; force a window boundary at the checkpoint position
+        ckpt_at = req.ckpt_at if (req.ckpt_at is not None and reuse < req.ckpt_at < plen) else None
+        pos = reuse
+        logits = None
+        h_last = None
+        did_ckpt = False
+        while pos < plen:
+            end = min(plen, pos + self.window)
+            if ckpt_at is not None and pos < ckpt_at < end:
+                end = ckpt_at
+            logits, hidden = r.prefill(slot, prompt[pos:end], pos)
+            if self.has_mtp and hidden is not None:
+                self._mtp_prime(slot, prompt, pos, end, hidden, h_last)
+                h_last = hidden[-1].clone()
+            self.stats["prefill_tokens"] += end - pos
+            pos = end
+            if ckpt_at is not None and pos == ckpt_at:
+                r.copy_state(slot, self.prompt_ckpt_base + slot)
+                self.slot_ckpt_seq[slot] = prompt[:pos]
+                did_ckpt = True
+        if not did_ckpt and self.prefix_cache and kind != "ckpt":
+            r.copy_state(slot, self.prompt_ckpt_base + slot)
+            self.slot_ckpt_seq[slot] = prompt[:plen]
+        self.slot_cache[slot] = list(prompt)
+        key = req.params.seed if req.params.seed is not None else S.hash_tokens(prompt)
+        key &= S.MASK64
+        first = self._pick_token(logits.reshape(1, -1), [req.params], [[]], [key])[0]
+        key = S.splitmix64(key)
+        req.t_first = time.time()
+        lane = Lane(req, slot, plen, first, 1, [first], key, h_last, self.has_mtp and h_last is not None)
+        self.stats["admitted"] += 1
+        self.lanes.append(lane)
+        self._emit(lane, [first])
+        self._retire_finished()
+
+    def _mtp_prime(self, slot, prompt, pos, end, hidden, h_before):
+        """Feed (hidden[t], token[t+1]) pairs of this window into the draft head's KV cache."""
+        toks, hs, ps = [], [], []
+        if h_before is not None and pos > 0:
+            toks.append(prompt[pos]); hs.append(h_before); ps.append(pos - 1)
+        for t in range(pos, end - 1):
+            toks.append(prompt[t + 1]); hs.append(hidden[t - pos]); ps.append(t)
+        self._mtp_prime_small(slot, toks, hs, ps)
+
+    def _mtp_prime_small(self, slot, toks, hs, ps):
+        for o in range(0, len(toks), MAX_VERIFY_COLS):
+            self.r.mtp_forward(slot, toks[o:o + MAX_VERIFY_COLS], torch.stack(hs[o:o + MAX_VERIFY_COLS]),
+                               ps[o:o + MAX_VERIFY_COLS])
+
+    # ------------------------------------------------------------------ token selection
+    def _pick_token(self, logits: torch.Tensor, params: Sequence[SamplingParams], histories: Sequence[Sequence[int]],
+                    keys: Sequence[int]) -> List[int]:
+        """One token per row: penalties, then arg-max or a seeded nucleus draw."""
+        n = logits.shape[0]
+        if any(p.has_penalty and h for p, h in zip(params, histories)):
+            logits = logits.clone() if logits.dtype == torch.float32 else logits.float()
+            for i in range(n):
+                if params[i].has_penalty and histories[i]:
+                    logits[i] = S.apply_penalties(logits[i], histories[i], params[i])
+        if all(p.greedy for p in params):
+            return S.argmax_rows(logits if logits.dtype == torch.float32 else logits.float())
+        nuclei = S.nucleus_rows(logits, params)
+        return [nuc.draw(S.rng_uniform(keys[i], S.DOMAIN_SAMPLE, 0)) for i, nuc in enumerate(nuclei)]
+
+    # ------------------------------------------------------------------ emission / retirement
+    def _emit(self, lane: Lane, toks: Sequence[int]):
+        """Deliver tokens with the budget and stop-set discipline (applies to accepted drafts too)."""
+        req = lane.req
+        for t in toks:
+            if lane.done:
+                break
+            if t in self.eos or t in req.stop_ids:
+                lane.done = "stop"
+                break
+            if req.on_token:
+                req.on_token(t)
+            self.stats["tokens"] += 1
+            if lane.generated >= min(req.max_new_tokens, self.max_seq - len(req.prompt)):
+                lane.done = "length"
+        if lane.pos + 1 >= self.max_seq and not lane.done:
+            lane.done = "length"
+
+    def _retire_finished(self):
+        keep = []
+        for lane in self.lanes:
+            if lane.req.cancelled and not lane.done:
+                lane.done = "cancelled"
+            if lane.done:
+                self.free_slots.append(lane.slot)
+                if lane.done != "cancelled":
+                    self._finish_req(lane.req, lane.done, len(lane.req.prompt), lane.generated)
+                self.log.append(f"[req] {lane.req.id} done {lane.done} generated {lane.generated}")
+            else:
+                keep.append(lane)
+        self.lanes = keep
+
+    def _push_history(self, lane: Lane, toks: Sequence[int]):
+        lane.history.extend(toks)
+        if len(lane.history) > S.HISTORY_CAP:
+            del lane.history[:S.HISTORY_CAP // 2]
+
+    # ------------------------------------------------------------------ decode step
+    def _decode_step(self):
+        for lane in self.lanes:
+            if lane.req.cancelled:
+                lane.done = "cancelled"
+        self._retire_finished()
+        if not self.lanes:
+            return
+        handled: List[Lane] = []
+        if self.policy.active and self.has_mtp:
+            ready = [l for l in self.lanes if l.mtp_ok]
+            if len(self.lanes) == 1 and ready:
+                lane = ready[0]
+                if lane.req.params.greedy:
+                    if self.tree and self.ngram > 0:
+                        self._mtp_tree_step(lane)
+                    else:
+                        self._mtp_chain_step(lane)
+                else:
+                    self._mtp_sample_step(lane)
+                handled.append(lane)
+            elif self.mtp_lanes and len(self.lanes) >= 2:
+                greedy = [l for l in ready if l.req.params.greedy and not l.req.params.has_penalty][:MAX_FOREST_LANES]
+                if len(greedy) >= 2:
+                    self._mtp_forest_step(greedy)
+                    handled.extend(greedy)
+                for l in ready:
+                    if l not in handled and not l.req.params.greedy:
+                        self._mtp_sample_step(l)
+                        handled.append(l)
+        self.policy.tick()
+        rest = [l for l in self.lanes if l not in handled and not l.done]
+        if rest:
+            self._batched_decode(rest)
+        self._retire_finished()
+
+    def _batched_decode(self, lanes: List[Lane]):
+        toks = [l.last_tok for l in lanes]
+        pos = [l.pos for l in lanes]
+        slots = [l.slot for l in lanes]
+        plain = all(l.req.params.greedy and not l.req.params.has_penalty for l in lanes)
+        if plain and self.use_graphs and not self.has_mtp:
+            new = self.r.replay_decode(toks, pos, slots).tolist()
+            hidden = None
+        else:
+            logits, hidden = self.r.decode(toks, pos, slots)
+            new = self._pick_token(logits, [l.req.params for l in lanes], [l.history for l in lanes],
+                                   [l.key for l in lanes])
+        self.stats["decode_steps"] += 1
+        for i, lane in enumerate(lanes):
+            self.slot_cache[lane.slot].append(lane.last_tok)          # the FED token; invariant len == pos
+            lane.pos += 1
+            lane.key = S.splitmix64(lane.key)
+            lane.last_tok = new[i]
+            lane.generated += 1
+            self._push_history(lane, [new[i]])
+            # a plain decode leaves the draft head's cache without this position: the lane stops speculating
+            lane.mtp_ok = False
+            if hidden is not None and self.has_mtp:
+                lane.h_prev = hidden[i].clone()
+            self._emit(lane, [new[i]])
+
+    # ------------------------------------------------------------------ speculation: drafting
+    def _draft_chain(self, lane: Lane, n_drafts: int) -> Tuple[List[int], Optional[torch.Tensor]]:
+        """Greedy draft chain from the MTP head: feeds (h, token) pairs, each step reusing the head's own
+        hidden. Returns the draft tokens."""
+        drafts: List[int] = []
+        h = lane.h_prev
+        tok = lane.last_tok
+        p = lane.pos - 1
+        for d in range(n_drafts):
+            if self.ngram > 0:
+                ng = self._ngram_lookup(lane, drafts)
+                if ng is not None and d > 0:
+                    drafts.append(ng)
+                    # keep the head's cache in step even when its own guess is overridden
+                    logits, hh = self.r.mtp_forward(lane.slot, [tok], h.reshape(1, -1), [p])
+                    h, tok, p = hh[0].clone(), ng, p + 1
+                    continue
+            logits, hh = self.r.mtp_forward(lane.slot, [tok], h.reshape(1, -1), [p])
+            nxt = S.argmax_rows(logits if logits.dtype == torch.float32 else logits.float())[0]
+            drafts.append(nxt)
+            h, tok, p = hh[0].clone(), nxt, p + 1
+        return drafts, h
+
+    def _ngram_lookup(self, lane: Lane, pending: Sequence[int]) -> Optional[int]:
+        """Prompt-lookup continuation: the token that followed the last ``ngram`` tokens earlier in the
+        sequence (searching from the most recent occurrence)."""
+        n = self.ngram
+        seq = self.slot_cache[lane.slot] + [lane.last_tok] + list(pending)
+        if n <= 0 or len(seq) <= n:
+            return None
+        key = seq[-n:]
+        for s in range(len(seq) - n - 1, -1, -1):
+            if seq[s:s + n] == key:
+                return seq[s + n]
+        return None
+
+    def _reprime(self, lane: Lane, fed: Sequence[int], hidden: torch.Tensor, pos0: int):
+        """Rewrite the draft head's cache for the accepted columns with backbone hiddens: pairs
+        (hidden[t-1], fed[t]) at head position pos0 - 1 + t for t >= 1."""
+        n = len(fed)
+        if n > 1:
+            self.r.mtp_forward(lane.slot, list(fed[1:]), hidden[:n - 1], [pos0 + t - 1 for t in range(1, n)])
+
+    def _commit(self, lane: Lane, fed: Sequence[int], new_last: int, emitted: Sequence[int], hidden_row: torch.Tensor):
+        self.slot_cache[lane.slot].extend(fed)
+        lane.pos += len(fed)
+        lane.key = S.splitmix64(lane.key)
+        lane.last_tok = new_last
+        lane.h_prev = hidden_row.clone()
+        for t in emitted:
+            if lane.done:
+                break
+            lane.generated += 1
+            self._push_history(lane, [t])
+            self._emit(lane, [t])
+
+    # ------------------------------------------------------------------ speculation: steps
+    def _depth_for(self, lane: Lane, cap: int = MAX_VERIFY_COLS) -> int:
+        room = self.max_seq - lane.pos - 1
+        return max(1, min(self.policy.depth, cap, room))
+
+    def _mtp_chain_step(self, lane: Lane):
+        depth = self._depth_for(lane)
+        drafts, _ = self._draft_chain(lane, depth - 1)
+        cols = [lane.last_tok] + drafts
+        logits, hidden = self.r.verify(lane.slot, cols, lane.pos, self.ckpt_base)
+        if lane.req.params.has_penalty:
+            logits = logits.clone()
+            hist = list(lane.history)
+            for t in range(len(cols)):
+                logits[t] = S.apply_penalties(logits[t], hist, lane.req.params)
+                if t < len(drafts):
+                    hist.append(drafts[t])
+        preds = S.argmax_rows(logits if logits.dtype == torch.float32 else logits.float())
+        nacc = S.greedy_accept(preds, drafts)
+        bonus = preds[nacc]
+        pos0 = lane.pos
+        self.r.copy_state(self.ckpt_base + nacc, lane.slot)           # recurrent state after column nacc
+        fed = cols[:nacc + 1]
+        hid = hidden[:nacc + 1].clone()
+        self._reprime(lane, fed, hid, pos0)
+        self._commit(lane, fed, bonus, drafts[:nacc] + [bonus], hid[nacc])
+        self.policy.record_step(len(drafts), nacc, nacc + 1)
+        self.stats["mtp_steps"] += 1
+
+    def _mtp_sample_step(self, lane: Lane):
+        depth = self._depth_for(lane)
+        drafts, _ = self._draft_chain(lane, depth - 1)
+        cols = [lane.last_tok] + drafts
+        logits, hidden = self.r.verify(lane.slot, cols, lane.pos, self.ckpt_base)
+        logits = logits.clone() if logits.dtype == torch.float32 else logits.float()
+        if lane.req.params.has_penalty:
+            hist = list(lane.history)
+            for t in range(len(cols)):
+                logits[t] = S.apply_penalties(logits[t], hist, lane.req.params)
+                if t < len(drafts):
+                    hist.append(drafts[t])
+        nuclei = S.nucleus_rows(logits, [lane.req.params] * len(cols))
+        nacc, nxt = S.stochastic_accept(nuclei, drafts, lane.key)
+        pos0 = lane.pos
+        self.r.copy_state(self.ckpt_base + nacc, lane.slot)
+        fed = cols[:nacc + 1]
+        hid = hidden[:nacc + 1].clone()
+        self._reprime(lane, fed, hid, pos0)
+        self._commit(lane, fed, nxt, drafts[:nacc] + [nxt], hid[nacc])
+        self.policy.record_step(len(drafts), nacc, nacc + 1)
+        self.stats["mtp_steps"] += 1
+
+    def _mtp_tree_step(self, lane: Lane):
+        """Fork drafting: branch A is the head's greedy chain, branch B a pure n-gram continuation; the fork
+        is kept only when B exists and starts with a different token."""
+        depth = self._depth_for(lane)
+        ng = self.ngram
+        self.ngram = 0
+        a, _ = self._draft_chain(lane, depth - 1)
+        self.ngram = ng
+        b: List[int] = []
+        for _ in range(min(depth - 1, MAX_VERIFY_COLS - 1 - len(a))):
+            t = self._ngram_lookup(lane, b)
+            if t is None:
+                break
+            b.append(t)
+        if not b or not a or b[0] == a[0]:
+            b = []
+        tokens = [lane.last_tok] + a + b
+        parent = [-1] + [i for i in range(len(a))] + ([0] + [len(a) + 1 + i for i in range(len(b) - 1)] if b else [])
+        if not b:
+            logits, hidden = self.r.verify(lane.slot, tokens, lane.pos, self.ckpt_base)
+        else:
+            logits, hidden = self.r.verify(lane.slot, tokens, lane.pos, self.ckpt_base, parent=parent)
+        preds = S.argmax_rows(logits if logits.dtype == torch.float32 else logits.float())
+        path = S.tree_accept_walk(parent, tokens, preds)
+        nacc = len(path) - 1
+        last_col = path[-1]
+        bonus = preds[last_col]
+        pos0 = lane.pos
+        if b and path != list(range(len(path))):
+            self.r.compact_kv(lane.slot, pos0, path)
+        self.r.copy_state(self.ckpt_base + last_col, lane.slot)
+        fed = [tokens[c] for c in path]
+        hid = torch.stack([hidden[c] for c in path])
+        self._reprime(lane, fed, hid, pos0)
+        self._commit(lane, fed, bonus, fed[1:] + [bonus], hid[-1])
+        self.policy.record_step(len(a), nacc, nacc + 1)
+        self.stats["mtp_steps"] += 1
+        self.stats["tree_steps"] += 1
+
+    def _mtp_forest_step(self, lanes: List[Lane]):
+        """Pack several greedy lanes' draft chains into one verify of at most 16 columns."""
+        p = len(lanes)
+        d = max(1, min(self.policy.depth, MAX_VERIFY_COLS // p - 1))
+        plans = []
+        base = self.ckpt_base
+        for lane in lanes:
+            depth = max(1, min(d + 1, self.max_seq - lane.pos - 1))
+            drafts, _ = self._draft_chain(lane, depth - 1)
+            cols = [lane.last_tok] + drafts
+            plans.append((lane, cols, drafts, base))
+            base += len(cols)
+        outs = self.r.verify_forest([(lane.slot, cols, lane.pos, b) for lane, cols, _, b in plans])
+        for (lane, cols, drafts, b), (logits, hidden) in zip(plans, outs):
+            preds = S.argmax_rows(logits if logits.dtype == torch.float32 else logits.float())
+            nacc = S.greedy_accept(preds, drafts)
+            pos0 = lane.pos
+            self.r.copy_state(b + nacc, lane.slot)
+            fed = cols[:nacc + 1]
+            hid = hidden[:nacc + 1].clone()
+            self._reprime(lane, fed, hid, pos0)
+            self._commit(lane, fed, preds[nacc], drafts[:nacc] + [preds[nacc]], hid[nacc])
+            self.policy.record_step(len(drafts), nacc, nacc + 1)
+        self.stats["mtp_steps"] += 1
+        self.stats["forest_steps"] += 1
+
+    # ------------------------------------------------------------------ divergence guard
+    def state_hash(self) -> int:
+        """FNV hash of the lane table; tensor-parallel ranks compare it every step."""
+        h = 0xCBF29CE484222325
+        for lane in self.lanes:
+            for v in (lane.slot, lane.pos, lane.last_tok, lane.generated, lane.req.id):
+                h = ((h ^ (v & 0xFFFFFFFF)) * 0x100000001B3) & S.MASK64
+        h = ((h ^ self.policy.depth) * 0x100000001B3) & S.MASK64
+        return h

@@ -368,6 +368,10 @@ class OracleModel:
         x = x + (self.moe(n2, L.moe) if L.moe is not None else self.mlp(n2, L.mlp))
         return self._rd(x)
 
+    def verify_forest(self, lanes):
+        """Several lanes' chain verifies in one call: list of (slot, tokens, pos_start, ckpt_base)."""
+        return [self.verify(slot, toks, pos, ck) for slot, toks, pos, ck in lanes]
+
     def compact_kv(self, slot: int, pos_start: int, cols: Sequence[int]):
         """Move the KV rows of accepted tree columns to contiguous positions."""
         for li in self.state.k:

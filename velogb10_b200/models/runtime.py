@@ -357,6 +357,17 @@ class GpuModel:
             return self.forward(Plan.chain(slot, tokens, pos_start, ckpt_base))
         return self.forward(Plan.tree(slot, tokens, pos_start, ckpt_base, parent))
 
+    def verify_forest(self, lanes):
+        """Several lanes' chain verifies packed into one forward of at most ``max_cols`` columns:
+        list of (slot, tokens, pos_start, ckpt_base) -> list of (logits, hidden) clones per lane."""
+        plans = [Plan.chain(slot, toks, pos, ck) for slot, toks, pos, ck in lanes]
+        logits, hidden = self.forward(Plan.concat(plans))
+        outs, o = [], 0
+        for pl in plans:
+            outs.append((logits[o:o + pl.n].clone(), hidden[o:o + pl.n].clone()))
+            o += pl.n
+        return outs
+
     def prefill(self, slot: int, tokens: Sequence[int], pos_start: int = 0, want_hidden: bool = True):
         """Chunked prefill of one lane; state carried in the lane's slot. Returns (logits of the last
         token [V_local] fp32, hidden [N, h] bf16 or None)."""
