@@ -51,6 +51,30 @@ int vg_nucleus(const float* logits, int N, int V, int ld, const float* temp, con
                const unsigned* seed, int* out_tok, int* ids, float* probs, int* n_keep, cudaStream_t stream);
 int vg_nll(const float* logits, int N, int V, int ld, const int* target, float* out, cudaStream_t stream);
 
+// Peer-memory communication context (one per rank; data[q] is rank q's symmetric arena mapped here).
+typedef struct VgCommCtx {
+  int rank, world;
+  unsigned char* data[8];
+  unsigned long long flags_off, slots_off, slot_bytes, result_off, result_bytes;
+  unsigned int* epoch;       // device-resident epoch counter of this rank
+  unsigned int* done_ctr;    // CTA completion counter
+  int* status;               // error status word (0 = ok)
+  unsigned long long timeout_ns;
+} VgCommCtx;
+
+int vg_comm_alloc(void** ptr, unsigned long long bytes);
+int vg_comm_free(void* ptr);
+int vg_comm_export(void* ptr, void* handle64);
+int vg_comm_import(const void* handle64, void** ptr);
+int vg_comm_close(void* ptr);
+int vg_comm_handle_bytes(void);
+int vg_comm_allreduce(const VgCommCtx* ctx, const void* in, int in_is_f32, void* out_bf16, float* out_f32, long long n,
+                      cudaStream_t stream);
+int vg_comm_allgather_small(const VgCommCtx* ctx, const void* in, void* out, int bytes, cudaStream_t stream);
+int vg_comm_argmax_merge(const VgCommCtx* ctx, const float* val, const int* idx, int ncols, float* scratch_pairs,
+                         float* gathered, int* out, cudaStream_t stream);
+int vg_comm_wait_timeout_probe(const VgCommCtx* ctx, unsigned long long budget_ns, cudaStream_t stream);
+
 const char* vg_build_id(void);
 
 #ifdef __cplusplus

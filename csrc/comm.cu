@@ -1,0 +1,311 @@
+// Peer-memory collectives over NVLink / NVSwitch for tensor and expert parallelism (one process per GPU).
+//
+// Substrate: every rank cudaMalloc's one "symmetric" arena of the same size, exports it with a CUDA IPC
+// handle and maps every peer's arena; kernels then use plain ld/st on the peer pointers. The arena holds
+//   flags   [2 sets][8 source ranks][64 CTAs] one 32-bit flag per 128-byte line
+//   slots   [2 sets][8 source ranks][slot_bytes] receive buffers, written by the source rank
+//   result  [2 sets][result_bytes] all-gather landing zone of the two-shot all-reduce
+// plus a device-resident epoch counter, so a kernel captured in a CUDA graph advances its own epoch on
+// every replay. Epoch e uses set e & 1: a rank can only start epoch e+2 after it has seen every peer's
+// epoch e+1 flag, which the peer sets after it finished reading epoch e, so two sets are enough.
+//
+// All reductions add the ranks' fp32 partials in rank order 0..W-1 on every rank: results are bit-identical
+// across ranks and run to run. Waits on peer flags are bounded by a wall-clock budget; on expiry the kernel
+// stores an error code in the status word and returns (no trap, no hang), the device-side analogue of the
+// reference's cooperative abort word (reference: native/tp_doorbell.h:24-31, kernels/gpu_batch.cu:141-238,
+// native/net_shim.c:457-623 describe the two-box doorbell transport this replaces).
+//
+// No multimem / NVLS and no TMA multicast are used here: only plain peer loads and stores.
+#include "common.cuh"
+#include "api.h"
+
+namespace {
+using namespace vg;
+
+constexpr int MAX_RANKS = 8;
+constexpr int MAX_CTAS = 64;
+constexpr int FLAG_STRIDE = 32;      // uint32 per flag line (128 bytes)
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Wait until *p has reached epoch e (wrap-safe). False when the budget ran out.
+__device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t e, uint64_t budget_ns) {
+  for (int i = 0; i < 256; ++i)
+    if ((int32_t)(ld_acquire_sys(p) - e) >= 0) return true;
+  const uint64_t t0 = global_ns();
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if ((int32_t)(ld_acquire_sys(p) - e) >= 0) return true;
+    if (global_ns() - t0 > budget_ns) return false;
+  }
+}
+
+__device__ __forceinline__ size_t flag_index(int set, int src, int cta) {
+  return ((size_t)(set * MAX_RANKS + src) * MAX_CTAS + cta) * FLAG_STRIDE;
+}
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// One-shot all-reduce: every rank pushes its whole vector (as fp32) into its slot on every rank, raises a
+// per-CTA flag there, waits for the W flags of its own chunk and sums the W slots in rank order.
+template <typename TIn>
+__global__ void __launch_bounds__(256) allreduce_oneshot_kernel(VgCommCtx c, const TIn* __restrict__ in,
+                                                                 __nv_bfloat16* __restrict__ out_bf, float* __restrict__ out_f32,
+                                                                 int n) {
+  __shared__ int failed;
+  const uint32_t e = *c.epoch + 1;
+  const int set = e & 1;
+  const int cta = blockIdx.x, nct = gridDim.x;
+  const int per = ((n + nct - 1) / nct + 3) & ~3;
+  const int lo = min(n, cta * per), hi = min(n, lo + per);
+  if (threadIdx.x == 0) failed = 0;
+  for (int p = 0; p < c.world; ++p) {
+    const int peer = (c.rank + p) % c.world;          // start with a different peer on every rank
+    float* dst = reinterpret_cast<float*>(c.data[peer] + c.slots_off + (size_t)(set * MAX_RANKS + c.rank) * c.slot_bytes);
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) dst[i] = to_f32<TIn>(in[i]);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < c.world) {
+    uint32_t* f = reinterpret_cast<uint32_t*>(c.data[threadIdx.x] + c.flags_off) + flag_index(set, c.rank, cta);
+    st_release_sys(f, e);
+  }
+  if (threadIdx.x < c.world) {
+    const uint32_t* f = reinterpret_cast<const uint32_t*>(c.data[c.rank] + c.flags_off) + flag_index(set, threadIdx.x, cta);
+    if (!wait_flag(f, e, c.timeout_ns)) { atomicCAS(c.status, 0, VG_ERR_PEER_WAIT); failed = 1; }
+  }
+  __syncthreads();
+  if (!failed) {
+    const float* base = reinterpret_cast<const float*>(c.data[c.rank] + c.slots_off + (size_t)set * MAX_RANKS * c.slot_bytes);
+    const size_t stride = c.slot_bytes / sizeof(float);
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      float s = 0.f;
+      for (int q = 0; q < c.world; ++q) s += __ldcg(&base[(size_t)q * stride + i]);
+      if (out_bf) out_bf[i] = __float2bfloat16_rn(s);
+      if (out_f32) out_f32[i] = s;
+    }
+  }
+  // the last CTA to finish publishes the new epoch for the next launch
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(c.done_ctr, 1u) == (unsigned)nct - 1) { *c.done_ctr = 0; *c.epoch = e; }
+  }
+}
+
+// Two-shot all-reduce for long vectors: reduce-scatter (rank r owns segment r and receives every rank's
+// partial of it), rank-order sum, then all-gather by pushing the reduced bf16 segment into every rank's
+// result area. Each CTA handles the same sub-chunk of every segment and uses its own flags.
+template <typename TIn>
+__global__ void __launch_bounds__(256) allreduce_twoshot_kernel(VgCommCtx c, const TIn* __restrict__ in,
+                                                                 __nv_bfloat16* __restrict__ out, int n) {
+  __shared__ int failed;
+  const uint32_t e = *c.epoch + 1;
+  const int set = e & 1;
+  const int W = c.world, cta = blockIdx.x, nct = gridDim.x;
+  const int seg = ((n + W - 1) / W + 7) & ~7;                    // elements per segment
+  const int per = ((seg + nct - 1) / nct + 7) & ~7;              // elements per CTA within a segment
+  const int lo = min(seg, cta * per), hi = min(seg, lo + per);
+  if (threadIdx.x == 0) failed = 0;
+  // phase 1: push my partial of segment p to rank p
+  for (int k = 0; k < W; ++k) {
+    const int p = (c.rank + k) % W;
+    float* dst = reinterpret_cast<float*>(c.data[p] + c.slots_off + (size_t)(set * MAX_RANKS + c.rank) * c.slot_bytes);
+    const int g0 = p * seg;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      const int g = g0 + i;
+      dst[i] = g < n ? to_f32<TIn>(in[g]) : 0.f;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < W)
+    st_release_sys(reinterpret_cast<uint32_t*>(c.data[threadIdx.x] + c.flags_off) + flag_index(set, c.rank, cta), e);
+  if (threadIdx.x < W) {
+    const uint32_t* f = reinterpret_cast<const uint32_t*>(c.data[c.rank] + c.flags_off) + flag_index(set, threadIdx.x, cta);
+    if (!wait_flag(f, e, c.timeout_ns)) { atomicCAS(c.status, 0, VG_ERR_PEER_WAIT); failed = 1; }
+  }
+  __syncthreads();
+  // phase 2: reduce my segment in rank order and push it to everyone's result area
+  if (!failed) {
+    const float* base = reinterpret_cast<const float*>(c.data[c.rank] + c.slots_off + (size_t)set * MAX_RANKS * c.slot_bytes);
+    const size_t stride = c.slot_bytes / sizeof(float);
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      float s = 0.f;
+      for (int q = 0; q < W; ++q) s += __ldcg(&base[(size_t)q * stride + i]);
+      const __nv_bfloat16 v = __float2bfloat16_rn(s);
+      const size_t g = (size_t)c.rank * seg + i;
+      for (int k = 0; k < W; ++k) {
+        const int p = (c.rank + k) % W;
+        reinterpret_cast<__nv_bfloat16*>(c.data[p] + c.result_off + (size_t)set * c.result_bytes)[g] = v;
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  // second flag round: set index 2 + set keeps it apart from phase 1
+  if (threadIdx.x < W)
+    st_release_sys(reinterpret_cast<uint32_t*>(c.data[threadIdx.x] + c.flags_off) + flag_index(2 + set, c.rank, cta), e);
+  if (threadIdx.x < W) {
+    const uint32_t* f = reinterpret_cast<const uint32_t*>(c.data[c.rank] + c.flags_off) + flag_index(2 + set, threadIdx.x, cta);
+    if (!wait_flag(f, e, c.timeout_ns)) { atomicCAS(c.status, 0, VG_ERR_PEER_WAIT); failed = 1; }
+  }
+  __syncthreads();
+  if (!failed) {
+    const __nv_bfloat16* res = reinterpret_cast<const __nv_bfloat16*>(c.data[c.rank] + c.result_off + (size_t)set * c.result_bytes);
+    for (int q = 0; q < W; ++q)
+      for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const size_t g = (size_t)q * seg + i;
+        if (g < (size_t)n) out[g] = __ldcg(&res[g]);
+      }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(c.done_ctr, 1u) == (unsigned)nct - 1) { *c.done_ctr = 0; *c.epoch = e; }
+  }
+}
+
+// All-gather of a small payload (<= slot_bytes) from every rank: out[q * bytes ...] = rank q's payload.
+__global__ void __launch_bounds__(256) allgather_small_kernel(VgCommCtx c, const uint8_t* __restrict__ in,
+                                                               uint8_t* __restrict__ out, int bytes) {
+  __shared__ int failed;
+  const uint32_t e = *c.epoch + 1;
+  const int set = e & 1;
+  if (threadIdx.x == 0) failed = 0;
+  for (int p = 0; p < c.world; ++p) {
+    uint8_t* dst = c.data[p] + c.slots_off + (size_t)(set * MAX_RANKS + c.rank) * c.slot_bytes;
+    for (int i = threadIdx.x; i < bytes; i += blockDim.x) dst[i] = in[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < c.world)
+    st_release_sys(reinterpret_cast<uint32_t*>(c.data[threadIdx.x] + c.flags_off) + flag_index(set, c.rank, 0), e);
+  if (threadIdx.x < c.world) {
+    const uint32_t* f = reinterpret_cast<const uint32_t*>(c.data[c.rank] + c.flags_off) + flag_index(set, threadIdx.x, 0);
+    if (!wait_flag(f, e, c.timeout_ns)) { atomicCAS(c.status, 0, VG_ERR_PEER_WAIT); failed = 1; }
+  }
+  __syncthreads();
+  if (!failed) {
+    for (int q = 0; q < c.world; ++q) {
+      const uint8_t* src = c.data[c.rank] + c.slots_off + (size_t)(set * MAX_RANKS + q) * c.slot_bytes;
+      for (int i = threadIdx.x; i < bytes; i += blockDim.x) out[(size_t)q * bytes + i] = __ldcg(&src[i]);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) { __threadfence(); *c.epoch = e; }
+}
+
+// Vocabulary-parallel arg-max merge: pairs[q][col] = (value, global index) from rank q; the winner is the
+// largest value, lowest index on ties (rank order == ascending vocabulary order).
+__global__ void argmax_merge_kernel(const float* __restrict__ pairs, int world, int ncols, int* __restrict__ out) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= ncols) return;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int q = 0; q < world; ++q) {
+    const float v = pairs[((size_t)q * ncols + col) * 2];
+    const int i = __float_as_int(pairs[((size_t)q * ncols + col) * 2 + 1]);
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+  }
+  out[col] = bi;
+}
+
+__global__ void pack_pairs_kernel(const float* __restrict__ val, const int* __restrict__ idx, int n, float* __restrict__ out) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) { out[2 * i] = val[i]; out[2 * i + 1] = __int_as_float(idx[i]); }
+}
+
+// A wait that nothing satisfies: exercises the bounded-wait error path without any peer (tests only use
+// it with a short budget; the context stays usable).
+__global__ void wait_timeout_probe_kernel(VgCommCtx c, unsigned long long budget_ns) {
+  const uint32_t* f = reinterpret_cast<const uint32_t*>(c.data[c.rank] + c.flags_off) + flag_index(3, MAX_RANKS - 1, MAX_CTAS - 1);
+  if (!wait_flag(f, 0x7fffffffu, budget_ns)) atomicCAS(c.status, 0, VG_ERR_PEER_WAIT);
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------ host API
+
+extern "C" int vg_comm_alloc(void** ptr, unsigned long long bytes) {
+  cudaError_t e = cudaMalloc(ptr, bytes);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaMemset(*ptr, 0, bytes);
+}
+extern "C" int vg_comm_free(void* ptr) { return (int)cudaFree(ptr); }
+extern "C" int vg_comm_export(void* ptr, void* handle64) {
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, ptr);
+  if (e != cudaSuccess) return (int)e;
+  memcpy(handle64, &h, sizeof(h));
+  return 0;
+}
+extern "C" int vg_comm_import(const void* handle64, void** ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  return (int)cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+}
+extern "C" int vg_comm_close(void* ptr) { return (int)cudaIpcCloseMemHandle(ptr); }
+extern "C" int vg_comm_handle_bytes(void) { return (int)sizeof(cudaIpcMemHandle_t); }
+
+static int pick_ctas(long long n, int max_ctas) {
+  long long c = (n + 4095) / 4096;
+  if (c < 1) c = 1;
+  if (c > max_ctas) c = max_ctas;
+  return (int)c;
+}
+
+extern "C" int vg_comm_allreduce(const VgCommCtx* ctx, const void* in, int in_is_f32, void* out_bf16, float* out_f32,
+                                 long long n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  const VgCommCtx c = *ctx;
+  if (c.world < 1 || c.world > MAX_RANKS) return -2;
+  const bool one_shot = (unsigned long long)n * 4ull <= c.slot_bytes && n <= (1 << 20);
+  if (one_shot) {
+    const int ctas = pick_ctas(n, 32);
+    if (in_is_f32)
+      allreduce_oneshot_kernel<float><<<ctas, 256, 0, st>>>(c, static_cast<const float*>(in), static_cast<__nv_bfloat16*>(out_bf16), out_f32, (int)n);
+    else
+      allreduce_oneshot_kernel<__nv_bfloat16><<<ctas, 256, 0, st>>>(c, static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out_bf16), out_f32, (int)n);
+    return (int)cudaGetLastError();
+  }
+  const long long seg = (((n + c.world - 1) / c.world) + 7) & ~7ll;
+  if ((unsigned long long)seg * 4ull > c.slot_bytes || (unsigned long long)seg * c.world * 2ull > c.result_bytes || out_f32) return -3;
+  const int ctas = pick_ctas(seg, MAX_CTAS);
+  if (in_is_f32)
+    allreduce_twoshot_kernel<float><<<ctas, 256, 0, st>>>(c, static_cast<const float*>(in), static_cast<__nv_bfloat16*>(out_bf16), (int)n);
+  else
+    allreduce_twoshot_kernel<__nv_bfloat16><<<ctas, 256, 0, st>>>(c, static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out_bf16), (int)n);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int vg_comm_allgather_small(const VgCommCtx* ctx, const void* in, void* out, int bytes, cudaStream_t st) {
+  const VgCommCtx c = *ctx;
+  if (bytes <= 0 || (unsigned long long)bytes > c.slot_bytes) return -2;
+  allgather_small_kernel<<<1, 256, 0, st>>>(c, static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), bytes);
+  return (int)cudaGetLastError();
+}
+
+// Local arg-max values/indices (already offset to global vocabulary ids) -> global arg-max on every rank.
+extern "C" int vg_comm_argmax_merge(const VgCommCtx* ctx, const float* val, const int* idx, int ncols, float* scratch_pairs,
+                                    float* gathered, int* out, cudaStream_t st) {
+  const VgCommCtx c = *ctx;
+  pack_pairs_kernel<<<(ncols + 127) / 128, 128, 0, st>>>(val, idx, ncols, scratch_pairs);
+  int rc = vg_comm_allgather_small(ctx, scratch_pairs, gathered, ncols * 8, st);
+  if (rc) return rc;
+  argmax_merge_kernel<<<(ncols + 127) / 128, 128, 0, st>>>(gathered, c.world, ncols, out);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int vg_comm_wait_timeout_probe(const VgCommCtx* ctx, unsigned long long budget_ns, cudaStream_t st) {
+  wait_timeout_probe_kernel<<<1, 1, 0, st>>>(*ctx, budget_ns);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,88 @@
+"""Worker for test_gpu_comm: checks the peer-memory all-reduce / all-gather / arg-max merge against the
+library collectives, determinism across repeats and graph replay, and the bounded-wait error path."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    from velogb10_b200.parallel.comm import CommError, TpComm
+    comm = TpComm(rank, world, dev, max_elems=1 << 22, timeout_s=5.0)
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    for rows, h in ((1, 5120), (16, 5120), (3, 256), (700, 5120)):      # one-shot and two-shot sizes
+        x = torch.randn(rows, h, generator=g, device=dev).to(torch.bfloat16)
+        ref = x.float().clone()
+        dist.all_reduce(ref)
+        for rep in range(3):
+            y = x.clone()
+            comm.all_reduce_rows(y, rows)
+            torch.cuda.synchronize()
+            comm.check()
+            err = (y.float() - ref).abs().max().item()
+            assert err <= 0.02 * ref.abs().max().item() + 1e-3, (rows, h, rep, err)
+            if rep == 0:
+                first = y.clone()
+            assert torch.equal(y, first), "all-reduce must be deterministic"
+        # every rank holds identical bits
+        both = comm.all_gather_small(first[:1, :64].contiguous())
+        torch.cuda.synchronize()
+        assert torch.equal(both[0], both[-1])
+    # graph replay advances the device-side epoch by itself
+    x = torch.randn(4, 1024, generator=g, device=dev).to(torch.bfloat16)
+    buf = x.clone()
+    comm.all_reduce_rows(buf, 4)
+    torch.cuda.synchronize()
+    want = buf.clone()
+    buf.copy_(x)
+    gr = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        comm.all_reduce_rows(buf, 4)
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    dist.barrier()
+    buf.copy_(x)
+    with torch.cuda.graph(gr):
+        comm.all_reduce_rows(buf, 4)
+    for _ in range(3):
+        buf.copy_(x)
+        gr.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(buf, want)
+    comm.check()
+    # vocabulary-parallel arg-max
+    logits = torch.randn(5, 1000, generator=g, device=dev)
+    toks = comm.argmax_vocab_parallel(logits)
+    full = comm.gather_logits(logits)
+    assert toks == full.argmax(-1).tolist()
+    # bounded wait: a flag nothing sets times out, reports, and leaves the context usable
+    dist.barrier()
+    comm.wait_timeout_probe(0.05)
+    torch.cuda.synchronize()
+    try:
+        comm.check()
+        raise AssertionError("timeout was not reported")
+    except CommError:
+        pass
+    y = x.clone()
+    comm.all_reduce_rows(y, 4)
+    torch.cuda.synchronize()
+    comm.check()
+    assert torch.equal(y, want)
+    dist.barrier()
+    if rank == 0:
+        print("COMM_OK")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -79,16 +79,10 @@ class LLM:
     def decode_step(self, tokens, pos, slots, use_graph: bool = True) -> List[int]:
         """One greedy decode step for ``len(tokens)`` lanes; returns the new token ids on the host."""
         gm = self.model
-        if gm.comm is not None and gm.comm.world > 1:
-            logits, _ = gm.decode(tokens, pos, slots) if not use_graph else gm.replay_decode_logits(tokens, pos, slots)
-            return self._argmax_global(logits)
         if use_graph:
             return gm.replay_decode(tokens, pos, slots).tolist()
         logits, _ = gm.decode(tokens, pos, slots)
         return logits.argmax(-1).tolist()
 
     def _argmax_global(self, logits: torch.Tensor) -> List[int]:
-        gm = self.model
-        if gm.comm is not None and gm.comm.world > 1:
-            return gm.comm.argmax_vocab_parallel(logits)
-        return logits.argmax(-1).tolist()
+        return logits.argmax(-1).tolist()      # logits returned by the runtime are already full-vocabulary

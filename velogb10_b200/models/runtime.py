@@ -347,7 +347,7 @@ class GpuModel:
         seq_mode = any(l > 1 for _, l in plan.chains)
         self._backbone(ws, n, len(plan.chains), seq_mode, plan.direct_attn, any(plan.path),
                        None if want_logits else (0, 0))
-        return (ws.logits[:n] if want_logits else None), ws.x[:n]
+        return (self._full_logits(ws.logits[:n]) if want_logits else None), ws.x[:n]
 
     def decode(self, tokens, pos, slots):
         return self.forward(Plan.decode(tokens, pos, slots))
@@ -390,7 +390,7 @@ class GpuModel:
             if want_hidden:
                 hs.append(ws.x[:n].clone())
             if last:
-                logits = ws.logits[0]
+                logits = self._full_logits(ws.logits[:1])[0]
         return logits, (torch.cat(hs, 0) if want_hidden else None)
 
     # ---------------------------------------------------------------- MTP head
@@ -418,7 +418,27 @@ class GpuModel:
             self.comm = comm
         K.add_rmsnorm(ws.x, ws.delta, m.norm, c.rms_eps, n, out16=ws.xn16)
         G.linear(self.w.lm_head, ws.xn16, n, out=ws.logits, out_f32=True)
-        return ws.logits[:n], ws.x[:n]
+        return self._full_logits(ws.logits[:n]), ws.x[:n]
+
+    # ---------------------------------------------------------------- vocabulary-parallel head
+    @property
+    def tp(self) -> int:
+        return self.comm.world if self.comm is not None else 1
+
+    def _full_logits(self, local: torch.Tensor) -> torch.Tensor:
+        """Under tensor parallelism the LM head is vocabulary-sharded: gather the shards (sampling paths)."""
+        if self.tp == 1:
+            return local
+        return self.comm.gather_logits(local)
+
+    def _greedy_tail(self, ws: Workspace, b: int):
+        """Arg-max over the (possibly sharded) vocabulary into ws.out_tok; enqueue-only."""
+        if self.tp == 1:
+            K.argmax(ws.logits, b, ws.out_tok, ws.out_val)
+        else:
+            vl = ws.logits.shape[1]
+            K.argmax(ws.logits, b, self.comm._idx, ws.out_val, idx_offset=self.comm.rank * vl)
+            self.comm.argmax_merge(ws.out_val, self.comm._idx, b, ws.out_tok)
 
     # ---------------------------------------------------------------- CUDA graphs
     def capture_decode(self, b: int):
@@ -437,13 +457,13 @@ class GpuModel:
         with torch.cuda.stream(s):
             for _ in range(2):
                 self._backbone(ws, b, b, False, False, False)
-                K.argmax(ws.logits, b, ws.out_tok, ws.out_val)
+                self._greedy_tail(ws, b)
         torch.cuda.current_stream(self.dev).wait_stream(s)
         torch.cuda.synchronize(self.dev)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             self._backbone(ws, b, b, False, False, False)
-            K.argmax(ws.logits, b, ws.out_tok, ws.out_val)
+            self._greedy_tail(ws, b)
         for t, keep in saved:
             if t is self.kc or t is self.vc:
                 t[:, :b, :, :1].copy_(keep)

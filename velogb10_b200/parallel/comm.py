@@ -1,0 +1,162 @@
+"""Tensor-parallel communicator over NVLink peer memory.
+
+``TpComm`` allocates this rank's symmetric arena, exchanges CUDA IPC handles through ``torch.distributed``
+(the process group is only used for this bootstrap, for barriers and as the measured baseline), maps every
+peer's arena and drives the peer-memory kernels of ``csrc/comm.cu``: one-shot / two-shot all-reduce with
+rank-order fp32 sums, small all-gather, and the vocabulary-parallel arg-max merge. ``use_nccl=True``
+switches every collective to the library implementation (the comparison baseline, never the default).
+It replaces the reference's two-node RDMA link (reference: src/net.rs:151-267, src/tp.rs:116-188).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import lib as _lib
+from ..ops.lib import c_int, c_ll, ptr, stream
+
+FLAGS_BYTES = 4 * 8 * 64 * 128
+CTRL_BYTES = 256
+
+
+class VgCommCtx(ctypes.Structure):
+    _fields_ = [("rank", ctypes.c_int), ("world", ctypes.c_int), ("data", ctypes.c_void_p * 8),
+                ("flags_off", ctypes.c_ulonglong), ("slots_off", ctypes.c_ulonglong), ("slot_bytes", ctypes.c_ulonglong),
+                ("result_off", ctypes.c_ulonglong), ("result_bytes", ctypes.c_ulonglong),
+                ("epoch", ctypes.c_void_p), ("done_ctr", ctypes.c_void_p), ("status", ctypes.c_void_p),
+                ("timeout_ns", ctypes.c_ulonglong)]
+
+
+class CommError(RuntimeError):
+    pass
+
+
+class TpComm:
+    def __init__(self, rank: int, world: int, device: torch.device, max_elems: int = 4096 * 8192, use_nccl: bool = False,
+                 timeout_s: float = 5.0, group=None):
+        self.rank, self.world, self.dev = rank, world, torch.device(device)
+        self.use_nccl = use_nccl
+        self.group = group
+        self.L = _lib.lib()
+        seg = ((max_elems + world - 1) // world + 7) & ~7
+        # a slot must hold a whole one-shot vector (<= 1 Mi elements) or one two-shot segment, in fp32
+        self.slot_bytes = max(seg * 4, 4 << 20)
+        self.result_bytes = ((seg * world * 2 + 255) // 256) * 256
+        self.flags_off = CTRL_BYTES
+        self.slots_off = self.flags_off + FLAGS_BYTES
+        self.result_off = self.slots_off + 2 * 8 * self.slot_bytes
+        self.total = self.result_off + 2 * self.result_bytes
+        with torch.cuda.device(self.dev):
+            base = ctypes.c_void_p()
+            _lib.check(self.L.vg_comm_alloc(ctypes.byref(base), ctypes.c_ulonglong(self.total)), "vg_comm_alloc")
+            self.base = base.value
+            hb = self.L.vg_comm_handle_bytes()
+            handle = (ctypes.c_ubyte * hb)()
+            _lib.check(self.L.vg_comm_export(base, handle), "vg_comm_export")
+            mine = bytes(handle)
+            handles: List[Optional[bytes]] = [None] * world
+            dist.all_gather_object(handles, mine, group=group)
+            self.peers: List[int] = []
+            for q in range(world):
+                if q == rank:
+                    self.peers.append(self.base)
+                    continue
+                p = ctypes.c_void_p()
+                buf = (ctypes.c_ubyte * hb).from_buffer_copy(handles[q])
+                _lib.check(self.L.vg_comm_import(buf, ctypes.byref(p)), "vg_comm_import")
+                self.peers.append(p.value)
+        ctx = VgCommCtx()
+        ctx.rank, ctx.world = rank, world
+        for q in range(8):
+            ctx.data[q] = self.peers[q] if q < world else None
+        ctx.flags_off, ctx.slots_off, ctx.slot_bytes = self.flags_off, self.slots_off, self.slot_bytes
+        ctx.result_off, ctx.result_bytes = self.result_off, self.result_bytes
+        ctx.epoch, ctx.done_ctr, ctx.status = self.base, self.base + 4, self.base + 8
+        ctx.timeout_ns = int(timeout_s * 1e9)
+        self.ctx = ctx
+        self._status_view = self._view(8, 1, torch.int32)
+        self._pairs = torch.zeros(2 * 64, dtype=torch.float32, device=self.dev)
+        self._gathered = torch.zeros(2 * 64 * world, dtype=torch.float32, device=self.dev)
+        self._out_tok = torch.zeros(64, dtype=torch.int32, device=self.dev)
+        self._val = torch.zeros(64, dtype=torch.float32, device=self.dev)
+        self._idx = torch.zeros(64, dtype=torch.int32, device=self.dev)
+        dist.barrier(group=group)
+
+    def _view(self, offset: int, n: int, dtype) -> torch.Tensor:
+        """Torch view of a piece of this rank's arena."""
+        class _Arr:
+            pass
+        a = _Arr()
+        item = torch.tensor([], dtype=dtype).element_size()
+        typestr = {torch.int32: "<i4", torch.float32: "<f4", torch.uint8: "|u1"}[dtype]
+        a.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (self.base + offset, False), "version": 2}
+        return torch.as_tensor(a, device=self.dev)
+
+    # ------------------------------------------------------------ collectives
+    def all_reduce_rows(self, t: torch.Tensor, n_rows: int):
+        """In-place sum over ranks of the first ``n_rows`` rows of a contiguous bf16/f32 ``[rows, h]`` tensor."""
+        n = n_rows * t.shape[1]
+        if self.use_nccl:
+            dist.all_reduce(t[:n_rows], group=self.group)
+            return
+        assert t.is_contiguous() and t.dtype in (torch.bfloat16, torch.float32)
+        is32 = t.dtype == torch.float32
+        rc = self.L.vg_comm_allreduce(ctypes.byref(self.ctx), ptr(t), c_int(1 if is32 else 0),
+                                      ptr(None if is32 else t), ptr(t if is32 else None), c_ll(n), stream())
+        _lib.check(rc, "vg_comm_allreduce")
+
+    def all_gather_small(self, t: torch.Tensor) -> torch.Tensor:
+        """[world, ...] stack of a small contiguous tensor from every rank."""
+        out = torch.empty((self.world,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+        if self.use_nccl:
+            dist.all_gather_into_tensor(out, t.contiguous(), group=self.group)
+            return out
+        rc = self.L.vg_comm_allgather_small(ctypes.byref(self.ctx), ptr(t), ptr(out), c_int(t.numel() * t.element_size()),
+                                            stream())
+        _lib.check(rc, "vg_comm_allgather_small")
+        return out
+
+    def argmax_merge(self, val: torch.Tensor, idx: torch.Tensor, n: int, out: torch.Tensor):
+        """Global arg-max from per-rank (value, global index) pairs; enqueue-only (graph capturable)."""
+        rc = self.L.vg_comm_argmax_merge(ctypes.byref(self.ctx), ptr(val), ptr(idx), c_int(n), ptr(self._pairs),
+                                         ptr(self._gathered), ptr(out), stream())
+        _lib.check(rc, "vg_comm_argmax_merge")
+
+    def argmax_vocab_parallel(self, logits: torch.Tensor) -> List[int]:
+        """Greedy token per row from vocabulary-sharded fp32 logits ``[n, V_local]``."""
+        from ..ops import kernels as K
+        n, vl = logits.shape
+        lg = logits if logits.dtype == torch.float32 else logits.float()
+        K.argmax(lg, n, self._idx, self._val, idx_offset=self.rank * vl)
+        if self.use_nccl:
+            pairs = torch.stack([self._val[:n], self._idx[:n].float()], -1)
+            allp = self.all_gather_small(pairs)
+            best = allp[..., 0].argmax(0)       # first maximum = lowest rank = lowest index
+            return [int(allp[int(best[c]), c, 1]) for c in range(n)]
+        self.argmax_merge(self._val, self._idx, n, self._out_tok)
+        return self._out_tok[:n].tolist()
+
+    def gather_logits(self, logits: torch.Tensor) -> torch.Tensor:
+        """Full ``[n, V]`` logits from vocabulary shards (library all-gather; sampling paths only)."""
+        n, vl = logits.shape
+        out = torch.empty((self.world, n, vl), dtype=logits.dtype, device=logits.device)
+        dist.all_gather_into_tensor(out, logits.contiguous(), group=self.group)
+        return out.permute(1, 0, 2).reshape(n, self.world * vl)
+
+    # ------------------------------------------------------------ health
+    def check(self):
+        v = int(self._status_view.item())
+        if v != 0:
+            self._status_view.zero_()
+            raise CommError(f"peer-memory collective reported error {v} (4 = a peer's flag did not arrive in time)")
+
+    def wait_timeout_probe(self, budget_s: float = 0.05):
+        """Runs a wait nothing will satisfy; afterwards ``check()`` must raise. Test hook for the bounded-wait path."""
+        rc = self.L.vg_comm_wait_timeout_probe(ctypes.byref(self.ctx), ctypes.c_ulonglong(int(budget_s * 1e9)), stream())
+        _lib.check(rc, "vg_comm_wait_timeout_probe")
+
+    def barrier(self):
+        dist.barrier(group=self.group)
