@@ -16,6 +16,9 @@ extern "C" {
 
 int vg_gemm_tc(const void* wt, const float* row_scale, const void* x_f16, int x_rows, int ldx, void* out, int out_f32,
                int M, int K, int N, int ldo, int wfmt, int splitk, int* err, cudaStream_t stream);
+int vg_gemm_tc_grouped(const void* wt, const float* row_scale, const void* x_f16, int x_rows, int ldx, void* out, int out_f32,
+                       int M, int K, int ldo, int wfmt, int bn, int max_items, const int* g_exp, const int* g_off,
+                       const int* g_cnt, const int* tilemap, const int* n_items, int x_div, int* err, cudaStream_t stream);
 int vg_gemm_tc_resident_ctas(int wfmt);
 void vg_gemm_tc_set_variant(int variant, int dbg);
 void vg_gemm_tc_set_trace(long long* buf);
@@ -50,6 +53,16 @@ int vg_penalty(float* logits, int N, int V, int ld, const int* toks, const int* 
 int vg_nucleus(const float* logits, int N, int V, int ld, const float* temp, const int* top_k, const float* top_p,
                const unsigned* seed, int* out_tok, int* ids, float* probs, int* n_keep, cudaStream_t stream);
 int vg_nll(const float* logits, int N, int V, int ld, const int* target, float* out, cudaStream_t stream);
+
+int vg_moe_router(const float* logits, int N, int E, int K, int sigmoid_mode, const float* bias, int norm, float scaling,
+                  int e_base, int n_local, int* ids, float* wts, int* g_exp, int* g_off, int* g_cnt, cudaStream_t stream);
+int vg_moe_sort(const int* ids, int P, int e_base, int n_local, int bn, int* cnt, int* cursor, int* g_exp, int* g_off,
+                int* g_cnt, int* tilemap, int* n_items, int* perm, int* inv, int* total, cudaStream_t stream);
+int vg_moe_gather(const void* x_f16, int ldx, const int* perm, const int* total, int max_rows, int topk, int h,
+                  void* out_f16, cudaStream_t stream);
+int vg_moe_combine(const void* y, int ldy, const int* inv, const float* wts, int N, int topk, const void* shared,
+                   const float* gate_logit, void* out, int h, cudaStream_t stream);
+int vg_moe_add_shared(void* out, const void* shared, const float* gate_logit, int N, int h, cudaStream_t stream);
 
 // Peer-memory communication context (one per rank; data[q] is rank q's symmetric arena mapped here).
 typedef struct VgCommCtx {

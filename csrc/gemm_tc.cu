@@ -58,6 +58,15 @@ struct GemmParams {
   int* err;
   int dbg;     // diagnostics: bit 0 skips the dequantisation math, bit 1 skips the MMA issue
   long long* trace;   // optional [9][64] cycle stamps of CTA (0,0,0): per-role pipeline events per slab
+  // grouped (mixture-of-experts) mode: blockIdx.y walks work items = (group, n-tile)
+  int grouped;
+  const int* g_exp;      // [groups] expert of the group, -1 = not resident here (skipped)
+  const int* g_off;      // [groups] first row of the group in X / Y
+  const int* g_cnt;      // [groups] rows in the group
+  const int* tilemap;    // [items][2] (group, n-tile) or null: item i = group i, n-tile 0
+  const int* n_items;    // device count of valid items, or null: all of gridDim.y
+  int tiles_per_expert;  // row tiles of one expert's matrix
+  int x_div;             // X row = Y row / x_div (decode: one activation row feeds top-k pairs)
 };
 
 constexpr uint32_t pow2_cols(uint32_t c) { return c <= 32 ? 32 : c <= 64 ? 64 : c <= 128 ? 128 : c <= 256 ? 256 : 512; }
@@ -161,15 +170,32 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int mt = blockIdx.x, nt = blockIdx.y;
+  int mt = blockIdx.x, nt = blockIdx.y;
   const int S = gridDim.z, z = blockIdx.z;
+  int row0 = nt * BN;              // first output row (token) of this CTA
+  int rows_valid = p.N - row0;     // rows of it that exist
+  int m_base = 0;                  // row offset of the expert inside the stacked weight
+  if (p.grouped) {
+    // uniform for the CTA (and its cluster): safe to leave before any barrier is touched
+    if (p.n_items && (int)blockIdx.y >= *p.n_items) return;
+    const int g = p.tilemap ? p.tilemap[2 * blockIdx.y] : (int)blockIdx.y;
+    const int gnt = p.tilemap ? p.tilemap[2 * blockIdx.y + 1] : 0;
+    const int e = p.g_exp[g];
+    if (e < 0 || gnt * BN >= p.g_cnt[g]) return;
+    row0 = p.g_off[g] + gnt * BN;
+    rows_valid = p.g_cnt[g] - gnt * BN;
+    mt = e * p.tiles_per_expert + (int)blockIdx.x;
+    m_base = e * p.M;
+    nt = 0;
+  }
+  const int x_row0 = p.grouped ? row0 / p.x_div : row0;
   const int ks0 = (int)(((long long)z * p.ks_total) / S);
   const int ks1 = (int)(((long long)(z + 1) * p.ks_total) / S);
   const int nks = ks1 - ks0;
   // Each row tile walks its K range from a different starting slab (wrapping around), so the CTAs of a
   // wave do not all ask L2 for the same activation lines at the same moment. The order is a function of
   // the tile index only, hence identical for every batch width.
-  const int rot = nks > 0 ? (int)(((unsigned)mt * 7u + (unsigned)z * 3u) % (unsigned)nks) : 0;
+  const int rot = nks > 0 ? (int)(((unsigned)blockIdx.x * 7u + (unsigned)z * 3u) % (unsigned)nks) : 0;
   auto slab_of = [&](int i) { int k = i + rot; return ks0 + (k >= nks ? k - nks : k); };
 
   if (threadIdx.x == 0) {
@@ -212,8 +238,8 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
         mbar_arrive_expect_tx(&b_full[b], C::b_bytes);
         uint8_t* bdst = sB + (size_t)b * C::b_bytes;
         const int ks = slab_of(i);
-        tma_tensor2d_g2s(bdst, &tmap_x, ks * BK, nt * BN, &b_full[b]);
-        tma_tensor2d_g2s(bdst + BN * 128, &tmap_x, ks * BK + 64, nt * BN, &b_full[b]);
+        tma_tensor2d_g2s(bdst, &tmap_x, ks * BK, x_row0, &b_full[b]);
+        tma_tensor2d_g2s(bdst + BN * 128, &tmap_x, ks * BK + 64, x_row0, &b_full[b]);
       }
     }
   } else if (warp == 1 || warp == 11) {
@@ -360,13 +386,14 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
     cluster_sync_all();
   }
   if (epi && have_acc && z == 0) {
-    const int m = mt * BM + m_local;
+    const int m = (int)blockIdx.x * BM + m_local;       // row inside this (expert's) matrix
     if (m < p.M) {
-      const float rsc = p.row_scale ? p.row_scale[m] : 1.0f;
+      const float rsc = p.row_scale ? p.row_scale[m_base + m] : 1.0f;
 #pragma unroll
       for (int c = 0; c < CPW; ++c) {
-        const int n = nt * BN + grp * CPW + c;
-        if (n < p.N) {
+        const int cc = grp * CPW + c;
+        const int n = row0 + cc;
+        if (cc < rows_valid) {
           const float v = acc[c] * rsc;
           if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)n * p.ldo + m] = v;
           else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)n * p.ldo + m] = __float2bfloat16_rn(v);
@@ -506,12 +533,51 @@ extern "C" int vg_gemm_tc(const void* wt, const float* row_scale, const void* x_
   p.err = err;
   p.dbg = g_dbg;
   p.trace = g_trace;
+  p.grouped = 0;
   if (splitk > p.ks_total) splitk = p.ks_total;
   if (N > 64) splitk = 1;
   switch (wfmt) {
     case VG_WF_NVFP4: return dispatch_bn<VG_WF_NVFP4>(p, x_f16, ldx, splitk, stream);
     case VG_WF_FP8: return dispatch_bn<VG_WF_FP8>(p, x_f16, ldx, splitk, stream);
     case VG_WF_F16: return dispatch_bn<VG_WF_F16>(p, x_f16, ldx, splitk, stream);
+  }
+  return -3;
+}
+
+// Grouped (mixture-of-experts) GEMM over stacked expert weights [E][M, K] (tile-major per expert).
+// Work item i (blockIdx.y) = (group, n-tile): rows [g_off[g] + nt*BN, ...) of X/Y use expert g_exp[g].
+// bn selects the tile width: 16 for decode (one pair per group), 128 for prefill (tokens sorted by expert).
+extern "C" int vg_gemm_tc_grouped(const void* wt, const float* row_scale, const void* x_f16, int x_rows, int ldx, void* out,
+                                  int out_f32, int M, int K, int ldo, int wfmt, int bn, int max_items, const int* g_exp,
+                                  const int* g_off, const int* g_cnt, const int* tilemap, const int* n_items, int x_div,
+                                  int* err, cudaStream_t stream) {
+  if (M <= 0 || K <= 0 || max_items <= 0 || (K % 16) != 0 || (M % BM) != 0 || x_div < 1) return -2;
+  if (ldx < K || (ldx % 8) != 0 || (reinterpret_cast<uintptr_t>(x_f16) & 15) != 0) return -4;
+  GemmParams p;
+  p.wt = static_cast<const uint8_t*>(wt);
+  p.row_scale = row_scale;
+  p.out = out;
+  p.M = M; p.K = K; p.ldo = ldo;
+  p.N = bn == 16 ? 16 : 128;                 // selects the tile width; the real row counts come from g_cnt
+  p.ks_total = (K + BK - 1) / BK;
+  p.out_f32 = out_f32;
+  p.err = err;
+  p.dbg = 0;
+  p.trace = nullptr;
+  p.grouped = 1;
+  p.g_exp = g_exp; p.g_off = g_off; p.g_cnt = g_cnt; p.tilemap = tilemap; p.n_items = n_items;
+  p.tiles_per_expert = M / BM;
+  p.x_div = x_div;
+  CUtensorMap tm;
+  int rc = get_tmap_x(x_f16, x_rows, K, bn == 16 ? 16 : 128, ldx, &tm);
+  if (rc) return rc;
+  // items ride on gridDim.y: launch() derives gridDim.y from N, so pass N = items * tile width
+  GemmParams q = p;
+  q.N = max_items * (bn == 16 ? 16 : 128);
+  switch (wfmt) {
+    case VG_WF_NVFP4: return bn == 16 ? launch_bn<VG_WF_NVFP4, 16>(q, tm, 1, stream) : launch_bn<VG_WF_NVFP4, 128>(q, tm, 1, stream);
+    case VG_WF_FP8: return bn == 16 ? launch_bn<VG_WF_FP8, 16>(q, tm, 1, stream) : launch_bn<VG_WF_FP8, 128>(q, tm, 1, stream);
+    case VG_WF_F16: return bn == 16 ? launch_bn<VG_WF_F16, 16>(q, tm, 1, stream) : launch_bn<VG_WF_F16, 128>(q, tm, 1, stream);
   }
   return -3;
 }

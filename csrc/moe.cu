@@ -1,0 +1,219 @@
+// Mixture-of-experts support kernels around the grouped tensor-core GEMM:
+//   vg_moe_router     top-k selection + combine weights from fp32 router logits; also emits the per-pair
+//                     group table (expert rebased to this rank's resident band, -1 when not resident)
+//   vg_moe_sort       counting sort of (token, slot) pairs by expert: counts, offsets, work-item tile map,
+//                     permutation - entirely on the device (no host read-back of the offsets, unlike the
+//                     reference at src/gpu.rs:2323-2325)
+//   vg_moe_gather     activation rows permuted into expert order for the prefill grouped GEMM
+//   vg_moe_combine    weighted sum of a token's expert outputs in slot order (+ gated shared expert)
+// Router math (reference: kernels/gpu_batch.cu:3102-3240): softmax flavour selects the top-k logits (lowest
+// index wins ties) and weights them exp(l - max) / sum over the selected k; sigmoid flavour selects by
+// sigmoid(l) + bias and weights by the unbiased sigmoid, renormalised and scaled. The combine adds slots in
+// slot order, so the result does not depend on the (atomic) order pairs were scattered in.
+#include "common.cuh"
+#include "api.h"
+
+namespace {
+using namespace vg;
+
+constexpr int MAX_E = 1024;
+constexpr int MAX_K = 16;
+
+__global__ void __launch_bounds__(256) router_kernel(const float* __restrict__ logits, int E, int K, int sigmoid_mode,
+                                                      const float* __restrict__ bias, int norm, float scaling, int e_base,
+                                                      int n_local, int* __restrict__ ids, float* __restrict__ wts,
+                                                      int* __restrict__ g_exp, int* __restrict__ g_off, int* __restrict__ g_cnt) {
+  __shared__ float score[MAX_E];
+  __shared__ float raw[MAX_E];
+  __shared__ float bv[8];
+  __shared__ int bi[8];
+  __shared__ float selv[MAX_K];
+  __shared__ int seli[MAX_K];
+  const int n = blockIdx.x;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const float l = logits[(size_t)n * E + e];
+    const float s = sigmoid_mode ? sigmoidf(l) : l;
+    raw[e] = s;
+    score[e] = sigmoid_mode && bias ? s + bias[e] : s;
+  }
+  __syncthreads();
+  for (int r = 0; r < K; ++r) {
+    float v = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int e = threadIdx.x; e < E; e += blockDim.x)
+      if (score[e] > v || (score[e] == v && e < idx)) { v = score[e]; idx = e; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+      if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = v; bi[threadIdx.x >> 5] = idx; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+        if (bv[w] > v || (bv[w] == v && bi[w] < idx)) { v = bv[w]; idx = bi[w]; }
+      seli[r] = idx;
+      selv[r] = raw[idx];
+      score[idx] = -INFINITY;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    float w[MAX_K];
+    if (sigmoid_mode) {
+      float sum = 0.f;
+      for (int r = 0; r < K; ++r) { w[r] = selv[r]; sum += w[r]; }
+      for (int r = 0; r < K; ++r) w[r] = (norm ? w[r] / sum : w[r]) * scaling;
+    } else {
+      const float mx = selv[0];
+      float sum = 0.f;
+      for (int r = 0; r < K; ++r) { w[r] = __expf(selv[r] - mx); sum += w[r]; }
+      for (int r = 0; r < K; ++r) w[r] /= sum;
+    }
+    for (int r = 0; r < K; ++r) {
+      const int p = n * K + r;
+      ids[p] = seli[r];
+      wts[p] = w[r];
+      const int loc = seli[r] - e_base;
+      if (g_exp) { g_exp[p] = (loc >= 0 && loc < n_local) ? loc : -1; g_off[p] = p; g_cnt[p] = 1; }
+    }
+  }
+}
+
+__global__ void moe_count_kernel(const int* __restrict__ ids, int P, int e_base, int n_local, int* __restrict__ cnt) {
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= P) return;
+  const int loc = ids[p] - e_base;
+  if (loc >= 0 && loc < n_local) atomicAdd(&cnt[loc], 1);
+}
+
+// One block: exclusive scan of the counts -> offsets and cursors, group table, tile map, item count.
+__global__ void __launch_bounds__(1024) moe_scan_kernel(int* __restrict__ cnt, int n_local, int bn, int* __restrict__ g_exp,
+                                                         int* __restrict__ g_off, int* __restrict__ g_cnt,
+                                                         int* __restrict__ cursor, int* __restrict__ tilemap,
+                                                         int* __restrict__ n_items) {
+  __shared__ int off[MAX_E + 1], toff[MAX_E + 1];
+  if (threadIdx.x == 0) {
+    int o = 0, t = 0;
+    for (int e = 0; e < n_local; ++e) {
+      off[e] = o; toff[e] = t;
+      o += cnt[e];
+      t += (cnt[e] + bn - 1) / bn;
+    }
+    off[n_local] = o; toff[n_local] = t;
+    *n_items = t;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < n_local; e += blockDim.x) {
+    g_exp[e] = e; g_off[e] = off[e]; g_cnt[e] = cnt[e]; cursor[e] = off[e];
+    for (int t = toff[e]; t < toff[e + 1]; ++t) { tilemap[2 * t] = e; tilemap[2 * t + 1] = t - toff[e]; }
+  }
+}
+
+__global__ void moe_scatter_kernel(const int* __restrict__ ids, int P, int e_base, int n_local, int* __restrict__ cursor,
+                                   int* __restrict__ perm, int* __restrict__ inv) {
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p >= P) return;
+  const int loc = ids[p] - e_base;
+  if (loc >= 0 && loc < n_local) {
+    const int pos = atomicAdd(&cursor[loc], 1);
+    perm[pos] = p;
+    inv[p] = pos;
+  } else {
+    inv[p] = -1;
+  }
+}
+
+__global__ void moe_gather_kernel(const __half* __restrict__ x, int ldx, const int* __restrict__ perm, const int* __restrict__ total,
+                                  int topk, int h, __half* __restrict__ out) {
+  const int pos = blockIdx.x;
+  if (pos >= *total) return;
+  const int tok = perm[pos] / topk;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)tok * ldx);
+  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)pos * h);
+  for (int i = threadIdx.x; i < h / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+__global__ void moe_total_kernel(const int* __restrict__ g_off, const int* __restrict__ g_cnt, int n_local, int* __restrict__ total) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) *total = n_local > 0 ? g_off[n_local - 1] + g_cnt[n_local - 1] : 0;
+}
+
+// out[t, :] = sum_slot w[t, slot] * y[inv[t*K + slot], :]   (slot order; non-resident pairs contribute 0)
+//           (+ gate[t] * shared[t, :] when a shared expert is given)
+__global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, int ldy, const int* __restrict__ inv,
+                                   const float* __restrict__ wts, int topk, const __nv_bfloat16* __restrict__ shared,
+                                   const float* __restrict__ gate_logit, __nv_bfloat16* __restrict__ out, int h) {
+  const int t = blockIdx.x;
+  const float g = gate_logit ? sigmoidf(gate_logit[t]) : 1.0f;
+  for (int i = threadIdx.x; i < h; i += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < topk; ++s) {
+      const int pos = inv ? inv[t * topk + s] : t * topk + s;
+      if (pos >= 0) acc += wts[t * topk + s] * __bfloat162float(y[(size_t)pos * ldy + i]);
+    }
+    if (shared) acc += g * __bfloat162float(shared[(size_t)t * h + i]);
+    out[(size_t)t * h + i] = __float2bfloat16_rn(acc);
+  }
+}
+
+__global__ void moe_add_shared_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ shared,
+                                      const float* __restrict__ gate_logit, int h, size_t total) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int t = (int)(i / h);
+  const float g = gate_logit ? sigmoidf(gate_logit[t]) : 1.0f;
+  out[i] = __float2bfloat16_rn(__bfloat162float(out[i]) + g * __bfloat162float(shared[i]));
+}
+
+}  // namespace
+
+extern "C" int vg_moe_router(const float* logits, int N, int E, int K, int sigmoid_mode, const float* bias, int norm,
+                             float scaling, int e_base, int n_local, int* ids, float* wts, int* g_exp, int* g_off,
+                             int* g_cnt, cudaStream_t st) {
+  if (N <= 0) return 0;
+  if (E > MAX_E || K > MAX_K || K > E) return -2;
+  router_kernel<<<N, 256, 0, st>>>(logits, E, K, sigmoid_mode, bias, norm, scaling, e_base, n_local, ids, wts, g_exp, g_off, g_cnt);
+  return (int)cudaGetLastError();
+}
+
+// Prefill-side sort. cnt/cursor: [n_local] scratch; perm/inv: [P]; tilemap: [max_items][2]; total: [1].
+extern "C" int vg_moe_sort(const int* ids, int P, int e_base, int n_local, int bn, int* cnt, int* cursor, int* g_exp,
+                           int* g_off, int* g_cnt, int* tilemap, int* n_items, int* perm, int* inv, int* total,
+                           cudaStream_t st) {
+  if (P <= 0) return 0;
+  if (n_local > MAX_E) return -2;
+  cudaMemsetAsync(cnt, 0, sizeof(int) * n_local, st);
+  moe_count_kernel<<<(P + 255) / 256, 256, 0, st>>>(ids, P, e_base, n_local, cnt);
+  moe_scan_kernel<<<1, 1024, 0, st>>>(cnt, n_local, bn, g_exp, g_off, g_cnt, cursor, tilemap, n_items);
+  moe_scatter_kernel<<<(P + 255) / 256, 256, 0, st>>>(ids, P, e_base, n_local, cursor, perm, inv);
+  moe_total_kernel<<<1, 32, 0, st>>>(g_off, g_cnt, n_local, total);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int vg_moe_gather(const void* x_f16, int ldx, const int* perm, const int* total, int max_rows, int topk, int h,
+                             void* out_f16, cudaStream_t st) {
+  if (max_rows <= 0) return 0;
+  if (h % 8) return -2;
+  moe_gather_kernel<<<max_rows, 128, 0, st>>>(static_cast<const __half*>(x_f16), ldx, perm, total, topk, h,
+                                               static_cast<__half*>(out_f16));
+  return (int)cudaGetLastError();
+}
+
+extern "C" int vg_moe_combine(const void* y, int ldy, const int* inv, const float* wts, int N, int topk, const void* shared,
+                              const float* gate_logit, void* out, int h, cudaStream_t st) {
+  if (N <= 0) return 0;
+  moe_combine_kernel<<<N, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(y), ldy, inv, wts, topk,
+                                        static_cast<const __nv_bfloat16*>(shared), gate_logit,
+                                        static_cast<__nv_bfloat16*>(out), h);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int vg_moe_add_shared(void* out, const void* shared, const float* gate_logit, int N, int h, cudaStream_t st) {
+  const size_t total = (size_t)N * h;
+  if (!total) return 0;
+  moe_add_shared_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(static_cast<__nv_bfloat16*>(out),
+                                                                         static_cast<const __nv_bfloat16*>(shared),
+                                                                         gate_logit, h, total);
+  return (int)cudaGetLastError();
+}

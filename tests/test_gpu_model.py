@@ -98,3 +98,29 @@ def test_graph_replay_matches_eager():
     gm.S.copy_(S0); gm.conv.copy_(C0)
     got2 = gm.replay_decode([3, 4], [20, 30], [0, 1]).clone()
     assert torch.equal(got, want) and torch.equal(got2, want)
+
+
+def test_moe_model_matches_oracle_and_is_batch_invariant():
+    """MoE FFN: per-pair decode path and sorted grouped prefill path against the oracle; verify == decode."""
+    from velogb10_b200.models.runtime import GpuModel
+    cfg, w = _build("all", moe=True)
+    orc = _oracle(cfg, w)
+    gm = GpuModel(w, keep_canonical=True)
+    gm.alloc_state(2, 2 + 17, 256)
+    orc.alloc_state(2, 2 + 17, 256)
+    g = torch.Generator().manual_seed(4)
+    prompt = torch.randint(0, cfg.vocab_size, (40,), generator=g).tolist()
+    lg, _ = gm.prefill(0, prompt)          # 40 columns -> grouped path
+    lo, _ = orc.prefill(0, prompt)
+    rel = (lg.float().cpu() - lo).norm() / lo.norm()
+    assert rel < 0.06, rel
+    toks = [int(lo.argmax()), 3, 9, 27]
+    S0, C0, K0, V0 = gm.S.clone(), gm.conv.clone(), gm.kc.clone(), gm.vc.clone()
+    lv, _ = gm.verify(0, toks, 40, ckpt_base=2)
+    lv = lv.clone()
+    lov, _ = orc.verify(0, toks, 40, ckpt_base=2)
+    assert ((lv.float().cpu() - lov).norm() / lov.norm()) < 0.06
+    gm.S.copy_(S0); gm.conv.copy_(C0); gm.kc.copy_(K0); gm.vc.copy_(V0)
+    for t in range(4):
+        ld, _ = gm.decode([toks[t]], [40 + t], [0])
+        assert torch.equal(ld[0], lv[t]), t

@@ -1,0 +1,129 @@
+"""Mixture-of-experts FFN on the GPU: router -> (per-pair decode path | sorted grouped prefill path) ->
+slot-order combine -> expert-parallel reduction -> gated shared expert.
+
+Counterpart of the reference's ``moe_batch`` (reference: src/gpu.rs:2199-2414): the decode / verify path
+(<= 16 columns) runs one grouped-GEMM work item per (token, slot) pair, so every column is computed the same
+way whatever the batch width; longer inputs are sorted by expert on the device and run through the grouped
+tensor-core GEMM with 128-token tiles. Under expert parallelism each rank holds a contiguous band of
+experts, computes only its pairs and the partial outputs are summed with the peer-memory all-reduce before
+the replicated shared expert is added.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..ops import gemm as G
+from ..ops import kernels as K
+from ..ops import lib as _lib
+from ..ops.lib import c_float, c_int, ptr, stream
+from .weights import MoeW
+
+DECODE_MAX = 16
+
+
+class MoeBuffers:
+    def __init__(self, cfg, M: MoeW, cap: int, dev):
+        E, topk, I, h = cfg.num_experts, cfg.num_experts_per_tok, cfg.moe_intermediate_size, cfg.hidden_size
+        P = cap * topk
+        i32 = lambda *s: torch.zeros(s, dtype=torch.int32, device=dev)
+        self.cap, self.P = cap, P
+        self.logits = torch.zeros((cap, E), dtype=torch.float32, device=dev)
+        self.ids, self.wts = i32(P), torch.zeros(P, dtype=torch.float32, device=dev)
+        ng = max(P, M.n_local)
+        self.g_exp, self.g_off, self.g_cnt = i32(ng), i32(ng), i32(ng)
+        rows = max(P, 16) + 128
+        self.gu = torch.zeros((rows, 2 * I), dtype=torch.bfloat16, device=dev)
+        self.a16 = torch.zeros((rows, I), dtype=torch.float16, device=dev)
+        self.y = torch.zeros((rows, h), dtype=torch.bfloat16, device=dev)
+        self.gate_logit = torch.zeros((max(cap, 16), 1), dtype=torch.float32, device=dev)
+        self.shared = torch.zeros((max(cap, 16), h), dtype=torch.bfloat16, device=dev)
+        if cap > DECODE_MAX:
+            self.max_items = (P + 127) // 128 + M.n_local
+            self.cnt, self.cursor = i32(M.n_local), i32(M.n_local)
+            self.tilemap, self.n_items, self.total = i32(self.max_items, 2), i32(1), i32(1)
+            self.perm, self.inv = i32(P), i32(P)
+            self.xperm = torch.zeros((rows, h), dtype=torch.float16, device=dev)
+
+
+def _buffers(model, ws, M: MoeW) -> MoeBuffers:
+    cache: Dict = model.__dict__.setdefault("_moe_bufs", {})
+    key = (id(ws), M.n_local)
+    b = cache.get(key)
+    if b is None:
+        b = MoeBuffers(model.cfg, M, ws.cap, model.dev)
+        cache[key] = b
+    return b
+
+
+def _prep_experts(q):
+    """Tile-major layout of a stacked expert tensor (each expert's rows are a multiple of 128)."""
+    tw = G.prepare(q, keep_canonical=False, splitk=1)
+    return tw
+
+
+def _grouped(tw, m_per_expert, x16, out, bn, max_items, g_exp, g_off, g_cnt, tilemap, n_items, x_div, dev):
+    rc = _lib.lib().vg_gemm_tc_grouped(ptr(tw.wt), ptr(tw.row_scale), ptr(x16), c_int(x16.shape[0]), c_int(x16.stride(0)),
+                                       ptr(out), c_int(0), c_int(m_per_expert), c_int(tw.k), c_int(out.stride(0)),
+                                       c_int(tw.fmt), c_int(bn), c_int(max_items), ptr(g_exp), ptr(g_off), ptr(g_cnt),
+                                       ptr(tilemap), ptr(n_items), c_int(x_div), ptr(_lib.err_word(dev)), stream())
+    _lib.check(rc, "vg_gemm_tc_grouped")
+
+
+def moe_forward(model, ws, M: MoeW, n: int):
+    """Reads ws.xn16[:n] (normed hidden, f16); writes the FFN output into ws.delta[:n] (bf16)."""
+    cfg = model.cfg
+    L = _lib.lib()
+    E, topk, I, h = cfg.num_experts, cfg.num_experts_per_tok, cfg.moe_intermediate_size, cfg.hidden_size
+    b = _buffers(model, ws, M)
+    gu_w, dn_w = _prep_experts(M.gate_up), _prep_experts(M.down)
+    G.linear_simt(M.router, ws.xn16, n, out=b.logits, out_f32=True)
+    P = n * topk
+    decode = ws.cap <= DECODE_MAX
+    rc = L.vg_moe_router(ptr(b.logits), c_int(n), c_int(E), c_int(topk), c_int(1 if cfg.router_sigmoid else 0),
+                         ptr(M.expert_bias if cfg.router_expert_bias else None), c_int(1 if cfg.route_norm else 0),
+                         c_float(cfg.router_scaling), c_int(M.e_base), c_int(M.n_local), ptr(b.ids), ptr(b.wts),
+                         ptr(b.g_exp if decode else None), ptr(b.g_off if decode else None),
+                         ptr(b.g_cnt if decode else None), stream())
+    _lib.check(rc, "vg_moe_router")
+    if decode:
+        _grouped(gu_w, 2 * I, ws.xn16, b.gu, 16, P, b.g_exp, b.g_off, b.g_cnt, None, None, topk, model.dev)
+        K.swiglu(b.gu, b.a16, P, I)
+        _grouped(dn_w, h, b.a16, b.y, 16, P, b.g_exp, b.g_off, b.g_cnt, None, None, 1, model.dev)
+        inv = None
+        # non-resident pairs were skipped by the GEMM: make the combine skip them too
+        if M.n_local < E:
+            inv = b.g_exp_inv = getattr(b, "g_exp_inv", None)
+            if inv is None:
+                inv = b.g_exp_inv = torch.zeros(b.P, dtype=torch.int32, device=model.dev)
+            torch.where(b.g_exp[:P] >= 0, b.g_off[:P], torch.full_like(b.g_off[:P], -1), out=inv[:P])
+    else:
+        rc = L.vg_moe_sort(ptr(b.ids), c_int(P), c_int(M.e_base), c_int(M.n_local), c_int(128), ptr(b.cnt), ptr(b.cursor),
+                           ptr(b.g_exp), ptr(b.g_off), ptr(b.g_cnt), ptr(b.tilemap), ptr(b.n_items), ptr(b.perm),
+                           ptr(b.inv), ptr(b.total), stream())
+        _lib.check(rc, "vg_moe_sort", 5)
+        rc = L.vg_moe_gather(ptr(ws.xn16), c_int(ws.xn16.stride(0)), ptr(b.perm), ptr(b.total), c_int(P), c_int(topk),
+                             c_int(h), ptr(b.xperm), stream())
+        _lib.check(rc, "vg_moe_gather")
+        items = (P + 127) // 128 + M.n_local
+        _grouped(gu_w, 2 * I, b.xperm, b.gu, 128, items, b.g_exp, b.g_off, b.g_cnt, b.tilemap, b.n_items, 1, model.dev)
+        K.swiglu(b.gu, b.a16, P, I)
+        _grouped(dn_w, h, b.a16, b.y, 128, items, b.g_exp, b.g_off, b.g_cnt, b.tilemap, b.n_items, 1, model.dev)
+        inv = b.inv
+    shared = gate = None
+    if M.shared is not None:
+        model._mlp(ws, M.shared, n, b.shared, reduce=False)
+        shared = b.shared
+        if M.shared_gate is not None:
+            G.linear_simt(M.shared_gate, ws.xn16, n, out=b.gate_logit, out_f32=True)
+            gate = b.gate_logit
+    ep = model.comm is not None and model.comm.world > 1 and M.n_local < E
+    rc = L.vg_moe_combine(ptr(b.y), c_int(b.y.stride(0)), ptr(inv), ptr(b.wts), c_int(n), c_int(topk),
+                          ptr(None if ep else shared), ptr(None if ep else gate), ptr(ws.delta), c_int(h), stream())
+    _lib.check(rc, "vg_moe_combine")
+    if ep:
+        model.comm.all_reduce_rows(ws.delta, n)
+        if shared is not None:
+            rc = L.vg_moe_add_shared(ptr(ws.delta), ptr(shared), ptr(gate), c_int(n), c_int(h), stream())
+            _lib.check(rc, "vg_moe_add_shared")
