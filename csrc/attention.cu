@@ -12,8 +12,12 @@
 // gate applied directly (it is outside the batch-invariance contract).
 //
 // The partial buffer (m, l, acc[hd]) per (column, head, split) is scratch memory owned by the caller.
+#include <cstdio>
+#include <mutex>
+
 #include "common.cuh"
 #include "api.h"
+#include "attention_static.h"
 
 namespace {
 using namespace vg;
@@ -219,4 +223,51 @@ extern "C" int vg_attn_decode(const void* q, const void* kc, const void* vc, con
 
 extern "C" long long vg_attn_scratch_floats(int N, int nh, int hd, int ns_grid) {
   return (long long)N * nh * ns_grid * (hd + 2);
+}
+
+// ------------------------------------------------------------------ allocation-free variant
+namespace {
+// Split-K partials for vg_attn_decode_static: lives in the library image, one copy per GPU.
+static __device__ __align__(256) float g_attn_static_scratch[VG_ATTN_STATIC_MAX_FLOATS];
+
+constexpr int kMaxDevices = 64;
+float* g_static_ptr[kMaxDevices] = {};
+std::mutex g_static_mu;
+
+// Device address of the static array on the current device (the host-side symbol is only a stand-in and
+// must never be handed to a kernel). Looked up once per device.
+int static_scratch_ptr(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return -2;
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_attn_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" int vg_attn_decode_static(const void* q, const void* kc, const void* vc, const int* lens, const int* slots,
+                                     const int* base, const int* path, int path_ld, int N, int nh, int nkv, int hd,
+                                     int max_seq, int ns_grid, int direct, const void* gate, int ld_gate, void* out,
+                                     cudaStream_t stream) {
+  const long long need = direct ? 0 : vg_attn_scratch_floats(N, nh, hd, ns_grid);
+  if (need > VG_ATTN_STATIC_MAX_FLOATS) {
+    fprintf(stderr,
+            "vg_attn_decode_static: %lld floats of split-K scratch needed (N=%d heads=%d head_dim=%d splits=%d) but the "
+            "built-in buffer holds %lld; use vg_attn_decode with a caller-provided buffer\n",
+            need, N, nh, hd, ns_grid, (long long)VG_ATTN_STATIC_MAX_FLOATS);
+    return VG_ERR_STATIC_SCRATCH;
+  }
+  float* part = nullptr;
+  const int rc = static_scratch_ptr(&part);
+  if (rc) return rc;
+  return vg_attn_decode(q, kc, vc, lens, slots, base, path, path_ld, part, N, nh, nkv, hd, max_seq, ns_grid, direct, gate,
+                        ld_gate, out, stream);
 }

@@ -87,6 +87,7 @@ struct Cfg {
   static constexpr uint32_t acc_cols = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators (one per MMA issuer)
   static constexpr uint32_t tmem_cols = pow2_cols(acc_cols + (quant ? NA * A_COLS : 0));
   static_assert(NP * pack >= BN * BM * 4 || BN > 64, "split-K staging must fit in the weight stages");
+  static_assert(NP % 2 == 0 && NA % 2 == 0, "ring sizes must be even: one MMA issuer per stage");
 };
 
 __device__ __forceinline__ uint32_t cvt_e4m3x2_f16x2(uint16_t v) {
@@ -490,11 +491,15 @@ int launch(const GemmParams& p, const CUtensorMap& tm, int splitk, cudaStream_t 
   return (int)cudaLaunchKernelEx(&cfg, kern, p, tm);
 }
 
-// Stage counts: NVFP4 decode keeps 8 x 9 KB weight stages in flight per CTA and fits two CTAs per SM.
+// Stage counts. Both ring sizes are even: slab i always lands in a stage of the same parity as i, so each
+// stage and each of its barriers is consumed by one MMA issuer only, in order. (With an odd ring an
+// issuer would skip every other phase of a barrier and a one-bit parity wait could pass a phase early
+// when bulk copies complete out of order.) NVFP4 decode keeps 8 x 9 KB weight stages in flight per CTA
+// and fits two CTAs per SM.
 template <int WFMT, int BN> struct Stages;
-template <int BN> struct Stages<VG_WF_NVFP4, BN> { static constexpr int np = BN <= 64 ? 8 : 6, na = 3; };
-template <int BN> struct Stages<VG_WF_FP8, BN> { static constexpr int np = BN <= 32 ? 5 : 4, na = 3; };
-template <int BN> struct Stages<VG_WF_F16, BN> { static constexpr int np = 3, na = 3; };
+template <int BN> struct Stages<VG_WF_NVFP4, BN> { static constexpr int np = BN <= 64 ? 8 : 6, na = 2; };
+template <int BN> struct Stages<VG_WF_FP8, BN> { static constexpr int np = 4, na = 2; };
+template <int BN> struct Stages<VG_WF_F16, BN> { static constexpr int np = 4, na = 2; };
 
 template <int WFMT, int BN>
 int launch_bn(const GemmParams& p, const CUtensorMap& tm, int splitk, cudaStream_t st) {
@@ -593,12 +598,27 @@ extern "C" int vg_gemm_tc_resident_ctas(int wfmt) {
   int dev = 0, sms = 0, per_sm = 1;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  // residency of the decode tile from its resources: shared memory (1 KB reserved per CTA, 228 KB per SM),
+  // TMEM columns (512 per SM) and threads
+  auto fit = [](int smem, unsigned cols) {
+    int by_smem = (228 * 1024) / (smem + 1024);
+    int by_tmem = (int)(512 / cols);
+    int by_thr = 2048 / NTHREADS;
+    int r = by_smem < by_tmem ? by_smem : by_tmem;
+    return r < by_thr ? r : by_thr;
+  };
   if (wfmt == VG_WF_NVFP4) {
     using S = Stages<VG_WF_NVFP4, 16>;
     using C = Cfg<VG_WF_NVFP4, 16, S::np, S::na>;
-    auto kern = gemm_tc_kernel<VG_WF_NVFP4, 16, S::np, S::na>;
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smem_total);
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, NTHREADS, C::smem_total);
+    per_sm = fit(C::smem_total, C::tmem_cols);
+  } else if (wfmt == VG_WF_FP8) {
+    using S = Stages<VG_WF_FP8, 16>;
+    using C = Cfg<VG_WF_FP8, 16, S::np, S::na>;
+    per_sm = fit(C::smem_total, C::tmem_cols);
+  } else {
+    using S = Stages<VG_WF_F16, 16>;
+    using C = Cfg<VG_WF_F16, 16, S::np, S::na>;
+    per_sm = fit(C::smem_total, C::tmem_cols);
   }
   return sms * (per_sm > 0 ? per_sm : 1);
 }

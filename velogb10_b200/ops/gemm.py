@@ -80,7 +80,7 @@ _resident = {}
 
 def _resident_ctas(fmt: int) -> int:
     if fmt not in _resident:
-        _resident[fmt] = max(1, int(_lib.lib().vg_gemm_tc_resident_ctas(c_int(WF_NVFP4))))
+        _resident[fmt] = max(1, int(_lib.lib().vg_gemm_tc_resident_ctas(c_int(fmt))))
     return _resident[fmt]
 
 
