@@ -190,17 +190,20 @@ def run_server(args: Dict[str, str]):
             print(f"[mtp] calibration skipped: {e}", file=sys.stderr)
     name = derive_model_name(args)
     presence = float(args.get("--default-presence-penalty", "2.0" if "2b" in name.lower() else "1.5"))
-    engine = EngineLoop(sched)
+    rank, world, _ = dist_env()
+    lockstep = None
+    if world > 1:
+        from .parallel.lockstep import Lockstep, run_mirror
+        if rank != 0:
+            # non-zero ranks replay rank 0's scheduling decisions and never open a port
+            run_mirror(sched)
+            return
+        lockstep = Lockstep(sched)
+    engine = EngineLoop(sched, lockstep)
     engine.start()
     state = AppState(engine, tok, name, max_seq, int(args.get("--max-tokens", "8192")),
                      float(args.get("--default-repetition-penalty", "1.0")), presence,
                      float(args.get("--default-frequency-penalty", "0.0")), args.get("--reasoning-effort"))
-    rank, world, _ = dist_env()
-    if world > 1 and rank != 0:
-        # non-zero ranks mirror rank 0's scheduling decisions (see parallel.lockstep)
-        from .parallel.lockstep import run_mirror
-        run_mirror(sched)
-        return
     app = create_app(state)
 
     @app.on_event("shutdown")

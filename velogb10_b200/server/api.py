@@ -40,8 +40,10 @@ class EngineLoop:
     If the scheduler raises, the loop records the error and fails every pending request instead of
     leaving clients hanging (the reference exits the process; embedding hosts can check ``error``)."""
 
-    def __init__(self, scheduler: Scheduler):
+    def __init__(self, scheduler: Scheduler, lockstep=None):
         self.s = scheduler
+        self.lockstep = lockstep          # parallel.lockstep.Lockstep on the head rank of a multi-process TP group
+        self._sent_cancels = set()
         self.inbox: "queue.Queue[Optional[Request]]" = queue.Queue()
         self.thread = threading.Thread(target=self._run, daemon=True, name="engine-loop")
         self.error: Optional[BaseException] = None
@@ -71,8 +73,30 @@ class EngineLoop:
         except queue.Empty:
             pass
 
+    def _run_lockstep(self):
+        """Head loop of a tensor-parallel group: ship each step's admissions and cancellations to the
+        mirror ranks before acting on them."""
+        while self.running:
+            admits = []
+            try:
+                item = self.inbox.get(block=self.s.idle(), timeout=0.5)
+                while True:
+                    if item is not None:
+                        admits.append(item)
+                    item = self.inbox.get_nowait()
+            except queue.Empty:
+                pass
+            cancels = [l.req.id for l in self.s.lanes if l.req.cancelled and l.req.id not in self._sent_cancels]
+            self._sent_cancels.update(cancels)
+            if admits or not self.s.idle():
+                self.lockstep.head_step(admits, cancels)
+        self.lockstep.head_step([], [], stop=True)
+
     def _run(self):
         try:
+            if self.lockstep is not None:
+                self._run_lockstep()
+                return
             while self.running:
                 self._drain(block=self.s.idle())
                 if not self.s.idle():
