@@ -14,8 +14,20 @@
 extern "C" {
 #endif
 
+// Peer-memory communication context (one per rank; data[q] is rank q's symmetric arena mapped here).
+typedef struct VgCommCtx {
+  int rank, world;
+  unsigned char* data[8];
+  unsigned long long flags_off, slots_off, slot_bytes, result_off, result_bytes;
+  unsigned int* epoch;       // device-resident epoch counter of this rank
+  unsigned int* done_ctr;    // CTA completion counter
+  int* status;               // error status word (0 = ok)
+  unsigned long long timeout_ns;
+} VgCommCtx;
+
 int vg_gemm_tc(const void* wt, const float* row_scale, const void* x_f16, int x_rows, int ldx, void* out, int out_f32,
-               int M, int K, int N, int ldo, int wfmt, int splitk, int* err, cudaStream_t stream);
+               int M, int K, int N, int ldo, int wfmt, int splitk, int* err, const VgCommCtx* ar_ctx,
+               cudaStream_t stream);
 int vg_gemm_tc_grouped(const void* wt, const float* row_scale, const void* x_f16, int x_rows, int ldx, void* out, int out_f32,
                        int M, int K, int ldo, int wfmt, int bn, int max_items, const int* g_exp, const int* g_off,
                        const int* g_cnt, const int* tilemap, const int* n_items, int x_div, int* err, cudaStream_t stream);
@@ -63,17 +75,6 @@ int vg_moe_gather(const void* x_f16, int ldx, const int* perm, const int* total,
 int vg_moe_combine(const void* y, int ldy, const int* inv, const float* wts, int N, int topk, const void* shared,
                    const float* gate_logit, void* out, int h, cudaStream_t stream);
 int vg_moe_add_shared(void* out, const void* shared, const float* gate_logit, int N, int h, cudaStream_t stream);
-
-// Peer-memory communication context (one per rank; data[q] is rank q's symmetric arena mapped here).
-typedef struct VgCommCtx {
-  int rank, world;
-  unsigned char* data[8];
-  unsigned long long flags_off, slots_off, slot_bytes, result_off, result_bytes;
-  unsigned int* epoch;       // device-resident epoch counter of this rank
-  unsigned int* done_ctr;    // CTA completion counter
-  int* status;               // error status word (0 = ok)
-  unsigned long long timeout_ns;
-} VgCommCtx;
 
 int vg_comm_alloc(void** ptr, unsigned long long bytes);
 int vg_comm_free(void* ptr);

@@ -2,7 +2,7 @@
 //
 // Substrate: every rank cudaMalloc's one "symmetric" arena of the same size, exports it with a CUDA IPC
 // handle and maps every peer's arena; kernels then use plain ld/st on the peer pointers. The arena holds
-//   flags   [2 sets][8 source ranks][64 CTAs] one 32-bit flag per 128-byte line
+//   flags   [4 sets][8 source ranks][64 CTAs] one 32-bit flag per 128-byte line (sets 2,3: second phase)
 //   slots   [2 sets][8 source ranks][slot_bytes] receive buffers, written by the source rank
 //   result  [2 sets][result_bytes] all-gather landing zone of the two-shot all-reduce
 // plus a device-resident epoch counter, so a kernel captured in a CUDA graph advances its own epoch on
@@ -21,34 +21,6 @@
 
 namespace {
 using namespace vg;
-
-constexpr int MAX_RANKS = 8;
-constexpr int MAX_CTAS = 64;
-constexpr int FLAG_STRIDE = 32;      // uint32 per flag line (128 bytes)
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-// Wait until *p has reached epoch e (wrap-safe). False when the budget ran out.
-__device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t e, uint64_t budget_ns) {
-  for (int i = 0; i < 256; ++i)
-    if ((int32_t)(ld_acquire_sys(p) - e) >= 0) return true;
-  const uint64_t t0 = global_ns();
-  for (;;) {
-    for (int i = 0; i < 64; ++i)
-      if ((int32_t)(ld_acquire_sys(p) - e) >= 0) return true;
-    if (global_ns() - t0 > budget_ns) return false;
-  }
-}
-
-__device__ __forceinline__ size_t flag_index(int set, int src, int cta) {
-  return ((size_t)(set * MAX_RANKS + src) * MAX_CTAS + cta) * FLAG_STRIDE;
-}
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }

@@ -171,6 +171,36 @@ VG_DEVINL float dsmem_ld_f32(uint32_t addr) {
   return v;
 }
 
+// ------------------------------------------------------------------ peer-memory flags
+constexpr int MAX_RANKS = 8;
+constexpr int MAX_CTAS = 64;
+constexpr int FLAG_STRIDE = 32;      // uint32 per flag line (128 bytes)
+
+VG_DEVINL void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+VG_DEVINL uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Wait until *p has reached epoch e (wrap-safe). False when the budget ran out.
+VG_DEVINL bool wait_flag(const uint32_t* p, uint32_t e, uint64_t budget_ns) {
+  for (int i = 0; i < 256; ++i)
+    if ((int32_t)(ld_acquire_sys(p) - e) >= 0) return true;
+  const uint64_t t0 = global_ns();
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if ((int32_t)(ld_acquire_sys(p) - e) >= 0) return true;
+    if (global_ns() - t0 > budget_ns) return false;
+  }
+}
+
+VG_DEVINL size_t flag_index(int set, int src, int cta) {
+  return ((size_t)(set * MAX_RANKS + src) * MAX_CTAS + cta) * FLAG_STRIDE;
+}
+
+
 // ------------------------------------------------------------------ numerics
 VG_DEVINL float bf16_to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 VG_DEVINL float silu(float x) { return x / (1.0f + __expf(-x)); }

@@ -22,6 +22,9 @@
 // already in UMMA layout and used as a shared-memory A operand.
 // Split-K runs as a thread-block cluster along z: partial tiles are summed through distributed
 // shared memory in cluster-rank order by the rank-0 CTA, so no global scratch or atomics are needed.
+// With a communication context the epilogue of a row-parallel GEMM is also the tensor-parallel all-reduce:
+// fp32 partial tiles are pushed to all peers with plain stores over NVLink, a flag per (rank, tile) is
+// raised with st.release.sys, and each rank adds the W partials in rank order - no separate collective.
 // All mbarrier waits are bounded; on expiry an error code is stored to the status word and the CTA
 // unwinds through its normal teardown (TMEM is always freed).
 #include <cuda.h>
@@ -67,6 +70,11 @@ struct GemmParams {
   const int* n_items;    // device count of valid items, or null: all of gridDim.y
   int tiles_per_expert;  // row tiles of one expert's matrix
   int x_div;             // X row = Y row / x_div (decode: one activation row feeds top-k pairs)
+  // fused tensor-parallel reduction (row-parallel layers, N <= 16): the epilogue pushes this rank's fp32
+  // partial tile into every rank's receive slot, raises a per-tile flag, waits for the other ranks' tiles
+  // and stores the rank-order sum. ar == 0: plain store.
+  int ar;
+  VgCommCtx comm;
 };
 
 constexpr uint32_t pow2_cols(uint32_t c) { return c <= 32 ? 32 : c <= 64 ? 64 : c <= 128 ? 128 : c <= 256 ? 256 : 512; }
@@ -190,6 +198,8 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
     nt = 0;
   }
   const int x_row0 = p.grouped ? row0 / p.x_div : row0;
+  // every CTA reads the collective epoch before any tile can publish the next one
+  const uint32_t ar_epoch = p.ar ? *p.comm.epoch + 1 : 0;
   const int ks0 = (int)(((long long)z * p.ks_total) / S);
   const int ks1 = (int)(((long long)(z + 1) * p.ks_total) / S);
   const int nks = ks1 - ks0;
@@ -386,7 +396,58 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
     }
     cluster_sync_all();
   }
-  if (epi && have_acc && z == 0) {
+  if (epi && z == 0 && p.ar) {
+    // ---- fused all-reduce epilogue (all 256 epilogue threads take part, also on the error path)
+    __shared__ int ar_failed;
+    const VgCommCtx& c = p.comm;
+    const uint32_t e = ar_epoch;
+    const int set = e & 1;
+    const int et = threadIdx.x - 64;                      // 0..255 among the epilogue warps
+    const int m = (int)blockIdx.x * BM + m_local;
+    const float rsc = (p.row_scale && m < p.M) ? p.row_scale[m] : 1.0f;
+    if (et == 0) ar_failed = 0;
+    if (have_acc && m < p.M) {
+      for (int k = 0; k < c.world; ++k) {
+        const int peer = (c.rank + k) % c.world;
+        float* dst = reinterpret_cast<float*>(c.data[peer] + c.slots_off + (size_t)(set * MAX_RANKS + c.rank) * c.slot_bytes);
+#pragma unroll
+        for (int cc = 0; cc < CPW; ++cc) {
+          const int col = grp * CPW + cc;
+          if (col < rows_valid) dst[(size_t)(row0 + col) * p.M + m] = acc[cc] * rsc;
+        }
+      }
+    }
+    __threadfence_system();
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (et < c.world)
+      st_release_sys(reinterpret_cast<uint32_t*>(c.data[et] + c.flags_off) + flag_index(set, c.rank, (int)blockIdx.x), e);
+    if (et < c.world) {
+      const uint32_t* f = reinterpret_cast<const uint32_t*>(c.data[c.rank] + c.flags_off) + flag_index(set, et, (int)blockIdx.x);
+      if (!wait_flag(f, e, c.timeout_ns)) { atomicCAS(c.status, 0, VG_ERR_PEER_WAIT); ar_failed = 1; }
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (!ar_failed && have_acc && m < p.M) {
+      const float* base = reinterpret_cast<const float*>(c.data[c.rank] + c.slots_off + (size_t)set * MAX_RANKS * c.slot_bytes);
+      const size_t stride = c.slot_bytes / sizeof(float);
+#pragma unroll
+      for (int cc = 0; cc < CPW; ++cc) {
+        const int col = grp * CPW + cc;
+        if (col < rows_valid) {
+          const size_t idx = (size_t)(row0 + col) * p.M + m;
+          float sum = 0.f;
+          for (int q2 = 0; q2 < c.world; ++q2) sum += __ldcg(&base[(size_t)q2 * stride + idx]);
+          if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)(row0 + col) * p.ldo + m] = sum;
+          else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)(row0 + col) * p.ldo + m] = __float2bfloat16_rn(sum);
+        }
+      }
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (et == 0) {
+      // the last tile to finish publishes the new epoch for the next collective
+      __threadfence();
+      if (atomicAdd(c.done_ctr, 1u) == gridDim.x * gridDim.y - 1) { *c.done_ctr = 0; *c.epoch = e; }
+    }
+  } else if (epi && have_acc && z == 0) {
     const int m = (int)blockIdx.x * BM + m_local;       // row inside this (expert's) matrix
     if (m < p.M) {
       const float rsc = p.row_scale ? p.row_scale[m_base + m] : 1.0f;
@@ -525,7 +586,7 @@ int dispatch_bn(const GemmParams& p, const void* x, int ldx, int splitk, cudaStr
 
 extern "C" int vg_gemm_tc(const void* wt, const float* row_scale, const void* x_f16, int x_rows, int ldx, void* out,
                           int out_f32, int M, int K, int N, int ldo, int wfmt, int splitk, int* err,
-                          cudaStream_t stream) {
+                          const VgCommCtx* ar_ctx, cudaStream_t stream) {
   if (M <= 0 || K <= 0 || N <= 0 || (K % 16) != 0 || splitk < 1 || splitk > 8 || x_rows < N) return -2;
   if (ldx < K || (ldx % 8) != 0 || (reinterpret_cast<uintptr_t>(x_f16) & 15) != 0) return -4;
   GemmParams p;
@@ -539,6 +600,13 @@ extern "C" int vg_gemm_tc(const void* wt, const float* row_scale, const void* x_
   p.dbg = g_dbg;
   p.trace = g_trace;
   p.grouped = 0;
+  p.ar = 0;
+  if (ar_ctx && ar_ctx->world > 1) {
+    // fused reduction: decode widths only, one flag per row tile
+    if (N > 16 || (M + BM - 1) / BM > MAX_CTAS || (unsigned long long)N * M * 4ull > ar_ctx->slot_bytes) return -5;
+    p.ar = 1;
+    p.comm = *ar_ctx;
+  }
   if (splitk > p.ks_total) splitk = p.ks_total;
   if (N > 64) splitk = 1;
   switch (wfmt) {
@@ -570,6 +638,7 @@ extern "C" int vg_gemm_tc_grouped(const void* wt, const float* row_scale, const 
   p.dbg = 0;
   p.trace = nullptr;
   p.grouped = 1;
+  p.ar = 0;
   p.g_exp = g_exp; p.g_off = g_off; p.g_cnt = g_cnt; p.tilemap = tilemap; p.n_items = n_items;
   p.tiles_per_expert = M / BM;
   p.x_div = x_div;

@@ -49,6 +49,13 @@ def main():
     for t in range(4):
         ld, _ = tp.decode([toks[t]], [300 + t], [0])
         assert torch.equal(ld[0], lv[t]), t
+    # the fused GEMM-epilogue all-reduce and the separate all-reduce kernel give the same tokens
+    tp.S.copy_(S0); tp.conv.copy_(C0); tp.kc.copy_(K0); tp.vc.copy_(V0)
+    tp.fuse_allreduce = False
+    lu, _ = tp.verify(0, toks, 300, ckpt_base=2)
+    tp.fuse_allreduce = True
+    rel = ((lu.float() - lv.float()).norm() / lv.float().norm()).item()
+    assert rel < 0.02 and lu.argmax(-1).tolist() == lv.argmax(-1).tolist(), rel
     # graph replay under tensor parallelism
     tp.S.copy_(S0); tp.conv.copy_(C0); tp.kc.copy_(K0); tp.vc.copy_(V0)
     want = int(lv[0].argmax())

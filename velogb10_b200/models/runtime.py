@@ -10,6 +10,7 @@ decode, chain, tree and forest verify and prefill.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -156,6 +157,7 @@ class GpuModel:
         self.comm = comm
         self.max_cols = max_cols
         self.prefill_chunk = prefill_chunk
+        self.fuse_allreduce = os.environ.get("VELO_NO_FUSED_ALLREDUCE", "0") != "1"
         _lib.lib()
         with torch.cuda.device(self.dev):
             for name, q in weights.linears():
@@ -254,6 +256,18 @@ class GpuModel:
         if self.comm is not None and self.comm.world > 1:
             self.comm.all_reduce_rows(t, n)
 
+    def _row_parallel(self, q: QLinear, x16: torch.Tensor, n: int, out: torch.Tensor, reduce: bool = True):
+        """Row-parallel linear + tensor-parallel sum. For decode / verify widths the reduction is fused into
+        the GEMM epilogue (peer-memory pushes + flags inside the same kernel); longer inputs run the GEMM and
+        then the two-shot peer-memory all-reduce."""
+        tp = reduce and self.comm is not None and self.comm.world > 1
+        if tp and n <= 16 and not self.comm.use_nccl and self.fuse_allreduce and (q.m + 127) // 128 <= 64:
+            G.linear(q, x16, n, out=out, comm=self.comm)
+            return
+        G.linear(q, x16, n, out=out)
+        if tp:
+            self._reduce(out, n)
+
     def _attn(self, ws: Workspace, L: LayerW, n: int, kc, vc, plan_direct: bool, use_path: bool):
         c, A = self.cfg, L.attn
         qkv = ws.wide[:, :A.qkv.m]
@@ -264,8 +278,7 @@ class GpuModel:
         K.attn_decode(ws.q, kc, vc, ws.lens, ws.kv_slot, self.attn_part, a16, n, A.nh, A.nkv, c.head_dim,
                       gate=qkv if c.attn_out_gate else None, base=ws.base if use_path else None,
                       path=ws.path if use_path else None, ns_grid=self.ns_grid, direct=plan_direct)
-        G.linear(A.o, a16, n, out=ws.delta)
-        self._reduce(ws.delta, n)
+        self._row_parallel(A.o, a16, n, ws.delta)
 
     def _gdn(self, ws: Workspace, L: LayerW, li: int, n: int, n_chains: int, seq_mode: bool):
         c, Gd = self.cfg, L.gdn
@@ -286,17 +299,14 @@ class GpuModel:
         K.gdn_step(ws.conv_out, proj, conv_dim, conv_dim + value_dim, conv_dim + value_dim + Gd.nv, self.S[gi],
                    Gd.A_log, Gd.dt_bias, Gd.norm, ws.chain_start, ws.chain_len, n_chains, ws.st_in, ws.parent,
                    ws.st_out, g16, Gd.nk, Gd.nv, c.lin_k_dim, c.lin_v_dim, c.rms_eps)
-        G.linear(Gd.out, g16, n, out=ws.delta)
-        self._reduce(ws.delta, n)
+        self._row_parallel(Gd.out, g16, n, ws.delta)
 
     def _mlp(self, ws: Workspace, M, n: int, out: torch.Tensor, reduce: bool = True):
         gu = ws.wide[:, :M.gate_up.m]
         G.linear(M.gate_up, ws.xn16, n, out=gu)
         a16 = ws.a16(M.down.k)
         K.swiglu(gu, a16, n, M.inter)
-        G.linear(M.down, a16, n, out=out)
-        if reduce:
-            self._reduce(out, n)
+        self._row_parallel(M.down, a16, n, out, reduce)
 
     def _moe(self, ws: Workspace, M: MoeW, n: int):
         from . import moe_runtime
