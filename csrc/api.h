@@ -28,6 +28,13 @@ typedef struct VgCommCtx {
 int vg_gemm_tc(const void* wt, const float* row_scale, const void* x_f16, int x_rows, int ldx, void* out, int out_f32,
                int M, int K, int N, int ldo, int wfmt, int splitk, int* err, const VgCommCtx* ar_ctx,
                cudaStream_t stream);
+int vg_act_quant_fp4(const void* x_f16, int ldx, int N, int K, void* bq, int ldb, void* sfb, float* g0, cudaStream_t stream);
+int vg_swiglu_fp4(const void* gu, int ld, int N, int I, void* bq, int ldb, void* sfb, float* g0, void* out16,
+                  cudaStream_t stream);
+int vg_add_rmsnorm_fp4(void* res, const void* delta, const float* w, int N, int h, float eps, int plus_one, int ld_res,
+                       int ld_delta, void* bq, int ldb, void* sfb, float* g0, void* out16, cudaStream_t stream);
+int vg_gemm_fp4(const void* wt, const float* row_scale, const void* bq, int ldb, const void* sfb, const float* g0, void* out,
+                int out_f32, int M, int K, int N, int ldo, int splitk, int* err, const VgCommCtx* ar_ctx, cudaStream_t stream);
 int vg_gemm_tc_grouped(const void* wt, const float* row_scale, const void* x_f16, int x_rows, int ldx, void* out, int out_f32,
                        int M, int K, int ldo, int wfmt, int bn, int max_items, const int* g_exp, const int* g_off,
                        const int* g_cnt, const int* tilemap, const int* n_items, int x_div, int* err, cudaStream_t stream);

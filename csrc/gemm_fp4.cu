@@ -1,0 +1,391 @@
+// Decode / verify GEMM on the block-scaled FP4 tensor-core path (tcgen05.mma kind::mxf4nvf4, sm_100a).
+//
+//   Y[n, m] = row_scale[m] * sum_k nvfp4(W[m, k]) * X[n, k],   N <= 16
+//
+// The f16 path (gemm_tc.cu) retires one M128 x N16 x K16 MMA per ~106 cycles per SM, which caps a 4-bit
+// weight stream at about 3 TB/s. Here one instruction covers K = 64 and the packed e2m1 weights and their
+// e4m3 block scales are consumed straight from shared memory / TMEM with no dequantisation work at all.
+// The hardware needs both operands in FP4, so each activation column is expanded into a four-term NVFP4
+// residual series  x ~ x0 + x1 + x2 + x3  (term t quantises what terms < t left over, with a fixed global
+// scale ratio of 1/8 between terms); the four terms of the 16 columns form the 64 rows of the B operand,
+// one MMA multiplies the weights with all of them, and the epilogue recombines
+//   y = g0[n] * (D0 + D1/8 + D2/64 + D3/512).
+// Four e2m1 terms carry ~10 bits of each 16-element block's range, i.e. the activation precision of the
+// 16-bit path; weights are exact. Every column is quantised on its own and MMA columns are independent, so
+// the result of a column does not depend on the batch width.
+//
+// CTA (256 threads): warp 0 weight producer (bulk copies of pre-tiled 128 x 256 slabs: 16 KB packed values
+// in the UMMA 128-byte-swizzle layout + 2 KB scales in the scale-factor chunk layout), warp 1 activation
+// producer (tensor copy of the 64 x 256 B tile + bulk copy of its scale chunks), warps 2-3 MMA issuers
+// (even / odd slabs, separate accumulators; each copies its slab's scale factors to TMEM with tcgen05.cp and
+// issues four K=64 MMAs), warps 4-7 epilogue. Split-K over a thread-block cluster with a rank-order DSMEM
+// reduction, exactly as in gemm_tc.cu. All waits are bounded.
+#include <cuda.h>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+#include "api.h"
+
+namespace {
+using namespace vg;
+
+constexpr int BM = 128;
+constexpr int BKQ = 256;                    // K elements per slab
+constexpr int NT = 64;                      // B rows: 4 terms x 16 columns
+constexpr int TERMS = 4;
+constexpr int A_BYTES = BM * BKQ / 2;       // 16384
+constexpr int SF_BYTES = 4 * 512;           // scale chunks of one slab (4 K=64 steps)
+constexpr int B_BYTES = NT * BKQ / 2;       // 8192
+constexpr int STAGE = A_BYTES + SF_BYTES + B_BYTES + SF_BYTES;   // 28672
+constexpr int NS = 6;                       // stages (even: one issuer per stage)
+constexpr int THREADS = 256;
+constexpr uint32_t ACC_W = 64;              // columns of one accumulator
+constexpr uint32_t SF_COLS = 32;            // TMEM columns of one slab's scale factors (A: 16, B: 16)
+constexpr uint32_t TMEM_COLS = 256;         // 2 accumulators + 2 issuers x 2 scale buffers
+
+struct Fp4Params {
+  const uint8_t* wt;          // [MT][KS][A_BYTES + SF_BYTES]
+  const float* row_scale;
+  const uint8_t* sfb;         // [KS][SF_BYTES] activation scale chunks
+  const float* g0;            // [16] per-column global scale of term 0
+  void* out;
+  int M, N, ldo, ks_total, out_f32;
+  int* err;
+  int ar;
+  VgCommCtx comm;
+};
+
+constexpr int SMEM_TOTAL = NS * STAGE + (2 * NS + 1) * 8 + 16 + 1024;
+
+// instruction descriptor for kind::mxf4nvf4, e2m1 x e2m1, ue4m3 scales, K = 64, both operands K-major
+__device__ __forceinline__ constexpr uint32_t idesc_fp4(int m, int n) {
+  return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | (0u << 23) | ((uint32_t)(m >> 4) << 24);
+}
+// shared-memory descriptor of a 32 x 16-byte scale chunk (no swizzle: 8-row groups are 128 bytes apart)
+__device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)(16 >> 4) << 16;        // leading byte offset (one 16-byte column only)
+  d |= (uint64_t)(128 >> 4) << 32;       // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void umma_fp4(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
+                                         uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void fail(int* err, int code, volatile int* abort_flag) {
+  if (err) atomicCAS(err, 0, code);
+  *abort_flag = 1;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + NS * STAGE);
+  uint64_t* full = bars;                 // both producers arrive (count 2) + their bytes
+  uint64_t* empty = full + NS;           // MMA commit
+  uint64_t* acc_full = empty + NS;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int mt = blockIdx.x;
+  const int S = gridDim.z, z = blockIdx.z;
+  const int ks0 = (int)(((long long)z * p.ks_total) / S);
+  const int ks1 = (int)(((long long)(z + 1) * p.ks_total) / S);
+  const int nks = ks1 - ks0;
+  const int rot = nks > 0 ? (int)(((unsigned)mt * 7u + (unsigned)z * 3u) % (unsigned)nks) : 0;
+  auto slab_of = [&](int i) { int k = i + rot; return ks0 + (k >= nks ? k - nks : k); };
+  const uint32_t ar_epoch = p.ar ? *p.comm.epoch + 1 : 0;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NS; ++i) { mbar_init(&full[i], 2); mbar_init(&empty[i], 1); }
+    mbar_init(acc_full, 2);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < nks && !*abort_flag; ++i) {
+        const int s = i % NS;
+        if (!mbar_wait(&empty[s], ((i / NS) & 1) ^ 1)) { fail(p.err, VG_ERR_EMPTY_WAIT, abort_flag); break; }
+        uint8_t* st = smem + (size_t)s * STAGE;
+        mbar_arrive_expect_tx(&full[s], A_BYTES + SF_BYTES);
+        tma_bulk_g2s(st, p.wt + ((size_t)mt * p.ks_total + slab_of(i)) * (A_BYTES + SF_BYTES), A_BYTES + SF_BYTES, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      for (int i = 0; i < nks && !*abort_flag; ++i) {
+        const int s = i % NS;
+        if (!mbar_wait(&empty[s], ((i / NS) & 1) ^ 1)) { fail(p.err, VG_ERR_EMPTY_WAIT, abort_flag); break; }
+        uint8_t* st = smem + (size_t)s * STAGE + A_BYTES + SF_BYTES;
+        const int ks = slab_of(i);
+        mbar_arrive_expect_tx(&full[s], B_BYTES + SF_BYTES);
+        tma_tensor2d_g2s(st, &tmap_b, ks * (BKQ / 2), 0, &full[s]);
+        tma_bulk_g2s(st + B_BYTES, p.sfb + (size_t)ks * SF_BYTES, SF_BYTES, &full[s]);
+      }
+    }
+  } else if (warp == 2 || warp == 3) {
+    if (lane == 0) {
+      const int me = warp - 2;
+      const uint32_t idesc = idesc_fp4(BM, NT);
+      const uint32_t tmem_acc = tmem_base + (uint32_t)me * ACC_W;
+      const uint32_t tmem_sf0 = tmem_base + 2 * ACC_W + (uint32_t)me * 2 * SF_COLS;
+      bool ok = true;
+      int mine = 0;
+      for (int i = me; i < nks && !*abort_flag; i += 2, ++mine) {
+        const int s = i % NS;
+        if (!mbar_wait(&full[s], (i / NS) & 1)) { fail(p.err, VG_ERR_TMA_WAIT, abort_flag); ok = false; break; }
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE);
+        const uint32_t sfa_addr = a_addr + A_BYTES;
+        const uint32_t b_addr = sfa_addr + SF_BYTES;
+        const uint32_t sfb_addr = b_addr + B_BYTES;
+        const uint32_t sf_t = tmem_sf0 + (uint32_t)(mine & 1) * SF_COLS;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          tmem_cp_sf(sf_t + 4 * j, sf_desc(sfa_addr + 512 * j));
+          tmem_cp_sf(sf_t + 16 + 4 * j, sf_desc(sfb_addr + 512 * j));
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          umma_fp4(tmem_acc, umma_desc_sw128(a_addr + 32 * j), umma_desc_sw128(b_addr + 32 * j), idesc, sf_t + 4 * j,
+                   sf_t + 16 + 4 * j, (i >= 2 || j != 0) ? 1u : 0u);
+        }
+        umma_commit(&empty[s]);
+      }
+      if (ok) umma_commit(acc_full);
+    }
+  }
+  __syncwarp();
+
+  // ---------------------------------------------------------------- epilogue: warps 4..7, thread = weight row
+  const bool epi = warp >= 4;
+  const int q = warp & 3;
+  const int m_local = q * 32 + lane;
+  float y[16];
+  bool have = false;
+  if (epi) {
+    if (mbar_wait(acc_full, 0)) {
+      tc_fence_after();
+#pragma unroll
+      for (int n = 0; n < 16; ++n) y[n] = 0.f;
+      const float tw[TERMS] = {1.0f, 0.125f, 0.015625f, 0.001953125f};
+#pragma unroll
+      for (int t = 0; t < TERMS; ++t) {
+        uint32_t a0[16], a1[16];
+        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * 16), a0);
+        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + ACC_W + (uint32_t)(t * 16), a1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int n = 0; n < 16; ++n) {
+          const float d = nks >= 2 ? __uint_as_float(a0[n]) + __uint_as_float(a1[n]) : __uint_as_float(a0[n]);
+          y[n] = fmaf(d, tw[t], y[n]);
+        }
+      }
+      have = true;
+    } else {
+      fail(p.err, VG_ERR_MMA_WAIT, abort_flag);
+    }
+  }
+  if (S > 1) {
+    float* red = reinterpret_cast<float*>(smem);          // stage 0 is idle once every MMA has completed
+    if (epi && have) {
+#pragma unroll
+      for (int n = 0; n < 16; ++n) red[n * BM + m_local] = y[n];
+    }
+    cluster_sync_all();
+    if (z == 0 && epi && have) {
+      const uint32_t red_addr = smem_u32(red);
+      for (int s = 1; s < S; ++s) {
+        const uint32_t remote = dsmem_map(red_addr, (uint32_t)s);
+#pragma unroll
+        for (int n = 0; n < 16; ++n) y[n] += dsmem_ld_f32(remote + (uint32_t)((n * BM + m_local) * 4));
+      }
+    }
+    cluster_sync_all();
+  }
+  const int m = mt * BM + m_local;
+  if (epi && z == 0 && p.ar) {
+    // fused tensor-parallel all-reduce (same protocol as gemm_tc.cu)
+    __shared__ int ar_failed;
+    const VgCommCtx& c = p.comm;
+    const uint32_t e = ar_epoch;
+    const int set = e & 1;
+    const int et = threadIdx.x - 128;
+    const float rsc = (p.row_scale && m < p.M) ? p.row_scale[m] : 1.0f;
+    if (et == 0) ar_failed = 0;
+    if (have && m < p.M) {
+      for (int k = 0; k < c.world; ++k) {
+        const int peer = (c.rank + k) % c.world;
+        float* dst = reinterpret_cast<float*>(c.data[peer] + c.slots_off + (size_t)(set * MAX_RANKS + c.rank) * c.slot_bytes);
+#pragma unroll
+        for (int n = 0; n < 16; ++n)
+          if (n < p.N) dst[(size_t)n * p.M + m] = y[n] * p.g0[n] * rsc;
+      }
+    }
+    __threadfence_system();
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (et < c.world)
+      st_release_sys(reinterpret_cast<uint32_t*>(c.data[et] + c.flags_off) + flag_index(set, c.rank, (int)blockIdx.x), e);
+    if (et < c.world) {
+      const uint32_t* f = reinterpret_cast<const uint32_t*>(c.data[c.rank] + c.flags_off) + flag_index(set, et, (int)blockIdx.x);
+      if (!wait_flag(f, e, c.timeout_ns)) { atomicCAS(c.status, 0, VG_ERR_PEER_WAIT); ar_failed = 1; }
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (!ar_failed && have && m < p.M) {
+      const float* base = reinterpret_cast<const float*>(c.data[c.rank] + c.slots_off + (size_t)set * MAX_RANKS * c.slot_bytes);
+      const size_t stride = c.slot_bytes / sizeof(float);
+#pragma unroll
+      for (int n = 0; n < 16; ++n) {
+        if (n < p.N) {
+          const size_t idx = (size_t)n * p.M + m;
+          float sum = 0.f;
+          for (int q2 = 0; q2 < c.world; ++q2) sum += __ldcg(&base[(size_t)q2 * stride + idx]);
+          if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)n * p.ldo + m] = sum;
+          else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)n * p.ldo + m] = __float2bfloat16_rn(sum);
+        }
+      }
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (et == 0) {
+      __threadfence();
+      if (atomicAdd(c.done_ctr, 1u) == gridDim.x - 1) { *c.done_ctr = 0; *c.epoch = e; }
+    }
+  } else if (epi && have && z == 0 && m < p.M) {
+    const float rsc = p.row_scale ? p.row_scale[m] : 1.0f;
+#pragma unroll
+    for (int n = 0; n < 16; ++n) {
+      if (n < p.N) {
+        const float v = y[n] * p.g0[n] * rsc;
+        if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)n * p.ldo + m] = v;
+        else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)n * p.ldo + m] = __float2bfloat16_rn(v);
+      }
+    }
+  }
+  if (*abort_flag && threadIdx.x == 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode4() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(f);
+  });
+  return fn;
+}
+std::map<std::tuple<const void*, int>, CUtensorMap> g_bmaps;
+std::mutex g_bmu;
+
+int get_tmap_b(const void* bq, int ldb, CUtensorMap* out) {
+  std::lock_guard<std::mutex> lk(g_bmu);
+  auto key = std::make_tuple(bq, ldb);
+  auto it = g_bmaps.find(key);
+  if (it != g_bmaps.end()) { *out = it->second; return 0; }
+  EncodeTiledFn enc = get_encode4();
+  if (!enc) return -1;
+  cuuint64_t gdim[2] = {(cuuint64_t)ldb, (cuuint64_t)NT};
+  cuuint64_t gstride[1] = {(cuuint64_t)ldb};
+  cuuint32_t box[2] = {128, (cuuint32_t)NT};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap tm;
+  CUresult r = enc(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(bq), gdim, gstride, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return -(int)r - 100;
+  if (g_bmaps.size() > 1024) g_bmaps.clear();
+  g_bmaps[key] = tm;
+  *out = tm;
+  return 0;
+}
+}  // namespace
+
+extern "C" int vg_gemm_fp4(const void* wt, const float* row_scale, const void* bq, int ldb, const void* sfb, const float* g0,
+                           void* out, int out_f32, int M, int K, int N, int ldo, int splitk, int* err,
+                           const VgCommCtx* ar_ctx, cudaStream_t stream) {
+  if (M <= 0 || K <= 0 || N < 1 || N > 16 || splitk < 1 || splitk > 8 || (ldb % 128) != 0) return -2;
+  Fp4Params p;
+  p.wt = static_cast<const uint8_t*>(wt);
+  p.row_scale = row_scale;
+  p.sfb = static_cast<const uint8_t*>(sfb);
+  p.g0 = g0;
+  p.out = out;
+  p.M = M; p.N = N; p.ldo = ldo;
+  p.ks_total = (K + BKQ - 1) / BKQ;
+  if (p.ks_total * (BKQ / 2) > ldb) return -4;
+  p.out_f32 = out_f32;
+  p.err = err;
+  p.ar = 0;
+  if (ar_ctx && ar_ctx->world > 1) {
+    if ((M + BM - 1) / BM > MAX_CTAS || (unsigned long long)N * M * 4ull > ar_ctx->slot_bytes) return -5;
+    p.ar = 1;
+    p.comm = *ar_ctx;
+  }
+  if (splitk > p.ks_total) splitk = p.ks_total;
+  CUtensorMap tm;
+  int rc = get_tmap_b(bq, ldb, &tm);
+  if (rc) return rc;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_fp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((M + BM - 1) / BM, 1, splitk);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = SMEM_TOTAL;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = splitk;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, gemm_fp4_kernel, p, tm);
+}

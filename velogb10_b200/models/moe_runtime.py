@@ -71,7 +71,7 @@ def _grouped(tw, m_per_expert, x16, out, bn, max_items, g_exp, g_off, g_cnt, til
     _lib.check(rc, "vg_gemm_tc_grouped")
 
 
-def moe_forward(model, ws, M: MoeW, n: int):
+def moe_forward(model, ws, M: MoeW, n: int, act=None):
     """Reads ws.xn16[:n] (normed hidden, f16); writes the FFN output into ws.delta[:n] (bf16)."""
     cfg = model.cfg
     L = _lib.lib()
@@ -113,7 +113,7 @@ def moe_forward(model, ws, M: MoeW, n: int):
         inv = b.inv
     shared = gate = None
     if M.shared is not None:
-        model._mlp(ws, M.shared, n, b.shared, reduce=False)
+        model._mlp(ws, M.shared, n, b.shared, reduce=False, act=act)
         shared = b.shared
         if M.shared_gate is not None:
             G.linear_simt(M.shared_gate, ws.xn16, n, out=b.gate_logit, out_f32=True)

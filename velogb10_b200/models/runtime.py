@@ -158,6 +158,8 @@ class GpuModel:
         self.max_cols = max_cols
         self.prefill_chunk = prefill_chunk
         self.fuse_allreduce = os.environ.get("VELO_NO_FUSED_ALLREDUCE", "0") != "1"
+        # decode / verify widths run NVFP4 linears on the block-scaled FP4 tensor-core kernel
+        self.use_fp4 = os.environ.get("VELO_NO_FP4_MMA", "0") != "1"
         _lib.lib()
         with torch.cuda.device(self.dev):
             for name, q in weights.linears():
@@ -166,10 +168,14 @@ class GpuModel:
                 small = q.m < 128 or name.endswith(("router", "shared_gate"))
                 if name == "embed":
                     if weights.lm_head is weights.embed:
+                        if self.use_fp4 and q.fmt == "nvfp4" and q.packed is not None:
+                            G.prepare_fp4(q)
                         G.prepare(q, keep_canonical=True)
                     continue
                 if small or q.experts > 1:
                     continue
+                if self.use_fp4 and q.fmt == "nvfp4" and q.packed is not None:
+                    G.prepare_fp4(q)
                 G.prepare(q, keep_canonical=keep_canonical)
         self.ws = Workspace(self.cfg, weights, max_cols, self.dev, max_cols)
         self.ws_prefill: Optional[Workspace] = None
@@ -256,22 +262,40 @@ class GpuModel:
         if self.comm is not None and self.comm.world > 1:
             self.comm.all_reduce_rows(t, n)
 
-    def _row_parallel(self, q: QLinear, x16: torch.Tensor, n: int, out: torch.Tensor, reduce: bool = True):
+    def _fp4_ok(self, q: QLinear, n: int) -> bool:
+        return self.use_fp4 and n <= 16 and getattr(q, "kernel4", None) is not None
+
+    def _norm(self, ws: Workspace, delta, w: torch.Tensor, n: int):
+        """Residual add + RMSNorm into ``ws.xn16``; at decode widths the same kernel also emits the FP4
+        activation series, returned for the linears that read this input."""
+        if self.use_fp4 and n <= 16 and ws.x.shape[1] % 16 == 0:
+            return G.add_rmsnorm_fp4(ws.x, delta, w, self.cfg.rms_eps, n, out16=ws.xn16)
+        K.add_rmsnorm(ws.x, delta, w, self.cfg.rms_eps, n, out16=ws.xn16)
+        return None
+
+    def _linear(self, q: QLinear, x16: torch.Tensor, n: int, out: torch.Tensor, act=None, out_f32: bool = False,
+                comm=None):
+        if self._fp4_ok(q, n):
+            G.linear_fp4(q, x16, n, out=out, out_f32=out_f32, comm=comm, act=act)
+        else:
+            G.linear(q, x16, n, out=out, out_f32=out_f32, comm=comm)
+
+    def _row_parallel(self, q: QLinear, x16: torch.Tensor, n: int, out: torch.Tensor, reduce: bool = True, act=None):
         """Row-parallel linear + tensor-parallel sum. For decode / verify widths the reduction is fused into
         the GEMM epilogue (peer-memory pushes + flags inside the same kernel); longer inputs run the GEMM and
         then the two-shot peer-memory all-reduce."""
         tp = reduce and self.comm is not None and self.comm.world > 1
         if tp and n <= 16 and not self.comm.use_nccl and self.fuse_allreduce and (q.m + 127) // 128 <= 64:
-            G.linear(q, x16, n, out=out, comm=self.comm)
+            self._linear(q, x16, n, out, act=act, comm=self.comm)
             return
-        G.linear(q, x16, n, out=out)
+        self._linear(q, x16, n, out, act=act)
         if tp:
             self._reduce(out, n)
 
-    def _attn(self, ws: Workspace, L: LayerW, n: int, kc, vc, plan_direct: bool, use_path: bool):
+    def _attn(self, ws: Workspace, L: LayerW, n: int, kc, vc, plan_direct: bool, use_path: bool, act=None):
         c, A = self.cfg, L.attn
         qkv = ws.wide[:, :A.qkv.m]
-        G.linear(A.qkv, ws.xn16, n, out=qkv)
+        self._linear(A.qkv, ws.xn16, n, qkv, act=act)
         K.attn_prep(qkv, A.q_norm, A.k_norm, ws.pos, ws.kv_slot, ws.kv_row, ws.q, kc, vc, n, A.nh, A.nkv,
                     c.head_dim, c.rotary_dim, c.rms_eps, c.rope_theta, c.attn_out_gate)
         a16 = ws.a16(A.o.k)
@@ -280,11 +304,11 @@ class GpuModel:
                       path=ws.path if use_path else None, ns_grid=self.ns_grid, direct=plan_direct)
         self._row_parallel(A.o, a16, n, ws.delta)
 
-    def _gdn(self, ws: Workspace, L: LayerW, li: int, n: int, n_chains: int, seq_mode: bool):
+    def _gdn(self, ws: Workspace, L: LayerW, li: int, n: int, n_chains: int, seq_mode: bool, act=None):
         c, Gd = self.cfg, L.gdn
         gi = self.gdn_index[li]
         proj = ws.wide[:, :Gd.in_proj.m]
-        G.linear(Gd.in_proj, ws.xn16, n, out=proj)
+        self._linear(Gd.in_proj, ws.xn16, n, proj, act=act)
         conv_dim = Gd.conv_w.shape[0]
         value_dim = Gd.nv * c.lin_v_dim
         if seq_mode:
@@ -301,29 +325,33 @@ class GpuModel:
                    ws.st_out, g16, Gd.nk, Gd.nv, c.lin_k_dim, c.lin_v_dim, c.rms_eps)
         self._row_parallel(Gd.out, g16, n, ws.delta)
 
-    def _mlp(self, ws: Workspace, M, n: int, out: torch.Tensor, reduce: bool = True):
+    def _mlp(self, ws: Workspace, M, n: int, out: torch.Tensor, reduce: bool = True, act=None):
         gu = ws.wide[:, :M.gate_up.m]
-        G.linear(M.gate_up, ws.xn16, n, out=gu)
+        self._linear(M.gate_up, ws.xn16, n, gu, act=act)
         a16 = ws.a16(M.down.k)
+        if self._fp4_ok(M.down, n) and M.inter % 8 == 0:
+            act_d = G.swiglu_fp4(gu, n, M.inter)
+            self._row_parallel(M.down, a16, n, out, reduce, act=act_d)
+            return
         K.swiglu(gu, a16, n, M.inter)
         self._row_parallel(M.down, a16, n, out, reduce)
 
-    def _moe(self, ws: Workspace, M: MoeW, n: int):
+    def _moe(self, ws: Workspace, M: MoeW, n: int, act=None):
         from . import moe_runtime
-        moe_runtime.moe_forward(self, ws, M, n)
+        moe_runtime.moe_forward(self, ws, M, n, act=act)
 
     def _layer(self, ws, L: LayerW, li, n, n_chains, seq_mode, direct, use_path, kc, vc, first_delta):
         c = self.cfg
-        K.add_rmsnorm(ws.x, first_delta, L.input_norm, c.rms_eps, n, out16=ws.xn16)
+        act = self._norm(ws, first_delta, L.input_norm, n)
         if L.attn is not None:
-            self._attn(ws, L, n, kc, vc, direct, use_path)
+            self._attn(ws, L, n, kc, vc, direct, use_path, act=act)
         else:
-            self._gdn(ws, L, li, n, n_chains, seq_mode)
-        K.add_rmsnorm(ws.x, ws.delta, L.post_norm, c.rms_eps, n, out16=ws.xn16)
+            self._gdn(ws, L, li, n, n_chains, seq_mode, act=act)
+        act = self._norm(ws, ws.delta, L.post_norm, n)
         if L.moe is not None:
-            self._moe(ws, L.moe, n)
+            self._moe(ws, L.moe, n, act=act)
         else:
-            self._mlp(ws, L.mlp, n, ws.delta)
+            self._mlp(ws, L.mlp, n, ws.delta, act=act)
 
     def _backbone(self, ws: Workspace, n: int, n_chains: int, seq_mode: bool, direct: bool, use_path: bool,
                   logits_rows: Optional[Tuple[int, int]] = None):
@@ -339,14 +367,15 @@ class GpuModel:
                 kc, vc = self.kc[ai], self.vc[ai]
             self._layer(ws, L, li, n, n_chains, seq_mode, direct, use_path, kc, vc, delta)
             delta = ws.delta
-        K.add_rmsnorm(ws.x, delta, self.w.final_norm, c.rms_eps, n, out16=ws.xn16)
+        act = self._norm(ws, delta, self.w.final_norm, n)
         r0, r1 = (0, n) if logits_rows is None else logits_rows
         if r1 > r0:
             if r0 != 0:
                 # the LM head always reads from the start of the buffer (one cached tensor map)
                 assert r0 >= r1 - r0
                 ws.xn16[:r1 - r0].copy_(ws.xn16[r0:r1])
-            G.linear(self.w.lm_head, ws.xn16, r1 - r0, out=ws.logits, out_f32=True)
+                act = None
+            self._linear(self.w.lm_head, ws.xn16, r1 - r0, ws.logits, act=act, out_f32=True)
 
     # ---------------------------------------------------------------- public forwards
     def forward(self, plan: Plan, want_logits: bool = True) -> Tuple[Optional[torch.Tensor], torch.Tensor]:
@@ -420,14 +449,14 @@ class GpuModel:
         ws.hidden_keep[:n].copy_(hidden[:n])
         K.add_rmsnorm(ws.hidden_keep, None, m.norm_hidden, c.rms_eps, n, out_bf=ws.x)
         ws.cat16[:n, h:].copy_(ws.x[:n])
-        G.linear(m.fc, ws.cat16, n, out=ws.x)
+        self._linear(m.fc, ws.cat16, n, ws.x)
         comm, self.comm = self.comm, None          # the draft head is unsharded: no reductions
         try:
             self._layer(ws, m.layer, -1, n, 1, True, False, False, self.mtp_kc, self.mtp_vc, None)
         finally:
             self.comm = comm
-        K.add_rmsnorm(ws.x, ws.delta, m.norm, c.rms_eps, n, out16=ws.xn16)
-        G.linear(self.w.lm_head, ws.xn16, n, out=ws.logits, out_f32=True)
+        act = self._norm(ws, ws.delta, m.norm, n)
+        self._linear(self.w.lm_head, ws.xn16, n, ws.logits, act=act, out_f32=True)
         return self._full_logits(ws.logits[:n]), ws.x[:n]
 
     # ---------------------------------------------------------------- vocabulary-parallel head

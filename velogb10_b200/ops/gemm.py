@@ -155,3 +155,116 @@ def linear_simt(q: QLinear, x16: torch.Tensor, n: Optional[int] = None, out: Opt
                         c_int(x16.stride(0)), c_int(out.stride(0)), c_int(_FMT_CODE[q.fmt]), stream())
     _lib.check(rc, "vg_gemm_simt")
     return out
+
+
+# ------------------------------------------------------------------ block-scaled FP4 path (N <= 16)
+
+@dataclass
+class Fp4Weight:
+    wt: torch.Tensor               # uint8 [MT][K/256][16384 packed (128B-swizzled rows) + 2048 scale chunks]
+    row_scale: Optional[torch.Tensor]
+    m: int
+    k: int
+    kp: int                        # K padded to a multiple of 256
+    splitk: int
+
+
+def tile_nvfp4_mma(packed: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """Canonical NVFP4 -> the layout the FP4 tensor-core kernel consumes without any dequantisation:
+    per (128-row tile, 256-k slab) the packed rows as a K-major UMMA tile with the 128-byte swizzle, followed
+    by the block scales as four scale-factor chunks (one per K=64 step) in ``[row % 32][row // 32][k-block]``
+    byte order, the order tcgen05.cp expects."""
+    m, kh = packed.shape
+    k = kh * 2
+    mt, ksq = (m + 127) // 128, (k + 255) // 256
+    p = _pad2(packed, mt * 128, ksq * 128).view(mt, 128, ksq, 8, 16).permute(0, 2, 1, 3, 4)
+    p = _swizzle_chunks(p, lambda r: r & 7).reshape(mt, ksq, 16384)
+    s = _pad2(scales, mt * 128, ksq * 16).view(mt, 4, 32, ksq, 4, 4)          # [mt, r1, r0, slab, step, kb]
+    s = s.permute(0, 3, 4, 2, 1, 5).reshape(mt, ksq, 2048)                      # [mt, slab, step, r0, r1, kb]
+    return torch.cat([p, s], dim=-1).contiguous()
+
+
+def prepare_fp4(q: QLinear, splitk: Optional[int] = None) -> Fp4Weight:
+    k4 = getattr(q, "kernel4", None)
+    if k4 is not None:
+        return k4
+    assert q.fmt == "nvfp4" and q.packed is not None
+    wt = tile_nvfp4_mma(q.packed, q.scales)
+    mt = (q.m + 127) // 128
+    rs = q.row_scale
+    if rs.numel() < mt * 128:
+        rs = torch.cat([rs, torch.zeros(mt * 128 - rs.numel(), dtype=rs.dtype, device=rs.device)])
+    kp = ((q.k + 255) // 256) * 256
+    if splitk is None:
+        # one CTA per SM: never more CTAs than SMs, and at least eight 256-deep slabs per CTA (measured:
+        # a second wave or a shorter K loop costs more than the extra parallelism returns)
+        tiles, ks = mt, kp // 256
+        sms = max(1, _resident_ctas(WF_NVFP4) // 2)
+        splitk = max(1, min(8, sms // max(tiles, 1), ks // 8))
+    q.kernel4 = Fp4Weight(wt, rs, q.m, q.k, kp, splitk)
+    return q.kernel4
+
+
+_fp4_act = {}
+
+
+def _fp4_buffers(dev, kp: int):
+    key = (str(dev), kp)
+    b = _fp4_act.get(key)
+    if b is None:
+        b = (torch.zeros((64, kp // 2), dtype=torch.uint8, device=dev),
+             torch.zeros((kp // 256, 2048), dtype=torch.uint8, device=dev),
+             torch.zeros(16, dtype=torch.float32, device=dev))
+        _fp4_act[key] = b
+    return b
+
+
+def quantize_act_fp4(x16: torch.Tensor, n: int, kp: int):
+    """Expand ``n <= 16`` f16 rows into the four-term NVFP4 series the FP4 GEMM consumes."""
+    bq, sfb, g0 = _fp4_buffers(x16.device, kp)
+    rc = _lib.lib().vg_act_quant_fp4(ptr(x16), c_int(x16.stride(0)), c_int(n), c_int(x16.shape[1]), ptr(bq),
+                                     c_int(bq.stride(0)), ptr(sfb), ptr(g0), stream())
+    _lib.check(rc, "vg_act_quant_fp4")
+    return bq, sfb, g0
+
+
+def swiglu_fp4(gu: torch.Tensor, n: int, inter: int, out16: Optional[torch.Tensor] = None):
+    """SwiGLU of ``gu[:n] = [gate | up]`` (bf16) emitted directly as the FP4 series for the down projection."""
+    kp = ((inter + 255) // 256) * 256
+    bq, sfb, g0 = _fp4_buffers(gu.device, kp)
+    rc = _lib.lib().vg_swiglu_fp4(ptr(gu), c_int(gu.stride(0)), c_int(n), c_int(inter), ptr(bq), c_int(bq.stride(0)),
+                                  ptr(sfb), ptr(g0), ptr(out16) if out16 is not None else c_void_p(0), stream())
+    _lib.check(rc, "vg_swiglu_fp4")
+    return bq, sfb, g0
+
+
+def add_rmsnorm_fp4(res: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor, eps: float, n: int,
+                    out16: Optional[torch.Tensor] = None, plus_one: bool = True):
+    """``res += delta``; RMSNorm; the normalised rows leave as the FP4 series (and as f16 when ``out16`` is
+    given, for consumers that are not on the FP4 path)."""
+    h = res.shape[1]
+    kp = ((h + 255) // 256) * 256
+    bq, sfb, g0 = _fp4_buffers(res.device, kp)
+    rc = _lib.lib().vg_add_rmsnorm_fp4(ptr(res), ptr(delta) if delta is not None else c_void_p(0), ptr(w), c_int(n),
+                                       c_int(h), c_float(eps), c_int(1 if plus_one else 0), c_int(res.stride(0)),
+                                       c_int(delta.stride(0) if delta is not None else 0), ptr(bq), c_int(bq.stride(0)),
+                                       ptr(sfb), ptr(g0), ptr(out16) if out16 is not None else c_void_p(0), stream())
+    _lib.check(rc, "vg_add_rmsnorm_fp4")
+    return bq, sfb, g0
+
+
+def linear_fp4(q: QLinear, x16: torch.Tensor, n: int, out: Optional[torch.Tensor] = None, out_f32: bool = False,
+               comm=None, act=None) -> torch.Tensor:
+    """Decode-width linear on the block-scaled FP4 tensor-core path. ``act`` may carry an already quantised
+    activation (several linears reading the same input share it)."""
+    tw = prepare_fp4(q)
+    assert n <= 16 and x16.shape[1] == tw.k
+    bq, sfb, g0 = act if act is not None else quantize_act_fp4(x16, n, tw.kp)
+    if out is None:
+        out = torch.empty((n, tw.m), dtype=torch.float32 if out_f32 else torch.bfloat16, device=x16.device)
+    rc = _lib.lib().vg_gemm_fp4(ptr(tw.wt), ptr(tw.row_scale), ptr(bq), c_int(bq.stride(0)), ptr(sfb), ptr(g0), ptr(out),
+                                c_int(1 if out.dtype == torch.float32 else 0), c_int(tw.m), c_int(tw.k), c_int(n),
+                                c_int(out.stride(0)), c_int(tw.splitk), ptr(_lib.err_word(x16.device)),
+                                ctypes.byref(comm.ctx) if comm is not None else c_void_p(0), stream())
+    _lib.check(rc, "vg_gemm_fp4")
+    return out

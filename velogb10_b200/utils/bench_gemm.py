@@ -30,6 +30,7 @@ def main():
     ap.add_argument("--dbg", default="0")
     ap.add_argument("--splitk", default="auto")
     ap.add_argument("--only", default="")
+    ap.add_argument("--fp4", action="store_true", help="time the block-scaled FP4 path (nvfp4 weights, N <= 16)")
     args = ap.parse_args()
     from ..models.weights import QLinear
     from ..ops import gemm as G, lib as vlib
@@ -50,6 +51,34 @@ def main():
             tw.wt = tw.wt.clone()
             tws.append(qc)
         x = torch.randn(max(16, args.n), k, device="cuda").to(torch.float16)
+        if args.fp4:
+            qs = []
+            for c in range(copies):
+                qc = QLinear(q.fmt, q.m, q.k, q.packed, q.scales, q.codes, q.row_scale, q.w)
+                G.prepare_fp4(qc)
+                qs.append(qc)
+            out4 = torch.empty(16, m, dtype=torch.bfloat16, device="cuda")
+            sks = [qs[0].kernel4.splitk] if args.splitk == "auto" else [int(s_) for s_ in args.splitk.split(",")]
+            act = G.quantize_act_fp4(x, args.n, qs[0].kernel4.kp)
+            for sk in sks:
+                for qc in qs:
+                    qc.kernel4.splitk = sk
+                for mode in ("gemm", "quant+gemm"):
+                    a = act if mode == "gemm" else None
+                    for i in range(3):
+                        G.linear_fp4(qs[i % copies], x, args.n, out=out4, act=a)
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    for i in range(args.iters):
+                        G.linear_fp4(qs[i % copies], x, args.n, out=out4, act=a)
+                    e1.record()
+                    torch.cuda.synchronize()
+                    us = e0.elapsed_time(e1) * 1e3 / args.iters
+                    print(json.dumps({"shape": name, "m": m, "k": k, "n": args.n, "path": "fp4 " + mode, "splitk": sk,
+                                      "us": round(us, 2), "GBs": round(bytes_w / us / 1e3, 1)}))
+            vlib.check_err_word()
+            continue
         out = torch.empty(max(16, args.n), m, dtype=torch.bfloat16, device="cuda")
         sks = [tws[0].kernel.splitk] if args.splitk == "auto" else [int(s) for s in args.splitk.split(",")]
         for variant in [int(v) for v in args.variants.split(",")]:
