@@ -11,102 +11,38 @@
 //   g0   [16]             amax / (6 * 448) of each row; term t uses the global scale g0 / 8^t
 // Rows >= N are left untouched: their accumulator columns are never stored.
 #include "common.cuh"
+#include "act_quant.cuh"
 #include "api.h"
 
 namespace {
 using namespace vg;
 
-constexpr int TERMS = 4;
-constexpr int SF_BYTES = 2048;
-
-__device__ __forceinline__ uint8_t f32_to_e4m3(float v) {
-  uint16_t r;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(0.0f), "f"(v));
-  return (uint8_t)(r & 0xff);
-}
-__device__ __forceinline__ float e4m3_to_f32(uint8_t c) {
-  uint32_t h;
-  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h) : "h"((uint16_t)c));
-  return __half22float2(*reinterpret_cast<__half2*>(&h)).x;
-}
-__device__ __forceinline__ uint32_t f32x2_to_e2m1x2(float lo, float hi) {
-  uint32_t r;
-  asm("{\n\t.reg .b8 b0;\n\tcvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\tcvt.u32.u8 %0, b0;\n\t}\n" : "=r"(r) : "f"(lo), "f"(hi));
-  return r & 0xffu;
-}
-__device__ __forceinline__ float2 e2m1x2_to_f32(uint32_t c) {
-  uint32_t h;
-  asm("{\n\t.reg .b8 b0;\n\tcvt.u8.u32 b0, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, b0;\n\t}\n" : "=r"(h) : "r"(c));
-  return __half22float2(*reinterpret_cast<__half2*>(&h));
-}
-// eight values -> four bytes of e2m1 codes (low nibble = first element of each pair)
-__device__ __forceinline__ uint32_t f32x8_to_e2m1(const float* v) {
-  return f32x2_to_e2m1x2(v[0], v[1]) | (f32x2_to_e2m1x2(v[2], v[3]) << 8) | (f32x2_to_e2m1x2(v[4], v[5]) << 16) |
-         (f32x2_to_e2m1x2(v[6], v[7]) << 24);
-}
-__device__ __forceinline__ void e2m1x8_to_f32(uint32_t w, float* o) {
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 f = e2m1x2_to_f32((w >> (8 * i)) & 0xffu);
-    o[2 * i] = f.x;
-    o[2 * i + 1] = f.y;
-  }
-}
-
-// Quantise one 16-element block (values in r, consumed) of row n, block index b, into the four terms.
-__device__ __forceinline__ void quant_block(float* r, float g, int n, int b, uint8_t* __restrict__ bq, int ldb,
-                                            uint8_t* __restrict__ sfb) {
-  const int slab = b >> 4, step = (b & 15) >> 2, kb = b & 3;
-  float gt = g;
-#pragma unroll
-  for (int t = 0; t < TERMS; ++t) {
-    float bmax = 0.f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(r[i]));
-    const uint8_t sc = f32_to_e4m3(bmax / (6.0f * gt));
-    const float s = e4m3_to_f32(sc) * gt;
-    const float inv = s > 0.f ? 1.0f / s : 0.f;
-    float v[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = r[i] * inv;
-    const uint32_t w0 = f32x8_to_e2m1(v), w1 = f32x8_to_e2m1(v + 8);
-    float d[16];
-    e2m1x8_to_f32(w0, d);
-    e2m1x8_to_f32(w1, d + 8);
-#pragma unroll
-    for (int i = 0; i < 16; ++i) r[i] = fmaf(-d[i], s, r[i]);
-    const int row = t * 16 + n;
-    *reinterpret_cast<uint2*>(bq + (size_t)row * ldb + b * 8) = make_uint2(w0, w1);
-    sfb[(size_t)slab * SF_BYTES + step * 512 + (row & 31) * 16 + (row >> 5) * 4 + kb] = sc;
-    gt *= 0.125f;
-  }
-}
-
-__device__ __forceinline__ float block_max(float v, float* red) {
-  v = warp_max(v);
-  __syncthreads();
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
-  __syncthreads();
-  float t = (threadIdx.x & 31) < ((blockDim.x + 31) >> 5) ? red[threadIdx.x & 31] : 0.f;
-  return warp_max(t);
-}
+using namespace vg::aq;
 
 constexpr int MAXB = 3;     // 16-element blocks a thread may hold
 
 // mode 0: x is the f16 row.  mode 1: SwiGLU of a bf16 [gate | up] row.  Both: quantise to FP4 terms.
 template <int MODE>
-__global__ void __launch_bounds__(1024) act_quant_kernel(const void* __restrict__ xin, int ldx, int K, int Kpad,
+__global__ void __launch_bounds__(512) act_quant_kernel(const void* __restrict__ xin, int ldx, int K, int Kpad,
                                                           uint8_t* __restrict__ bq, int ldb, uint8_t* __restrict__ sfb,
                                                           float* __restrict__ g0, __half* __restrict__ out16) {
   __shared__ float red[32];
-  const int n = blockIdx.x;
+  if (threadIdx.x == 0) trace(32);
+  pdl_trigger();
+  pdl_wait();
+  if (threadIdx.x == 0) trace(33);
+  // a cluster of gridDim.x CTAs shares one row: CTA c owns blocks [c * bpc, (c + 1) * bpc)
+  __shared__ float cl_amax;
+  const int n = blockIdx.y, C = gridDim.x, c = blockIdx.x;
   const int nblk = Kpad >> 4;
+  const int bpc = (nblk + C - 1) / C;
+  const int b_end = min(nblk, (c + 1) * bpc);
   float r[MAXB][16];
   float amax = 0.f;
 #pragma unroll
   for (int j = 0; j < MAXB; ++j) {
-    const int b = threadIdx.x + j * blockDim.x;
-    if (b < nblk) {
+    const int b = c * bpc + threadIdx.x + j * blockDim.x;
+    if (b < b_end) {
       const int k0 = b * 16;
       if (k0 + 16 <= K) {
         if (MODE == 0) {
@@ -163,22 +99,42 @@ __global__ void __launch_bounds__(1024) act_quant_kernel(const void* __restrict_
     }
   }
   amax = block_max(amax, red);
+  if (C > 1) {
+    if (threadIdx.x == 0) cl_amax = amax;
+    cluster_sync_all();
+    const uint32_t a = smem_u32(&cl_amax);
+    for (int q = 0; q < C; ++q) amax = fmaxf(amax, dsmem_ld_f32(dsmem_map(a, (uint32_t)q)));
+  }
   const float g = amax > 0.f ? amax / (6.0f * 448.0f) : 1.0f;
-  if (threadIdx.x == 0) g0[n] = g;
+  if (threadIdx.x == 0 && c == 0) g0[n] = g;
 #pragma unroll
   for (int j = 0; j < MAXB; ++j) {
-    const int b = threadIdx.x + j * blockDim.x;
-    if (b < nblk) quant_block(r[j], g, n, b, bq, ldb, sfb);
+    const int b = c * bpc + threadIdx.x + j * blockDim.x;
+    if (b < b_end) quant_block(r[j], g, n, b, bq, ldb, sfb);
   }
+  if (C > 1) cluster_sync_all();          // peers may still be reading cl_amax
+  if (threadIdx.x == 0) trace(2 * 16 + 2);
 }
 
 // residual += delta; y = rmsnorm(residual) * (1 + w); emit y as FP4 terms (and optionally as f16).
-__global__ void __launch_bounds__(1024) add_rmsnorm_fp4_kernel(__nv_bfloat16* res, const __nv_bfloat16* delta, const float* w,
+__global__ void __launch_bounds__(512) add_rmsnorm_fp4_kernel(__nv_bfloat16* res, const __nv_bfloat16* delta, const float* w,
                                                                 int h, float eps, int plus_one, int ld_res, int ld_delta,
                                                                 int Kpad, uint8_t* __restrict__ bq, int ldb,
                                                                 uint8_t* __restrict__ sfb, float* __restrict__ g0,
                                                                 __half* __restrict__ out16) {
   __shared__ float red[32];
+  if (threadIdx.x == 0) trace(16);
+  pdl_trigger();
+  // the norm weights do not depend on the preceding kernel: fetch the first block's before waiting for it
+  float4 w0[4];
+  {
+    const int hb = h >> 4;
+    const float4* wp = reinterpret_cast<const float4*>(w + (size_t)min((int)threadIdx.x, hb - 1) * 16);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w0[i] = wp[i];
+  }
+  pdl_wait();
+  if (threadIdx.x == 0) trace(17);
   const int n = blockIdx.x;
   __nv_bfloat16* rp = res + (size_t)n * ld_res;
   const __nv_bfloat16* dp = delta ? delta + (size_t)n * ld_delta : nullptr;
@@ -227,7 +183,7 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_fp4_kernel(__nv_bfloat16* re
       __half* h1 = reinterpret_cast<__half*>(&o1);
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const float wv = w[b * 16 + i];
+        const float wv = j == 0 ? reinterpret_cast<const float*>(w0)[i] : w[b * 16 + i];
         // round through f16 so both outputs describe the same values
         const __half y = f32_to_f16_sat(r[j][i] * inv * (plus_one ? 1.0f + wv : wv));
         if (i < 8) h0[i] = y; else h1[i - 8] = y;
@@ -245,12 +201,19 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_fp4_kernel(__nv_bfloat16* re
     const int b = threadIdx.x + j * blockDim.x;
     if (b < nblk) quant_block(r[j], g, n, b, bq, ldb, sfb);
   }
+  if (threadIdx.x == 0) trace(1 * 16 + 2);
 }
 
+constexpr int MAX_THREADS = 512;
 int threads_for(int nblk) {
   int t = (nblk + 31) / 32 * 32;
-  if (t > 1024) t = (((nblk + MAXB - 1) / MAXB) + 31) / 32 * 32;
+  if (t > MAX_THREADS) t = (((nblk + MAXB - 1) / MAXB) + 31) / 32 * 32;
   return t < 32 ? 32 : t;
+}
+// CTAs per row for the stand-alone quantisers: about 128 blocks per CTA, at most a portable cluster.
+int cluster_for(int nblk) {
+  int c = (nblk + 127) / 128;
+  return c < 1 ? 1 : (c > 8 ? 8 : c);
 }
 
 }  // namespace
@@ -259,20 +222,20 @@ int threads_for(int nblk) {
 extern "C" int vg_act_quant_fp4(const void* x_f16, int ldx, int N, int K, void* bq, int ldb, void* sfb, float* g0,
                                 cudaStream_t st) {
   const int Kpad = ldb * 2;
-  if (N < 1 || N > 16 || (ldb % 128) != 0 || Kpad < K || (K % 8) != 0 || (ldx % 8) != 0 || (Kpad >> 4) > 1024 * MAXB) return -2;
-  act_quant_kernel<0><<<N, threads_for(Kpad >> 4), 0, st>>>(x_f16, ldx, K, Kpad, static_cast<uint8_t*>(bq), ldb,
-                                                            static_cast<uint8_t*>(sfb), g0, nullptr);
-  return (int)cudaGetLastError();
+  if (N < 1 || N > 16 || (ldb % 128) != 0 || Kpad < K || (K % 8) != 0 || (ldx % 8) != 0 || (Kpad >> 4) > MAX_THREADS * MAXB) return -2;
+  const int C = cluster_for(Kpad >> 4), bpc = ((Kpad >> 4) + C - 1) / C;
+  return (int)launch_pdl_cluster(act_quant_kernel<0>, dim3(C, N), dim3(threads_for(bpc)), (unsigned)C, 0, st, x_f16, ldx, K,
+                                 Kpad, static_cast<uint8_t*>(bq), ldb, static_cast<uint8_t*>(sfb), g0, (__half*)nullptr);
 }
 
 // gu [N, 2*I] bf16 (row stride ld) -> SwiGLU -> FP4 terms (and f16 copy when out16 != null, [N, I] contiguous).
 extern "C" int vg_swiglu_fp4(const void* gu, int ld, int N, int I, void* bq, int ldb, void* sfb, float* g0, void* out16,
                              cudaStream_t st) {
   const int Kpad = ldb * 2;
-  if (N < 1 || N > 16 || (ldb % 128) != 0 || Kpad < I || (I % 8) != 0 || (ld % 8) != 0 || (Kpad >> 4) > 1024 * MAXB) return -2;
-  act_quant_kernel<1><<<N, threads_for(Kpad >> 4), 0, st>>>(gu, ld, I, Kpad, static_cast<uint8_t*>(bq), ldb,
-                                                            static_cast<uint8_t*>(sfb), g0, static_cast<__half*>(out16));
-  return (int)cudaGetLastError();
+  if (N < 1 || N > 16 || (ldb % 128) != 0 || Kpad < I || (I % 8) != 0 || (ld % 8) != 0 || (Kpad >> 4) > MAX_THREADS * MAXB) return -2;
+  const int C = cluster_for(Kpad >> 4), bpc = ((Kpad >> 4) + C - 1) / C;
+  return (int)launch_pdl_cluster(act_quant_kernel<1>, dim3(C, N), dim3(threads_for(bpc)), (unsigned)C, 0, st, gu, ld, I, Kpad,
+                                 static_cast<uint8_t*>(bq), ldb, static_cast<uint8_t*>(sfb), g0, static_cast<__half*>(out16));
 }
 
 extern "C" int vg_add_rmsnorm_fp4(void* res, const void* delta, const float* w, int N, int h, float eps, int plus_one,
@@ -280,11 +243,12 @@ extern "C" int vg_add_rmsnorm_fp4(void* res, const void* delta, const float* w, 
                                   cudaStream_t st) {
   const int Kpad = ldb * 2;
   if (N < 1 || N > 16 || (ldb % 128) != 0 || Kpad < h || (h % 16) != 0 || (ld_res % 8) != 0 || (ld_delta % 8) != 0 ||
-      (Kpad >> 4) > 1024 * MAXB)
+      (Kpad >> 4) > MAX_THREADS * MAXB)
     return -2;
-  add_rmsnorm_fp4_kernel<<<N, threads_for(Kpad >> 4), 0, st>>>(static_cast<__nv_bfloat16*>(res),
-                                                               static_cast<const __nv_bfloat16*>(delta), w, h, eps, plus_one,
-                                                               ld_res, ld_delta, Kpad, static_cast<uint8_t*>(bq), ldb,
-                                                               static_cast<uint8_t*>(sfb), g0, static_cast<__half*>(out16));
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(add_rmsnorm_fp4_kernel, dim3(N), dim3(threads_for(Kpad >> 4)), 0, st,
+                         static_cast<__nv_bfloat16*>(res), static_cast<const __nv_bfloat16*>(delta), w, h, eps, plus_one,
+                         ld_res, ld_delta, Kpad, static_cast<uint8_t*>(bq), ldb, static_cast<uint8_t*>(sfb), g0,
+                         static_cast<__half*>(out16));
 }
+
+VG_TRACE_SETTER(vg_trace_set_act_quant)

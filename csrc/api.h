@@ -25,6 +25,20 @@ typedef struct VgCommCtx {
   unsigned long long timeout_ns;
 } VgCommCtx;
 
+// Optional epilogue of the decode-width GEMM that produces the GatedDeltaNet input projection: rows below
+// conv_dim are conv channels, and the thread that owns a row runs the depthwise causal conv + SiLU for every
+// column and updates the rolling conv state, so no separate conv kernel is needed
+// (column bookkeeping as in vg_gdn_conv).
+typedef struct VgConvEpi {
+  float* state;              // [slot][conv_dim][ck]
+  const float* w;            // [conv_dim][ck]
+  const int* in_slot;
+  const int* parent;
+  const int* out_slot;
+  float* out;                // [N][conv_dim] fp32
+  int conv_dim, ck;
+} VgConvEpi;
+
 int vg_gemm_tc(const void* wt, const float* row_scale, const void* x_f16, int x_rows, int ldx, void* out, int out_f32,
                int M, int K, int N, int ldo, int wfmt, int splitk, int* err, const VgCommCtx* ar_ctx,
                cudaStream_t stream);
@@ -34,7 +48,8 @@ int vg_swiglu_fp4(const void* gu, int ld, int N, int I, void* bq, int ldb, void*
 int vg_add_rmsnorm_fp4(void* res, const void* delta, const float* w, int N, int h, float eps, int plus_one, int ld_res,
                        int ld_delta, void* bq, int ldb, void* sfb, float* g0, void* out16, cudaStream_t stream);
 int vg_gemm_fp4(const void* wt, const float* row_scale, const void* bq, int ldb, const void* sfb, const float* g0, void* out,
-                int out_f32, int M, int K, int N, int ldo, int splitk, int* err, const VgCommCtx* ar_ctx, cudaStream_t stream);
+                int out_f32, int M, int K, int N, int ldo, int splitk, int* err, const VgCommCtx* ar_ctx,
+                const VgConvEpi* conv, cudaStream_t stream);
 int vg_gemm_tc_grouped(const void* wt, const float* row_scale, const void* x_f16, int x_rows, int ldx, void* out, int out_f32,
                        int M, int K, int ldo, int wfmt, int bn, int max_items, const int* g_exp, const int* g_off,
                        const int* g_cnt, const int* tilemap, const int* n_items, int x_div, int* err, cudaStream_t stream);
@@ -61,10 +76,10 @@ long long vg_attn_scratch_floats(int N, int nh, int hd, int ns_grid);
 
 int vg_gdn_conv(const void* x, int ldx, float* state, const float* w, const int* in_slot, const int* parent,
                 const int* out_slot, float* out, int N, int conv_dim, int ck, int phase, cudaStream_t stream);
-int vg_gdn_step(const float* qkv, const void* proj, int ldp, int off_z, int off_b, int off_a, float* S,
-                const float* A_log, const float* dt_bias, const float* norm_w, const int* chain_start,
-                const int* chain_len, int n_chains, const int* in_slot, const int* parent, const int* out_slot,
-                void* out_f16, int nk, int nv, int kd, int vd, float eps, cudaStream_t stream);
+int vg_gdn_step(const float* qkv, const void* proj, int ldp, int off_z, int off_b, int off_a, float* S, const float* A_log,
+                const float* dt_bias, const float* norm_w, const int* chain_start, const int* chain_len, int n_chains,
+                const int* in_slot, const int* parent, const int* out_slot, void* out_f16, int nk, int nv, int kd, int vd,
+                float eps, void* bq, int ldb, void* sfb, float* g0, unsigned int* col_ctr, cudaStream_t stream);
 
 int vg_argmax(const float* logits, int N, int V, int ld, int* out, float* out_val, int idx_offset, cudaStream_t stream);
 int vg_penalty(float* logits, int N, int V, int ld, const int* toks, const int* counts, const int* n_toks, int max_toks,

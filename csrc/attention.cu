@@ -35,6 +35,8 @@ __global__ void __launch_bounds__(NW * 32) attn_split_kernel(
     const int* __restrict__ lens, const int* __restrict__ slots, const int* __restrict__ base,
     const int* __restrict__ path, int path_ld, float* __restrict__ part, int nh, int nkv, int max_seq, int ns_grid,
     float scale, int direct, const __nv_bfloat16* __restrict__ gate, int ld_gate, int gate_off, __half* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int DPL = HD / 32;              // dims per lane
   const int col = blockIdx.x;
   const int G = nh / nkv;
@@ -143,6 +145,8 @@ __global__ void __launch_bounds__(NW * 32) attn_split_kernel(
 template <int HD>
 __global__ void attn_merge_kernel(const float* __restrict__ part, const int* __restrict__ lens, int nh, int ns_grid,
                                   const __nv_bfloat16* __restrict__ gate, int ld_gate, __half* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   const int col = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
   const int ns = splits_for(lens[col]);
   const float* pp = part + ((size_t)col * nh + head) * ns_grid * (HD + 2);
@@ -167,7 +171,7 @@ int launch_split(const void* q, const void* kc, const void* vc, const int* lens,
                  const void* gate, int ld_gate, void* out, cudaStream_t st) {
   const int G = nh / nkv;
   dim3 grid(N, nkv * (G / GT), direct ? 1 : ns_grid);
-  attn_split_kernel<HD, GT><<<grid, NW * 32, 0, st>>>(
+  launch_pdl(attn_split_kernel<HD, GT>, dim3(grid), dim3(NW * 32), 0, st, 
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(kc),
       static_cast<const __nv_bfloat16*>(vc), lens, slots, base, path, path_ld, part, nh, nkv, max_seq, ns_grid,
       rsqrtf((float)HD), direct, static_cast<const __nv_bfloat16*>(gate), ld_gate, HD, static_cast<__half*>(out));
@@ -214,9 +218,9 @@ extern "C" int vg_attn_decode(const void* q, const void* kc, const void* vc, con
   if (rc || direct) return rc;
   dim3 grid(N, nh);
   switch (hd) {
-    case 64: attn_merge_kernel<64><<<grid, 64, 0, st>>>(part, lens, nh, ns_grid, static_cast<const __nv_bfloat16*>(gate), ld_gate, static_cast<__half*>(out)); break;
-    case 128: attn_merge_kernel<128><<<grid, 128, 0, st>>>(part, lens, nh, ns_grid, static_cast<const __nv_bfloat16*>(gate), ld_gate, static_cast<__half*>(out)); break;
-    case 256: attn_merge_kernel<256><<<grid, 256, 0, st>>>(part, lens, nh, ns_grid, static_cast<const __nv_bfloat16*>(gate), ld_gate, static_cast<__half*>(out)); break;
+    case 64: launch_pdl(attn_merge_kernel<64>, dim3(grid), dim3(64), 0, st, part, lens, nh, ns_grid, static_cast<const __nv_bfloat16*>(gate), ld_gate, static_cast<__half*>(out)); break;
+    case 128: launch_pdl(attn_merge_kernel<128>, dim3(grid), dim3(128), 0, st, part, lens, nh, ns_grid, static_cast<const __nv_bfloat16*>(gate), ld_gate, static_cast<__half*>(out)); break;
+    case 256: launch_pdl(attn_merge_kernel<256>, dim3(grid), dim3(256), 0, st, part, lens, nh, ns_grid, static_cast<const __nv_bfloat16*>(gate), ld_gate, static_cast<__half*>(out)); break;
   }
   return (int)cudaGetLastError();
 }

@@ -7,6 +7,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <utility>
 
 #define VG_DEVINL __device__ __forceinline__
 
@@ -233,6 +235,80 @@ VG_DEVINL float block_sum(float v, float* red) {
   float t = (lane < nw) ? red[lane] : 0.0f;
   t = warp_sum(t);
   return t;
+}
+
+// ---------------------------------------------------------------- device timeline (builds with -DVG_TRACE only)
+// trace(code) appends (global nanosecond timer, code, blockIdx.x) to a host-provided buffer; buffer word 0 is
+// the record counter. Each translation unit has its own pointer, set through the setter VG_TRACE_SETTER
+// defines. Without -DVG_TRACE both compile to nothing.
+#ifdef VG_TRACE
+static __device__ unsigned long long* vg_trace_buf = nullptr;
+static __device__ unsigned int vg_trace_cap = 0;
+VG_DEVINL void trace(int code) {
+  unsigned long long* b = vg_trace_buf;
+  if (!b) return;
+  const unsigned i = atomicAdd(reinterpret_cast<unsigned int*>(b), 1u);
+  if (i < vg_trace_cap) {
+    b[1 + 2 * i] = global_ns();
+    b[2 + 2 * i] = ((unsigned long long)blockIdx.x << 32) | ((unsigned long long)blockIdx.z << 16) | (unsigned)code;
+  }
+}
+#define VG_TRACE_SETTER(fn)                                            \
+  extern "C" int fn(void* buf, unsigned cap) {                         \
+    cudaError_t e = cudaMemcpyToSymbol(vg_trace_buf, &buf, sizeof(buf)); \
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(vg_trace_cap, &cap, sizeof(cap)); \
+    return (int)e;                                                     \
+  }
+#else
+VG_DEVINL void trace(int) {}
+#define VG_TRACE_SETTER(fn) \
+  extern "C" int fn(void*, unsigned) { return -1; }
+#endif
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched through launch_pdl may start while its predecessor in the stream is still running.
+// Every such kernel executes pdl_wait() before it reads anything a predecessor wrote or writes anything a
+// predecessor may still read (it returns at once when there is no programmatic dependency), so completion of
+// a kernel implies completion of all earlier ones. pdl_trigger() lets the successor be scheduled as soon as
+// every CTA of this grid has started; work that does not depend on the predecessor (streaming weights into
+// shared memory, barrier and TMEM setup) then overlaps the predecessor's tail.
+VG_DEVINL void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+VG_DEVINL void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool pdl_on() {
+  static const bool on = [] { const char* e = getenv("VELO_NO_PDL"); return !(e && e[0] == '1'); }();
+  return on;
+}
+// `cluster_x` > 1 launches thread-block clusters of that many CTAs along x (grid.x must be a multiple).
+template <typename... KA, typename... A>
+inline cudaError_t launch_pdl_cluster(void (*kernel)(KA...), dim3 grid, dim3 block, unsigned cluster_x, size_t smem,
+                                      cudaStream_t st, A&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (cluster_x > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = cluster_x;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  if (pdl_on()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<A>(args)...);
+}
+template <typename... KA, typename... A>
+inline cudaError_t launch_pdl(void (*kernel)(KA...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, A&&... args) {
+  return launch_pdl_cluster(kernel, grid, block, 1u, smem, st, std::forward<A>(args)...);
 }
 
 }  // namespace vg

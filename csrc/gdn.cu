@@ -16,6 +16,7 @@
 // no cross-thread reduction. State layout [slot][nv][kd][vd] fp32; conv state [slot][conv_dim][ck] fp32
 // with the newest sample last.
 #include "common.cuh"
+#include "act_quant.cuh"
 #include "api.h"
 
 namespace {
@@ -27,6 +28,10 @@ __global__ void gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, fl
                                 const float* __restrict__ w, const int* __restrict__ in_slot,
                                 const int* __restrict__ parent, const int* __restrict__ out_slot,
                                 float* __restrict__ out, int N, int conv_dim, int ck, int phase) {
+  if (threadIdx.x == 0) trace(80);
+  pdl_trigger();
+  pdl_wait();
+  if (threadIdx.x == 0) trace(81);
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (size_t)N * conv_dim) return;
   const int t = (int)(idx / conv_dim), c = (int)(idx % conv_dim);
@@ -58,22 +63,36 @@ __global__ void __launch_bounds__(VD) gdn_step_kernel(
     float* __restrict__ S, const float* __restrict__ A_log, const float* __restrict__ dt_bias,
     const float* __restrict__ norm_w, const int* __restrict__ chain_start, const int* __restrict__ chain_len,
     const int* __restrict__ in_slot, const int* __restrict__ parent, const int* __restrict__ out_slot,
-    __half* __restrict__ out, int nk, int nv, float eps) {
+    __half* __restrict__ out, int nk, int nv, float eps, uint8_t* __restrict__ bq, int ldb, uint8_t* __restrict__ sfb,
+    float* __restrict__ g0, unsigned int* __restrict__ col_ctr) {
+  if (threadIdx.x == 0) trace(96);
+  pdl_trigger();
   __shared__ float red[32];
   __shared__ __align__(16) float ks[KD];
   __shared__ __align__(16) float qs[KD];
+  __shared__ int is_last;
   const int vh = blockIdx.x, chain = blockIdx.y, j = threadIdx.x;
   const int kh = vh * nk / nv;
   const int key_dim = nk * KD, conv_dim = 2 * key_dim + nv * VD;
+  // Per-head constants, the column bookkeeping (uploaded at the start of the step) and the lane's input state
+  // (last written by the previous step) do not depend on the preceding kernel: fetch them before waiting for it.
   const int t0 = chain_start[chain], tn = chain_len[chain];
   const float a_coef = -__expf(A_log[vh]);
   const float dtb = dt_bias[vh];
   const float nw = norm_w[j];
   float s[KD];
   int loaded_from = -2;      // column whose output state is in registers (-2: nothing)
+  const bool preloaded = tn > 0 && parent[t0] < 0;
+  if (preloaded) {
+    const float* sp = S + (((size_t)in_slot[t0] * nv + vh) * KD) * VD + j;
+#pragma unroll
+    for (int a = 0; a < KD; ++a) s[a] = sp[(size_t)a * VD];
+  }
+  pdl_wait();
+  if (threadIdx.x == 0) trace(97);
   for (int t = t0; t < t0 + tn; ++t) {
     const int par = parent[t];
-    if (t == t0 || par != loaded_from) {
+    if (t == t0 ? !preloaded : par != loaded_from) {
       const int src = par < 0 ? in_slot[t] : out_slot[par];
       const float* sp = S + (((size_t)src * nv + vh) * KD) * VD + j;
 #pragma unroll
@@ -131,8 +150,55 @@ __global__ void __launch_bounds__(VD) gdn_step_kernel(
       for (int a = 0; a < KD; ++a) dp[(size_t)a * VD] = s[a];
     }
     loaded_from = t;
+    if (bq) {
+      // The head that completes column t quantises the whole row for the output projection (FP4 series), so
+      // no separate quantiser kernel runs. Heads publish with a fence + counter; the last one reads through L2.
+      __threadfence();
+      __syncthreads();
+      if (j == 0) is_last = atomicAdd(&col_ctr[t], 1u) == (unsigned)nv - 1u;
+      __syncthreads();
+      if (is_last) {
+        __threadfence();
+        const int K = nv * VD, nblk = ldb >> 3;          // ldb bytes per row = Kpad / 2
+        const __half* row16 = out + (size_t)t * K;
+        float amax = 0.f;
+        for (int b = j; b * 16 < K; b += VD) {
+          const uint4 u0 = __ldcg(reinterpret_cast<const uint4*>(row16 + b * 16));
+          const uint4 u1 = __ldcg(reinterpret_cast<const uint4*>(row16 + b * 16) + 1);
+          const __half2* h0 = reinterpret_cast<const __half2*>(&u0);
+          const __half2* h1 = reinterpret_cast<const __half2*>(&u1);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 a = __half22float2(h0[i]), c = __half22float2(h1[i]);
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(c.x), fabsf(c.y))));
+          }
+        }
+        amax = aq::block_max(amax, red);
+        const float gq = amax > 0.f ? amax / (6.0f * 448.0f) : 1.0f;
+        if (j == 0) { g0[t] = gq; col_ctr[t] = 0; }
+        for (int b = j; b < nblk; b += VD) {
+          float r[16];
+          if (b * 16 < K) {
+            const uint4 u0 = __ldcg(reinterpret_cast<const uint4*>(row16 + b * 16));
+            const uint4 u1 = __ldcg(reinterpret_cast<const uint4*>(row16 + b * 16) + 1);
+            const __half2* h0 = reinterpret_cast<const __half2*>(&u0);
+            const __half2* h1 = reinterpret_cast<const __half2*>(&u1);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 a = __half22float2(h0[i]), c = __half22float2(h1[i]);
+              r[2 * i] = a.x; r[2 * i + 1] = a.y; r[8 + 2 * i] = c.x; r[8 + 2 * i + 1] = c.y;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) r[i] = 0.f;
+          }
+          aq::quant_block(r, gq, t, b, bq, ldb, sfb);
+        }
+      }
+    }
     __syncthreads();   // qs/ks are rewritten by the next column
   }
+  if (threadIdx.x == 0) trace(6 * 16 + 2);
 }
 
 }  // namespace
@@ -142,24 +208,33 @@ extern "C" int vg_gdn_conv(const void* x, int ldx, float* state, const float* w,
   if (N <= 0) return 0;
   if (ck > MAX_CK) return -2;
   const size_t total = (size_t)N * conv_dim;
-  gdn_conv_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), ldx, state, w,
+  launch_pdl(gdn_conv_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(x), ldx, state, w,
                                                                    in_slot, parent, out_slot, out, N, conv_dim, ck, phase);
   return (int)cudaGetLastError();
 }
 
+// bq / sfb / g0 / col_ctr (all or none): also emit each column's output row as the FP4 activation series for
+// the output projection; col_ctr is a zero-initialised counter per column that the kernel leaves zeroed.
+// Needs column index < 16, (nv * vd) % 16 == 0 and ldb * 2 >= nv * vd with ldb % 128 == 0.
 extern "C" int vg_gdn_step(const float* qkv, const void* proj, int ldp, int off_z, int off_b, int off_a, float* S,
                            const float* A_log, const float* dt_bias, const float* norm_w, const int* chain_start,
                            const int* chain_len, int n_chains, const int* in_slot, const int* parent, const int* out_slot,
-                           void* out_f16, int nk, int nv, int kd, int vd, float eps, cudaStream_t st) {
+                           void* out_f16, int nk, int nv, int kd, int vd, float eps, void* bq, int ldb, void* sfb,
+                           float* g0, unsigned int* col_ctr, cudaStream_t st) {
   if (n_chains <= 0) return 0;
+  if (bq && (!sfb || !g0 || !col_ctr || (ldb % 128) != 0 || ldb * 2 < nv * vd || ((nv * vd) % 16) != 0)) return -2;
   dim3 grid(nv, n_chains);
   const __nv_bfloat16* pj = static_cast<const __nv_bfloat16*>(proj);
   __half* o = static_cast<__half*>(out_f16);
+  uint8_t* bqp = static_cast<uint8_t*>(bq);
+  uint8_t* sfp = static_cast<uint8_t*>(sfb);
   if (kd == 128 && vd == 128)
-    gdn_step_kernel<128, 128><<<grid, 128, 0, st>>>(qkv, pj, ldp, off_z, off_b, off_a, S, A_log, dt_bias, norm_w, chain_start, chain_len, in_slot, parent, out_slot, o, nk, nv, eps);
+    launch_pdl(gdn_step_kernel<128, 128>, dim3(grid), dim3(128), 0, st, qkv, pj, ldp, off_z, off_b, off_a, S, A_log, dt_bias, norm_w, chain_start, chain_len, in_slot, parent, out_slot, o, nk, nv, eps, bqp, ldb, sfp, g0, col_ctr);
   else if (kd == 64 && vd == 64)
-    gdn_step_kernel<64, 64><<<grid, 64, 0, st>>>(qkv, pj, ldp, off_z, off_b, off_a, S, A_log, dt_bias, norm_w, chain_start, chain_len, in_slot, parent, out_slot, o, nk, nv, eps);
+    launch_pdl(gdn_step_kernel<64, 64>, dim3(grid), dim3(64), 0, st, qkv, pj, ldp, off_z, off_b, off_a, S, A_log, dt_bias, norm_w, chain_start, chain_len, in_slot, parent, out_slot, o, nk, nv, eps, bqp, ldb, sfp, g0, col_ctr);
   else
     return -3;
   return (int)cudaGetLastError();
 }
+
+VG_TRACE_SETTER(vg_trace_set_gdn)

@@ -54,10 +54,14 @@ struct Fp4Params {
   int M, N, ldo, ks_total, out_f32;
   int* err;
   int ar;
+  int has_conv;
+  VgConvEpi conv;
   VgCommCtx comm;
 };
 
 constexpr int SMEM_TOTAL = NS * STAGE + (2 * NS + 1) * 8 + 16 + 1024;
+constexpr int CONV_MAX_CK = 4;            // taps the fused conv epilogue supports
+constexpr int CONV_SMEM = 16 * (CONV_MAX_CK - 1) * BM * 4;   // prefetched state samples, appended after SMEM_TOTAL
 
 // instruction descriptor for kind::mxf4nvf4, e2m1 x e2m1, ue4m3 scales, K = 64, both operands K-major
 __device__ __forceinline__ constexpr uint32_t idesc_fp4(int m, int n) {
@@ -116,7 +120,8 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
   const int nks = ks1 - ks0;
   const int rot = nks > 0 ? (int)(((unsigned)mt * 7u + (unsigned)z * 3u) % (unsigned)nks) : 0;
   auto slab_of = [&](int i) { int k = i + rot; return ks0 + (k >= nks ? k - nks : k); };
-  const uint32_t ar_epoch = p.ar ? *p.comm.epoch + 1 : 0;
+  if (threadIdx.x == 0) trace(4 * 16);
+  pdl_trigger();
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NS; ++i) { mbar_init(&full[i], 2); mbar_init(&empty[i], 1); }
@@ -133,19 +138,26 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) trace(4 * 16 + 5);
 
   if (warp == 0) {
     if (lane == 0) {
+      // Weights do not depend on the preceding kernel: the ring fills before that kernel has finished (the
+      // activation producer and the epilogue do the waiting). Asking L2 for further slabs ahead of time with
+      // bulk prefetches measured slower at every depth, so only the ring runs ahead.
+      const uint8_t* wbase = p.wt + (size_t)mt * p.ks_total * (A_BYTES + SF_BYTES);
       for (int i = 0; i < nks && !*abort_flag; ++i) {
         const int s = i % NS;
         if (!mbar_wait(&empty[s], ((i / NS) & 1) ^ 1)) { fail(p.err, VG_ERR_EMPTY_WAIT, abort_flag); break; }
         uint8_t* st = smem + (size_t)s * STAGE;
         mbar_arrive_expect_tx(&full[s], A_BYTES + SF_BYTES);
-        tma_bulk_g2s(st, p.wt + ((size_t)mt * p.ks_total + slab_of(i)) * (A_BYTES + SF_BYTES), A_BYTES + SF_BYTES, &full[s]);
+        tma_bulk_g2s(st, wbase + (size_t)slab_of(i) * (A_BYTES + SF_BYTES), A_BYTES + SF_BYTES, &full[s]);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
+      pdl_wait();                          // the activation series comes from the preceding kernel
+      trace(4 * 16 + 1);
       for (int i = 0; i < nks && !*abort_flag; ++i) {
         const int s = i % NS;
         if (!mbar_wait(&empty[s], ((i / NS) & 1) ^ 1)) { fail(p.err, VG_ERR_EMPTY_WAIT, abort_flag); break; }
@@ -167,6 +179,7 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
       for (int i = me; i < nks && !*abort_flag; i += 2, ++mine) {
         const int s = i % NS;
         if (!mbar_wait(&full[s], (i / NS) & 1)) { fail(p.err, VG_ERR_TMA_WAIT, abort_flag); ok = false; break; }
+        if (i == 0) trace(4 * 16 + 3);
         tc_fence_after();
         const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE);
         const uint32_t sfa_addr = a_addr + A_BYTES;
@@ -196,8 +209,31 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
   const int m_local = q * 32 + lane;
   float y[16];
   bool have = false;
+  uint32_t ar_epoch = 0;
+  // fused conv: state samples and taps of this thread's channel, fetched while the main loop runs
+  const bool conv_row = epi && p.has_conv && mt * BM + m_local < p.conv.conv_dim && z == 0;
+  float* conv_pre = reinterpret_cast<float*>(smem + SMEM_TOTAL - 1024);      // [16][CONV_MAX_CK - 1][BM]
+  float wk[CONV_MAX_CK];
+  uint32_t n_state = 0;                    // 2 bits per column: samples that come from the rolling state
   if (epi) {
+    pdl_wait();                            // before g0 / epoch reads and every output write
+    ar_epoch = p.ar ? *p.comm.epoch + 1 : 0;
+    if (conv_row) {
+      const VgConvEpi& cv = p.conv;
+      const int ck = cv.ck, ch = mt * BM + m_local;
+#pragma unroll
+      for (int i = 0; i < CONV_MAX_CK; ++i) wk[i] = i < ck ? cv.w[(size_t)ch * ck + i] : 0.f;
+      for (int t = 0; t < p.N; ++t) {
+        int cur = t, j = ck - 1;
+        for (; j >= 0 && cur >= 0; --j) cur = cv.parent[cur];
+        const int d = ck - 1 - j;
+        const float* st = cv.state + ((size_t)cv.in_slot[t] * cv.conv_dim + ch) * ck;
+        for (int jj = j; jj >= 0; --jj) conv_pre[(t * (CONV_MAX_CK - 1) + jj) * BM + m_local] = st[jj + d];
+        n_state |= (uint32_t)(j + 1) << (2 * t);
+      }
+    }
     if (mbar_wait(acc_full, 0)) {
+      if (threadIdx.x == 128) trace(4 * 16 + 4);
       tc_fence_after();
 #pragma unroll
       for (int n = 0; n < 16; ++n) y[n] = 0.f;
@@ -285,12 +321,42 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
     }
   } else if (epi && have && z == 0 && m < p.M) {
     const float rsc = p.row_scale ? p.row_scale[m] : 1.0f;
+    float* xs = reinterpret_cast<float*>(smem) + 16 * BM;     // second half of idle stage 0: [n][row] samples
 #pragma unroll
     for (int n = 0; n < 16; ++n) {
       if (n < p.N) {
         const float v = y[n] * p.g0[n] * rsc;
         if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)n * p.ldo + m] = v;
         else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)n * p.ldo + m] = __float2bfloat16_rn(v);
+        if (conv_row) xs[n * BM + m_local] = __bfloat162float(__float2bfloat16_rn(v));   // what a reader of `out` sees
+      }
+    }
+    if (conv_row) {
+      // Depthwise causal conv + SiLU of this channel for every column, then the state update. Only this thread
+      // touches the channel, so computing every output before any state write needs no barrier.
+      const VgConvEpi& cv = p.conv;
+      const int ck = cv.ck;
+      for (int pass = 0; pass < 2; ++pass) {
+        for (int t = 0; t < p.N; ++t) {
+          const int os = cv.out_slot[t];
+          if (pass == 1 && os < 0) continue;
+          float win[CONV_MAX_CK];
+          const int ns = (int)((n_state >> (2 * t)) & 3u);
+          int cur = t;
+          for (int j = ck - 1; j >= ns; --j) {
+            win[j] = xs[cur * BM + m_local];
+            cur = cv.parent[cur];
+          }
+          for (int jj = 0; jj < ns; ++jj) win[jj] = conv_pre[(t * (CONV_MAX_CK - 1) + jj) * BM + m_local];
+          if (pass == 0) {
+            float acc = 0.f;
+            for (int i = 0; i < ck; ++i) acc = fmaf(wk[i], win[i], acc);
+            cv.out[(size_t)t * cv.conv_dim + m] = silu(acc);
+          } else {
+            float* dst = cv.state + ((size_t)os * cv.conv_dim + m) * ck;
+            for (int i = 0; i < ck; ++i) dst[i] = win[i];
+          }
+        }
       }
     }
   }
@@ -299,6 +365,7 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
   }
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) trace(4 * 16 + 2);
   if (warp == 2) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
@@ -346,7 +413,7 @@ int get_tmap_b(const void* bq, int ldb, CUtensorMap* out) {
 
 extern "C" int vg_gemm_fp4(const void* wt, const float* row_scale, const void* bq, int ldb, const void* sfb, const float* g0,
                            void* out, int out_f32, int M, int K, int N, int ldo, int splitk, int* err,
-                           const VgCommCtx* ar_ctx, cudaStream_t stream) {
+                           const VgCommCtx* ar_ctx, const VgConvEpi* conv, cudaStream_t stream) {
   if (M <= 0 || K <= 0 || N < 1 || N > 16 || splitk < 1 || splitk > 8 || (ldb % 128) != 0) return -2;
   Fp4Params p;
   p.wt = static_cast<const uint8_t*>(wt);
@@ -360,6 +427,12 @@ extern "C" int vg_gemm_fp4(const void* wt, const float* row_scale, const void* b
   p.out_f32 = out_f32;
   p.err = err;
   p.ar = 0;
+  p.has_conv = 0;
+  if (conv && conv->conv_dim > 0) {
+    if (conv->ck < 1 || conv->ck > CONV_MAX_CK || out_f32 || (ar_ctx && ar_ctx->world > 1)) return -6;
+    p.has_conv = 1;
+    p.conv = *conv;
+  }
   if (ar_ctx && ar_ctx->world > 1) {
     if ((M + BM - 1) / BM > MAX_CTAS || (unsigned long long)N * M * 4ull > ar_ctx->slot_bytes) return -5;
     p.ar = 1;
@@ -371,21 +444,25 @@ extern "C" int vg_gemm_fp4(const void* wt, const float* row_scale, const void* b
   if (rc) return rc;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_fp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    cudaError_t e = cudaFuncSetAttribute(gemm_fp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL + CONV_SMEM);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((M + BM - 1) / BM, 1, splitk);
   cfg.blockDim = dim3(THREADS);
-  cfg.dynamicSmemBytes = SMEM_TOTAL;
+  cfg.dynamicSmemBytes = SMEM_TOTAL + (p.has_conv ? CONV_SMEM : 0);
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = splitk;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_on() ? 2 : 1;
   return (int)cudaLaunchKernelEx(&cfg, gemm_fp4_kernel, p, tm);
 }
+
+VG_TRACE_SETTER(vg_trace_set_gemm_fp4)

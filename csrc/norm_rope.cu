@@ -20,6 +20,8 @@ constexpr int NORM_MAXC = 4;
 __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(__nv_bfloat16* res, const __nv_bfloat16* delta, const float* w,
                                                             __half* out16, __nv_bfloat16* out_bf, int h, float eps,
                                                             int plus_one, int ld_res, int ld_delta) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[32];
   const int n = blockIdx.x;
   __nv_bfloat16* r = res + (size_t)n * ld_res;
@@ -88,6 +90,8 @@ __global__ void attn_prep_kernel(const __nv_bfloat16* qkv, int ld_qkv, const flo
                                  const int* pos, const int* slot, const int* kv_row, __nv_bfloat16* q_out,
                                  __nv_bfloat16* kc, __nv_bfloat16* vc, int nh, int nkv, int hd, int rdim, int max_seq,
                                  float eps, float log2_theta, int gated) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[32];
   extern __shared__ float xs[];
   const int n = blockIdx.x, hs = blockIdx.y, d = threadIdx.x;
@@ -126,6 +130,8 @@ __global__ void attn_prep_kernel(const __nv_bfloat16* qkv, int ld_qkv, const flo
 }
 
 __global__ void swiglu_kernel(const __nv_bfloat16* gu, __half* out, int I, int ld, size_t total) {
+  pdl_trigger();
+  pdl_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const size_t n = i / I, c = i % I;
@@ -142,6 +148,8 @@ __global__ void cast_f16_kernel(const T* in, __half* out, size_t total) {
 
 __global__ void embed_gather_kernel(const void* table, const uint8_t* scales, const float* row_scale, const int* tok,
                                     __nv_bfloat16* out, int h, int wfmt) {
+  pdl_trigger();
+  pdl_wait();
   const int n = blockIdx.x;
   const size_t t = (size_t)tok[n];
   for (int i = threadIdx.x; i < h; i += blockDim.x) {
@@ -174,7 +182,7 @@ extern "C" int vg_add_rmsnorm(void* res, const void* delta, const float* w, void
   if ((h & 7) || (ld_res & 7) || (ld_delta & 7) || h > 8 * 1024 * NORM_MAXC) return -2;
   int threads = ((h >> 3) + 31) / 32 * 32;
   if (threads > 1024) threads = ((((h >> 3) + NORM_MAXC - 1) / NORM_MAXC) + 31) / 32 * 32;
-  add_rmsnorm_kernel<<<N, threads, 0, st>>>(static_cast<__nv_bfloat16*>(res),
+  launch_pdl(add_rmsnorm_kernel, dim3(N), dim3(threads), 0, st, static_cast<__nv_bfloat16*>(res),
                                                        static_cast<const __nv_bfloat16*>(delta), w,
                                                        static_cast<__half*>(out_f16),
                                                        static_cast<__nv_bfloat16*>(out_bf16), h, eps, plus_one, ld_res,
@@ -188,7 +196,7 @@ extern "C" int vg_attn_prep(const void* qkv, int ld_qkv, const float* q_norm, co
   if (N <= 0) return 0;
   if (hd > 1024 || (hd & 31)) return -2;
   dim3 grid(N, nh + 2 * nkv);
-  attn_prep_kernel<<<grid, hd, hd * sizeof(float), st>>>(
+  launch_pdl(attn_prep_kernel, dim3(grid), dim3(hd), hd * sizeof(float), st, 
       static_cast<const __nv_bfloat16*>(qkv), ld_qkv, q_norm, k_norm, pos, slot, kv_row,
       static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(kc), static_cast<__nv_bfloat16*>(vc), nh, nkv, hd,
       rdim, max_seq, eps, log2f(theta), gated);
@@ -198,7 +206,7 @@ extern "C" int vg_attn_prep(const void* qkv, int ld_qkv, const float* q_norm, co
 extern "C" int vg_swiglu(const void* gu, void* out_f16, int N, int I, int ld, cudaStream_t st) {
   const size_t total = (size_t)N * I;
   if (!total) return 0;
-  swiglu_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(gu),
+  launch_pdl(swiglu_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(gu),
                                                                  static_cast<__half*>(out_f16), I, ld, total);
   return (int)cudaGetLastError();
 }
@@ -214,7 +222,7 @@ extern "C" int vg_cast_f16(const void* in, int in_is_f32, void* out_f16, long lo
 extern "C" int vg_embed_gather(const void* table, const void* scales, const float* row_scale, const int* tok, void* out,
                                int N, int h, int wfmt, cudaStream_t st) {
   if (N <= 0) return 0;
-  embed_gather_kernel<<<N, 256, 0, st>>>(table, static_cast<const uint8_t*>(scales), row_scale, tok,
+  launch_pdl(embed_gather_kernel, dim3(N), dim3(256), 0, st, table, static_cast<const uint8_t*>(scales), row_scale, tok,
                                          static_cast<__nv_bfloat16*>(out), h, wfmt);
   return (int)cudaGetLastError();
 }

@@ -42,6 +42,8 @@ __device__ __forceinline__ Best block_best(Best b, Best* sm) {
 
 __global__ void __launch_bounds__(1024) argmax_kernel(const float* logits, int V, int ld, int* out, float* out_val,
                                                        int idx_offset) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ Best sm[32];
   const float* row = logits + (size_t)blockIdx.x * ld;
   Best b{-INFINITY, 0x7fffffff};
@@ -152,7 +154,7 @@ __global__ void __launch_bounds__(1024) nll_kernel(const float* logits, int V, i
 extern "C" int vg_argmax(const float* logits, int N, int V, int ld, int* out, float* out_val, int idx_offset,
                          cudaStream_t st) {
   if (N <= 0) return 0;
-  argmax_kernel<<<N, 1024, 0, st>>>(logits, V, ld, out, out_val, idx_offset);
+  launch_pdl(argmax_kernel, dim3(N), dim3(1024), 0, st, logits, V, ld, out, out_val, idx_offset);
   return (int)cudaGetLastError();
 }
 

@@ -178,6 +178,7 @@ class GpuModel:
                     G.prepare_fp4(q)
                 G.prepare(q, keep_canonical=keep_canonical)
         self.ws = Workspace(self.cfg, weights, max_cols, self.dev, max_cols)
+        self.col_ctr = torch.zeros(16, dtype=torch.int32, device=self.dev)     # per-column arrival counters
         self.ws_prefill: Optional[Workspace] = None
         self.state_ready = False
         self.graphs: Dict[Tuple[str, int], torch.cuda.CUDAGraph] = {}
@@ -308,22 +309,33 @@ class GpuModel:
         c, Gd = self.cfg, L.gdn
         gi = self.gdn_index[li]
         proj = ws.wide[:, :Gd.in_proj.m]
-        self._linear(Gd.in_proj, ws.xn16, n, proj, act=act)
         conv_dim = Gd.conv_w.shape[0]
         value_dim = Gd.nv * c.lin_v_dim
-        if seq_mode:
+        if self._fp4_ok(Gd.in_proj, n) and c.conv_kernel <= 8:
+            # the conv runs in the GEMM epilogue: each output row is one conv channel
+            cv = G.ConvEpi.make(self.conv[gi], Gd.conv_w, ws.st_in, ws.parent, ws.st_out, ws.conv_out, conv_dim,
+                                c.conv_kernel)
+            G.linear_fp4(Gd.in_proj, ws.xn16, n, out=proj, act=act, conv=cv)
+        elif seq_mode:
+            self._linear(Gd.in_proj, ws.xn16, n, proj, act=act)
             K.gdn_conv(proj, self.conv[gi], Gd.conv_w, ws.st_in, ws.parent, ws.st_out, ws.conv_out, n, conv_dim,
                        c.conv_kernel, phase=1)
             K.gdn_conv(proj, self.conv[gi], Gd.conv_w, ws.st_in, ws.parent, ws.st_out, ws.conv_out, n, conv_dim,
                        c.conv_kernel, phase=2)
         else:
+            self._linear(Gd.in_proj, ws.xn16, n, proj, act=act)
             K.gdn_conv(proj, self.conv[gi], Gd.conv_w, ws.st_in, ws.parent, ws.st_out, ws.conv_out, n, conv_dim,
                        c.conv_kernel, phase=3)
         g16 = ws.a16(Gd.out.k)
+        act_o = None
+        if self._fp4_ok(Gd.out, n) and value_dim % 16 == 0:
+            # the recurrence kernel quantises its own output rows for the output projection
+            act_o = G.fp4_buffers(self.dev, Gd.out.kernel4.kp)
         K.gdn_step(ws.conv_out, proj, conv_dim, conv_dim + value_dim, conv_dim + value_dim + Gd.nv, self.S[gi],
                    Gd.A_log, Gd.dt_bias, Gd.norm, ws.chain_start, ws.chain_len, n_chains, ws.st_in, ws.parent,
-                   ws.st_out, g16, Gd.nk, Gd.nv, c.lin_k_dim, c.lin_v_dim, c.rms_eps)
-        self._row_parallel(Gd.out, g16, n, ws.delta)
+                   ws.st_out, g16, Gd.nk, Gd.nv, c.lin_k_dim, c.lin_v_dim, c.rms_eps,
+                   quant=act_o + (self.col_ctr,) if act_o is not None else None)
+        self._row_parallel(Gd.out, g16, n, ws.delta, act=act_o)
 
     def _mlp(self, ws: Workspace, M, n: int, out: torch.Tensor, reduce: bool = True, act=None):
         gu = ws.wide[:, :M.gate_up.m]

@@ -21,6 +21,8 @@ ID_PATH = os.path.join(ROOT, "build", "build_id.txt")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--use_fast_math", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
+if os.environ.get("VELO_TRACE", "0") == "1":        # device timeline stamps (profiling builds only)
+    NVCC_FLAGS.append("-DVG_TRACE")
 
 
 def sources() -> List[str]:

@@ -208,7 +208,8 @@ def prepare_fp4(q: QLinear, splitk: Optional[int] = None) -> Fp4Weight:
 _fp4_act = {}
 
 
-def _fp4_buffers(dev, kp: int):
+def fp4_buffers(dev, kp: int):
+    """The shared FP4 activation buffers (terms, scale chunks, per-row global scales) for inputs padded to ``kp``."""
     key = (str(dev), kp)
     b = _fp4_act.get(key)
     if b is None:
@@ -221,7 +222,7 @@ def _fp4_buffers(dev, kp: int):
 
 def quantize_act_fp4(x16: torch.Tensor, n: int, kp: int):
     """Expand ``n <= 16`` f16 rows into the four-term NVFP4 series the FP4 GEMM consumes."""
-    bq, sfb, g0 = _fp4_buffers(x16.device, kp)
+    bq, sfb, g0 = fp4_buffers(x16.device, kp)
     rc = _lib.lib().vg_act_quant_fp4(ptr(x16), c_int(x16.stride(0)), c_int(n), c_int(x16.shape[1]), ptr(bq),
                                      c_int(bq.stride(0)), ptr(sfb), ptr(g0), stream())
     _lib.check(rc, "vg_act_quant_fp4")
@@ -231,7 +232,7 @@ def quantize_act_fp4(x16: torch.Tensor, n: int, kp: int):
 def swiglu_fp4(gu: torch.Tensor, n: int, inter: int, out16: Optional[torch.Tensor] = None):
     """SwiGLU of ``gu[:n] = [gate | up]`` (bf16) emitted directly as the FP4 series for the down projection."""
     kp = ((inter + 255) // 256) * 256
-    bq, sfb, g0 = _fp4_buffers(gu.device, kp)
+    bq, sfb, g0 = fp4_buffers(gu.device, kp)
     rc = _lib.lib().vg_swiglu_fp4(ptr(gu), c_int(gu.stride(0)), c_int(n), c_int(inter), ptr(bq), c_int(bq.stride(0)),
                                   ptr(sfb), ptr(g0), ptr(out16) if out16 is not None else c_void_p(0), stream())
     _lib.check(rc, "vg_swiglu_fp4")
@@ -244,7 +245,7 @@ def add_rmsnorm_fp4(res: torch.Tensor, delta: Optional[torch.Tensor], w: torch.T
     given, for consumers that are not on the FP4 path)."""
     h = res.shape[1]
     kp = ((h + 255) // 256) * 256
-    bq, sfb, g0 = _fp4_buffers(res.device, kp)
+    bq, sfb, g0 = fp4_buffers(res.device, kp)
     rc = _lib.lib().vg_add_rmsnorm_fp4(ptr(res), ptr(delta) if delta is not None else c_void_p(0), ptr(w), c_int(n),
                                        c_int(h), c_float(eps), c_int(1 if plus_one else 0), c_int(res.stride(0)),
                                        c_int(delta.stride(0) if delta is not None else 0), ptr(bq), c_int(bq.stride(0)),
@@ -253,10 +254,24 @@ def add_rmsnorm_fp4(res: torch.Tensor, delta: Optional[torch.Tensor], w: torch.T
     return bq, sfb, g0
 
 
+class ConvEpi(ctypes.Structure):
+    """Mirror of ``VgConvEpi``: the depthwise causal conv the GEMM epilogue runs on its conv-channel rows."""
+    _fields_ = [("state", c_void_p), ("w", c_void_p), ("in_slot", c_void_p), ("parent", c_void_p),
+                ("out_slot", c_void_p), ("out", c_void_p), ("conv_dim", c_int), ("ck", c_int)]
+
+    @staticmethod
+    def make(state, w, in_slot, parent, out_slot, out, conv_dim: int, ck: int) -> "ConvEpi":
+        assert state.dtype == torch.float32 and w.dtype == torch.float32 and out.dtype == torch.float32
+        assert out.is_contiguous() and state.is_contiguous()       # `out` is addressed as [n][conv_dim]
+        return ConvEpi(state.data_ptr(), w.data_ptr(), in_slot.data_ptr(), parent.data_ptr(), out_slot.data_ptr(),
+                       out.data_ptr(), conv_dim, ck)
+
+
 def linear_fp4(q: QLinear, x16: torch.Tensor, n: int, out: Optional[torch.Tensor] = None, out_f32: bool = False,
-               comm=None, act=None) -> torch.Tensor:
+               comm=None, act=None, conv: Optional[ConvEpi] = None) -> torch.Tensor:
     """Decode-width linear on the block-scaled FP4 tensor-core path. ``act`` may carry an already quantised
-    activation (several linears reading the same input share it)."""
+    activation (several linears reading the same input share it). ``conv`` fuses the GatedDeltaNet causal
+    conv of the leading ``conv_dim`` output rows into the epilogue."""
     tw = prepare_fp4(q)
     assert n <= 16 and x16.shape[1] == tw.k
     bq, sfb, g0 = act if act is not None else quantize_act_fp4(x16, n, tw.kp)
@@ -265,6 +280,7 @@ def linear_fp4(q: QLinear, x16: torch.Tensor, n: int, out: Optional[torch.Tensor
     rc = _lib.lib().vg_gemm_fp4(ptr(tw.wt), ptr(tw.row_scale), ptr(bq), c_int(bq.stride(0)), ptr(sfb), ptr(g0), ptr(out),
                                 c_int(1 if out.dtype == torch.float32 else 0), c_int(tw.m), c_int(tw.k), c_int(n),
                                 c_int(out.stride(0)), c_int(tw.splitk), ptr(_lib.err_word(x16.device)),
-                                ctypes.byref(comm.ctx) if comm is not None else c_void_p(0), stream())
+                                ctypes.byref(comm.ctx) if comm is not None else c_void_p(0),
+                                ctypes.byref(conv) if conv is not None else c_void_p(0), stream())
     _lib.check(rc, "vg_gemm_fp4")
     return out

@@ -83,11 +83,15 @@ def gdn_conv(x, state, w, in_slot, parent, out_slot, out, n, conv_dim, ck, phase
 
 
 def gdn_step(qkv, proj, off_z, off_b, off_a, S, A_log, dt_bias, norm_w, chain_start, chain_len, n_chains,
-             in_slot, parent, out_slot, out16, nk, nv, kd, vd, eps):
+             in_slot, parent, out_slot, out16, nk, nv, kd, vd, eps, quant=None):
+    """``quant = (bq, sfb, g0, col_ctr)`` makes the kernel also emit every output row as the FP4 activation
+    series (the head that finishes a column last quantises it)."""
+    bq, sfb, g0, ctr = quant if quant is not None else (None, None, None, None)
     rc = _lib.lib().vg_gdn_step(ptr(qkv), ptr(proj), c_int(proj.stride(0)), c_int(off_z), c_int(off_b), c_int(off_a),
                                 ptr(S), ptr(A_log), ptr(dt_bias), ptr(norm_w), ptr(chain_start), ptr(chain_len),
                                 c_int(n_chains), ptr(in_slot), ptr(parent), ptr(out_slot), ptr(out16), c_int(nk),
-                                c_int(nv), c_int(kd), c_int(vd), c_float(eps), stream())
+                                c_int(nv), c_int(kd), c_int(vd), c_float(eps), ptr(bq),
+                                c_int(bq.stride(0) if bq is not None else 0), ptr(sfb), ptr(g0), ptr(ctr), stream())
     _lib.check(rc, "vg_gdn_step")
 
 
