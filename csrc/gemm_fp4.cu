@@ -369,7 +369,188 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
   if (warp == 2) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// ------------------------------------------------------------------ persistent variant
+// For weights with more 128-row tiles than SMs (gate_up, LM head): one CTA per SM walks its tiles
+// (blockIdx.x, blockIdx.x + gridDim.x, ...) with the ring running straight through tile boundaries, so there is
+// no drain / refill between tiles and no ragged last wave of cold CTAs. Accumulators are double-buffered in
+// TMEM (2 tiles x 2 issuers): the epilogue of tile i overlaps the main loop of tile i + 1. Plain epilogue only
+// (no split-K, fused all-reduce or conv); needs at least two slabs per tile.
+constexpr uint32_t P_TMEM_COLS = 512;      // 4 accumulators (cols 0..255) + 2 issuers x 2 scale buffers (256..383)
+constexpr int P_SMEM_TOTAL = NS * STAGE + (2 * NS + 4) * 8 + 16 + 1024;
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_fp4_persist_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b, int tiles) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + NS * STAGE);
+  uint64_t* empty = full + NS;
+  uint64_t* acc_full = empty + NS;       // [2] both issuers commit
+  uint64_t* acc_empty = acc_full + 2;    // [2] one arrival per epilogue warp
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nks = p.ks_total;
+  const int nt = ((int)blockIdx.x < tiles) ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  const int total = nt * nks;
+  if (threadIdx.x == 0) trace(4 * 16);
+  pdl_trigger();
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NS; ++i) { mbar_init(&full[i], 2); mbar_init(&empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 2); mbar_init(&acc_empty[i], 4); }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, P_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int ti = 0, sl = 0;
+      for (int it = 0; it < total && !*abort_flag; ++it) {
+        const int mt = (int)blockIdx.x + ti * (int)gridDim.x;
+        const int rot = (int)(((unsigned)mt * 7u) % (unsigned)nks);
+        const int ks = sl + rot >= nks ? sl + rot - nks : sl + rot;
+        const int s = it % NS;
+        if (!mbar_wait(&empty[s], ((it / NS) & 1) ^ 1)) { fail(p.err, VG_ERR_EMPTY_WAIT, abort_flag); break; }
+        mbar_arrive_expect_tx(&full[s], A_BYTES + SF_BYTES);
+        tma_bulk_g2s(smem + (size_t)s * STAGE, p.wt + ((size_t)mt * nks + ks) * (A_BYTES + SF_BYTES), A_BYTES + SF_BYTES,
+                     &full[s]);
+        if (++sl == nks) { sl = 0; ++ti; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      pdl_wait();                          // the activation series comes from the preceding kernel
+      trace(4 * 16 + 1);
+      int ti = 0, sl = 0;
+      for (int it = 0; it < total && !*abort_flag; ++it) {
+        const int mt = (int)blockIdx.x + ti * (int)gridDim.x;
+        const int rot = (int)(((unsigned)mt * 7u) % (unsigned)nks);
+        const int ks = sl + rot >= nks ? sl + rot - nks : sl + rot;
+        const int s = it % NS;
+        if (!mbar_wait(&empty[s], ((it / NS) & 1) ^ 1)) { fail(p.err, VG_ERR_EMPTY_WAIT, abort_flag); break; }
+        uint8_t* st = smem + (size_t)s * STAGE + A_BYTES + SF_BYTES;
+        mbar_arrive_expect_tx(&full[s], B_BYTES + SF_BYTES);
+        tma_tensor2d_g2s(st, &tmap_b, ks * (BKQ / 2), 0, &full[s]);
+        tma_bulk_g2s(st + B_BYTES, p.sfb + (size_t)ks * SF_BYTES, SF_BYTES, &full[s]);
+        if (++sl == nks) { sl = 0; ++ti; }
+      }
+    }
+  } else if (warp == 2 || warp == 3) {
+    if (lane == 0) {
+      const int me = warp - 2;
+      const uint32_t idesc = idesc_fp4(BM, NT);
+      const uint32_t tmem_sf0 = tmem_base + 4 * ACC_W + (uint32_t)me * 2 * SF_COLS;
+      int mine = 0;
+      for (int it = me; it < total && !*abort_flag; it += 2, ++mine) {
+        const int ti = it / nks, sl = it - ti * nks;
+        const int buf = ti & 1;
+        const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * 2 + me) * ACC_W;
+        if (sl < 2) {
+          // first slab of this issuer in the tile: the epilogue must have drained the buffer (two tiles ago)
+          if (!mbar_wait(&acc_empty[buf], (((ti >> 1) & 1) ^ 1))) { fail(p.err, VG_ERR_MMA_WAIT, abort_flag); break; }
+          tc_fence_after();
+        }
+        const int s = it % NS;
+        if (!mbar_wait(&full[s], (it / NS) & 1)) { fail(p.err, VG_ERR_TMA_WAIT, abort_flag); break; }
+        if (it == 0) trace(4 * 16 + 3);
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE);
+        const uint32_t sfa_addr = a_addr + A_BYTES;
+        const uint32_t b_addr = sfa_addr + SF_BYTES;
+        const uint32_t sfb_addr = b_addr + B_BYTES;
+        const uint32_t sf_t = tmem_sf0 + (uint32_t)(mine & 1) * SF_COLS;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          tmem_cp_sf(sf_t + 4 * j, sf_desc(sfa_addr + 512 * j));
+          tmem_cp_sf(sf_t + 16 + 4 * j, sf_desc(sfb_addr + 512 * j));
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          umma_fp4(tmem_acc, umma_desc_sw128(a_addr + 32 * j), umma_desc_sw128(b_addr + 32 * j), idesc, sf_t + 4 * j,
+                   sf_t + 16 + 4 * j, (sl >= 2 || j != 0) ? 1u : 0u);
+        }
+        umma_commit(&empty[s]);
+        if (sl >= nks - 2) umma_commit(&acc_full[buf]);      // this issuer's last slab of the tile
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps 4..7, thread = weight row
+    const int q = warp & 3;
+    const int m_local = q * 32 + lane;
+    pdl_wait();                            // before g0 reads and every output write
+    float g0r[16];
+#pragma unroll
+    for (int n = 0; n < 16; ++n) g0r[n] = n < p.N ? p.g0[n] : 0.f;
+    const float tw[TERMS] = {1.0f, 0.125f, 0.015625f, 0.001953125f};
+    for (int ti = 0; ti < nt && !*abort_flag; ++ti) {
+      const int buf = ti & 1;
+      const int mt = (int)blockIdx.x + ti * (int)gridDim.x;
+      const int m = mt * BM + m_local;
+      const float rsc = (p.row_scale && m < p.M) ? p.row_scale[m] : 1.0f;
+      if (!mbar_wait(&acc_full[buf], (ti >> 1) & 1)) { fail(p.err, VG_ERR_MMA_WAIT, abort_flag); break; }
+      if (threadIdx.x == 128 && ti == 0) trace(4 * 16 + 4);
+      tc_fence_after();
+      float y[16];
+#pragma unroll
+      for (int n = 0; n < 16; ++n) y[n] = 0.f;
+#pragma unroll
+      for (int t = 0; t < TERMS; ++t) {
+        uint32_t a0[16], a1[16];
+        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 2) * ACC_W + (uint32_t)(t * 16), a0);
+        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 2 + 1) * ACC_W + (uint32_t)(t * 16), a1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int n = 0; n < 16; ++n) y[n] = fmaf(__uint_as_float(a0[n]) + __uint_as_float(a1[n]), tw[t], y[n]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      if (m < p.M) {
+#pragma unroll
+        for (int n = 0; n < 16; ++n) {
+          if (n < p.N) {
+            const float v = y[n] * g0r[n] * rsc;
+            if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)n * p.ldo + m] = v;
+            else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)n * p.ldo + m] = __float2bfloat16_rn(v);
+          }
+        }
+      }
+    }
+  }
+  __syncwarp();
+  if (*abort_flag && threadIdx.x == 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0) trace(4 * 16 + 2);
+  if (warp == 2) tmem_dealloc(tmem_base, P_TMEM_COLS);
+}
+
 // ------------------------------------------------------------------ host
+bool persist_on() {
+  static const bool on = [] { const char* e = getenv("VELO_NO_PERSISTENT_GEMM"); return !(e && e[0] == '1'); }();
+  return on;
+}
+int sm_count() {
+  static const int n = [] {
+    int dev = 0, v = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    return v > 0 ? v : 1;
+  }();
+  return n;
+}
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -442,6 +623,21 @@ extern "C" int vg_gemm_fp4(const void* wt, const float* row_scale, const void* b
   CUtensorMap tm;
   int rc = get_tmap_b(bq, ldb, &tm);
   if (rc) return rc;
+  const int tiles = (M + BM - 1) / BM;
+  if (splitk == 1 && !p.ar && !p.has_conv && p.ks_total >= 2 && tiles > sm_count() && persist_on()) {
+    static bool configured_p = false;
+    if (!configured_p) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_fp4_persist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_TOTAL);
+      if (e != cudaSuccess) return (int)e;
+      configured_p = true;
+    }
+    // Deep tile loops only (LM head): measured inside the decode chain, a persistent gate_up (1.8 tiles per SM)
+    // is faster in isolation but ends on every SM at once, which costs the following kernels more overlap than
+    // the kernel itself gains.
+    static const int pmin = [] { const char* e = getenv("VELO_PERSIST_MIN_TILES"); return e ? atoi(e) : 4 * sm_count(); }();
+    if (tiles >= pmin)
+      return (int)launch_pdl(gemm_fp4_persist_kernel, dim3(sm_count()), dim3(THREADS), P_SMEM_TOTAL, stream, p, tm, tiles);
+  }
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_fp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL + CONV_SMEM);

@@ -13,7 +13,8 @@ def _mk(m, k, seed=0):
 
 
 @pytest.mark.parametrize("m,k,n", [(128, 256, 1), (256, 512, 16), (384, 1024, 5), (1552, 256, 3), (5120, 5120, 16),
-                                   (640, 2176, 7), (5120, 17408, 2)])
+                                   (640, 2176, 7), (5120, 17408, 2),
+                                   (76032, 512, 3), (80000, 768, 16), (75904, 1280, 1)])   # deep tile loops: persistent kernel
 def test_fp4_gemm_matches_reference(m, k, n):
     from velogb10_b200.ops import gemm as G, lib
     q = _mk(m, k)
