@@ -3,7 +3,7 @@
 // One CTA serves (column, kv head, query sub-group, split). Its 8 warps walk the split's keys in a
 // fixed interleave (warp w takes keys k0+w, k0+w+8, ...), each lane owning hd/32 dims, with an online
 // softmax per query head in fp32; the warps' (m, l, acc) are merged in warp order. The number of
-// splits is a pure function of the column's own key count, ns = clamp(len/256, 1, 32), so a column is
+// splits is a pure function of the column's own key count, ns = clamp(len/64, 1, 32), so a column is
 // computed the same way whether it runs alone or beside 15 others (reference:
 // kernels/gpu_batch.cu:1443-1477, :1491-1606, :2151-2186). Keys at or beyond `base[col]` are addressed
 // through a per-column row list (tree / forest verify); before it, key t is cache row t.
@@ -25,8 +25,21 @@ using namespace vg;
 constexpr int NW = 8;   // warps per CTA
 
 __device__ __forceinline__ int splits_for(int len) {
-  int ns = len / 256;
+  int ns = len / 64;
   return ns < 1 ? 1 : (ns > 32 ? 32 : ns);
+}
+
+// One lane's DPL consecutive bf16 values of a cache row, fetched with a single vector load.
+template <int DPL> struct RowVec;
+template <> struct RowVec<8> { using T = uint4; };
+template <> struct RowVec<4> { using T = uint2; };
+template <> struct RowVec<2> { using T = uint32_t; };
+template <> struct RowVec<1> { using T = unsigned short; };
+template <int DPL>
+__device__ __forceinline__ void unpack_row(const typename RowVec<DPL>::T& raw, float* f) {
+  const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) f[i] = __bfloat162float(h[i]);
 }
 
 template <int HD, int GT>
@@ -71,39 +84,41 @@ __global__ void __launch_bounds__(NW * 32) attn_split_kernel(
   const __nv_bfloat16* kslot = kc + ((size_t)slot * nkv + kvh) * (size_t)max_seq * HD;
   const __nv_bfloat16* vslot = vc + ((size_t)slot * nkv + kvh) * (size_t)max_seq * HD;
 
-  for (int t = k0 + warp; t < k1; t += NW) {
-    const int row = t < kbase ? t : path[(size_t)col * path_ld + (t - kbase)];
-    float kf[DPL], vf[DPL];
-    if (DPL == 8) {
-      const uint4 kv4 = *reinterpret_cast<const uint4*>(kslot + (size_t)row * HD + lane * 8);
-      const uint4 vv4 = *reinterpret_cast<const uint4*>(vslot + (size_t)row * HD + lane * 8);
-      const __nv_bfloat162* kp = reinterpret_cast<const __nv_bfloat162*>(&kv4);
-      const __nv_bfloat162* vp = reinterpret_cast<const __nv_bfloat162*>(&vv4);
+  // Keys of this warp in batches of U: all loads of a batch are issued before its first dot product, so a
+  // warp keeps U rows of K and V in flight; the keys are still folded in in ascending order.
+  constexpr int U = 4;
+  using Raw = typename RowVec<DPL>::T;
+  for (int tb = k0 + warp; tb < k1; tb += NW * U) {
+    Raw kraw[U], vraw[U];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 a = __bfloat1622float2(kp[i]), b = __bfloat1622float2(vp[i]);
-        kf[2 * i] = a.x; kf[2 * i + 1] = a.y; vf[2 * i] = b.x; vf[2 * i + 1] = b.y;
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < DPL; ++i) {
-        kf[i] = __bfloat162float(kslot[(size_t)row * HD + lane * DPL + i]);
-        vf[i] = __bfloat162float(vslot[(size_t)row * HD + lane * DPL + i]);
+    for (int u = 0; u < U; ++u) {
+      const int t = tb + u * NW;
+      if (t < k1) {
+        const int row = t < kbase ? t : path[(size_t)col * path_ld + (t - kbase)];
+        kraw[u] = *reinterpret_cast<const Raw*>(kslot + (size_t)row * HD + lane * DPL);
+        vraw[u] = *reinterpret_cast<const Raw*>(vslot + (size_t)row * HD + lane * DPL);
       }
     }
 #pragma unroll
-    for (int g = 0; g < GT; ++g) {
-      float s = 0.f;
+    for (int u = 0; u < U; ++u) {
+      if (tb + u * NW >= k1) break;
+      float kf[DPL], vf[DPL];
+      unpack_row<DPL>(kraw[u], kf);
+      unpack_row<DPL>(vraw[u], vf);
 #pragma unroll
-      for (int i = 0; i < DPL; ++i) s = fmaf(qf[g][i], kf[i], s);
-      s = warp_sum(s);
-      const float mn = fmaxf(m[g], s);
-      const float corr = __expf(m[g] - mn);
-      const float p = __expf(s - mn);
-      l[g] = l[g] * corr + p;
+      for (int g = 0; g < GT; ++g) {
+        float s = 0.f;
 #pragma unroll
-      for (int i = 0; i < DPL; ++i) acc[g][i] = fmaf(p, vf[i], acc[g][i] * corr);
-      m[g] = mn;
+        for (int i = 0; i < DPL; ++i) s = fmaf(qf[g][i], kf[i], s);
+        s = warp_sum(s);
+        const float mn = fmaxf(m[g], s);
+        const float corr = __expf(m[g] - mn);
+        const float p = __expf(s - mn);
+        l[g] = l[g] * corr + p;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[g][i] = fmaf(p, vf[i], acc[g][i] * corr);
+        m[g] = mn;
+      }
     }
   }
 
