@@ -117,29 +117,40 @@ __global__ void __launch_bounds__(VD) gdn_step_kernel(
     const float beta = sigmoidf(bb);
     const float sp_ = aa > 20.f ? aa : log1pf(__expf(aa));
     const float g = __expf(a_coef * sp_);
-    // decay + kv_mem (four interleaved partial sums in a fixed order)
-    float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
+    // decay + kv_mem. Canonical summation order (shared with the prefill kernel, where two threads split a
+    // column): each half of the key range keeps four interleaved partial sums, halves are added last.
+    constexpr int HK = KD / 2;
+    float hsum[2];
 #pragma unroll
-    for (int a = 0; a < KD; a += 4) {
-      const float4 k4 = *reinterpret_cast<const float4*>(&ks[a]);
-      s[a] *= g; s[a + 1] *= g; s[a + 2] *= g; s[a + 3] *= g;
-      m0 = fmaf(s[a], k4.x, m0); m1 = fmaf(s[a + 1], k4.y, m1);
-      m2 = fmaf(s[a + 2], k4.z, m2); m3 = fmaf(s[a + 3], k4.w, m3);
+    for (int h = 0; h < 2; ++h) {
+      float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
+#pragma unroll
+      for (int a = h * HK; a < (h + 1) * HK; a += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(&ks[a]);
+        s[a] *= g; s[a + 1] *= g; s[a + 2] *= g; s[a + 3] *= g;
+        m0 = fmaf(s[a], k4.x, m0); m1 = fmaf(s[a + 1], k4.y, m1);
+        m2 = fmaf(s[a + 2], k4.z, m2); m3 = fmaf(s[a + 3], k4.w, m3);
+      }
+      hsum[h] = (m0 + m1) + (m2 + m3);
     }
-    const float kv_mem = ((m0 + m1) + (m2 + m3)) * ksc;
+    const float kv_mem = (hsum[0] + hsum[1]) * ksc;
     const float delta = (v - kv_mem) * beta;
     const float dk = delta * ksc;
-    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-    for (int a = 0; a < KD; a += 4) {
-      const float4 k4 = *reinterpret_cast<const float4*>(&ks[a]);
-      const float4 q4 = *reinterpret_cast<const float4*>(&qs[a]);
-      s[a] = fmaf(k4.x, dk, s[a]); s[a + 1] = fmaf(k4.y, dk, s[a + 1]);
-      s[a + 2] = fmaf(k4.z, dk, s[a + 2]); s[a + 3] = fmaf(k4.w, dk, s[a + 3]);
-      o0 = fmaf(s[a], q4.x, o0); o1 = fmaf(s[a + 1], q4.y, o1);
-      o2 = fmaf(s[a + 2], q4.z, o2); o3 = fmaf(s[a + 3], q4.w, o3);
+    for (int h = 0; h < 2; ++h) {
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+      for (int a = h * HK; a < (h + 1) * HK; a += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(&ks[a]);
+        const float4 q4 = *reinterpret_cast<const float4*>(&qs[a]);
+        s[a] = fmaf(k4.x, dk, s[a]); s[a + 1] = fmaf(k4.y, dk, s[a + 1]);
+        s[a + 2] = fmaf(k4.z, dk, s[a + 2]); s[a + 3] = fmaf(k4.w, dk, s[a + 3]);
+        o0 = fmaf(s[a], q4.x, o0); o1 = fmaf(s[a + 1], q4.y, o1);
+        o2 = fmaf(s[a + 2], q4.z, o2); o3 = fmaf(s[a + 3], q4.w, o3);
+      }
+      hsum[h] = (o0 + o1) + (o2 + o3);
     }
-    const float o = ((o0 + o1) + (o2 + o3)) * qsc;
+    const float o = (hsum[0] + hsum[1]) * qsc;
     const float ss = block_sum(o * o, red);
     const float z = __bfloat162float(proj[(size_t)t * ldp + off_z + vh * VD + j]);
     out[((size_t)t * nv + vh) * VD + j] = f32_to_f16_sat(o * rsqrtf(ss / (float)VD + eps) * nw * silu(z));
@@ -213,6 +224,203 @@ extern "C" int vg_gdn_conv(const void* x, int ldx, float* state, const float* w,
   return (int)cudaGetLastError();
 }
 
+namespace {
+using namespace vg;
+
+// ------------------------------------------------------------------ prefill: one long chain per CTA
+// Same arithmetic, in the same order, as gdn_step_kernel applied token by token (so a prefilled state is
+// bit-identical to stepping through the prompt), restructured so the per-token critical path is only the
+// thread-local FMA chains: tokens arrive in batches of TB through a double-buffered cp.async ring, the three
+// block-wide reductions of a token (|q|^2, |k|^2, |o|^2) are computed for a whole batch at once by the warps
+// with the exact shuffle tree block_sum uses, and there is one barrier pair per batch instead of seven per
+// token. Linear chains only (parent[t] = t - 1).
+VG_DEVINL void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+VG_DEVINL void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+VG_DEVINL void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// block_sum(v) of a VD-thread block whose thread c holds x[c], reproduced by one warp (VD == 128).
+template <int VD>
+VG_DEVINL float block_sum_by_warp(const float* x, int lane) {
+  float p[VD / 32];
+#pragma unroll
+  for (int w = 0; w < VD / 32; ++w) p[w] = warp_sum(x[32 * w + lane]);
+  float r = 0.f;
+#pragma unroll
+  for (int w = 0; w < VD / 32; ++w) r = lane == w ? p[w] : r;
+  return warp_sum(r);
+}
+
+template <int KD, int VD, int TB>
+__global__ void __launch_bounds__(2 * VD) gdn_prefill_kernel(
+    const float* __restrict__ qkv, const __nv_bfloat16* __restrict__ proj, int ldp, int off_z, int off_b, int off_a,
+    float* __restrict__ S, const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+    const float* __restrict__ norm_w, int t0, int tn, const int* __restrict__ in_slot, const int* __restrict__ out_slot,
+    __half* __restrict__ out, int nk, int nv, float eps) {
+  constexpr int NT = 2 * VD, NWARP = NT / 32, HK = KD / 2;
+  static_assert(KD == VD && VD % 32 == 0 && TB % NWARP == 0 && KD % 8 == 0, "layout");
+  extern __shared__ __align__(16) float sm[];
+  float* qb = sm;                          // [2][TB][KD] raw q
+  float* kb = qb + 2 * TB * KD;            // [2][TB][KD] raw k
+  float* vb = kb + 2 * TB * KD;            // [2][TB][VD]
+  float* ob = vb + 2 * TB * VD;            // [TB][VD]    o before the output norm
+  float* sq = ob + TB * VD;                // [TB][VD]    o^2 staging for the batched reductions
+  float* sc = sq + TB * VD;                // [TB][4]     g, beta, ksc, qsc
+  float* ssb = sc + TB * 4;                // [TB]        sum o^2
+  float* bab = ssb + TB;                   // [TB][2]     b, a of the batch (as float)
+  int* osl = reinterpret_cast<int*>(bab + TB * 2);                       // [TB] out_slot
+  __nv_bfloat16* zb = reinterpret_cast<__nv_bfloat16*>(osl + TB);        // [2][TB][VD] gate z
+  pdl_trigger();
+  pdl_wait();
+  const int vh = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c = tid >> 1, h = tid & 1;     // column of the state and which half of the key range
+  const int kh = vh * nk / nv;
+  const int key_dim = nk * KD, conv_dim = 2 * key_dim + nv * VD;
+  const float a_coef = -__expf(A_log[vh]);
+  const float dtb = dt_bias[vh];
+  const float nw = norm_w[c];
+  constexpr int TPW = TB / NWARP;          // tokens per warp in the batched phases
+
+  float s[HK];
+  {
+    const float* sp = S + (((size_t)in_slot[t0] * nv + vh) * KD + h * HK) * VD + c;
+#pragma unroll
+    for (int a = 0; a < HK; ++a) s[a] = sp[(size_t)a * VD];
+  }
+  auto issue = [&](int b) {                // batch b -> buffer b & 1
+    const int base = t0 + b * TB, cnt = min(TB, tn - b * TB);
+    float* q_ = qb + (b & 1) * TB * KD;
+    float* k_ = kb + (b & 1) * TB * KD;
+    float* v_ = vb + (b & 1) * TB * VD;
+    __nv_bfloat16* z_ = zb + (b & 1) * TB * VD;
+    constexpr int CPT = KD / 4;            // 16-byte chunks per fp32 token row
+    for (int i = tid; i < cnt * CPT; i += NT) {
+      const int tt = i / CPT, o4 = (i % CPT) * 4;
+      const float* row = qkv + (size_t)(base + tt) * conv_dim;
+      cp_async16(q_ + tt * KD + o4, row + kh * KD + o4);
+      cp_async16(k_ + tt * KD + o4, row + key_dim + kh * KD + o4);
+      cp_async16(v_ + tt * VD + o4, row + 2 * key_dim + vh * VD + o4);
+    }
+    constexpr int CPZ = VD / 8;            // 16-byte chunks per bf16 z row
+    for (int i = tid; i < cnt * CPZ; i += NT) {
+      const int tt = i / CPZ, o8 = (i % CPZ) * 8;
+      cp_async16(z_ + tt * VD + o8, proj + (size_t)(base + tt) * ldp + off_z + vh * VD + o8);
+    }
+    cp_async_commit();
+  };
+  // b / a / out_slot of a batch: fetched one batch ahead into registers by the first TB threads
+  float nb_b = 0.f, nb_a = 0.f;
+  int nb_os = -1;
+  auto fetch_scalars = [&](int b) {
+    const int tt = tid;
+    if (tt < TB && b * TB + tt < tn) {
+      const int t = t0 + b * TB + tt;
+      nb_b = __bfloat162float(proj[(size_t)t * ldp + off_b + vh]);
+      nb_a = __bfloat162float(proj[(size_t)t * ldp + off_a + vh]);
+      nb_os = out_slot[t];
+    }
+  };
+  const int nb = (tn + TB - 1) / TB;
+  if (nb > 0) { issue(0); fetch_scalars(0); }
+  for (int b = 0; b < nb; ++b) {
+    const int base = t0 + b * TB, cnt = min(TB, tn - b * TB);
+    const float* q_ = qb + (b & 1) * TB * KD;
+    const float* k_ = kb + (b & 1) * TB * KD;
+    const float* v_ = vb + (b & 1) * TB * VD;
+    const __nv_bfloat16* z_ = zb + (b & 1) * TB * VD;
+    if (tid < TB) { bab[tid * 2] = nb_b; bab[tid * 2 + 1] = nb_a; osl[tid] = nb_os; }
+    cp_async_wait_all();
+    __syncthreads();                       // batch b landed; everyone is done with batch b - 1
+    if (b + 1 < nb) { issue(b + 1); fetch_scalars(b + 1); }
+    // ---- per-token scalars of the batch (warp w: tokens w*TPW ..), block_sum order reproduced per warp
+    for (int u = 0; u < TPW; ++u) {
+      const int tt = warp * TPW + u;
+      if (tt >= cnt) break;
+      float pq[VD / 32], pk[VD / 32];
+#pragma unroll
+      for (int w = 0; w < VD / 32; ++w) {
+        const float x = q_[tt * KD + 32 * w + lane], y = k_[tt * KD + 32 * w + lane];
+        pq[w] = warp_sum(x * x);
+        pk[w] = warp_sum(y * y);
+      }
+      float rq = 0.f, rk = 0.f;
+#pragma unroll
+      for (int w = 0; w < VD / 32; ++w) { rq = lane == w ? pq[w] : rq; rk = lane == w ? pk[w] : rk; }
+      const float qn = warp_sum(rq), kn = warp_sum(rk);
+      if (lane == 0) {
+        const float bb = bab[tt * 2];
+        const float aa = bab[tt * 2 + 1] + dtb;
+        const float sp_ = aa > 20.f ? aa : log1pf(__expf(aa));
+        sc[tt * 4 + 0] = __expf(a_coef * sp_);
+        sc[tt * 4 + 1] = sigmoidf(bb);
+        sc[tt * 4 + 2] = rsqrtf(kn + 1e-6f);
+        sc[tt * 4 + 3] = rsqrtf(qn + 1e-6f) * rsqrtf((float)KD);
+      }
+    }
+    __syncthreads();
+    // ---- the recurrence: thread-local FMA chains, one shuffle per dot product
+    for (int tt = 0; tt < cnt; ++tt) {
+      const float g = sc[tt * 4 + 0], beta = sc[tt * 4 + 1], ksc = sc[tt * 4 + 2], qsc = sc[tt * 4 + 3];
+      const float* ks = k_ + tt * KD + h * HK;
+      const float* qs = q_ + tt * KD + h * HK;
+      const float v = v_[tt * VD + c];
+      float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
+#pragma unroll
+      for (int a = 0; a < HK; a += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(&ks[a]);
+        s[a] *= g; s[a + 1] *= g; s[a + 2] *= g; s[a + 3] *= g;
+        m0 = fmaf(s[a], k4.x, m0); m1 = fmaf(s[a + 1], k4.y, m1);
+        m2 = fmaf(s[a + 2], k4.z, m2); m3 = fmaf(s[a + 3], k4.w, m3);
+      }
+      float mine = (m0 + m1) + (m2 + m3);
+      float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+      const float kv_mem = (h == 0 ? mine + other : other + mine) * ksc;
+      const float delta = (v - kv_mem) * beta;
+      const float dk = delta * ksc;
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+      for (int a = 0; a < HK; a += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(&ks[a]);
+        const float4 q4 = *reinterpret_cast<const float4*>(&qs[a]);
+        s[a] = fmaf(k4.x, dk, s[a]); s[a + 1] = fmaf(k4.y, dk, s[a + 1]);
+        s[a + 2] = fmaf(k4.z, dk, s[a + 2]); s[a + 3] = fmaf(k4.w, dk, s[a + 3]);
+        o0 = fmaf(s[a], q4.x, o0); o1 = fmaf(s[a + 1], q4.y, o1);
+        o2 = fmaf(s[a + 2], q4.z, o2); o3 = fmaf(s[a + 3], q4.w, o3);
+      }
+      mine = (o0 + o1) + (o2 + o3);
+      other = __shfl_xor_sync(0xffffffffu, mine, 1);
+      const float o = (h == 0 ? mine + other : other + mine) * qsc;
+      if (h == 0) {
+        ob[tt * VD + c] = o;
+        sq[tt * VD + c] = o * o;
+      }
+      const int os = osl[tt];
+      if (os >= 0) {
+        float* dp = S + (((size_t)os * nv + vh) * KD + h * HK) * VD + c;
+#pragma unroll
+        for (int a = 0; a < HK; ++a) dp[(size_t)a * VD] = s[a];
+      }
+    }
+    __syncthreads();
+    // ---- output norm of the batch
+    for (int u = 0; u < TPW; ++u) {
+      const int tt = warp * TPW + u;
+      if (tt >= cnt) break;
+      const float ss = block_sum_by_warp<VD>(sq + tt * VD, lane);
+      if (lane == 0) ssb[tt] = ss;
+    }
+    __syncthreads();
+    for (int tt = h; tt < cnt; tt += 2) {
+      const float z = __bfloat162float(z_[tt * VD + c]);
+      out[((size_t)(base + tt) * nv + vh) * VD + c] =
+          f32_to_f16_sat(ob[tt * VD + c] * rsqrtf(ssb[tt] / (float)VD + eps) * nw * silu(z));
+    }
+  }
+}
+
+}  // namespace
+
 // bq / sfb / g0 / col_ctr (all or none): also emit each column's output row as the FP4 activation series for
 // the output projection; col_ctr is a zero-initialised counter per column that the kernel leaves zeroed.
 // Needs column index < 16, (nv * vd) % 16 == 0 and ldb * 2 >= nv * vd with ldb % 128 == 0.
@@ -234,6 +442,30 @@ extern "C" int vg_gdn_step(const float* qkv, const void* proj, int ldp, int off_
     launch_pdl(gdn_step_kernel<64, 64>, dim3(grid), dim3(64), 0, st, qkv, pj, ldp, off_z, off_b, off_a, S, A_log, dt_bias, norm_w, chain_start, chain_len, in_slot, parent, out_slot, o, nk, nv, eps, bqp, ldb, sfp, g0, col_ctr);
   else
     return -3;
+  return (int)cudaGetLastError();
+}
+
+// One linear chain of `tn` columns starting at column t0 (prefill): same results as vg_gdn_step on that chain.
+extern "C" int vg_gdn_prefill(const float* qkv, const void* proj, int ldp, int off_z, int off_b, int off_a, float* S,
+                              const float* A_log, const float* dt_bias, const float* norm_w, int t0, int tn,
+                              const int* in_slot, const int* out_slot, void* out_f16, int nk, int nv, int kd, int vd,
+                              float eps, cudaStream_t st) {
+  if (tn <= 0) return 0;
+  if (kd != 128 || vd != 128) return -3;
+  // 16-byte async copies: every staged row must start on a 16-byte boundary
+  if ((ldp % 8) != 0 || (off_z % 8) != 0 || (reinterpret_cast<uintptr_t>(proj) & 15) || (reinterpret_cast<uintptr_t>(qkv) & 15))
+    return -2;
+  constexpr int TB = 16;
+  const size_t smem = (size_t)(2 * TB * 128 * 3 + 2 * TB * 128 + TB * 4 + TB + TB * 2) * sizeof(float) + TB * sizeof(int) +
+                      (size_t)2 * TB * 128 * sizeof(__nv_bfloat16);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gdn_prefill_kernel<128, 128, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  launch_pdl(gdn_prefill_kernel<128, 128, TB>, dim3(nv), dim3(256), smem, st, qkv, static_cast<const __nv_bfloat16*>(proj), ldp,
+             off_z, off_b, off_a, S, A_log, dt_bias, norm_w, t0, tn, in_slot, out_slot, static_cast<__half*>(out_f16), nk, nv, eps);
   return (int)cudaGetLastError();
 }
 

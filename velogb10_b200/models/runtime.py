@@ -307,6 +307,7 @@ class GpuModel:
 
     def _gdn(self, ws: Workspace, L: LayerW, li: int, n: int, n_chains: int, seq_mode: bool, act=None):
         c, Gd = self.cfg, L.gdn
+        linear_chain = seq_mode and n_chains == 1 and ws is self.ws_prefill      # prefill plans are one linear chain
         gi = self.gdn_index[li]
         proj = ws.wide[:, :Gd.in_proj.m]
         conv_dim = Gd.conv_w.shape[0]
@@ -331,10 +332,17 @@ class GpuModel:
         if self._fp4_ok(Gd.out, n) and value_dim % 16 == 0:
             # the recurrence kernel quantises its own output rows for the output projection
             act_o = G.fp4_buffers(self.dev, Gd.out.kernel4.kp)
-        K.gdn_step(ws.conv_out, proj, conv_dim, conv_dim + value_dim, conv_dim + value_dim + Gd.nv, self.S[gi],
-                   Gd.A_log, Gd.dt_bias, Gd.norm, ws.chain_start, ws.chain_len, n_chains, ws.st_in, ws.parent,
-                   ws.st_out, g16, Gd.nk, Gd.nv, c.lin_k_dim, c.lin_v_dim, c.rms_eps,
-                   quant=act_o + (self.col_ctr,) if act_o is not None else None)
+        if linear_chain and n > 16 and c.lin_k_dim == 128 and c.lin_v_dim == 128 and proj.stride(0) % 8 == 0 \
+                and conv_dim % 8 == 0:
+            # prefill chunk: one chain through all n columns
+            K.gdn_prefill(ws.conv_out, proj, conv_dim, conv_dim + value_dim, conv_dim + value_dim + Gd.nv, self.S[gi],
+                          Gd.A_log, Gd.dt_bias, Gd.norm, 0, n, ws.st_in, ws.st_out, g16, Gd.nk, Gd.nv, c.lin_k_dim,
+                          c.lin_v_dim, c.rms_eps)
+        else:
+            K.gdn_step(ws.conv_out, proj, conv_dim, conv_dim + value_dim, conv_dim + value_dim + Gd.nv, self.S[gi],
+                       Gd.A_log, Gd.dt_bias, Gd.norm, ws.chain_start, ws.chain_len, n_chains, ws.st_in, ws.parent,
+                       ws.st_out, g16, Gd.nk, Gd.nv, c.lin_k_dim, c.lin_v_dim, c.rms_eps,
+                       quant=act_o + (self.col_ctr,) if act_o is not None else None)
         self._row_parallel(Gd.out, g16, n, ws.delta, act=act_o)
 
     def _mlp(self, ws: Workspace, M, n: int, out: torch.Tensor, reduce: bool = True, act=None):
