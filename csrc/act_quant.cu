@@ -117,11 +117,14 @@ __global__ void __launch_bounds__(512) act_quant_kernel(const void* __restrict__
 }
 
 // residual += delta; y = rmsnorm(residual) * (1 + w); emit y as FP4 terms (and optionally as f16).
+// AR: delta is not a tensor but the sum over ranks of the fp32 partial rows in this rank's receive slots
+// (pushed there by every rank's row-parallel GEMM); the kernel waits for the tile flags and sums in rank order.
+template <bool AR>
 __global__ void __launch_bounds__(512) add_rmsnorm_fp4_kernel(__nv_bfloat16* res, const __nv_bfloat16* delta, const float* w,
                                                                 int h, float eps, int plus_one, int ld_res, int ld_delta,
                                                                 int Kpad, uint8_t* __restrict__ bq, int ldb,
                                                                 uint8_t* __restrict__ sfb, float* __restrict__ g0,
-                                                                __half* __restrict__ out16) {
+                                                                __half* __restrict__ out16, const VgCommCtx c) {
   __shared__ float red[32];
   if (threadIdx.x == 0) trace(16);
   pdl_trigger();
@@ -137,8 +140,14 @@ __global__ void __launch_bounds__(512) add_rmsnorm_fp4_kernel(__nv_bfloat16* res
   if (threadIdx.x == 0) trace(17);
   const int n = blockIdx.x;
   __nv_bfloat16* rp = res + (size_t)n * ld_res;
-  const __nv_bfloat16* dp = delta ? delta + (size_t)n * ld_delta : nullptr;
+  const __nv_bfloat16* dp = (!AR && delta) ? delta + (size_t)n * ld_delta : nullptr;
   const int nblk = Kpad >> 4, hblk = h >> 4;
+  uint32_t ar_e = 0;
+  int ar_set = 0;
+  if (AR) {
+    ar_e = *c.epoch + 1;
+    ar_set = ar_e & 1;
+  }
   float r[MAXB][16];
   float ss = 0.f;
 #pragma unroll
@@ -148,27 +157,55 @@ __global__ void __launch_bounds__(512) add_rmsnorm_fp4_kernel(__nv_bfloat16* res
     for (int i = 0; i < 16; ++i) r[j][i] = 0.f;
     if (b < hblk) {
       const uint4 a0 = reinterpret_cast<const uint4*>(rp + b * 16)[0], a1 = reinterpret_cast<const uint4*>(rp + b * 16)[1];
-      uint4 d0 = make_uint4(0, 0, 0, 0), d1 = d0;
-      if (dp) { d0 = reinterpret_cast<const uint4*>(dp + b * 16)[0]; d1 = reinterpret_cast<const uint4*>(dp + b * 16)[1]; }
       const __nv_bfloat16* x0 = reinterpret_cast<const __nv_bfloat16*>(&a0);
       const __nv_bfloat16* x1 = reinterpret_cast<const __nv_bfloat16*>(&a1);
-      const __nv_bfloat16* y0 = reinterpret_cast<const __nv_bfloat16*>(&d0);
-      const __nv_bfloat16* y1 = reinterpret_cast<const __nv_bfloat16*>(&d1);
+      float dv[16];
+      bool have_d = dp != nullptr;
+      if (AR) {
+        // the 16 elements lie in one 128-row GEMM tile: wait for that tile's flag from every rank
+        const int tile = (b * 16) >> 7;
+        const uint32_t* fl = reinterpret_cast<const uint32_t*>(c.data[c.rank] + c.flags_off);
+        bool ok = true;
+        for (int q = 0; q < c.world; ++q) ok = wait_flag(fl + flag_index(ar_set, q, tile), ar_e, c.timeout_ns) && ok;
+        if (!ok) atomicCAS(c.status, 0, VG_ERR_PEER_WAIT);
+        const float* base = reinterpret_cast<const float*>(c.data[c.rank] + c.slots_off + (size_t)ar_set * MAX_RANKS * c.slot_bytes);
+        const size_t stride = c.slot_bytes / sizeof(float);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) dv[i] = 0.f;
+        for (int q = 0; q < c.world; ++q) {
+          const float4* src = reinterpret_cast<const float4*>(base + (size_t)q * stride + (size_t)n * h + b * 16);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float4 f = __ldcg(src + i);
+            dv[4 * i] += f.x; dv[4 * i + 1] += f.y; dv[4 * i + 2] += f.z; dv[4 * i + 3] += f.w;
+          }
+        }
+        // the unfused path stores the sum as bf16 before the residual add: keep the same rounding
+#pragma unroll
+        for (int i = 0; i < 16; ++i) dv[i] = __bfloat162float(__float2bfloat16_rn(dv[i]));
+        have_d = true;
+      } else if (dp) {
+        const uint4 d0 = reinterpret_cast<const uint4*>(dp + b * 16)[0], d1 = reinterpret_cast<const uint4*>(dp + b * 16)[1];
+        const __nv_bfloat16* y0 = reinterpret_cast<const __nv_bfloat16*>(&d0);
+        const __nv_bfloat16* y1 = reinterpret_cast<const __nv_bfloat16*>(&d1);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { dv[i] = __bfloat162float(y0[i]); dv[8 + i] = __bfloat162float(y1[i]); }
+      }
       uint4 u0, u1;
       __nv_bfloat16* o0 = reinterpret_cast<__nv_bfloat16*>(&u0);
       __nv_bfloat16* o1 = reinterpret_cast<__nv_bfloat16*>(&u1);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         float v0 = __bfloat162float(x0[i]), v1 = __bfloat162float(x1[i]);
-        if (dp) {
-          o0[i] = __float2bfloat16_rn(v0 + __bfloat162float(y0[i]));
-          o1[i] = __float2bfloat16_rn(v1 + __bfloat162float(y1[i]));
+        if (have_d) {
+          o0[i] = __float2bfloat16_rn(v0 + dv[i]);
+          o1[i] = __float2bfloat16_rn(v1 + dv[8 + i]);
           v0 = __bfloat162float(o0[i]); v1 = __bfloat162float(o1[i]);
         }
         r[j][i] = v0; r[j][8 + i] = v1;
         ss += v0 * v0 + v1 * v1;
       }
-      if (dp) { reinterpret_cast<uint4*>(rp + b * 16)[0] = u0; reinterpret_cast<uint4*>(rp + b * 16)[1] = u1; }
+      if (have_d) { reinterpret_cast<uint4*>(rp + b * 16)[0] = u0; reinterpret_cast<uint4*>(rp + b * 16)[1] = u1; }
     }
   }
   ss = block_sum(ss, red);
@@ -200,6 +237,14 @@ __global__ void __launch_bounds__(512) add_rmsnorm_fp4_kernel(__nv_bfloat16* res
   for (int j = 0; j < MAXB; ++j) {
     const int b = threadIdx.x + j * blockDim.x;
     if (b < nblk) quant_block(r[j], g, n, b, bq, ldb, sfb);
+  }
+  if (AR) {
+    // every row has consumed the slots: the last CTA publishes the epoch for the next collective
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      if (atomicAdd(c.done_ctr, 1u) == gridDim.x - 1) { *c.done_ctr = 0; *c.epoch = ar_e; }
+    }
   }
   if (threadIdx.x == 0) trace(1 * 16 + 2);
 }
@@ -245,10 +290,22 @@ extern "C" int vg_add_rmsnorm_fp4(void* res, const void* delta, const float* w, 
   if (N < 1 || N > 16 || (ldb % 128) != 0 || Kpad < h || (h % 16) != 0 || (ld_res % 8) != 0 || (ld_delta % 8) != 0 ||
       (Kpad >> 4) > MAX_THREADS * MAXB)
     return -2;
-  return (int)launch_pdl(add_rmsnorm_fp4_kernel, dim3(N), dim3(threads_for(Kpad >> 4)), 0, st,
+  return (int)launch_pdl(add_rmsnorm_fp4_kernel<false>, dim3(N), dim3(threads_for(Kpad >> 4)), 0, st,
                          static_cast<__nv_bfloat16*>(res), static_cast<const __nv_bfloat16*>(delta), w, h, eps, plus_one,
                          ld_res, ld_delta, Kpad, static_cast<uint8_t*>(bq), ldb, static_cast<uint8_t*>(sfb), g0,
-                         static_cast<__half*>(out16));
+                         static_cast<__half*>(out16), VgCommCtx{});
+}
+
+extern "C" int vg_add_rmsnorm_fp4_ar(void* res, const float* w, int N, int h, float eps, int plus_one, int ld_res, void* bq,
+                                     int ldb, void* sfb, float* g0, void* out16, const VgCommCtx* ctx, cudaStream_t st) {
+  const int Kpad = ldb * 2;
+  if (!ctx || ctx->world < 2 || N < 1 || N > 16 || (ldb % 128) != 0 || Kpad < h || (h % 16) != 0 || (ld_res % 8) != 0 ||
+      (Kpad >> 4) > MAX_THREADS * MAXB)
+    return -2;
+  if ((h + 127) / 128 > MAX_CTAS || (unsigned long long)N * h * 4ull > ctx->slot_bytes) return -5;
+  return (int)launch_pdl(add_rmsnorm_fp4_kernel<true>, dim3(N), dim3(threads_for(Kpad >> 4)), 0, st,
+                         static_cast<__nv_bfloat16*>(res), (const __nv_bfloat16*)nullptr, w, h, eps, plus_one, ld_res, 0, Kpad,
+                         static_cast<uint8_t*>(bq), ldb, static_cast<uint8_t*>(sfb), g0, static_cast<__half*>(out16), *ctx);
 }
 
 VG_TRACE_SETTER(vg_trace_set_act_quant)

@@ -48,8 +48,13 @@ int vg_swiglu_fp4(const void* gu, int ld, int N, int I, void* bq, int ldb, void*
 int vg_add_rmsnorm_fp4(void* res, const void* delta, const float* w, int N, int h, float eps, int plus_one, int ld_res,
                        int ld_delta, void* bq, int ldb, void* sfb, float* g0, void* out16, cudaStream_t stream);
 int vg_gemm_fp4(const void* wt, const float* row_scale, const void* bq, int ldb, const void* sfb, const float* g0, void* out,
-                int out_f32, int M, int K, int N, int ldo, int splitk, int* err, const VgCommCtx* ar_ctx,
+                int out_f32, int M, int K, int N, int ldo, int splitk, int* err, const VgCommCtx* ar_ctx, int ar_push_only,
                 const VgConvEpi* conv, cudaStream_t stream);
+// Residual add + RMSNorm + FP4 quantisation whose `delta` is the tensor-parallel sum of the partial rows a
+// preceding vg_gemm_fp4(..., ar_push_only = 1) pushed into every rank's receive slots: waits for each
+// rank's tile flags (bounded), adds the partials in rank order, then proceeds as vg_add_rmsnorm_fp4.
+int vg_add_rmsnorm_fp4_ar(void* res, const float* w, int N, int h, float eps, int plus_one, int ld_res, void* bq, int ldb,
+                          void* sfb, float* g0, void* out16, const VgCommCtx* ctx, cudaStream_t stream);
 int vg_gemm_tc_grouped(const void* wt, const float* row_scale, const void* x_f16, int x_rows, int ldx, void* out, int out_f32,
                        int M, int K, int ldo, int wfmt, int bn, int max_items, const int* g_exp, const int* g_off,
                        const int* g_cnt, const int* tilemap, const int* n_items, int x_div, int* err, cudaStream_t stream);

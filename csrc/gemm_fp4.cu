@@ -291,8 +291,19 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
           if (n < p.N) dst[(size_t)n * p.M + m] = y[n] * p.g0[n] * rsc;
       }
     }
+    if (p.ar == 2) {
+      // Push only: the partial tiles and their flags go out and the kernel ends; the residual-add / RMSNorm
+      // kernel that follows waits for every rank's flag and does the rank-order sum while it loads its rows.
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (et == 0) trace(4 * 16 + 6);
+      if (et < c.world) {
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<uint32_t*>(c.data[et] + c.flags_off) + flag_index(set, c.rank, (int)blockIdx.x), e);
+      }
+    } else {
     __threadfence_system();
     asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (et == 0) trace(4 * 16 + 6);
     if (et < c.world)
       st_release_sys(reinterpret_cast<uint32_t*>(c.data[et] + c.flags_off) + flag_index(set, c.rank, (int)blockIdx.x), e);
     if (et < c.world) {
@@ -300,6 +311,7 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
       if (!wait_flag(f, e, c.timeout_ns)) { atomicCAS(c.status, 0, VG_ERR_PEER_WAIT); ar_failed = 1; }
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (et == 0) trace(4 * 16 + 7);
     if (!ar_failed && have && m < p.M) {
       const float* base = reinterpret_cast<const float*>(c.data[c.rank] + c.slots_off + (size_t)set * MAX_RANKS * c.slot_bytes);
       const size_t stride = c.slot_bytes / sizeof(float);
@@ -318,6 +330,7 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
     if (et == 0) {
       __threadfence();
       if (atomicAdd(c.done_ctr, 1u) == gridDim.x - 1) { *c.done_ctr = 0; *c.epoch = e; }
+    }
     }
   } else if (epi && have && z == 0 && m < p.M) {
     const float rsc = p.row_scale ? p.row_scale[m] : 1.0f;
@@ -594,7 +607,7 @@ int get_tmap_b(const void* bq, int ldb, CUtensorMap* out) {
 
 extern "C" int vg_gemm_fp4(const void* wt, const float* row_scale, const void* bq, int ldb, const void* sfb, const float* g0,
                            void* out, int out_f32, int M, int K, int N, int ldo, int splitk, int* err,
-                           const VgCommCtx* ar_ctx, const VgConvEpi* conv, cudaStream_t stream) {
+                           const VgCommCtx* ar_ctx, int ar_push_only, const VgConvEpi* conv, cudaStream_t stream) {
   if (M <= 0 || K <= 0 || N < 1 || N > 16 || splitk < 1 || splitk > 8 || (ldb % 128) != 0) return -2;
   Fp4Params p;
   p.wt = static_cast<const uint8_t*>(wt);
@@ -616,7 +629,7 @@ extern "C" int vg_gemm_fp4(const void* wt, const float* row_scale, const void* b
   }
   if (ar_ctx && ar_ctx->world > 1) {
     if ((M + BM - 1) / BM > MAX_CTAS || (unsigned long long)N * M * 4ull > ar_ctx->slot_bytes) return -5;
-    p.ar = 1;
+    p.ar = ar_push_only ? 2 : 1;
     p.comm = *ar_ctx;
   }
   if (splitk > p.ks_total) splitk = p.ks_total;

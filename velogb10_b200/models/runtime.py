@@ -160,6 +160,9 @@ class GpuModel:
         self.fuse_allreduce = os.environ.get("VELO_NO_FUSED_ALLREDUCE", "0") != "1"
         # decode / verify widths run NVFP4 linears on the block-scaled FP4 tensor-core kernel
         self.use_fp4 = os.environ.get("VELO_NO_FP4_MMA", "0") != "1"
+        # tensor-parallel decode: row-parallel GEMMs push partial rows, the following norm kernel sums them
+        self.split_allreduce = os.environ.get("VELO_NO_SPLIT_ALLREDUCE", "0") != "1"
+        self._pending_ar = False
         _lib.lib()
         with torch.cuda.device(self.dev):
             for name, q in weights.linears():
@@ -268,7 +271,12 @@ class GpuModel:
 
     def _norm(self, ws: Workspace, delta, w: torch.Tensor, n: int):
         """Residual add + RMSNorm into ``ws.xn16``; at decode widths the same kernel also emits the FP4
-        activation series, returned for the linears that read this input."""
+        activation series, returned for the linears that read this input. When the preceding row-parallel
+        linear only pushed its partial rows (``self._pending_ar``), the kernel also performs the
+        tensor-parallel sum."""
+        if self._pending_ar:
+            self._pending_ar = False
+            return G.add_rmsnorm_fp4_ar(ws.x, w, self.cfg.rms_eps, n, self.comm, out16=ws.xn16)
         if self.use_fp4 and n <= 16 and ws.x.shape[1] % 16 == 0:
             return G.add_rmsnorm_fp4(ws.x, delta, w, self.cfg.rms_eps, n, out16=ws.xn16)
         K.add_rmsnorm(ws.x, delta, w, self.cfg.rms_eps, n, out16=ws.xn16)
@@ -287,6 +295,12 @@ class GpuModel:
         then the two-shot peer-memory all-reduce."""
         tp = reduce and self.comm is not None and self.comm.world > 1
         if tp and n <= 16 and not self.comm.use_nccl and self.fuse_allreduce and (q.m + 127) // 128 <= 64:
+            # (a reduced row-parallel output is always the delta the next residual-add / RMSNorm consumes)
+            if self.split_allreduce and self._fp4_ok(q, n) and q.m == self.cfg.hidden_size and q.m % 16 == 0:
+                # push the partial rows; the next residual-add / RMSNorm kernel sums them
+                G.linear_fp4(q, x16, n, out=out, comm=self.comm, act=act, push_only=True)
+                self._pending_ar = True
+                return
             self._linear(q, x16, n, out, act=act, comm=self.comm)
             return
         self._linear(q, x16, n, out, act=act)
