@@ -162,23 +162,34 @@ __global__ void __launch_bounds__(512) add_rmsnorm_fp4_kernel(__nv_bfloat16* res
       float dv[16];
       bool have_d = dp != nullptr;
       if (AR) {
-        // the 16 elements lie in one 128-row GEMM tile: wait for that tile's flag from every rank
-        const int tile = (b * 16) >> 7;
-        const uint32_t* fl = reinterpret_cast<const uint32_t*>(c.data[c.rank] + c.flags_off);
-        bool ok = true;
-        for (int q = 0; q < c.world; ++q) ok = wait_flag(fl + flag_index(ar_set, q, tile), ar_e, c.timeout_ns) && ok;
-        if (!ok) atomicCAS(c.status, 0, VG_ERR_PEER_WAIT);
-        const float* base = reinterpret_cast<const float*>(c.data[c.rank] + c.slots_off + (size_t)ar_set * MAX_RANKS * c.slot_bytes);
-        const size_t stride = c.slot_bytes / sizeof(float);
+        // Pull every rank's (value, epoch) pairs for these 16 elements (peer memory for the others) and take
+        // them once all 16 carry this collective's epoch; sum in rank order. Bounded by the context's timeout.
+        const size_t stride = c.slot_bytes;
 #pragma unroll
         for (int i = 0; i < 16; ++i) dv[i] = 0.f;
         for (int q = 0; q < c.world; ++q) {
-          const float4* src = reinterpret_cast<const float4*>(base + (size_t)q * stride + (size_t)n * h + b * 16);
+          const uint4* src = reinterpret_cast<const uint4*>(c.data[q] + c.slots_off + (size_t)(ar_set * MAX_RANKS + q) * stride) +
+                             (((size_t)n * h + b * 16) >> 1);
+          uint4 v[8];
+          uint64_t t_start = 0;
+          for (int tries = 0;; ++tries) {
+            bool ok = true;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float4 f = __ldcg(src + i);
-            dv[4 * i] += f.x; dv[4 * i + 1] += f.y; dv[4 * i + 2] += f.z; dv[4 * i + 3] += f.w;
+            for (int i = 0; i < 8; ++i) {
+              asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(v[i].x), "=r"(v[i].y), "=r"(v[i].z), "=r"(v[i].w) : "l"(src + i) : "memory");
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ok = ok && v[i].y == ar_e && v[i].w == ar_e;
+            if (ok) break;
+            if (tries == 64) t_start = global_ns();
+            if (tries > 64 && (tries & 63) == 0 && global_ns() - t_start > c.timeout_ns) {
+              atomicCAS(c.status, 0, VG_ERR_PEER_WAIT);
+              break;
+            }
           }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { dv[2 * i] += __uint_as_float(v[i].x); dv[2 * i + 1] += __uint_as_float(v[i].z); }
         }
         // the unfused path stores the sum as bf16 before the residual add: keep the same rounding
 #pragma unroll
@@ -302,7 +313,7 @@ extern "C" int vg_add_rmsnorm_fp4_ar(void* res, const float* w, int N, int h, fl
   if (!ctx || ctx->world < 2 || N < 1 || N > 16 || (ldb % 128) != 0 || Kpad < h || (h % 16) != 0 || (ld_res % 8) != 0 ||
       (Kpad >> 4) > MAX_THREADS * MAXB)
     return -2;
-  if ((h + 127) / 128 > MAX_CTAS || (unsigned long long)N * h * 4ull > ctx->slot_bytes) return -5;
+  if ((unsigned long long)N * h * 8ull > ctx->slot_bytes) return -5;
   return (int)launch_pdl(add_rmsnorm_fp4_kernel<true>, dim3(N), dim3(threads_for(Kpad >> 4)), 0, st,
                          static_cast<__nv_bfloat16*>(res), (const __nv_bfloat16*)nullptr, w, h, eps, plus_one, ld_res, 0, Kpad,
                          static_cast<uint8_t*>(bq), ldb, static_cast<uint8_t*>(sfb), g0, static_cast<__half*>(out16), *ctx);

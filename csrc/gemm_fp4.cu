@@ -282,7 +282,7 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
     const int et = threadIdx.x - 128;
     const float rsc = (p.row_scale && m < p.M) ? p.row_scale[m] : 1.0f;
     if (et == 0) ar_failed = 0;
-    if (have && m < p.M) {
+    if (p.ar != 2 && have && m < p.M) {
       for (int k = 0; k < c.world; ++k) {
         const int peer = (c.rank + k) % c.world;
         float* dst = reinterpret_cast<float*>(c.data[peer] + c.slots_off + (size_t)(set * MAX_RANKS + c.rank) * c.slot_bytes);
@@ -292,14 +292,20 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
       }
     }
     if (p.ar == 2) {
-      // Push only: the partial tiles and their flags go out and the kernel ends; the residual-add / RMSNorm
-      // kernel that follows waits for every rank's flag and does the rank-order sum while it loads its rows.
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (et == 0) trace(4 * 16 + 6);
-      if (et < c.world) {
-        __threadfence_system();
-        st_release_sys(reinterpret_cast<uint32_t*>(c.data[et] + c.flags_off) + flag_index(set, c.rank, (int)blockIdx.x), e);
+      // Publish only: every value goes into this rank's own slot as an 8-byte (value, epoch) pair, one store, no
+      // fence; the residual-add / RMSNorm kernel that follows pulls the pairs of every rank over NVLink, takes a
+      // pair once its epoch matches and sums in rank order. Nothing remote is written, so this kernel's
+      // completion does not wait for NVLink round trips.
+      uint2* dst = reinterpret_cast<uint2*>(c.data[c.rank] + c.slots_off + (size_t)(set * MAX_RANKS + c.rank) * c.slot_bytes);
+      if (have && m < p.M) {
+#pragma unroll
+        for (int n = 0; n < 16; ++n)
+          if (n < p.N) {
+            const uint32_t bits = __float_as_uint(y[n] * p.g0[n] * rsc);
+            asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst + (size_t)n * p.M + m), "r"(bits), "r"(e) : "memory");
+          }
       }
+      if (et == 0) trace(4 * 16 + 6);
     } else {
     __threadfence_system();
     asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -628,7 +634,7 @@ extern "C" int vg_gemm_fp4(const void* wt, const float* row_scale, const void* b
     p.conv = *conv;
   }
   if (ar_ctx && ar_ctx->world > 1) {
-    if ((M + BM - 1) / BM > MAX_CTAS || (unsigned long long)N * M * 4ull > ar_ctx->slot_bytes) return -5;
+    if ((M + BM - 1) / BM > MAX_CTAS || (unsigned long long)N * M * 8ull > ar_ctx->slot_bytes) return -5;
     p.ar = ar_push_only ? 2 : 1;
     p.comm = *ar_ctx;
   }
