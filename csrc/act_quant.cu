@@ -162,13 +162,14 @@ __global__ void __launch_bounds__(512) add_rmsnorm_fp4_kernel(__nv_bfloat16* res
       float dv[16];
       bool have_d = dp != nullptr;
       if (AR) {
-        // Pull every rank's (value, epoch) pairs for these 16 elements (peer memory for the others) and take
-        // them once all 16 carry this collective's epoch; sum in rank order. Bounded by the context's timeout.
+        // Every rank stored its (value, epoch) pairs for these 16 elements into this rank's receive slots: poll
+        // them (local memory) and take them once all 16 carry this collective's epoch; sum in rank order.
+        // Bounded by the context's timeout.
         const size_t stride = c.slot_bytes;
 #pragma unroll
         for (int i = 0; i < 16; ++i) dv[i] = 0.f;
         for (int q = 0; q < c.world; ++q) {
-          const uint4* src = reinterpret_cast<const uint4*>(c.data[q] + c.slots_off + (size_t)(ar_set * MAX_RANKS + q) * stride) +
+          const uint4* src = reinterpret_cast<const uint4*>(c.data[c.rank] + c.slots_off + (size_t)(ar_set * MAX_RANKS + q) * stride) +
                              (((size_t)n * h + b * 16) >> 1);
           uint4 v[8];
           uint64_t t_start = 0;

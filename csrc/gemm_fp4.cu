@@ -292,18 +292,20 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
       }
     }
     if (p.ar == 2) {
-      // Publish only: every value goes into this rank's own slot as an 8-byte (value, epoch) pair, one store, no
-      // fence; the residual-add / RMSNorm kernel that follows pulls the pairs of every rank over NVLink, takes a
-      // pair once its epoch matches and sums in rank order. Nothing remote is written, so this kernel's
-      // completion does not wait for NVLink round trips.
-      uint2* dst = reinterpret_cast<uint2*>(c.data[c.rank] + c.slots_off + (size_t)(set * MAX_RANKS + c.rank) * c.slot_bytes);
+      // Publish only: every value goes to every rank's receive slot (this rank's own included) as an 8-byte
+      // (value, epoch) pair: one store each, no fence and no flag lines. The residual-add / RMSNorm kernel that
+      // follows polls its own memory, takes a pair once its epoch matches and sums in rank order.
       if (have && m < p.M) {
+        for (int k = 0; k < c.world; ++k) {
+          const int peer = (c.rank + k) % c.world;
+          uint2* dst = reinterpret_cast<uint2*>(c.data[peer] + c.slots_off + (size_t)(set * MAX_RANKS + c.rank) * c.slot_bytes);
 #pragma unroll
-        for (int n = 0; n < 16; ++n)
-          if (n < p.N) {
-            const uint32_t bits = __float_as_uint(y[n] * p.g0[n] * rsc);
-            asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst + (size_t)n * p.M + m), "r"(bits), "r"(e) : "memory");
-          }
+          for (int n = 0; n < 16; ++n)
+            if (n < p.N) {
+              const uint32_t bits = __float_as_uint(y[n] * p.g0[n] * rsc);
+              asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst + (size_t)n * p.M + m), "r"(bits), "r"(e) : "memory");
+            }
+        }
       }
       if (et == 0) trace(4 * 16 + 6);
     } else {
