@@ -77,6 +77,11 @@ int vg_embed_gather(const void* table, const void* scales, const float* row_scal
 int vg_attn_decode(const void* q, const void* kc, const void* vc, const int* lens, const int* slots, const int* base,
                    const int* path, int path_ld, float* part, int N, int nh, int nkv, int hd, int max_seq, int ns_grid,
                    int direct, const void* gate, int ld_gate, void* out, cudaStream_t stream);
+int vg_attn_transpose_v(const void* vc, void* vT, int slot, int nkv, int hd, int max_seq, int len, int vt_cap,
+                        cudaStream_t stream);
+int vg_attn_prefill_tc(const void* q, int q_cap, const void* kc, const void* vT, int vt_cap, int slot, int nkv, int nh,
+                       int hd, int max_seq, int pos0, int n, float scale, const void* gate, int ld_gate, void* out_f16,
+                       int* err, cudaStream_t stream);
 long long vg_attn_scratch_floats(int N, int nh, int hd, int ns_grid);
 
 int vg_gdn_conv(const void* x, int ldx, float* state, const float* w, const int* in_slot, const int* parent,

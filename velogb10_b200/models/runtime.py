@@ -163,6 +163,9 @@ class GpuModel:
         # tensor-parallel decode: row-parallel GEMMs push partial rows, the following norm kernel sums them
         self.split_allreduce = os.environ.get("VELO_NO_SPLIT_ALLREDUCE", "0") != "1"
         self._pending_ar = False
+        self.tc_prefill_attn = os.environ.get("VELO_NO_TC_PREFILL_ATTN", "0") != "1"
+        self._prefill_ctx = None              # (slot, first position) while a prefill chunk is running
+        self._vt = None
         _lib.lib()
         with torch.cuda.device(self.dev):
             for name, q in weights.linears():
@@ -307,6 +310,13 @@ class GpuModel:
         if tp:
             self._reduce(out, n)
 
+    def _vt_scratch(self, nkv: int, max_seq: int) -> torch.Tensor:
+        """Transposed-value scratch ``[nkv, head_dim, keys]`` of the lane being prefilled (shared by all layers)."""
+        cap = (max_seq + 127) // 128 * 128
+        if self._vt is None or self._vt.shape[0] < nkv or self._vt.shape[2] != cap:
+            self._vt = torch.zeros((nkv, self.cfg.head_dim, cap), dtype=torch.bfloat16, device=self.dev)
+        return self._vt[:nkv]
+
     def _attn(self, ws: Workspace, L: LayerW, n: int, kc, vc, plan_direct: bool, use_path: bool, act=None):
         c, A = self.cfg, L.attn
         qkv = ws.wide[:, :A.qkv.m]
@@ -314,9 +324,17 @@ class GpuModel:
         K.attn_prep(qkv, A.q_norm, A.k_norm, ws.pos, ws.kv_slot, ws.kv_row, ws.q, kc, vc, n, A.nh, A.nkv,
                     c.head_dim, c.rotary_dim, c.rms_eps, c.rope_theta, c.attn_out_gate)
         a16 = ws.a16(A.o.k)
-        K.attn_decode(ws.q, kc, vc, ws.lens, ws.kv_slot, self.attn_part, a16, n, A.nh, A.nkv, c.head_dim,
-                      gate=qkv if c.attn_out_gate else None, base=ws.base if use_path else None,
-                      path=ws.path if use_path else None, ns_grid=self.ns_grid, direct=plan_direct)
+        pf = self._prefill_ctx
+        if plan_direct and pf is not None and n >= 64 and c.head_dim == 256 and self.tc_prefill_attn \
+                and qkv.stride(0) % 8 == 0:
+            # prefill chunk of one lane: tensor-core flash attention over the lane's cache rows
+            slot, pos0 = pf
+            K.attn_prefill_tc(ws.q, kc, vc, self._vt_scratch(A.nkv, kc.shape[2]), slot, pos0, n, A.nh, A.nkv, c.head_dim,
+                              a16, gate=qkv if c.attn_out_gate else None)
+        else:
+            K.attn_decode(ws.q, kc, vc, ws.lens, ws.kv_slot, self.attn_part, a16, n, A.nh, A.nkv, c.head_dim,
+                          gate=qkv if c.attn_out_gate else None, base=ws.base if use_path else None,
+                          path=ws.path if use_path else None, ns_grid=self.ns_grid, direct=plan_direct)
         self._row_parallel(A.o, a16, n, ws.delta)
 
     def _gdn(self, ws: Workspace, L: LayerW, li: int, n: int, n_chains: int, seq_mode: bool, act=None):
@@ -459,7 +477,11 @@ class GpuModel:
             last = o + n >= N
             plan = Plan.chain(slot, toks, pos_start + o, None, final_to_slot=True, direct_attn=True)
             self._upload(ws, plan)
-            self._backbone(ws, n, 1, True, True, False, (n - 1, n) if last else (0, 0))
+            self._prefill_ctx = (slot, pos_start + o)
+            try:
+                self._backbone(ws, n, 1, True, True, False, (n - 1, n) if last else (0, 0))
+            finally:
+                self._prefill_ctx = None
             if want_hidden:
                 hs.append(ws.x[:n].clone())
             if last:

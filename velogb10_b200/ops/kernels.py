@@ -76,6 +76,22 @@ def attn_decode(q, kc, vc, lens, slots, part, out16, n, nh, nkv, hd, gate=None, 
     _lib.check(rc, "vg_attn_decode", 1 if direct else 2)
 
 
+def attn_prefill_tc(q, kc, vc, vT, slot: int, pos0: int, n: int, nh: int, nkv: int, hd: int, out16, gate=None):
+    """Causal prefill attention on the tensor cores for one lane: queries ``q[:n]`` (bf16 ``[cap, nh*hd]``) at
+    positions ``pos0 ..``, keys / values = the lane's cache rows ``[0, pos0 + n)``. ``vT`` is the transposed-value
+    scratch ``[nkv, hd, cap_keys]`` this call refreshes first."""
+    max_seq = kc.shape[2]
+    L = _lib.lib()
+    rc = L.vg_attn_transpose_v(ptr(vc), ptr(vT), c_int(slot), c_int(nkv), c_int(hd), c_int(max_seq), c_int(pos0 + n),
+                               c_int(vT.shape[2]), stream())
+    _lib.check(rc, "vg_attn_transpose_v")
+    rc = L.vg_attn_prefill_tc(ptr(q), c_int(q.shape[0]), ptr(kc), ptr(vT), c_int(vT.shape[2]), c_int(slot), c_int(nkv),
+                              c_int(nh), c_int(hd), c_int(max_seq), c_int(pos0), c_int(n), c_float(hd ** -0.5),
+                              ptr(gate), c_int(gate.stride(0) if gate is not None else 0), ptr(out16),
+                              ptr(_lib.err_word(q.device)), stream())
+    _lib.check(rc, "vg_attn_prefill_tc")
+
+
 def gdn_conv(x, state, w, in_slot, parent, out_slot, out, n, conv_dim, ck, phase: int = 3):
     rc = _lib.lib().vg_gdn_conv(ptr(x), c_int(x.stride(0)), ptr(state), ptr(w), ptr(in_slot), ptr(parent),
                                 ptr(out_slot), ptr(out), c_int(n), c_int(conv_dim), c_int(ck), c_int(phase), stream())
