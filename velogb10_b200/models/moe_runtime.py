@@ -71,6 +71,15 @@ def _grouped(tw, m_per_expert, x16, out, bn, max_items, g_exp, g_off, g_cnt, til
     _lib.check(rc, "vg_gemm_tc_grouped")
 
 
+def _small_linear(q, x16, n: int, out):
+    """Router / shared-gate logits (fp32): the CUDA-core GEMV at decode widths, the tensor-core GEMM over f16
+    tiles of the same weights for prefill widths (the GEMV walks the columns one by one)."""
+    if n > 16 and getattr(q, "kernel", None) is not None:
+        G.linear(q, x16, n, out=out, out_f32=True)
+    else:
+        G.linear_simt(q, x16, n, out=out, out_f32=True)
+
+
 def moe_forward(model, ws, M: MoeW, n: int, act=None):
     """Reads ws.xn16[:n] (normed hidden, f16); writes the FFN output into ws.delta[:n] (bf16)."""
     cfg = model.cfg
@@ -78,7 +87,7 @@ def moe_forward(model, ws, M: MoeW, n: int, act=None):
     E, topk, I, h = cfg.num_experts, cfg.num_experts_per_tok, cfg.moe_intermediate_size, cfg.hidden_size
     b = _buffers(model, ws, M)
     gu_w, dn_w = _prep_experts(M.gate_up), _prep_experts(M.down)
-    G.linear_simt(M.router, ws.xn16, n, out=b.logits, out_f32=True)
+    _small_linear(M.router, ws.xn16, n, b.logits)
     P = n * topk
     decode = ws.cap <= DECODE_MAX
     rc = L.vg_moe_router(ptr(b.logits), c_int(n), c_int(E), c_int(topk), c_int(1 if cfg.router_sigmoid else 0),
@@ -116,7 +125,7 @@ def moe_forward(model, ws, M: MoeW, n: int, act=None):
         model._mlp(ws, M.shared, n, b.shared, reduce=False, act=act)
         shared = b.shared
         if M.shared_gate is not None:
-            G.linear_simt(M.shared_gate, ws.xn16, n, out=b.gate_logit, out_f32=True)
+            _small_linear(M.shared_gate, ws.xn16, n, b.gate_logit)
             gate = b.gate_logit
     ep = model.comm is not None and model.comm.world > 1 and M.n_local < E
     rc = L.vg_moe_combine(ptr(b.y), c_int(b.y.stride(0)), ptr(inv), ptr(b.wts), c_int(n), c_int(topk),

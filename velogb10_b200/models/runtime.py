@@ -178,6 +178,9 @@ class GpuModel:
                             G.prepare_fp4(q)
                         G.prepare(q, keep_canonical=True)
                     continue
+                if small and q.experts <= 1 and q.w is not None and name.endswith(("router", "shared_gate")):
+                    G.prepare(q, keep_canonical=True)        # f16 tiles for prefill widths; decode keeps the GEMV
+                    continue
                 if small or q.experts > 1:
                     continue
                 if self.use_fp4 and q.fmt == "nvfp4" and q.packed is not None:
