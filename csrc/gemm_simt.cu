@@ -63,6 +63,8 @@ template <int WFMT>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const void* wq, const uint8_t* scales, const float* row_scale,
                                                          const __half* x, void* out, int M, int K, int N, int ldx,
                                                          int ldo, int out_f32) {
+  pdl_trigger();
+  pdl_wait();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= M) return;
@@ -128,9 +130,9 @@ extern "C" int vg_gemm_simt(const void* wq, const void* scales, const float* row
   const __half* x = static_cast<const __half*>(x_f16);
   const uint8_t* sc = static_cast<const uint8_t*>(scales);
   switch (wfmt) {
-    case VG_WF_NVFP4: gemm_simt_kernel<VG_WF_NVFP4><<<blocks, threads, 0, st>>>(wq, sc, row_scale, x, out, M, K, N, ldx, ldo, out_f32); break;
-    case VG_WF_FP8: gemm_simt_kernel<VG_WF_FP8><<<blocks, threads, 0, st>>>(wq, sc, row_scale, x, out, M, K, N, ldx, ldo, out_f32); break;
-    case VG_WF_BF16: gemm_simt_kernel<VG_WF_BF16><<<blocks, threads, 0, st>>>(wq, sc, row_scale, x, out, M, K, N, ldx, ldo, out_f32); break;
+    case VG_WF_NVFP4: launch_pdl(gemm_simt_kernel<VG_WF_NVFP4>, dim3(blocks), dim3(threads), 0, st, wq, sc, row_scale, x, out, M, K, N, ldx, ldo, out_f32); break;
+    case VG_WF_FP8: launch_pdl(gemm_simt_kernel<VG_WF_FP8>, dim3(blocks), dim3(threads), 0, st, wq, sc, row_scale, x, out, M, K, N, ldx, ldo, out_f32); break;
+    case VG_WF_BF16: launch_pdl(gemm_simt_kernel<VG_WF_BF16>, dim3(blocks), dim3(threads), 0, st, wq, sc, row_scale, x, out, M, K, N, ldx, ldo, out_f32); break;
     default: return -3;
   }
   return (int)cudaGetLastError();

@@ -178,6 +178,9 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  // successors launched with programmatic stream serialization may be scheduled once every CTA is here
+  pdl_trigger();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int mt = blockIdx.x, nt = blockIdx.y;
   const int S = gridDim.z, z = blockIdx.z;
@@ -542,12 +545,16 @@ int launch(const GemmParams& p, const CUtensorMap& tm, int splitk, cudaStream_t 
   cfg.blockDim = dim3(NTHREADS);
   cfg.dynamicSmemBytes = C::smem_total;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = splitk;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
+  // Launched as an ordinary dependent (measured: starting this kernel's CTAs early only takes SM slots from the
+  // kernel it waits for); the trigger at its top still lets its own successor be scheduled early.
   cfg.numAttrs = 1;
   return (int)cudaLaunchKernelEx(&cfg, kern, p, tm);
 }

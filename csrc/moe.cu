@@ -19,47 +19,53 @@ using namespace vg;
 constexpr int MAX_E = 1024;
 constexpr int MAX_K = 16;
 
-__global__ void __launch_bounds__(256) router_kernel(const float* __restrict__ logits, int E, int K, int sigmoid_mode,
-                                                      const float* __restrict__ bias, int norm, float scaling, int e_base,
-                                                      int n_local, int* __restrict__ ids, float* __restrict__ wts,
-                                                      int* __restrict__ g_exp, int* __restrict__ g_off, int* __restrict__ g_cnt) {
-  __shared__ float score[MAX_E];
-  __shared__ float raw[MAX_E];
-  __shared__ float bv[8];
-  __shared__ int bi[8];
-  __shared__ float selv[MAX_K];
-  __shared__ int seli[MAX_K];
-  const int n = blockIdx.x;
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    const float l = logits[(size_t)n * E + e];
-    const float s = sigmoid_mode ? sigmoidf(l) : l;
-    raw[e] = s;
-    score[e] = sigmoid_mode && bias ? s + bias[e] : s;
+// One warp per token: the E scores live in registers (E / 32 per lane), each of the K rounds is a local
+// arg-max plus a shuffle arg-max (ties to the lower expert index), no block barriers.
+template <int PER>
+__global__ void __launch_bounds__(32) router_kernel(const float* __restrict__ logits, int E, int K, int sigmoid_mode,
+                                                     const float* __restrict__ bias, int norm, float scaling, int e_base,
+                                                     int n_local, int* __restrict__ ids, float* __restrict__ wts,
+                                                     int* __restrict__ g_exp, int* __restrict__ g_off, int* __restrict__ g_cnt) {
+  pdl_trigger();
+  pdl_wait();
+  const int n = blockIdx.x, lane = threadIdx.x;
+  float score[PER], raw[PER];
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int e = j * 32 + lane;
+    score[j] = -INFINITY; raw[j] = 0.f;
+    if (e < E) {
+      const float l = logits[(size_t)n * E + e];
+      const float sv = sigmoid_mode ? sigmoidf(l) : l;
+      raw[j] = sv;
+      score[j] = sigmoid_mode && bias ? sv + bias[e] : sv;
+    }
   }
-  __syncthreads();
+  float selv[MAX_K];
+  int seli[MAX_K];
+#pragma unroll 1
   for (int r = 0; r < K; ++r) {
-    float v = -INFINITY;
+    float v = -INFINITY, rv = 0.f;
     int idx = 0x7fffffff;
-    for (int e = threadIdx.x; e < E; e += blockDim.x)
-      if (score[e] > v || (score[e] == v && e < idx)) { v = score[e]; idx = e; }
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int e = j * 32 + lane;
+      if (score[j] > v || (score[j] == v && e < idx)) { v = score[j]; idx = e; rv = raw[j]; }
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, v, o);
       const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-      if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+      const float orv = __shfl_xor_sync(0xffffffffu, rv, o);
+      if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; rv = orv; }
     }
-    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = v; bi[threadIdx.x >> 5] = idx; }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
-        if (bv[w] > v || (bv[w] == v && bi[w] < idx)) { v = bv[w]; idx = bi[w]; }
-      seli[r] = idx;
-      selv[r] = raw[idx];
-      score[idx] = -INFINITY;
-    }
-    __syncthreads();
+    selv[r] = rv;
+    seli[r] = idx;
+#pragma unroll
+    for (int j = 0; j < PER; ++j)
+      if (j * 32 + lane == idx) score[j] = -INFINITY;
   }
-  if (threadIdx.x == 0) {
+  if (lane == 0) {
     float w[MAX_K];
     if (sigmoid_mode) {
       float sum = 0.f;
@@ -141,19 +147,51 @@ __global__ void moe_total_kernel(const int* __restrict__ g_off, const int* __res
 
 // out[t, :] = sum_slot w[t, slot] * y[inv[t*K + slot], :]   (slot order; non-resident pairs contribute 0)
 //           (+ gate[t] * shared[t, :] when a shared expert is given)
-__global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, int ldy, const int* __restrict__ inv,
-                                   const float* __restrict__ wts, int topk, const __nv_bfloat16* __restrict__ shared,
-                                   const float* __restrict__ gate_logit, __nv_bfloat16* __restrict__ out, int h) {
+// out[t] = sum_s wts[t, s] * y[inv[t, s]] (slot order) + sigmoid(gate) * shared[t]; eight columns per thread,
+// all expert rows of a thread's columns are in flight before the first add.
+__global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* __restrict__ y, int ldy,
+                                                           const int* __restrict__ inv, const float* __restrict__ wts, int topk,
+                                                           const __nv_bfloat16* __restrict__ shared,
+                                                           const float* __restrict__ gate_logit, __nv_bfloat16* __restrict__ out,
+                                                           int h) {
+  __shared__ int spos[MAX_K];
+  __shared__ float sw[MAX_K];
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
+  if (threadIdx.x < topk) {
+    spos[threadIdx.x] = inv ? inv[t * topk + threadIdx.x] : t * topk + threadIdx.x;
+    sw[threadIdx.x] = wts[t * topk + threadIdx.x];
+  }
+  __syncthreads();
   const float g = gate_logit ? sigmoidf(gate_logit[t]) : 1.0f;
-  for (int i = threadIdx.x; i < h; i += blockDim.x) {
-    float acc = 0.f;
-    for (int s = 0; s < topk; ++s) {
-      const int pos = inv ? inv[t * topk + s] : t * topk + s;
-      if (pos >= 0) acc += wts[t * topk + s] * __bfloat162float(y[(size_t)pos * ldy + i]);
+  for (int i = threadIdx.x * 8; i < h; i += blockDim.x * 8) {
+    uint4 rows[MAX_K];
+#pragma unroll
+    for (int s = 0; s < MAX_K; ++s)
+      if (s < topk && spos[s] >= 0) rows[s] = *reinterpret_cast<const uint4*>(y + (size_t)spos[s] * ldy + i);
+    uint4 sh = make_uint4(0, 0, 0, 0);
+    if (shared) sh = *reinterpret_cast<const uint4*>(shared + (size_t)t * h + i);
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+#pragma unroll
+    for (int s = 0; s < MAX_K; ++s) {
+      if (s < topk && spos[s] >= 0) {
+        const __nv_bfloat16* r = reinterpret_cast<const __nv_bfloat16*>(&rows[s]);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] += sw[s] * __bfloat162float(r[k]);
+      }
     }
-    if (shared) acc += g * __bfloat162float(shared[(size_t)t * h + i]);
-    out[(size_t)t * h + i] = __float2bfloat16_rn(acc);
+    uint4 o4;
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&o4);
+    const __nv_bfloat16* shb = reinterpret_cast<const __nv_bfloat16*>(&sh);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (shared) acc[k] += g * __bfloat162float(shb[k]);
+      o[k] = __float2bfloat16_rn(acc[k]);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)t * h + i) = o4;
   }
 }
 
@@ -173,7 +211,12 @@ extern "C" int vg_moe_router(const float* logits, int N, int E, int K, int sigmo
                              int* g_cnt, cudaStream_t st) {
   if (N <= 0) return 0;
   if (E > MAX_E || K > MAX_K || K > E) return -2;
-  router_kernel<<<N, 256, 0, st>>>(logits, E, K, sigmoid_mode, bias, norm, scaling, e_base, n_local, ids, wts, g_exp, g_off, g_cnt);
+  if (E <= 256)
+    launch_pdl(router_kernel<8>, dim3(N), dim3(32), 0, st, logits, E, K, sigmoid_mode, bias, norm, scaling, e_base, n_local, ids,
+               wts, g_exp, g_off, g_cnt);
+  else
+    launch_pdl(router_kernel<MAX_E / 32>, dim3(N), dim3(32), 0, st, logits, E, K, sigmoid_mode, bias, norm, scaling, e_base,
+               n_local, ids, wts, g_exp, g_off, g_cnt);
   return (int)cudaGetLastError();
 }
 
@@ -203,9 +246,9 @@ extern "C" int vg_moe_gather(const void* x_f16, int ldx, const int* perm, const 
 extern "C" int vg_moe_combine(const void* y, int ldy, const int* inv, const float* wts, int N, int topk, const void* shared,
                               const float* gate_logit, void* out, int h, cudaStream_t st) {
   if (N <= 0) return 0;
-  moe_combine_kernel<<<N, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(y), ldy, inv, wts, topk,
-                                        static_cast<const __nv_bfloat16*>(shared), gate_logit,
-                                        static_cast<__nv_bfloat16*>(out), h);
+  if (topk > MAX_K || (h % 8) != 0 || (ldy % 8) != 0) return -2;
+  launch_pdl(moe_combine_kernel, dim3(N), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(y), ldy, inv, wts, topk,
+             static_cast<const __nv_bfloat16*>(shared), gate_logit, static_cast<__nv_bfloat16*>(out), h);
   return (int)cudaGetLastError();
 }
 
