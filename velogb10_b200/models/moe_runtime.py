@@ -10,6 +10,8 @@ the replicated shared expert is added.
 """
 from __future__ import annotations
 
+import contextlib
+
 from typing import Dict
 
 import torch
@@ -87,6 +89,27 @@ def moe_forward(model, ws, M: MoeW, n: int, act=None):
     E, topk, I, h = cfg.num_experts, cfg.num_experts_per_tok, cfg.moe_intermediate_size, cfg.hidden_size
     b = _buffers(model, ws, M)
     gu_w, dn_w = _prep_experts(M.gate_up), _prep_experts(M.down)
+    # The shared expert does not depend on the routing: at decode widths it runs on a second stream beside the
+    # routed experts (a fork / join that CUDA-graph capture records as two branches) and meets them at the combine.
+    shared = gate = joined = None
+    if M.shared is not None:
+        fork = n <= 16 and model.moe_side_stream is not None
+        if fork:
+            main = torch.cuda.current_stream()
+            model.moe_fork_event.record(main)
+            model.moe_side_stream.wait_event(model.moe_fork_event)
+            ctx = torch.cuda.stream(model.moe_side_stream)
+        else:
+            ctx = contextlib.nullcontext()
+        with ctx:
+            model._mlp(ws, M.shared, n, b.shared, reduce=False, act=act)
+            shared = b.shared
+            if M.shared_gate is not None:
+                _small_linear(M.shared_gate, ws.xn16, n, b.gate_logit)
+                gate = b.gate_logit
+            if fork:
+                joined = model.moe_join_event
+                joined.record(model.moe_side_stream)
     _small_linear(M.router, ws.xn16, n, b.logits)
     P = n * topk
     decode = ws.cap <= DECODE_MAX
@@ -120,13 +143,8 @@ def moe_forward(model, ws, M: MoeW, n: int, act=None):
         K.swiglu(b.gu, b.a16, P, I)
         _grouped(dn_w, h, b.a16, b.y, 128, items, b.g_exp, b.g_off, b.g_cnt, b.tilemap, b.n_items, 1, model.dev)
         inv = b.inv
-    shared = gate = None
-    if M.shared is not None:
-        model._mlp(ws, M.shared, n, b.shared, reduce=False, act=act)
-        shared = b.shared
-        if M.shared_gate is not None:
-            _small_linear(M.shared_gate, ws.xn16, n, b.gate_logit)
-            gate = b.gate_logit
+    if joined is not None:
+        torch.cuda.current_stream().wait_event(joined)
     ep = model.comm is not None and model.comm.world > 1 and M.n_local < E
     rc = L.vg_moe_combine(ptr(b.y), c_int(b.y.stride(0)), ptr(inv), ptr(b.wts), c_int(n), c_int(topk),
                           ptr(None if ep else shared), ptr(None if ep else gate), ptr(ws.delta), c_int(h), stream())

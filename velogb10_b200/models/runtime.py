@@ -165,6 +165,13 @@ class GpuModel:
         self._pending_ar = False
         self.tc_prefill_attn = os.environ.get("VELO_NO_TC_PREFILL_ATTN", "0") != "1"
         self._prefill_ctx = None              # (slot, first position) while a prefill chunk is running
+        # MoE decode: second stream for the shared expert (see moe_runtime.moe_forward)
+        self.moe_side_stream = None
+        if os.environ.get("VELO_NO_MOE_FORK", "0") != "1" and any(L.moe is not None for L in weights.layers):
+            with torch.cuda.device(self.dev):
+                self.moe_side_stream = torch.cuda.Stream()
+                self.moe_fork_event = torch.cuda.Event()
+                self.moe_join_event = torch.cuda.Event()
         self._vt = None
         _lib.lib()
         with torch.cuda.device(self.dev):
