@@ -5,7 +5,8 @@
 // outputs are GEMM inputs, so those rows never round-trip through memory in f16.
 //
 // Output layout (shared with gemm_fp4.cu):
-//   bq   [64][ldb bytes]  row t*16 + n = term t of row n, two e2m1 codes per byte (low nibble = even k)
+//   bq   [64][ldb bytes]  row t*16 + n = term t of row n, two e2m1 codes per byte (low nibble = even k);
+//                         rows 16.. of the stand-alone quantisers continue in further 64-row tiles (grouped GEMM)
 //   sfb  [K/256][4][512]  scale chunks: byte [r0*16 + r1*4 + kb] of step j = e4m3 scale of bq row
 //                         (r0 + 32*r1), 16-element block j*4 + kb of the slab
 //   g0   [16]             amax / (6 * 448) of each row; term t uses the global scale g0 / 8^t
@@ -279,7 +280,7 @@ int cluster_for(int nblk) {
 extern "C" int vg_act_quant_fp4(const void* x_f16, int ldx, int N, int K, void* bq, int ldb, void* sfb, float* g0,
                                 cudaStream_t st) {
   const int Kpad = ldb * 2;
-  if (N < 1 || N > 16 || (ldb % 128) != 0 || Kpad < K || (K % 8) != 0 || (ldx % 8) != 0 || (Kpad >> 4) > MAX_THREADS * MAXB) return -2;
+  if (N < 1 || N > 4096 || (ldb % 128) != 0 || Kpad < K || (K % 8) != 0 || (ldx % 8) != 0 || (Kpad >> 4) > MAX_THREADS * MAXB) return -2;
   const int C = cluster_for(Kpad >> 4), bpc = ((Kpad >> 4) + C - 1) / C;
   return (int)launch_pdl_cluster(act_quant_kernel<0>, dim3(C, N), dim3(threads_for(bpc)), (unsigned)C, 0, st, x_f16, ldx, K,
                                  Kpad, static_cast<uint8_t*>(bq), ldb, static_cast<uint8_t*>(sfb), g0, (__half*)nullptr);
@@ -289,7 +290,7 @@ extern "C" int vg_act_quant_fp4(const void* x_f16, int ldx, int N, int K, void* 
 extern "C" int vg_swiglu_fp4(const void* gu, int ld, int N, int I, void* bq, int ldb, void* sfb, float* g0, void* out16,
                              cudaStream_t st) {
   const int Kpad = ldb * 2;
-  if (N < 1 || N > 16 || (ldb % 128) != 0 || Kpad < I || (I % 8) != 0 || (ld % 8) != 0 || (Kpad >> 4) > MAX_THREADS * MAXB) return -2;
+  if (N < 1 || N > 4096 || (ldb % 128) != 0 || Kpad < I || (I % 8) != 0 || (ld % 8) != 0 || (Kpad >> 4) > MAX_THREADS * MAXB) return -2;
   const int C = cluster_for(Kpad >> 4), bpc = ((Kpad >> 4) + C - 1) / C;
   return (int)launch_pdl_cluster(act_quant_kernel<1>, dim3(C, N), dim3(threads_for(bpc)), (unsigned)C, 0, st, gu, ld, I, Kpad,
                                  static_cast<uint8_t*>(bq), ldb, static_cast<uint8_t*>(sfb), g0, static_cast<__half*>(out16));

@@ -44,9 +44,15 @@ __device__ __forceinline__ void e2m1x8_to_f32(uint32_t w, float* o) {
 }
 
 // Quantise one 16-element block (values in r, consumed) of row n, block index b, into the four terms.
+// Rows are grouped sixteen to a 64-row B tile: row n lives in tile n / 16 as column n % 16 (tile T starts at
+// bq row 64 T and at scale chunk T * (ldb / 128)).
 __device__ __forceinline__ void quant_block(float* r, float g, int n, int b, uint8_t* __restrict__ bq, int ldb,
                                             uint8_t* __restrict__ sfb) {
   const int slab = b >> 4, step = (b & 15) >> 2, kb = b & 3;
+  const int tile = n >> 4;
+  n &= 15;
+  bq += (size_t)tile * 64 * ldb;
+  sfb += (size_t)tile * (ldb >> 7) * SF_BYTES;
   float gt = g;
 #pragma unroll
   for (int t = 0; t < TERMS; ++t) {

@@ -55,6 +55,9 @@ int vg_gemm_fp4(const void* wt, const float* row_scale, const void* bq, int ldb,
 // rank's tile flags (bounded), adds the partials in rank order, then proceeds as vg_add_rmsnorm_fp4.
 int vg_add_rmsnorm_fp4_ar(void* res, const float* w, int N, int h, float eps, int plus_one, int ld_res, void* bq, int ldb,
                           void* sfb, float* g0, void* out16, const VgCommCtx* ctx, cudaStream_t stream);
+int vg_gemm_fp4_grouped(const void* wt, const float* row_scale, const void* bq, int ldb, int b_rows, const void* sfb,
+                        const float* g0, void* out, int out_f32, int M, int K, int ldo, int n_items, const int* g_exp,
+                        const int* g_off, int x_div, int* err, cudaStream_t stream);
 int vg_gemm_tc_grouped(const void* wt, const float* row_scale, const void* x_f16, int x_rows, int ldx, void* out, int out_f32,
                        int M, int K, int ldo, int wfmt, int bn, int max_items, const int* g_exp, const int* g_off,
                        const int* g_cnt, const int* tilemap, const int* n_items, int x_div, int* err, cudaStream_t stream);

@@ -54,6 +54,11 @@ struct Fp4Params {
   int M, N, ldo, ks_total, out_f32;
   int* err;
   int ar;
+  // grouped (MoE decode) mode: blockIdx.y = work item; the item's expert picks the weight tiles, its pair index
+  // picks the activation column (pair / x_div) and the output row (pair)
+  int grouped, tiles_per_expert, x_div;
+  const int* g_exp;
+  const int* g_off;
   int has_conv;
   VgConvEpi conv;
   VgCommCtx comm;
@@ -113,7 +118,18 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int mt = blockIdx.x;
+  int mt = blockIdx.x;
+  int b_tile = 0, b_col = 0, out_row = 0;
+  if (p.grouped) {
+    pdl_wait();                            // the group tables come from the router kernel
+    const int e = p.g_exp[blockIdx.y];
+    if (e < 0) return;                     // expert not resident on this rank (uniform for the CTA)
+    out_row = p.g_off[blockIdx.y];
+    const int src = out_row / p.x_div;     // activation row the pair reads
+    b_tile = src >> 4;
+    b_col = src & 15;
+    mt = e * p.tiles_per_expert + (int)blockIdx.x;
+  }
   const int S = gridDim.z, z = blockIdx.z;
   const int ks0 = (int)(((long long)z * p.ks_total) / S);
   const int ks1 = (int)(((long long)(z + 1) * p.ks_total) / S);
@@ -164,8 +180,8 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
         uint8_t* st = smem + (size_t)s * STAGE + A_BYTES + SF_BYTES;
         const int ks = slab_of(i);
         mbar_arrive_expect_tx(&full[s], B_BYTES + SF_BYTES);
-        tma_tensor2d_g2s(st, &tmap_b, ks * (BKQ / 2), 0, &full[s]);
-        tma_bulk_g2s(st + B_BYTES, p.sfb + (size_t)ks * SF_BYTES, SF_BYTES, &full[s]);
+        tma_tensor2d_g2s(st, &tmap_b, ks * (BKQ / 2), b_tile * NT, &full[s]);
+        tma_bulk_g2s(st + B_BYTES, p.sfb + ((size_t)b_tile * p.ks_total + ks) * SF_BYTES, SF_BYTES, &full[s]);
       }
     }
   } else if (warp == 2 || warp == 3) {
@@ -339,6 +355,16 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
       __threadfence();
       if (atomicAdd(c.done_ctr, 1u) == gridDim.x - 1) { *c.done_ctr = 0; *c.epoch = e; }
     }
+    }
+  } else if (p.grouped) {
+    const int mi = (int)blockIdx.x * BM + m_local;          // row inside the expert
+    if (epi && have && z == 0 && mi < p.M) {
+      float yv = 0.f;
+#pragma unroll
+      for (int n = 0; n < 16; ++n) yv = n == b_col ? y[n] : yv;
+      const float v = yv * p.g0[b_tile * 16 + b_col] * (p.row_scale ? p.row_scale[m] : 1.0f);
+      if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)out_row * p.ldo + mi] = v;
+      else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)out_row * p.ldo + mi] = __float2bfloat16_rn(v);
     }
   } else if (epi && have && z == 0 && m < p.M) {
     const float rsc = p.row_scale ? p.row_scale[m] : 1.0f;
@@ -590,14 +616,14 @@ EncodeTiledFn get_encode4() {
 std::map<std::tuple<const void*, int>, CUtensorMap> g_bmaps;
 std::mutex g_bmu;
 
-int get_tmap_b(const void* bq, int ldb, CUtensorMap* out) {
+int get_tmap_b(const void* bq, int ldb, int rows, CUtensorMap* out) {
   std::lock_guard<std::mutex> lk(g_bmu);
-  auto key = std::make_tuple(bq, ldb);
+  auto key = std::make_tuple(bq, ldb * 4096 + rows / NT);
   auto it = g_bmaps.find(key);
   if (it != g_bmaps.end()) { *out = it->second; return 0; }
   EncodeTiledFn enc = get_encode4();
   if (!enc) return -1;
-  cuuint64_t gdim[2] = {(cuuint64_t)ldb, (cuuint64_t)NT};
+  cuuint64_t gdim[2] = {(cuuint64_t)ldb, (cuuint64_t)rows};
   cuuint64_t gstride[1] = {(cuuint64_t)ldb};
   cuuint32_t box[2] = {128, (cuuint32_t)NT};
   cuuint32_t estr[2] = {1, 1};
@@ -629,6 +655,7 @@ extern "C" int vg_gemm_fp4(const void* wt, const float* row_scale, const void* b
   p.out_f32 = out_f32;
   p.err = err;
   p.ar = 0;
+  p.grouped = 0; p.tiles_per_expert = 0; p.x_div = 1; p.g_exp = nullptr; p.g_off = nullptr;
   p.has_conv = 0;
   if (conv && conv->conv_dim > 0) {
     if (conv->ck < 1 || conv->ck > CONV_MAX_CK || out_f32 || (ar_ctx && ar_ctx->world > 1)) return -6;
@@ -642,7 +669,7 @@ extern "C" int vg_gemm_fp4(const void* wt, const float* row_scale, const void* b
   }
   if (splitk > p.ks_total) splitk = p.ks_total;
   CUtensorMap tm;
-  int rc = get_tmap_b(bq, ldb, &tm);
+  int rc = get_tmap_b(bq, ldb, NT, &tm);
   if (rc) return rc;
   const int tiles = (M + BM - 1) / BM;
   if (splitk == 1 && !p.ar && !p.has_conv && p.ks_total >= 2 && tiles > sm_count() && persist_on()) {
@@ -680,6 +707,39 @@ extern "C" int vg_gemm_fp4(const void* wt, const float* row_scale, const void* b
   cfg.attrs = attr;
   cfg.numAttrs = pdl_on() ? 2 : 1;
   return (int)cudaLaunchKernelEx(&cfg, gemm_fp4_kernel, p, tm);
+}
+
+// MoE decode: `n_items` work items, item g = (expert g_exp[g] or -1, pair g_off[g]); the pair reads activation
+// row pair / x_div of the quantised series (rows grouped sixteen to a B tile, `b_rows` = 64 * tiles) and writes
+// out[pair][0 .. M). wt holds the experts stacked ([E * M, K] in the FP4 tile layout, M a multiple of 128).
+extern "C" int vg_gemm_fp4_grouped(const void* wt, const float* row_scale, const void* bq, int ldb, int b_rows, const void* sfb,
+                                   const float* g0, void* out, int out_f32, int M, int K, int ldo, int n_items, const int* g_exp,
+                                   const int* g_off, int x_div, int* err, cudaStream_t stream) {
+  if (M <= 0 || (M % BM) != 0 || K <= 0 || n_items < 1 || x_div < 1 || (ldb % 128) != 0 || (b_rows % NT) != 0) return -2;
+  Fp4Params p;
+  p.wt = static_cast<const uint8_t*>(wt);
+  p.row_scale = row_scale;
+  p.sfb = static_cast<const uint8_t*>(sfb);
+  p.g0 = g0;
+  p.out = out;
+  p.M = M; p.N = 16; p.ldo = ldo;
+  p.ks_total = (K + BKQ - 1) / BKQ;
+  if (p.ks_total * (BKQ / 2) > ldb) return -4;
+  p.out_f32 = out_f32;
+  p.err = err;
+  p.ar = 0;
+  p.has_conv = 0;
+  p.grouped = 1; p.tiles_per_expert = M / BM; p.x_div = x_div; p.g_exp = g_exp; p.g_off = g_off;
+  CUtensorMap tm;
+  int rc = get_tmap_b(bq, ldb, b_rows, &tm);
+  if (rc) return rc;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_fp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL + CONV_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  return (int)launch_pdl(gemm_fp4_kernel, dim3(M / BM, n_items, 1), dim3(THREADS), SMEM_TOTAL, stream, p, tm);
 }
 
 VG_TRACE_SETTER(vg_trace_set_gemm_fp4)

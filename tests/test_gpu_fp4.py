@@ -85,3 +85,45 @@ def test_fused_swiglu_quantiser(inter, n):
     torch.cuda.synchronize()
     lib.check_err_word()
     assert torch.equal(got, want)
+
+
+def test_grouped_fp4_matches_reference():
+    """MoE decode form: each work item multiplies one expert with one activation row and writes one output row."""
+    from velogb10_b200.models.weights import QLinear
+    from velogb10_b200.ops import gemm as G, lib
+    E, M, K, n_tok, topk = 6, 256, 512, 3, 4
+    g = torch.Generator(device="cuda").manual_seed(3)
+    w = (torch.randn(E * M, K, generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    q = QLinear.from_dense(w, "nvfp4")
+    wd = q.dequant(torch.float32).view(E, M, K)
+    x = torch.randn(16, K, generator=g, device="cuda").to(torch.float16)
+    act = G.quantize_act_fp4(x, n_tok, K)
+    P = n_tok * topk
+    ids = torch.tensor([0, 5, 2, 3, 1, 4, 0, 2, 5, 5, 3, 1], dtype=torch.int32, device="cuda")
+    g_exp = ids.clone()
+    g_exp[7] = -1                                            # a non-resident expert: row must stay untouched
+    g_off = torch.arange(P, dtype=torch.int32, device="cuda")
+    out = torch.full((P, M), 7.0, dtype=torch.bfloat16, device="cuda")
+    G.linear_fp4_grouped(q, act, out, g_exp, g_off, P, topk, M)
+    # second stage shape: one quantised row per pair (more than 16 rows -> several B tiles)
+    P2 = 40
+    y = torch.randn(P2, K, generator=g, device="cuda").to(torch.float16)
+    bufs = G.fp4_buffers("cuda", K, rows=P2, tag="test")
+    rc = lib.lib().vg_act_quant_fp4(lib.ptr(y), lib.c_int(y.stride(0)), lib.c_int(P2), lib.c_int(K), lib.ptr(bufs[0]),
+                                    lib.c_int(bufs[0].stride(0)), lib.ptr(bufs[1]), lib.ptr(bufs[2]), lib.stream())
+    assert rc == 0
+    ids2 = torch.randint(0, E, (P2,), generator=torch.Generator().manual_seed(1)).to(torch.int32).cuda()
+    off2 = torch.arange(P2, dtype=torch.int32, device="cuda")
+    out2 = torch.zeros((P2, M), dtype=torch.float32, device="cuda")
+    G.linear_fp4_grouped(q, bufs, out2, ids2, off2, P2, 1, M)
+    torch.cuda.synchronize()
+    lib.check_err_word()
+    for p_ in range(P):
+        if p_ == 7:
+            assert torch.all(out[p_].float() == 7.0)
+            continue
+        ref = wd[int(ids[p_])] @ x[p_ // topk].float()
+        rel = ((out[p_].float() - ref).norm() / ref.norm()).item()
+        assert rel < 8e-3, (p_, rel)
+    ref2 = torch.einsum("pmk,pk->pm", wd[ids2.long()], y.float())
+    assert ((out2 - ref2).norm() / ref2.norm()).item() < 3e-3

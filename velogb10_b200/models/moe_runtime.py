@@ -59,8 +59,11 @@ def _buffers(model, ws, M: MoeW) -> MoeBuffers:
     return b
 
 
-def _prep_experts(q):
-    """Tile-major layout of a stacked expert tensor (each expert's rows are a multiple of 128)."""
+def _prep_experts(q, fp4: bool):
+    """Tile-major layouts of a stacked expert tensor (each expert's rows are a multiple of 128): the 16-bit-MMA
+    tiles for sorted prefill and, for NVFP4 experts, the FP4 tiles for the per-pair decode path."""
+    if fp4 and q.fmt == "nvfp4" and getattr(q, "kernel4", None) is None and q.packed is not None:
+        G.prepare_fp4(q, splitk=1)
     tw = G.prepare(q, keep_canonical=False, splitk=1)
     return tw
 
@@ -88,7 +91,7 @@ def moe_forward(model, ws, M: MoeW, n: int, act=None):
     L = _lib.lib()
     E, topk, I, h = cfg.num_experts, cfg.num_experts_per_tok, cfg.moe_intermediate_size, cfg.hidden_size
     b = _buffers(model, ws, M)
-    gu_w, dn_w = _prep_experts(M.gate_up), _prep_experts(M.down)
+    gu_w, dn_w = _prep_experts(M.gate_up, model.use_fp4), _prep_experts(M.down, model.use_fp4)
     # The shared expert does not depend on the routing: at decode widths it runs on a second stream beside the
     # routed experts (a fork / join that CUDA-graph capture records as two branches) and meets them at the combine.
     shared = gate = joined = None
@@ -102,7 +105,7 @@ def moe_forward(model, ws, M: MoeW, n: int, act=None):
         else:
             ctx = contextlib.nullcontext()
         with ctx:
-            model._mlp(ws, M.shared, n, b.shared, reduce=False, act=act)
+            model._mlp(ws, M.shared, n, b.shared, reduce=False, act=act, buf_tag="shared" if fork else "")
             shared = b.shared
             if M.shared_gate is not None:
                 _small_linear(M.shared_gate, ws.xn16, n, b.gate_logit)
@@ -119,10 +122,19 @@ def moe_forward(model, ws, M: MoeW, n: int, act=None):
                          ptr(b.g_exp if decode else None), ptr(b.g_off if decode else None),
                          ptr(b.g_cnt if decode else None), stream())
     _lib.check(rc, "vg_moe_router")
-    if decode:
+    fp4 = (decode and act is not None and getattr(M.gate_up, "kernel4", None) is not None
+           and getattr(M.down, "kernel4", None) is not None and (2 * I) % 128 == 0 and h % 128 == 0 and I % 8 == 0)
+    if fp4:
+        # per-pair FP4 path: the token's quantised series feeds every selected expert's gate_up; SwiGLU emits one
+        # quantised row per pair (own buffers: the shared expert quantises on the other stream) for the down GEMM
+        G.linear_fp4_grouped(M.gate_up, act, b.gu, b.g_exp, b.g_off, P, topk, 2 * I)
+        act_p = G.swiglu_fp4(b.gu, P, I, bufs=G.fp4_buffers(model.dev, ((I + 255) // 256) * 256, rows=b.P, tag="moe"))
+        G.linear_fp4_grouped(M.down, act_p, b.y, b.g_exp, b.g_off, P, 1, h)
+    elif decode:
         _grouped(gu_w, 2 * I, ws.xn16, b.gu, 16, P, b.g_exp, b.g_off, b.g_cnt, None, None, topk, model.dev)
         K.swiglu(b.gu, b.a16, P, I)
         _grouped(dn_w, h, b.a16, b.y, 16, P, b.g_exp, b.g_off, b.g_cnt, None, None, 1, model.dev)
+    if decode:
         inv = None
         # non-resident pairs were skipped by the GEMM: make the combine skip them too
         if M.n_local < E:

@@ -387,12 +387,15 @@ class GpuModel:
                        quant=act_o + (self.col_ctr,) if act_o is not None else None)
         self._row_parallel(Gd.out, g16, n, ws.delta, act=act_o)
 
-    def _mlp(self, ws: Workspace, M, n: int, out: torch.Tensor, reduce: bool = True, act=None):
+    def _mlp(self, ws: Workspace, M, n: int, out: torch.Tensor, reduce: bool = True, act=None, buf_tag: str = ""):
+        """SwiGLU MLP. ``buf_tag`` selects a private set of FP4 activation buffers (an MLP that runs on a second
+        stream must not share them with the main stream's producers)."""
         gu = ws.wide[:, :M.gate_up.m]
         self._linear(M.gate_up, ws.xn16, n, gu, act=act)
         a16 = ws.a16(M.down.k)
         if self._fp4_ok(M.down, n) and M.inter % 8 == 0:
-            act_d = G.swiglu_fp4(gu, n, M.inter)
+            bufs = G.fp4_buffers(self.dev, ((M.inter + 255) // 256) * 256, tag=buf_tag) if buf_tag else None
+            act_d = G.swiglu_fp4(gu, n, M.inter, bufs=bufs)
             self._row_parallel(M.down, a16, n, out, reduce, act=act_d)
             return
         K.swiglu(gu, a16, n, M.inter)

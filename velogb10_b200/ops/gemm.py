@@ -208,14 +208,17 @@ def prepare_fp4(q: QLinear, splitk: Optional[int] = None) -> Fp4Weight:
 _fp4_act = {}
 
 
-def fp4_buffers(dev, kp: int):
-    """The shared FP4 activation buffers (terms, scale chunks, per-row global scales) for inputs padded to ``kp``."""
-    key = (str(dev), kp)
+def fp4_buffers(dev, kp: int, rows: int = 16, tag: str = ""):
+    """FP4 activation buffers (terms, scale chunks, per-row global scales) for inputs padded to ``kp``. Rows are
+    grouped sixteen to a 64-row B tile. Buffers are shared by (device, kp, rows, tag): producers that may run
+    concurrently (a second stream) use their own ``tag``."""
+    tiles = (max(rows, 1) + 15) // 16
+    key = (str(dev), kp, tiles, tag)
     b = _fp4_act.get(key)
     if b is None:
-        b = (torch.zeros((64, kp // 2), dtype=torch.uint8, device=dev),
-             torch.zeros((kp // 256, 2048), dtype=torch.uint8, device=dev),
-             torch.zeros(16, dtype=torch.float32, device=dev))
+        b = (torch.zeros((64 * tiles, kp // 2), dtype=torch.uint8, device=dev),
+             torch.zeros((tiles * (kp // 256), 2048), dtype=torch.uint8, device=dev),
+             torch.zeros(16 * tiles, dtype=torch.float32, device=dev))
         _fp4_act[key] = b
     return b
 
@@ -229,10 +232,12 @@ def quantize_act_fp4(x16: torch.Tensor, n: int, kp: int):
     return bq, sfb, g0
 
 
-def swiglu_fp4(gu: torch.Tensor, n: int, inter: int, out16: Optional[torch.Tensor] = None):
-    """SwiGLU of ``gu[:n] = [gate | up]`` (bf16) emitted directly as the FP4 series for the down projection."""
+def swiglu_fp4(gu: torch.Tensor, n: int, inter: int, out16: Optional[torch.Tensor] = None, bufs=None):
+    """SwiGLU of ``gu[:n] = [gate | up]`` (bf16) emitted directly as the FP4 series for the down projection.
+    ``bufs`` overrides the shared buffers (more than 16 rows, or a producer on another stream)."""
     kp = ((inter + 255) // 256) * 256
-    bq, sfb, g0 = fp4_buffers(gu.device, kp)
+    bq, sfb, g0 = bufs if bufs is not None else fp4_buffers(gu.device, kp)
+    assert bq.shape[0] >= 64 * ((n + 15) // 16) and bq.shape[1] * 2 == kp
     rc = _lib.lib().vg_swiglu_fp4(ptr(gu), c_int(gu.stride(0)), c_int(n), c_int(inter), ptr(bq), c_int(bq.stride(0)),
                                   ptr(sfb), ptr(g0), ptr(out16) if out16 is not None else c_void_p(0), stream())
     _lib.check(rc, "vg_swiglu_fp4")
@@ -301,4 +306,19 @@ def linear_fp4(q: QLinear, x16: torch.Tensor, n: int, out: Optional[torch.Tensor
                                 c_int(1 if push_only else 0),
                                 ctypes.byref(conv) if conv is not None else c_void_p(0), stream())
     _lib.check(rc, "vg_gemm_fp4")
+    return out
+
+
+def linear_fp4_grouped(q: QLinear, act, out: torch.Tensor, g_exp: torch.Tensor, g_off: torch.Tensor, n_items: int,
+                       x_div: int, m_per_expert: int) -> torch.Tensor:
+    """MoE decode on the FP4 path: work item g multiplies expert ``g_exp[g]`` (rows ``m_per_expert`` of the
+    stacked tensor ``q``) with activation row ``g_off[g] // x_div`` of the quantised series ``act`` and writes
+    ``out[g_off[g]]``. Items with ``g_exp < 0`` are skipped."""
+    tw = prepare_fp4(q, splitk=1)
+    bq, sfb, g0 = act
+    rc = _lib.lib().vg_gemm_fp4_grouped(ptr(tw.wt), ptr(tw.row_scale), ptr(bq), c_int(bq.stride(0)), c_int(bq.shape[0]),
+                                        ptr(sfb), ptr(g0), ptr(out), c_int(1 if out.dtype == torch.float32 else 0),
+                                        c_int(m_per_expert), c_int(tw.k), c_int(out.stride(0)), c_int(n_items), ptr(g_exp),
+                                        ptr(g_off), c_int(x_div), ptr(_lib.err_word(out.device)), stream())
+    _lib.check(rc, "vg_gemm_fp4_grouped")
     return out
