@@ -71,7 +71,7 @@ int vg_add_rmsnorm(void* res, const void* delta, const float* w, void* out_f16, 
                    int plus_one, int ld_res, int ld_delta, cudaStream_t stream);
 int vg_attn_prep(const void* qkv, int ld_qkv, const float* q_norm, const float* k_norm, const int* pos, const int* slot,
                  const int* kv_row, void* q_out, void* kc, void* vc, int N, int nh, int nkv, int hd, int rdim,
-                 int max_seq, float eps, float theta, int gated, cudaStream_t stream);
+                 int max_seq, float eps, float theta, int gated, void* k_scale, void* v_scale, cudaStream_t stream);
 int vg_swiglu(const void* gu, void* out_f16, int N, int I, int ld, cudaStream_t stream);
 int vg_cast_f16(const void* in, int in_is_f32, void* out_f16, long long total, cudaStream_t stream);
 int vg_embed_gather(const void* table, const void* scales, const float* row_scale, const int* tok, void* out, int N,
@@ -85,6 +85,12 @@ int vg_attn_transpose_v(const void* vc, void* vT, int slot, int nkv, int hd, int
 int vg_attn_prefill_tc(const void* q, int q_cap, const void* kc, const void* vT, int vt_cap, int slot, int nkv, int nh,
                        int hd, int max_seq, int pos0, int n, float scale, const void* gate, int ld_gate, void* out_f16,
                        int* err, cudaStream_t stream);
+int vg_attn_decode_q4(const void* q, const void* kq, const void* vq, const void* ks, const void* vs, const int* lens,
+                      const int* slots, const int* base, const int* path, int path_ld, float* part, int N, int nh, int nkv,
+                      int hd, int max_seq, int ns_grid, int direct, const void* gate, int ld_gate, void* out,
+                      cudaStream_t stream);
+int vg_kv_q4_dequant(const void* codes, const void* scales, int slot, int nkv, int hd, int max_seq, int len, void* out_rows,
+                     void* out_transposed, int t_cap, cudaStream_t stream);
 long long vg_attn_scratch_floats(int N, int nh, int hd, int ns_grid);
 
 int vg_gdn_conv(const void* x, int ldx, float* state, const float* w, const int* in_slot, const int* parent,

@@ -35,6 +35,12 @@ template <> struct RowVec<8> { using T = uint4; };
 template <> struct RowVec<4> { using T = uint2; };
 template <> struct RowVec<2> { using T = uint32_t; };
 template <> struct RowVec<1> { using T = unsigned short; };
+// DPL 4-bit codes of one lane (DPL / 2 bytes).
+template <int DPL> struct CodeVec;
+template <> struct CodeVec<8> { using T = uint32_t; };
+template <> struct CodeVec<4> { using T = unsigned short; };
+template <> struct CodeVec<2> { using T = uint8_t; };
+template <> struct CodeVec<1> { using T = uint8_t; };
 template <int DPL>
 __device__ __forceinline__ void unpack_row(const typename RowVec<DPL>::T& raw, float* f) {
   const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&raw);
@@ -42,10 +48,12 @@ __device__ __forceinline__ void unpack_row(const typename RowVec<DPL>::T& raw, f
   for (int i = 0; i < DPL; ++i) f[i] = __bfloat162float(h[i]);
 }
 
-template <int HD, int GT>
+// Q4: the cache holds 4-bit codes (two per byte, value + 8, symmetric +-7) with one f16 scale per 16 values;
+// kc / vc then point at the code bytes and ks / vs at the scales (reference: kernels/gpu_batch.cu:729-802, :1606).
+template <int HD, int GT, bool Q4>
 __global__ void __launch_bounds__(NW * 32) attn_split_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
-    const int* __restrict__ lens, const int* __restrict__ slots, const int* __restrict__ base,
+    const __half* __restrict__ ks, const __half* __restrict__ vs, const int* __restrict__ lens, const int* __restrict__ slots, const int* __restrict__ base,
     const int* __restrict__ path, int path_ld, float* __restrict__ part, int nh, int nkv, int max_seq, int ns_grid,
     float scale, int direct, const __nv_bfloat16* __restrict__ gate, int ld_gate, int gate_off, __half* __restrict__ out) {
   pdl_trigger();
@@ -81,8 +89,15 @@ __global__ void __launch_bounds__(NW * 32) attn_split_kernel(
 #pragma unroll
     for (int i = 0; i < DPL; ++i) acc[g][i] = 0.f;
   }
-  const __nv_bfloat16* kslot = kc + ((size_t)slot * nkv + kvh) * (size_t)max_seq * HD;
-  const __nv_bfloat16* vslot = vc + ((size_t)slot * nkv + kvh) * (size_t)max_seq * HD;
+  const size_t head_rows = ((size_t)slot * nkv + kvh) * (size_t)max_seq;
+  const __nv_bfloat16* kslot = kc + head_rows * HD;
+  const __nv_bfloat16* vslot = vc + head_rows * HD;
+  // 4-bit cache: DPL / 2 code bytes per lane and the scale of the 16-value block the lane's dims fall into
+  using Codes = typename CodeVec<DPL>::T;
+  const uint8_t* kq = reinterpret_cast<const uint8_t*>(kc) + head_rows * (HD / 2);
+  const uint8_t* vq = reinterpret_cast<const uint8_t*>(vc) + head_rows * (HD / 2);
+  const __half* ksc = Q4 ? ks + head_rows * (HD / 16) : nullptr;
+  const __half* vsc = Q4 ? vs + head_rows * (HD / 16) : nullptr;
 
   // Keys of this warp in batches of U: all loads of a batch are issued before its first dot product, so a
   // warp keeps U rows of K and V in flight; the keys are still folded in in ascending order.
@@ -90,21 +105,41 @@ __global__ void __launch_bounds__(NW * 32) attn_split_kernel(
   using Raw = typename RowVec<DPL>::T;
   for (int tb = k0 + warp; tb < k1; tb += NW * U) {
     Raw kraw[U], vraw[U];
+    Codes kcd[U], vcd[U];
+    __half ksv[U], vsv[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int t = tb + u * NW;
       if (t < k1) {
         const int row = t < kbase ? t : path[(size_t)col * path_ld + (t - kbase)];
-        kraw[u] = *reinterpret_cast<const Raw*>(kslot + (size_t)row * HD + lane * DPL);
-        vraw[u] = *reinterpret_cast<const Raw*>(vslot + (size_t)row * HD + lane * DPL);
+        if (Q4) {
+          kcd[u] = *reinterpret_cast<const Codes*>(kq + (size_t)row * (HD / 2) + lane * (DPL / 2));
+          vcd[u] = *reinterpret_cast<const Codes*>(vq + (size_t)row * (HD / 2) + lane * (DPL / 2));
+          ksv[u] = ksc[(size_t)row * (HD / 16) + (lane * DPL) / 16];
+          vsv[u] = vsc[(size_t)row * (HD / 16) + (lane * DPL) / 16];
+        } else {
+          kraw[u] = *reinterpret_cast<const Raw*>(kslot + (size_t)row * HD + lane * DPL);
+          vraw[u] = *reinterpret_cast<const Raw*>(vslot + (size_t)row * HD + lane * DPL);
+        }
       }
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       if (tb + u * NW >= k1) break;
       float kf[DPL], vf[DPL];
-      unpack_row<DPL>(kraw[u], kf);
-      unpack_row<DPL>(vraw[u], vf);
+      if (Q4) {
+        const uint8_t* kb = reinterpret_cast<const uint8_t*>(&kcd[u]);
+        const uint8_t* vb = reinterpret_cast<const uint8_t*>(&vcd[u]);
+        const float sk = __half2float(ksv[u]), sv = __half2float(vsv[u]);
+#pragma unroll
+        for (int i = 0; i < DPL / 2; ++i) {
+          kf[2 * i] = (float)((int)(kb[i] & 15) - 8) * sk; kf[2 * i + 1] = (float)((int)(kb[i] >> 4) - 8) * sk;
+          vf[2 * i] = (float)((int)(vb[i] & 15) - 8) * sv; vf[2 * i + 1] = (float)((int)(vb[i] >> 4) - 8) * sv;
+        }
+      } else {
+        unpack_row<DPL>(kraw[u], kf);
+        unpack_row<DPL>(vraw[u], vf);
+      }
 #pragma unroll
       for (int g = 0; g < GT; ++g) {
         float s = 0.f;
@@ -181,23 +216,29 @@ __global__ void attn_merge_kernel(const float* __restrict__ part, const int* __r
 }
 
 template <int HD, int GT>
-int launch_split(const void* q, const void* kc, const void* vc, const int* lens, const int* slots, const int* base,
+int launch_split(const void* q, const void* kc, const void* vc, const void* ks, const void* vs, const int* lens, const int* slots, const int* base,
                  const int* path, int path_ld, float* part, int N, int nh, int nkv, int max_seq, int ns_grid, int direct,
                  const void* gate, int ld_gate, void* out, cudaStream_t st) {
   const int G = nh / nkv;
   dim3 grid(N, nkv * (G / GT), direct ? 1 : ns_grid);
-  launch_pdl(attn_split_kernel<HD, GT>, dim3(grid), dim3(NW * 32), 0, st, 
-      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(kc),
-      static_cast<const __nv_bfloat16*>(vc), lens, slots, base, path, path_ld, part, nh, nkv, max_seq, ns_grid,
-      rsqrtf((float)HD), direct, static_cast<const __nv_bfloat16*>(gate), ld_gate, HD, static_cast<__half*>(out));
+  if (ks)
+    launch_pdl(attn_split_kernel<HD, GT, true>, dim3(grid), dim3(NW * 32), 0, st, static_cast<const __nv_bfloat16*>(q),
+               static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc), static_cast<const __half*>(ks),
+               static_cast<const __half*>(vs), lens, slots, base, path, path_ld, part, nh, nkv, max_seq, ns_grid,
+               rsqrtf((float)HD), direct, static_cast<const __nv_bfloat16*>(gate), ld_gate, HD, static_cast<__half*>(out));
+  else
+    launch_pdl(attn_split_kernel<HD, GT, false>, dim3(grid), dim3(NW * 32), 0, st, static_cast<const __nv_bfloat16*>(q),
+               static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc), (const __half*)nullptr,
+               (const __half*)nullptr, lens, slots, base, path, path_ld, part, nh, nkv, max_seq, ns_grid,
+               rsqrtf((float)HD), direct, static_cast<const __nv_bfloat16*>(gate), ld_gate, HD, static_cast<__half*>(out));
   return (int)cudaGetLastError();
 }
 
 template <int HD>
-int dispatch_gt(int G, const void* q, const void* kc, const void* vc, const int* lens, const int* slots, const int* base,
+int dispatch_gt(int G, const void* q, const void* kc, const void* vc, const void* ks, const void* vs, const int* lens, const int* slots, const int* base,
                 const int* path, int path_ld, float* part, int N, int nh, int nkv, int max_seq, int ns_grid, int direct,
                 const void* gate, int ld_gate, void* out, cudaStream_t st) {
-#define VG_ARGS q, kc, vc, lens, slots, base, path, path_ld, part, N, nh, nkv, max_seq, ns_grid, direct, gate, ld_gate, out, st
+#define VG_ARGS q, kc, vc, ks, vs, lens, slots, base, path, path_ld, part, N, nh, nkv, max_seq, ns_grid, direct, gate, ld_gate, out, st
   if (HD == 256) {
     if (G % 4 == 0) return launch_split<HD, 4>(VG_ARGS);
     if (G % 3 == 0) return launch_split<HD, 3>(VG_ARGS);
@@ -216,18 +257,18 @@ int dispatch_gt(int G, const void* q, const void* kc, const void* vc, const int*
 // q [N, nh, hd] bf16; kc/vc [slots, nkv, max_seq, hd] bf16; lens[N] keys per column; slots[N];
 // base[N]/path[N, path_ld] optional row indirection; part: scratch of vg_attn_scratch_floats() floats;
 // gate: fused qkv buffer (bf16, row stride ld_gate) or null; out [N, nh*hd] f16.
-extern "C" int vg_attn_decode(const void* q, const void* kc, const void* vc, const int* lens, const int* slots,
-                              const int* base, const int* path, int path_ld, float* part, int N, int nh, int nkv, int hd,
-                              int max_seq, int ns_grid, int direct, const void* gate, int ld_gate, void* out,
-                              cudaStream_t st) {
+namespace {
+int attn_decode_impl(const void* q, const void* kc, const void* vc, const void* ks, const void* vs, const int* lens,
+                     const int* slots, const int* base, const int* path, int path_ld, float* part, int N, int nh, int nkv,
+                     int hd, int max_seq, int ns_grid, int direct, const void* gate, int ld_gate, void* out, cudaStream_t st) {
   if (N <= 0) return 0;
   if (nh % nkv) return -2;
   const int G = nh / nkv;
   int rc;
   switch (hd) {
-    case 64: rc = dispatch_gt<64>(G, q, kc, vc, lens, slots, base, path, path_ld, part, N, nh, nkv, max_seq, ns_grid, direct, gate, ld_gate, out, st); break;
-    case 128: rc = dispatch_gt<128>(G, q, kc, vc, lens, slots, base, path, path_ld, part, N, nh, nkv, max_seq, ns_grid, direct, gate, ld_gate, out, st); break;
-    case 256: rc = dispatch_gt<256>(G, q, kc, vc, lens, slots, base, path, path_ld, part, N, nh, nkv, max_seq, ns_grid, direct, gate, ld_gate, out, st); break;
+    case 64: rc = dispatch_gt<64>(G, q, kc, vc, ks, vs, lens, slots, base, path, path_ld, part, N, nh, nkv, max_seq, ns_grid, direct, gate, ld_gate, out, st); break;
+    case 128: rc = dispatch_gt<128>(G, q, kc, vc, ks, vs, lens, slots, base, path, path_ld, part, N, nh, nkv, max_seq, ns_grid, direct, gate, ld_gate, out, st); break;
+    case 256: rc = dispatch_gt<256>(G, q, kc, vc, ks, vs, lens, slots, base, path, path_ld, part, N, nh, nkv, max_seq, ns_grid, direct, gate, ld_gate, out, st); break;
     default: return -3;
   }
   if (rc || direct) return rc;
@@ -238,6 +279,28 @@ extern "C" int vg_attn_decode(const void* q, const void* kc, const void* vc, con
     case 256: launch_pdl(attn_merge_kernel<256>, dim3(grid), dim3(256), 0, st, part, lens, nh, ns_grid, static_cast<const __nv_bfloat16*>(gate), ld_gate, static_cast<__half*>(out)); break;
   }
   return (int)cudaGetLastError();
+}
+}  // namespace
+
+// q [N, nh, hd] bf16; kc/vc [slots, nkv, max_seq, hd] bf16; lens[N] keys per column; slots[N];
+// base[N]/path[N, path_ld] optional row indirection; part: scratch of vg_attn_scratch_floats() floats;
+// gate: fused qkv buffer (bf16, row stride ld_gate) or null; out [N, nh*hd] f16.
+extern "C" int vg_attn_decode(const void* q, const void* kc, const void* vc, const int* lens, const int* slots,
+                              const int* base, const int* path, int path_ld, float* part, int N, int nh, int nkv, int hd,
+                              int max_seq, int ns_grid, int direct, const void* gate, int ld_gate, void* out,
+                              cudaStream_t st) {
+  return attn_decode_impl(q, kc, vc, nullptr, nullptr, lens, slots, base, path, path_ld, part, N, nh, nkv, hd, max_seq, ns_grid,
+                          direct, gate, ld_gate, out, st);
+}
+
+// Same over the 4-bit cache: kq/vq [slots, nkv, max_seq, hd/2] code bytes, ks/vs [slots, nkv, max_seq, hd/16] f16 scales.
+extern "C" int vg_attn_decode_q4(const void* q, const void* kq, const void* vq, const void* ks, const void* vs, const int* lens,
+                                 const int* slots, const int* base, const int* path, int path_ld, float* part, int N, int nh,
+                                 int nkv, int hd, int max_seq, int ns_grid, int direct, const void* gate, int ld_gate, void* out,
+                                 cudaStream_t st) {
+  if (!ks || !vs) return -2;
+  return attn_decode_impl(q, kq, vq, ks, vs, lens, slots, base, path, path_ld, part, N, nh, nkv, hd, max_seq, ns_grid, direct, gate,
+                          ld_gate, out, st);
 }
 
 extern "C" long long vg_attn_scratch_floats(int N, int nh, int hd, int ns_grid) {

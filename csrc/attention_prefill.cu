@@ -309,6 +309,37 @@ __global__ void transpose_v_kernel(const __nv_bfloat16* __restrict__ v, __nv_bfl
   }
 }
 
+// 4-bit cache -> bf16 staging for the tensor-core kernel: rows[kvh][t][d] and / or transposed[kvh][d][t], t < len
+// (zeros up to the end of the last 128-key tile in the transposed copy).
+__global__ void kv_q4_dequant_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ scales,
+                                     __nv_bfloat16* __restrict__ rows, __nv_bfloat16* __restrict__ tr, int hd, int max_seq,
+                                     int len, int t_cap) {
+  __shared__ __nv_bfloat16 tile[32][33];
+  pdl_trigger();
+  pdl_wait();
+  const int kvh = blockIdx.z, t0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+  const uint8_t* cs = codes + (size_t)kvh * max_seq * (hd / 2);
+  const __half* ss = scales + (size_t)kvh * max_seq * (hd / 16);
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int t = t0 + i, d = d0 + threadIdx.x;
+    float v = 0.f;
+    if (t < len) {
+      const uint8_t b = cs[(size_t)t * (hd / 2) + (d >> 1)];
+      const int code = (d & 1) ? (b >> 4) : (b & 15);
+      v = (float)(code - 8) * __half2float(ss[(size_t)t * (hd / 16) + (d >> 4)]);
+    }
+    const __nv_bfloat16 o = __float2bfloat16_rn(v);
+    tile[i][threadIdx.x] = o;
+    if (rows && t < len) rows[((size_t)kvh * max_seq + t) * hd + d] = o;
+  }
+  if (!tr) return;
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int t = t0 + threadIdx.x;
+    if (t < t_cap) tr[((size_t)kvh * hd + d0 + i) * t_cap + t] = tile[threadIdx.x][i];
+  }
+}
+
 // ------------------------------------------------------------------ host
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -359,6 +390,20 @@ extern "C" int vg_attn_transpose_v(const void* vc, void* vT, int slot, int nkv, 
   const int tcols = (((len + 127) / 128) * 128 + 31) / 32;        // whole key tiles are written (zeros beyond len)
   launch_pdl(transpose_v_kernel, dim3(tcols, HD / 32, nkv), dim3(32, 8), 0, st, src, static_cast<__nv_bfloat16*>(vT), max_seq, len,
              vt_cap);
+  return (int)cudaGetLastError();
+}
+
+// One lane's 4-bit cache rows [0, len) -> bf16: `out_rows` [nkv][max_seq][hd] (same row pitch as the cache, so it
+// can stand in for a one-slot bf16 cache) and / or `out_transposed` [nkv][hd][t_cap]; either may be null.
+extern "C" int vg_kv_q4_dequant(const void* codes, const void* scales, int slot, int nkv, int hd, int max_seq, int len,
+                                void* out_rows, void* out_transposed, int t_cap, cudaStream_t st) {
+  if ((hd % 32) != 0 || len > max_seq || (out_transposed && len > t_cap)) return -2;
+  if (len <= 0) return 0;
+  const uint8_t* c = static_cast<const uint8_t*>(codes) + (size_t)slot * nkv * max_seq * (hd / 2);
+  const __half* sc = static_cast<const __half*>(scales) + (size_t)slot * nkv * max_seq * (hd / 16);
+  const int tcols = (((len + 127) / 128) * 128 + 31) / 32;
+  launch_pdl(kv_q4_dequant_kernel, dim3(tcols, hd / 32, nkv), dim3(32, 8), 0, st, c, sc, static_cast<__nv_bfloat16*>(out_rows),
+             static_cast<__nv_bfloat16*>(out_transposed), hd, max_seq, len, t_cap);
   return (int)cudaGetLastError();
 }
 

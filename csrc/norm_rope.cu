@@ -86,12 +86,24 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(__nv_bfloat16* res, c
 
 // One CTA per (column, head slot). Head slots: [0, nh) query heads, [nh, nh+nkv) key heads,
 // [nh+nkv, nh+2nkv) value heads. blockDim.x == hd.
+// 4-bit cache write: sixteen consecutive dims share one f16 scale (amax / 7), codes are round(v / scale) + 8.
+VG_DEVINL void kv_q4_store(float v, int d, uint8_t* codes_row, __half* scale_row) {
+  float amax = fabsf(v);
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const __half sc = __float2half_rn(amax / 7.0f);
+  const float scf = __half2float(sc);
+  const float inv = scf > 0.f ? 1.0f / scf : 0.f;
+  const int code = (int)fminf(fmaxf(rintf(v * inv), -7.0f), 7.0f) + 8;
+  const int hi = __shfl_xor_sync(0xffffffffu, code, 1);
+  if ((d & 1) == 0) codes_row[d >> 1] = (uint8_t)(code | (hi << 4));
+  if ((d & 15) == 0) scale_row[d >> 4] = sc;
+}
+
 __global__ void attn_prep_kernel(const __nv_bfloat16* qkv, int ld_qkv, const float* q_norm, const float* k_norm,
                                  const int* pos, const int* slot, const int* kv_row, __nv_bfloat16* q_out,
                                  __nv_bfloat16* kc, __nv_bfloat16* vc, int nh, int nkv, int hd, int rdim, int max_seq,
-                                 float eps, float log2_theta, int gated) {
-  pdl_trigger();
-  pdl_wait();
+                                 float eps, float log2_theta, int gated, __half* k_scale, __half* v_scale) {
   __shared__ float red[32];
   extern __shared__ float xs[];
   const int n = blockIdx.x, hs = blockIdx.y, d = threadIdx.x;
@@ -104,7 +116,9 @@ __global__ void attn_prep_kernel(const __nv_bfloat16* qkv, int ld_qkv, const flo
   float v = __bfloat162float(src[d]);
   if (hs >= nh + nkv) {
     const int s = slot[n], row = kv_row[n];
-    vc[(((size_t)s * nkv + (hs - nh - nkv)) * max_seq + row) * hd + d] = __float2bfloat16_rn(v);
+    const size_t r = ((size_t)s * nkv + (hs - nh - nkv)) * max_seq + row;
+    if (v_scale) kv_q4_store(v, d, reinterpret_cast<uint8_t*>(vc) + r * (hd / 2), v_scale + r * (hd / 16));
+    else vc[r * hd + d] = __float2bfloat16_rn(v);
     return;
   }
   float ss = block_sum(v * v, red);
@@ -125,7 +139,9 @@ __global__ void attn_prep_kernel(const __nv_bfloat16* qkv, int ld_qkv, const flo
     q_out[((size_t)n * nh + hs) * hd + d] = __float2bfloat16_rn(v);
   } else {
     const int s = slot[n], row = kv_row[n];
-    kc[(((size_t)s * nkv + (hs - nh)) * max_seq + row) * hd + d] = __float2bfloat16_rn(v);
+    const size_t r = ((size_t)s * nkv + (hs - nh)) * max_seq + row;
+    if (k_scale) kv_q4_store(v, d, reinterpret_cast<uint8_t*>(kc) + r * (hd / 2), k_scale + r * (hd / 16));
+    else kc[r * hd + d] = __float2bfloat16_rn(v);
   }
 }
 
@@ -192,14 +208,15 @@ extern "C" int vg_add_rmsnorm(void* res, const void* delta, const float* w, void
 
 extern "C" int vg_attn_prep(const void* qkv, int ld_qkv, const float* q_norm, const float* k_norm, const int* pos,
                             const int* slot, const int* kv_row, void* q_out, void* kc, void* vc, int N, int nh, int nkv,
-                            int hd, int rdim, int max_seq, float eps, float theta, int gated, cudaStream_t st) {
+                            int hd, int rdim, int max_seq, float eps, float theta, int gated, void* k_scale, void* v_scale,
+                            cudaStream_t st) {
   if (N <= 0) return 0;
-  if (hd > 1024 || (hd & 31)) return -2;
+  if (hd > 1024 || (hd & 31) || ((k_scale == nullptr) != (v_scale == nullptr))) return -2;
   dim3 grid(N, nh + 2 * nkv);
   launch_pdl(attn_prep_kernel, dim3(grid), dim3(hd), hd * sizeof(float), st, 
       static_cast<const __nv_bfloat16*>(qkv), ld_qkv, q_norm, k_norm, pos, slot, kv_row,
       static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(kc), static_cast<__nv_bfloat16*>(vc), nh, nkv, hd,
-      rdim, max_seq, eps, log2f(theta), gated);
+      rdim, max_seq, eps, log2f(theta), gated, static_cast<__half*>(k_scale), static_cast<__half*>(v_scale));
   return (int)cudaGetLastError();
 }
 

@@ -124,3 +124,73 @@ def test_moe_model_matches_oracle_and_is_batch_invariant():
     for t in range(4):
         ld, _ = gm.decode([toks[t]], [40 + t], [0])
         assert torch.equal(ld[0], lv[t]), t
+
+
+def test_draft_vocabulary_head_is_exact_subset(monkeypatch):
+    """FR-Spec: the draft head scores a row subset of the real head; inside the subset the logits are those of
+    the full head, outside it they are -inf."""
+    from velogb10_b200.models.runtime import GpuModel
+    from velogb10_b200.models.weights import draft_vocab_rows
+    cfg, w_full = _build("all")
+    _, w_sub = _build("all")
+    monkeypatch.setenv("VELO_DRAFT_VOCAB", "0")
+    full = GpuModel(w_full, keep_canonical=True)
+    monkeypatch.setenv("VELO_DRAFT_VOCAB", "200")
+    sub = GpuModel(w_sub, keep_canonical=True)
+    assert full.draft_head is None and sub.draft_head is not None
+    top, tail_start = draft_vocab_rows(200, cfg.vocab_size)
+    assert (top + cfg.vocab_size - tail_start) % 128 == 0 and sub.draft_head.m == top + cfg.vocab_size - tail_start
+    for m in (full, sub):
+        m.alloc_state(2, 2 + 17, 256)
+    prompt = list(range(3, 40))
+    _, h1 = full.prefill(0, prompt)
+    _, h2 = sub.prefill(0, prompt)
+    assert torch.equal(h1, h2)
+    toks, pos = [5, 9, 11], [37, 38, 39]
+    lf, _ = full.mtp_forward(0, toks, h1[-3:], pos)
+    lf = lf.clone()
+    ls, _ = sub.mtp_forward(0, toks, h2[-3:], pos)
+    ids = sub.draft_ids
+    inside = torch.zeros(cfg.vocab_size, dtype=torch.bool, device="cuda")
+    inside[ids] = True
+    assert torch.isinf(ls[:, ~inside]).all() and (ls[:, ~inside] < 0).all()
+    rel = ((ls[:, inside] - lf[:, inside]).norm() / lf[:, inside].norm()).item()
+    assert rel < 2e-3, rel
+
+
+def test_four_bit_kv_cache(monkeypatch):
+    """--kv-cache q4: decode and tensor-core / scalar prefill over the 4-bit cache stay close to the bf16 cache,
+    verify is still bit-identical to sequential decode, and the cache is 4.5 bits per value."""
+    from velogb10_b200.models.runtime import GpuModel
+    cfg, w1 = _build("all")
+    _, w2 = _build("all")
+    ref = GpuModel(w1, keep_canonical=True)
+    monkeypatch.setenv("VELO_KV_QUANT", "q4")
+    gm = GpuModel(w2, keep_canonical=True)
+    assert gm.kv_q4 and not ref.kv_q4
+    for m in (ref, gm):
+        m.alloc_state(2, 2 + 17, 256)
+    assert gm.kc.dtype == torch.uint8 and gm.kc.numel() * 8 + gm.ks.numel() * 16 == ref.kc.numel() * 4.5
+    g = torch.Generator().manual_seed(11)
+    prompt = torch.randint(0, cfg.vocab_size, (150,), generator=g).tolist()
+    l1, _ = ref.prefill(0, prompt)
+    l2, _ = gm.prefill(0, prompt)
+    rel = ((l2.float() - l1.float()).norm() / l1.float().norm()).item()
+    assert rel < 0.08, rel
+    toks = [int(l2.argmax()), 3, 9, 27]
+    S0, C0 = gm.S.clone(), gm.conv.clone()
+    kv0 = [t.clone() for t in gm._kv_tensors()]
+    lv, _ = gm.verify(0, toks, 150, ckpt_base=2)
+    lv = lv.clone()
+    gm.S.copy_(S0); gm.conv.copy_(C0)
+    for t, k in zip(gm._kv_tensors(), kv0):
+        t.copy_(k)
+    for t in range(4):
+        ld, _ = gm.decode([toks[t]], [150 + t], [0])
+        assert torch.equal(ld[0], lv[t]), t
+    ld1, _ = ref.decode([toks[0]], [150], [0])
+    gm.S.copy_(S0); gm.conv.copy_(C0)
+    for t, k in zip(gm._kv_tensors(), kv0):
+        t.copy_(k)
+    ld2, _ = gm.decode([toks[0]], [150], [0])
+    assert ((ld2.float() - ld1.float()).norm() / ld1.float().norm()).item() < 0.08

@@ -76,14 +76,16 @@ def _rand_tokens(cfg, n: int, seed: int) -> List[int]:
 def _snapshot(runner):
     st = runner if hasattr(runner, "S") and not hasattr(runner, "state") else None
     if st is not None:                                  # CUDA runtime
-        return [t.clone() for t in (runner.S, runner.conv, runner.kc, runner.vc) if t is not None]
+        return [t.clone() for t in (runner.S, runner.conv, runner.kc, runner.vc, getattr(runner, "ks", None), getattr(runner, "vs", None))
+                if t is not None]
     s = runner.state                                    # oracle
     return [{k: v.clone() for k, v in d.items()} for d in (s.S, s.conv, s.k, s.v)]
 
 
 def _restore(runner, snap):
     if hasattr(runner, "S") and not hasattr(runner, "state"):
-        for t, c in zip([t for t in (runner.S, runner.conv, runner.kc, runner.vc) if t is not None], snap):
+        for t, c in zip([t for t in (runner.S, runner.conv, runner.kc, runner.vc, getattr(runner, "ks", None), getattr(runner, "vs", None))
+                if t is not None], snap):
             t.copy_(c)
         return
     s = runner.state

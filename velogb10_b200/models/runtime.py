@@ -165,6 +165,9 @@ class GpuModel:
         self._pending_ar = False
         self.tc_prefill_attn = os.environ.get("VELO_NO_TC_PREFILL_ATTN", "0") != "1"
         self._prefill_ctx = None              # (slot, first position) while a prefill chunk is running
+        self.kv_q4 = os.environ.get("VELO_KV_QUANT", "bf16").lower() == "q4"
+        self._kv_scales = None                # (k scales, v scales) of the layer being run, 4-bit cache only
+        self._k_rows = None                   # bf16 staging of a lane's keys for tensor-core prefill over a 4-bit cache
         # MoE decode: second stream for the shared expert (see moe_runtime.moe_forward)
         self.moe_side_stream = None
         if os.environ.get("VELO_NO_MOE_FORK", "0") != "1" and any(L.moe is not None for L in weights.layers):
@@ -174,7 +177,23 @@ class GpuModel:
                 self.moe_join_event = torch.cuda.Event()
         self._vt = None
         _lib.lib()
+        # FR-Spec: the draft head scores a subset of the vocabulary (rows of the real head: exact)
+        self.draft_head = None
+        self.draft_ids = None
+        dv = int(os.environ.get("VELO_DRAFT_VOCAB", "65536"))
+        head = weights.lm_head
+        if dv > 0 and weights.mtp is not None and (comm is None or comm.world == 1) and head.m > 2 * dv \
+                and (head.packed is not None or head.codes is not None or head.w is not None):
+            from .weights import draft_vocab_rows, fuse_rows
+            top, tail_start = draft_vocab_rows(dv, head.m)
+            if top + (head.m - tail_start) < head.m:
+                self.draft_head = fuse_rows([head.rows(0, top), head.rows(tail_start, head.m)])
+                self.draft_ids = torch.cat([torch.arange(0, top), torch.arange(tail_start, head.m)]).to(self.dev)
         with torch.cuda.device(self.dev):
+            if self.draft_head is not None:
+                if self.use_fp4 and self.draft_head.fmt == "nvfp4":
+                    G.prepare_fp4(self.draft_head)
+                G.prepare(self.draft_head, keep_canonical=False)
             for name, q in weights.linears():
                 if q.packed is None and q.codes is None and q.w is None:
                     continue
@@ -210,8 +229,17 @@ class GpuModel:
         self.attn_index = {li: j for j, li in enumerate(attn_layers)}
         self.gdn_index = {li: j for j, li in enumerate(gdn_layers)}
         nkv = self.w.layers[attn_layers[0]].attn.nkv if attn_layers else 1
-        self.kc = torch.zeros((len(attn_layers), n_slots, nkv, max_seq, c.head_dim), dtype=torch.bfloat16, device=dev)
-        self.vc = torch.zeros_like(self.kc)
+        hd = c.head_dim
+        self.ks = self.vs = self.mtp_ks = self.mtp_vs = None
+        if self.kv_q4:
+            # 4-bit cache: code bytes (two per byte) + one f16 scale per 16 values, 4.5 bits per value
+            assert hd % 32 == 0
+            self.kc = torch.zeros((len(attn_layers), n_slots, nkv, max_seq, hd // 2), dtype=torch.uint8, device=dev)
+            self.ks = torch.zeros((len(attn_layers), n_slots, nkv, max_seq, hd // 16), dtype=torch.float16, device=dev)
+            self.vc, self.vs = torch.zeros_like(self.kc), torch.zeros_like(self.ks)
+        else:
+            self.kc = torch.zeros((len(attn_layers), n_slots, nkv, max_seq, hd), dtype=torch.bfloat16, device=dev)
+            self.vc = torch.zeros_like(self.kc)
         if gdn_layers:
             g0 = self.w.layers[gdn_layers[0]].gdn
             self.S = torch.zeros((len(gdn_layers), n_state_slots, g0.nv, c.lin_k_dim, c.lin_v_dim),
@@ -222,8 +250,13 @@ class GpuModel:
             self.S = self.conv = None
         if self.w.mtp is not None:
             mn = self.w.mtp.layer.attn.nkv
-            self.mtp_kc = torch.zeros((n_slots, mn, max_seq, c.head_dim), dtype=torch.bfloat16, device=dev)
-            self.mtp_vc = torch.zeros_like(self.mtp_kc)
+            if self.kv_q4:
+                self.mtp_kc = torch.zeros((n_slots, mn, max_seq, hd // 2), dtype=torch.uint8, device=dev)
+                self.mtp_ks = torch.zeros((n_slots, mn, max_seq, hd // 16), dtype=torch.float16, device=dev)
+                self.mtp_vc, self.mtp_vs = torch.zeros_like(self.mtp_kc), torch.zeros_like(self.mtp_ks)
+            else:
+                self.mtp_kc = torch.zeros((n_slots, mn, max_seq, hd), dtype=torch.bfloat16, device=dev)
+                self.mtp_vc = torch.zeros_like(self.mtp_kc)
         nh = max([L.attn.nh for L in self.w.layers if L.attn] + ([self.w.mtp.layer.attn.nh] if self.w.mtp else []) or [1])
         self.attn_part = torch.zeros(K.attn_scratch_floats(max(self.max_cols, 16), nh, c.head_dim, self.ns_grid),
                                      dtype=torch.float32, device=dev)
@@ -240,16 +273,20 @@ class GpuModel:
             self.S[:, slot].zero_()
             self.conv[:, slot].zero_()
         if zero_kv:
-            self.kc[:, slot].zero_()
-            self.vc[:, slot].zero_()
+            for t in self._kv_tensors():
+                t[:, slot].zero_()
 
     def compact_kv(self, slot: int, pos_start: int, cols: Sequence[int]):
         """Move KV rows of accepted tree columns to contiguous positions (reference: src/gpu.rs:5325-5414)."""
         src = torch.tensor([pos_start + c_ for c_ in cols], device=self.dev)
         dst = torch.arange(pos_start, pos_start + len(cols), device=self.dev)
-        for cache in (self.kc, self.vc):
+        for cache in self._kv_tensors():
             rows = cache[:, slot].index_select(2, src)
             cache[:, slot].index_copy_(2, dst, rows)
+
+    def _kv_tensors(self):
+        """Main-model cache tensors, all shaped [attention layer, slot, kv head, position, ...]."""
+        return [t for t in (self.kc, self.vc, self.ks, self.vs) if t is not None]
 
     # ---------------------------------------------------------------- plan upload
     def _upload(self, ws: Workspace, p: Plan):
@@ -331,20 +368,27 @@ class GpuModel:
         c, A = self.cfg, L.attn
         qkv = ws.wide[:, :A.qkv.m]
         self._linear(A.qkv, ws.xn16, n, qkv, act=act)
+        ksc, vsc = self._kv_scales if self._kv_scales is not None else (None, None)
         K.attn_prep(qkv, A.q_norm, A.k_norm, ws.pos, ws.kv_slot, ws.kv_row, ws.q, kc, vc, n, A.nh, A.nkv,
-                    c.head_dim, c.rotary_dim, c.rms_eps, c.rope_theta, c.attn_out_gate)
+                    c.head_dim, c.rotary_dim, c.rms_eps, c.rope_theta, c.attn_out_gate, k_scale=ksc, v_scale=vsc)
         a16 = ws.a16(A.o.k)
         pf = self._prefill_ctx
         if plan_direct and pf is not None and n >= 64 and c.head_dim == 256 and self.tc_prefill_attn \
                 and qkv.stride(0) % 8 == 0:
             # prefill chunk of one lane: tensor-core flash attention over the lane's cache rows
             slot, pos0 = pf
+            k_rows = None
+            if ksc is not None:
+                if self._k_rows is None or self._k_rows.shape[1] < A.nkv or self._k_rows.shape[2] != kc.shape[2]:
+                    self._k_rows = torch.zeros((1, A.nkv, kc.shape[2], c.head_dim), dtype=torch.bfloat16, device=self.dev)
+                k_rows = self._k_rows
             K.attn_prefill_tc(ws.q, kc, vc, self._vt_scratch(A.nkv, kc.shape[2]), slot, pos0, n, A.nh, A.nkv, c.head_dim,
-                              a16, gate=qkv if c.attn_out_gate else None)
+                              a16, gate=qkv if c.attn_out_gate else None, k_scale=ksc, v_scale=vsc, k_rows=k_rows)
         else:
             K.attn_decode(ws.q, kc, vc, ws.lens, ws.kv_slot, self.attn_part, a16, n, A.nh, A.nkv, c.head_dim,
                           gate=qkv if c.attn_out_gate else None, base=ws.base if use_path else None,
-                          path=ws.path if use_path else None, ns_grid=self.ns_grid, direct=plan_direct)
+                          path=ws.path if use_path else None, ns_grid=self.ns_grid, direct=plan_direct,
+                          k_scale=ksc, v_scale=vsc)
         self._row_parallel(A.o, a16, n, ws.delta)
 
     def _gdn(self, ws: Workspace, L: LayerW, li: int, n: int, n_chains: int, seq_mode: bool, act=None):
@@ -430,6 +474,7 @@ class GpuModel:
             if L.attn is not None:
                 ai = self.attn_index[li]
                 kc, vc = self.kc[ai], self.vc[ai]
+                self._kv_scales = (self.ks[ai], self.vs[ai]) if self.kv_q4 else None
             self._layer(ws, L, li, n, n_chains, seq_mode, direct, use_path, kc, vc, delta)
             delta = ws.delta
         act = self._norm(ws, delta, self.w.final_norm, n)
@@ -521,10 +566,21 @@ class GpuModel:
         self._linear(m.fc, ws.cat16, n, ws.x)
         comm, self.comm = self.comm, None          # the draft head is unsharded: no reductions
         try:
+            self._kv_scales = (self.mtp_ks, self.mtp_vs) if self.kv_q4 else None
             self._layer(ws, m.layer, -1, n, 1, True, False, False, self.mtp_kc, self.mtp_vc, None)
         finally:
             self.comm = comm
         act = self._norm(ws, ws.delta, m.norm, n)
+        if self.draft_head is not None:
+            # score the draft vocabulary only; every other token gets -inf so arg-max / sampling stay inside it
+            dl = self._draft_logits[:n] if getattr(self, "_draft_logits", None) is not None else None
+            if dl is None:
+                self._draft_logits = torch.zeros((ws.logits.shape[0], self.draft_head.m), dtype=torch.float32, device=self.dev)
+                dl = self._draft_logits[:n]
+            self._linear(self.draft_head, ws.xn16, n, self._draft_logits, act=act, out_f32=True)
+            ws.logits[:n].fill_(float("-inf"))
+            ws.logits[:n].index_copy_(1, self.draft_ids, dl)
+            return ws.logits[:n], ws.x[:n]
         self._linear(self.w.lm_head, ws.xn16, n, ws.logits, act=act, out_f32=True)
         return self._full_logits(ws.logits[:n]), ws.x[:n]
 
@@ -557,7 +613,8 @@ class GpuModel:
         self._upload(ws, plan)
         # warm-up and capture run real steps on slots 0..b-1 at position 0: save what they touch
         saved = [(t, t[:, :b].clone()) for t in (self.S, self.conv) if t is not None]
-        saved += [(t, t[:, :b, :, :1].clone()) for t in (self.kc, self.vc)]
+        kv = self._kv_tensors()
+        saved += [(t, t[:, :b, :, :1].clone()) for t in kv]
         # the attention launch grid covers every possible split, so a graph captured here is valid at any position
         torch.cuda.synchronize(self.dev)
         s = torch.cuda.Stream(device=self.dev)
@@ -573,7 +630,7 @@ class GpuModel:
             self._backbone(ws, b, b, False, False, False)
             self._greedy_tail(ws, b)
         for t, keep in saved:
-            if t is self.kc or t is self.vc:
+            if any(t is x for x in kv):
                 t[:, :b, :, :1].copy_(keep)
             else:
                 t[:, :b].copy_(keep)

@@ -100,6 +100,21 @@ class QLinear:
         return n
 
 
+def draft_vocab_rows(top: int, vocab: int, align: int = 128):
+    """Row ranges of the smaller LM head the draft model scores (FR-Spec): the ``top`` lowest token ids (BPE
+    ids are ordered by merge rank, i.e. by corpus frequency) plus the tail of the id range, where the special
+    and added tokens live (a drafter that cannot propose the end-of-turn token cannot draft the end of a turn).
+    ``top`` grows with real rows until the total is a multiple of ``align``; no padding rows (a zero row would
+    score 0 and could win an arg-max against all-negative logits). Returns ``(top, tail_start)``
+    (reference: src/quant.rs:697-721)."""
+    tail = 512 if vocab >= 8192 else max(vocab // 8, 1)
+    tail_start = max(vocab - tail, 0)
+    top = min(max(top, 0), tail_start)
+    while (top + (vocab - tail_start)) % align != 0 and top < tail_start:
+        top += 1
+    return top, tail_start
+
+
 def fuse_rows(parts: List[QLinear]) -> QLinear:
     """Concatenate linears along M. All parts must share K and format; a format mismatch falls
     back to bf16 for the whole group."""

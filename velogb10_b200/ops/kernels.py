@@ -25,12 +25,15 @@ def add_rmsnorm(res: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tenso
     _lib.check(rc, "vg_add_rmsnorm")
 
 
-def attn_prep(qkv, q_norm, k_norm, pos, slot, kv_row, q_out, kc, vc, n, nh, nkv, hd, rdim, eps, theta, gated=True):
+def attn_prep(qkv, q_norm, k_norm, pos, slot, kv_row, q_out, kc, vc, n, nh, nkv, hd, rdim, eps, theta, gated=True,
+              k_scale=None, v_scale=None):
+    """q/k norm + partial RoPE + cache write. With ``k_scale`` / ``v_scale`` the cache is 4-bit: ``kc`` / ``vc`` hold
+    code bytes ``[slots, nkv, max_seq, hd/2]`` and the scales are f16 ``[slots, nkv, max_seq, hd/16]``."""
     max_seq = kc.shape[2]
     rc = _lib.lib().vg_attn_prep(ptr(qkv), c_int(qkv.stride(0)), ptr(q_norm), ptr(k_norm), ptr(pos), ptr(slot),
                                  ptr(kv_row), ptr(q_out), ptr(kc), ptr(vc), c_int(n), c_int(nh), c_int(nkv), c_int(hd),
                                  c_int(rdim), c_int(max_seq), c_float(eps), c_float(theta), c_int(1 if gated else 0),
-                                 stream())
+                                 ptr(k_scale), ptr(v_scale), stream())
     _lib.check(rc, "vg_attn_prep")
 
 
@@ -65,10 +68,19 @@ def attn_scratch_floats(n: int, nh: int, hd: int, ns_grid: int = 32) -> int:
 
 
 def attn_decode(q, kc, vc, lens, slots, part, out16, n, nh, nkv, hd, gate=None, base=None, path=None,
-                ns_grid: int = 32, direct: bool = False):
+                ns_grid: int = 32, direct: bool = False, k_scale=None, v_scale=None):
     """Split-K GQA attention of ``n`` columns over the slotted cache. ``lens[c]`` keys are attended by
-    column c; ``part`` is the fp32 partial buffer (scratch, ``attn_scratch_floats`` elements)."""
+    column c; ``part`` is the fp32 partial buffer (scratch, ``attn_scratch_floats`` elements). With
+    ``k_scale`` / ``v_scale`` the cache is 4-bit (see ``attn_prep``)."""
     max_seq = kc.shape[2]
+    if k_scale is not None:
+        rc = _lib.lib().vg_attn_decode_q4(ptr(q), ptr(kc), ptr(vc), ptr(k_scale), ptr(v_scale), ptr(lens), ptr(slots),
+                                          ptr(base), ptr(path), c_int(path.stride(0) if path is not None else 0), ptr(part),
+                                          c_int(n), c_int(nh), c_int(nkv), c_int(hd), c_int(max_seq), c_int(ns_grid),
+                                          c_int(1 if direct else 0), ptr(gate),
+                                          c_int(gate.stride(0) if gate is not None else 0), ptr(out16), stream())
+        _lib.check(rc, "vg_attn_decode_q4", 1 if direct else 2)
+        return
     rc = _lib.lib().vg_attn_decode(ptr(q), ptr(kc), ptr(vc), ptr(lens), ptr(slots), ptr(base), ptr(path),
                                    c_int(path.stride(0) if path is not None else 0), ptr(part), c_int(n), c_int(nh),
                                    c_int(nkv), c_int(hd), c_int(max_seq), c_int(ns_grid), c_int(1 if direct else 0),
@@ -76,15 +88,26 @@ def attn_decode(q, kc, vc, lens, slots, part, out16, n, nh, nkv, hd, gate=None, 
     _lib.check(rc, "vg_attn_decode", 1 if direct else 2)
 
 
-def attn_prefill_tc(q, kc, vc, vT, slot: int, pos0: int, n: int, nh: int, nkv: int, hd: int, out16, gate=None):
+def attn_prefill_tc(q, kc, vc, vT, slot: int, pos0: int, n: int, nh: int, nkv: int, hd: int, out16, gate=None,
+                    k_scale=None, v_scale=None, k_rows=None):
     """Causal prefill attention on the tensor cores for one lane: queries ``q[:n]`` (bf16 ``[cap, nh*hd]``) at
     positions ``pos0 ..``, keys / values = the lane's cache rows ``[0, pos0 + n)``. ``vT`` is the transposed-value
-    scratch ``[nkv, hd, cap_keys]`` this call refreshes first."""
+    scratch ``[nkv, hd, cap_keys]`` this call refreshes first. A 4-bit cache (``k_scale`` / ``v_scale``) is first
+    expanded to bf16: keys into ``k_rows`` ``[1, nkv, max_seq, hd]``, values straight into ``vT``."""
     max_seq = kc.shape[2]
     L = _lib.lib()
-    rc = L.vg_attn_transpose_v(ptr(vc), ptr(vT), c_int(slot), c_int(nkv), c_int(hd), c_int(max_seq), c_int(pos0 + n),
-                               c_int(vT.shape[2]), stream())
-    _lib.check(rc, "vg_attn_transpose_v")
+    if k_scale is not None:
+        rc = L.vg_kv_q4_dequant(ptr(kc), ptr(k_scale), c_int(slot), c_int(nkv), c_int(hd), c_int(max_seq), c_int(pos0 + n),
+                                ptr(k_rows), ptr(None), c_int(0), stream())
+        _lib.check(rc, "vg_kv_q4_dequant")
+        rc = L.vg_kv_q4_dequant(ptr(vc), ptr(v_scale), c_int(slot), c_int(nkv), c_int(hd), c_int(max_seq), c_int(pos0 + n),
+                                ptr(None), ptr(vT), c_int(vT.shape[2]), stream())
+        _lib.check(rc, "vg_kv_q4_dequant")
+        kc, slot = k_rows, 0
+    else:
+        rc = L.vg_attn_transpose_v(ptr(vc), ptr(vT), c_int(slot), c_int(nkv), c_int(hd), c_int(max_seq), c_int(pos0 + n),
+                                   c_int(vT.shape[2]), stream())
+        _lib.check(rc, "vg_attn_transpose_v")
     rc = L.vg_attn_prefill_tc(ptr(q), c_int(q.shape[0]), ptr(kc), ptr(vT), c_int(vT.shape[2]), c_int(slot), c_int(nkv),
                               c_int(nh), c_int(hd), c_int(max_seq), c_int(pos0), c_int(n), c_float(hd ** -0.5),
                               ptr(gate), c_int(gate.stride(0) if gate is not None else 0), ptr(out16),
