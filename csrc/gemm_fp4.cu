@@ -275,7 +275,8 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
     float* red = reinterpret_cast<float*>(smem);          // stage 0 is idle once every MMA has completed
     if (epi && have) {
 #pragma unroll
-      for (int n = 0; n < 16; ++n) red[n * BM + m_local] = y[n];
+      for (int n = 0; n < 16; ++n)
+        if (n < p.N) red[n * BM + m_local] = y[n];
     }
     cluster_sync_all();
     if (z == 0 && epi && have) {
@@ -283,7 +284,8 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
       for (int s = 1; s < S; ++s) {
         const uint32_t remote = dsmem_map(red_addr, (uint32_t)s);
 #pragma unroll
-        for (int n = 0; n < 16; ++n) y[n] += dsmem_ld_f32(remote + (uint32_t)((n * BM + m_local) * 4));
+        for (int n = 0; n < 16; ++n)                       // only the columns that exist cross the cluster
+          if (n < p.N) y[n] += dsmem_ld_f32(remote + (uint32_t)((n * BM + m_local) * 4));
       }
     }
     cluster_sync_all();

@@ -160,7 +160,7 @@ def test_draft_vocabulary_head_is_exact_subset(monkeypatch):
 
 def test_four_bit_kv_cache(monkeypatch):
     """--kv-cache q4: decode and tensor-core / scalar prefill over the 4-bit cache stay close to the bf16 cache,
-    verify is still bit-identical to sequential decode, and the cache is 4.5 bits per value."""
+    verify is still bit-identical to sequential decode, and the cache is 5 bits per value."""
     from velogb10_b200.models.runtime import GpuModel
     cfg, w1 = _build("all")
     _, w2 = _build("all")
@@ -170,7 +170,7 @@ def test_four_bit_kv_cache(monkeypatch):
     assert gm.kv_q4 and not ref.kv_q4
     for m in (ref, gm):
         m.alloc_state(2, 2 + 17, 256)
-    assert gm.kc.dtype == torch.uint8 and gm.kc.numel() * 8 + gm.ks.numel() * 16 == ref.kc.numel() * 4.5
+    assert gm.kc.dtype == torch.uint8 and gm.kc.numel() * 8 + gm.ks.numel() * 16 == ref.kc.numel() * 5
     g = torch.Generator().manual_seed(11)
     prompt = torch.randint(0, cfg.vocab_size, (150,), generator=g).tolist()
     l1, _ = ref.prefill(0, prompt)

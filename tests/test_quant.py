@@ -167,3 +167,14 @@ def test_checkpoint_roundtrip_and_requant(tmp_path):
     l4 = ModelBuilder(cfg2, io.SafetensorsSource(out4)).build()
     assert l4.layers[0].gdn.out.fmt == "nvfp4"
     assert l4.layers[0].mlp is None or l4.layers[0].mlp.down.fmt == "nvfp4"
+
+
+def test_draft_vocab_rows_rule():
+    """FR-Spec row selection: the most frequent ids plus the special-token tail, padded with real rows."""
+    from velogb10_b200.models.weights import draft_vocab_rows
+    top, tail = draft_vocab_rows(65536, 248320)
+    assert tail == 248320 - 512 and top >= 65536 and (top + 512) % 128 == 0 and top - 65536 < 128
+    top, tail = draft_vocab_rows(10 ** 9, 248320)              # asking for more than the vocabulary keeps every row once
+    assert top == tail
+    top, tail = draft_vocab_rows(200, 1024)
+    assert tail == 1024 - 128 and (top + 128) % 128 == 0

@@ -232,7 +232,7 @@ class GpuModel:
         hd = c.head_dim
         self.ks = self.vs = self.mtp_ks = self.mtp_vs = None
         if self.kv_q4:
-            # 4-bit cache: code bytes (two per byte) + one f16 scale per 16 values, 4.5 bits per value
+            # 4-bit cache: code bytes (two per byte) + one f16 scale per 16 values, 5 bits per value
             assert hd % 32 == 0
             self.kc = torch.zeros((len(attn_layers), n_slots, nkv, max_seq, hd // 2), dtype=torch.uint8, device=dev)
             self.ks = torch.zeros((len(attn_layers), n_slots, nkv, max_seq, hd // 16), dtype=torch.float16, device=dev)
