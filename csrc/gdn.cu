@@ -252,29 +252,35 @@ VG_DEVINL float block_sum_by_warp(const float* x, int lane) {
   return warp_sum(r);
 }
 
-template <int KD, int VD, int TB>
-__global__ void __launch_bounds__(2 * VD) gdn_prefill_kernel(
+// CS CTAs share one value head, each owning VD / CS state columns (the kernel stalls on shared-memory latency
+// with one CTA per head, and only nv SMs would be busy). With CS > 1 the gated output norm, the only step that
+// couples a head's columns, moves to gdn_out_norm_kernel: this kernel then stores the raw outputs (fp32).
+template <int KD, int VD, int TB, int CS>
+__global__ void __launch_bounds__(2 * VD / CS) gdn_prefill_kernel(
     const float* __restrict__ qkv, const __nv_bfloat16* __restrict__ proj, int ldp, int off_z, int off_b, int off_a,
     float* __restrict__ S, const float* __restrict__ A_log, const float* __restrict__ dt_bias,
     const float* __restrict__ norm_w, int t0, int tn, const int* __restrict__ in_slot, const int* __restrict__ out_slot,
-    __half* __restrict__ out, int nk, int nv, float eps) {
-  constexpr int NT = 2 * VD, NWARP = NT / 32, HK = KD / 2;
-  static_assert(KD == VD && VD % 32 == 0 && TB % NWARP == 0 && KD % 8 == 0, "layout");
+    __half* __restrict__ out, float* __restrict__ o_raw, int nk, int nv, float eps) {
+  constexpr int VC = VD / CS;              // state columns of this CTA
+  constexpr int NT = 2 * VC, NWARP = NT / 32, HK = KD / 2;
+  static_assert(KD == VD && VD % 32 == 0 && VC % 32 == 0 && TB % NWARP == 0 && KD % 8 == 0, "layout");
   extern __shared__ __align__(16) float sm[];
   float* qb = sm;                          // [2][TB][KD] raw q
   float* kb = qb + 2 * TB * KD;            // [2][TB][KD] raw k
-  float* vb = kb + 2 * TB * KD;            // [2][TB][VD]
-  float* ob = vb + 2 * TB * VD;            // [TB][VD]    o before the output norm
-  float* sq = ob + TB * VD;                // [TB][VD]    o^2 staging for the batched reductions
-  float* sc = sq + TB * VD;                // [TB][4]     g, beta, ksc, qsc
+  float* vb = kb + 2 * TB * KD;            // [2][TB][VC]
+  float* ob = vb + 2 * TB * VC;            // [TB][VC]    o before the output norm
+  float* sq = ob + TB * VC;                // [TB][VC]    o^2 staging for the batched reductions
+  float* sc = sq + TB * VC;                // [TB][4]     g, beta, ksc, qsc
   float* ssb = sc + TB * 4;                // [TB]        sum o^2
   float* bab = ssb + TB;                   // [TB][2]     b, a of the batch (as float)
   int* osl = reinterpret_cast<int*>(bab + TB * 2);                       // [TB] out_slot
-  __nv_bfloat16* zb = reinterpret_cast<__nv_bfloat16*>(osl + TB);        // [2][TB][VD] gate z
+  __nv_bfloat16* zb = reinterpret_cast<__nv_bfloat16*>(osl + TB);        // [2][TB][VC] gate z (CS == 1 only)
   pdl_trigger();
   pdl_wait();
-  const int vh = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int c = tid >> 1, h = tid & 1;     // column of the state and which half of the key range
+  const int vh = blockIdx.x / CS, part = blockIdx.x % CS;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int cl = tid >> 1, h = tid & 1;    // local column and which half of the key range
+  const int c = part * VC + cl;            // column of the head's state
   const int kh = vh * nk / nv;
   const int key_dim = nk * KD, conv_dim = 2 * key_dim + nv * VD;
   const float a_coef = -__expf(A_log[vh]);
@@ -292,20 +298,26 @@ __global__ void __launch_bounds__(2 * VD) gdn_prefill_kernel(
     const int base = t0 + b * TB, cnt = min(TB, tn - b * TB);
     float* q_ = qb + (b & 1) * TB * KD;
     float* k_ = kb + (b & 1) * TB * KD;
-    float* v_ = vb + (b & 1) * TB * VD;
-    __nv_bfloat16* z_ = zb + (b & 1) * TB * VD;
-    constexpr int CPT = KD / 4;            // 16-byte chunks per fp32 token row
+    float* v_ = vb + (b & 1) * TB * VC;
+    __nv_bfloat16* z_ = zb + (b & 1) * TB * VC;
+    constexpr int CPT = KD / 4;            // 16-byte chunks per fp32 q / k row
     for (int i = tid; i < cnt * CPT; i += NT) {
       const int tt = i / CPT, o4 = (i % CPT) * 4;
       const float* row = qkv + (size_t)(base + tt) * conv_dim;
       cp_async16(q_ + tt * KD + o4, row + kh * KD + o4);
       cp_async16(k_ + tt * KD + o4, row + key_dim + kh * KD + o4);
-      cp_async16(v_ + tt * VD + o4, row + 2 * key_dim + vh * VD + o4);
     }
-    constexpr int CPZ = VD / 8;            // 16-byte chunks per bf16 z row
-    for (int i = tid; i < cnt * CPZ; i += NT) {
-      const int tt = i / CPZ, o8 = (i % CPZ) * 8;
-      cp_async16(z_ + tt * VD + o8, proj + (size_t)(base + tt) * ldp + off_z + vh * VD + o8);
+    constexpr int CPV = VC / 4;
+    for (int i = tid; i < cnt * CPV; i += NT) {
+      const int tt = i / CPV, o4 = (i % CPV) * 4;
+      cp_async16(v_ + tt * VC + o4, qkv + (size_t)(base + tt) * conv_dim + 2 * key_dim + vh * VD + part * VC + o4);
+    }
+    if (CS == 1) {
+      constexpr int CPZ = VC / 8;          // 16-byte chunks per bf16 z row
+      for (int i = tid; i < cnt * CPZ; i += NT) {
+        const int tt = i / CPZ, o8 = (i % CPZ) * 8;
+        cp_async16(z_ + tt * VC + o8, proj + (size_t)(base + tt) * ldp + off_z + vh * VD + o8);
+      }
     }
     cp_async_commit();
   };
@@ -327,8 +339,8 @@ __global__ void __launch_bounds__(2 * VD) gdn_prefill_kernel(
     const int base = t0 + b * TB, cnt = min(TB, tn - b * TB);
     const float* q_ = qb + (b & 1) * TB * KD;
     const float* k_ = kb + (b & 1) * TB * KD;
-    const float* v_ = vb + (b & 1) * TB * VD;
-    const __nv_bfloat16* z_ = zb + (b & 1) * TB * VD;
+    const float* v_ = vb + (b & 1) * TB * VC;
+    const __nv_bfloat16* z_ = zb + (b & 1) * TB * VC;
     if (tid < TB) { bab[tid * 2] = nb_b; bab[tid * 2 + 1] = nb_a; osl[tid] = nb_os; }
     cp_async_wait_all();
     __syncthreads();                       // batch b landed; everyone is done with batch b - 1
@@ -364,7 +376,7 @@ __global__ void __launch_bounds__(2 * VD) gdn_prefill_kernel(
       const float g = sc[tt * 4 + 0], beta = sc[tt * 4 + 1], ksc = sc[tt * 4 + 2], qsc = sc[tt * 4 + 3];
       const float* ks = k_ + tt * KD + h * HK;
       const float* qs = q_ + tt * KD + h * HK;
-      const float v = v_[tt * VD + c];
+      const float v = v_[tt * VC + cl];
       float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
 #pragma unroll
       for (int a = 0; a < HK; a += 4) {
@@ -392,8 +404,8 @@ __global__ void __launch_bounds__(2 * VD) gdn_prefill_kernel(
       other = __shfl_xor_sync(0xffffffffu, mine, 1);
       const float o = (h == 0 ? mine + other : other + mine) * qsc;
       if (h == 0) {
-        ob[tt * VD + c] = o;
-        sq[tt * VD + c] = o * o;
+        ob[tt * VC + cl] = o;
+        if (CS == 1) sq[tt * VC + cl] = o * o;
       }
       const int os = osl[tt];
       if (os >= 0) {
@@ -403,6 +415,14 @@ __global__ void __launch_bounds__(2 * VD) gdn_prefill_kernel(
       }
     }
     __syncthreads();
+    if (CS > 1) {
+      // raw outputs of the batch, coalesced; the norm over the whole head runs in gdn_out_norm_kernel
+      for (int i = tid; i < cnt * VC; i += NT) {
+        const int tt = i / VC, cc = i % VC;
+        o_raw[((size_t)(base + tt) * nv + vh) * VD + part * VC + cc] = ob[tt * VC + cc];
+      }
+      continue;
+    }
     // ---- output norm of the batch
     for (int u = 0; u < TPW; ++u) {
       const int tt = warp * TPW + u;
@@ -417,6 +437,21 @@ __global__ void __launch_bounds__(2 * VD) gdn_prefill_kernel(
           f32_to_f16_sat(ob[tt * VD + c] * rsqrtf(ssb[tt] / (float)VD + eps) * nw * silu(z));
     }
   }
+}
+
+// Gated output norm of the column-split prefill: one CTA per (token, head), the same block_sum as the step kernel.
+template <int VD>
+__global__ void __launch_bounds__(VD) gdn_out_norm_kernel(const float* __restrict__ o_raw, const __nv_bfloat16* __restrict__ proj,
+                                                          int ldp, int off_z, const float* __restrict__ norm_w, int t0,
+                                                          __half* __restrict__ out, int nv, float eps) {
+  __shared__ float red[32];
+  pdl_trigger();
+  pdl_wait();
+  const int t = t0 + blockIdx.x, vh = blockIdx.y, j = threadIdx.x;
+  const float o = o_raw[((size_t)t * nv + vh) * VD + j];
+  const float ss = block_sum(o * o, red);
+  const float z = __bfloat162float(proj[(size_t)t * ldp + off_z + vh * VD + j]);
+  out[((size_t)t * nv + vh) * VD + j] = f32_to_f16_sat(o * rsqrtf(ss / (float)VD + eps) * norm_w[j] * silu(z));
 }
 
 }  // namespace
@@ -446,26 +481,46 @@ extern "C" int vg_gdn_step(const float* qkv, const void* proj, int ldp, int off_
 }
 
 // One linear chain of `tn` columns starting at column t0 (prefill): same results as vg_gdn_step on that chain.
+// `o_scratch` (fp32, at least (t0 + tn) * nv * vd elements, or null) enables the column-split form: `split` CTAs
+// per head (1, 2 or 4; 0 = pick so that the grid fills the SMs) plus a separate output-norm kernel.
 extern "C" int vg_gdn_prefill(const float* qkv, const void* proj, int ldp, int off_z, int off_b, int off_a, float* S,
                               const float* A_log, const float* dt_bias, const float* norm_w, int t0, int tn,
                               const int* in_slot, const int* out_slot, void* out_f16, int nk, int nv, int kd, int vd,
-                              float eps, cudaStream_t st) {
+                              float eps, float* o_scratch, int split, cudaStream_t st) {
   if (tn <= 0) return 0;
   if (kd != 128 || vd != 128) return -3;
   // 16-byte async copies: every staged row must start on a 16-byte boundary
   if ((ldp % 8) != 0 || (off_z % 8) != 0 || (reinterpret_cast<uintptr_t>(proj) & 15) || (reinterpret_cast<uintptr_t>(qkv) & 15))
     return -2;
   constexpr int TB = 16;
-  const size_t smem = (size_t)(2 * TB * 128 * 3 + 2 * TB * 128 + TB * 4 + TB + TB * 2) * sizeof(float) + TB * sizeof(int) +
-                      (size_t)2 * TB * 128 * sizeof(__nv_bfloat16);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gdn_prefill_kernel<128, 128, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
+  if (split == 0) split = !o_scratch ? 1 : (nv * 4 <= 160 ? 4 : (nv * 2 <= 160 ? 2 : 1));
+  if (split != 1 && (!o_scratch || (split != 2 && split != 4))) return -2;
+  auto smem_for = [](int cs) {
+    const int vc = 128 / cs;
+    return (size_t)(2 * TB * 128 * 2 + 2 * TB * vc + 2 * TB * vc + TB * 4 + TB + TB * 2) * sizeof(float) + TB * sizeof(int) +
+           (size_t)2 * TB * vc * sizeof(__nv_bfloat16);
+  };
+  const __nv_bfloat16* pj = static_cast<const __nv_bfloat16*>(proj);
+  __half* o16 = static_cast<__half*>(out_f16);
+#define VG_GDN_PF(CS)                                                                                                   \
+  {                                                                                                                     \
+    static bool configured = false;                                                                                     \
+    if (!configured) {                                                                                                  \
+      cudaError_t e = cudaFuncSetAttribute(gdn_prefill_kernel<128, 128, TB, CS>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                           (int)smem_for(CS));                                                          \
+      if (e != cudaSuccess) return (int)e;                                                                              \
+      configured = true;                                                                                                \
+    }                                                                                                                   \
+    launch_pdl(gdn_prefill_kernel<128, 128, TB, CS>, dim3(nv * CS), dim3(256 / CS), smem_for(CS), st, qkv, pj, ldp, off_z, off_b, \
+               off_a, S, A_log, dt_bias, norm_w, t0, tn, in_slot, out_slot, o16, o_scratch, nk, nv, eps);                 \
   }
-  launch_pdl(gdn_prefill_kernel<128, 128, TB>, dim3(nv), dim3(256), smem, st, qkv, static_cast<const __nv_bfloat16*>(proj), ldp,
-             off_z, off_b, off_a, S, A_log, dt_bias, norm_w, t0, tn, in_slot, out_slot, static_cast<__half*>(out_f16), nk, nv, eps);
+  if (split == 4) VG_GDN_PF(4)
+  else if (split == 2) VG_GDN_PF(2)
+  else VG_GDN_PF(1)
+#undef VG_GDN_PF
+  if (split > 1)
+    launch_pdl(gdn_out_norm_kernel<128>, dim3(tn, nv), dim3(128), 0, st, (const float*)o_scratch, pj, ldp, off_z, norm_w, t0, o16, nv,
+               eps);
   return (int)cudaGetLastError();
 }
 

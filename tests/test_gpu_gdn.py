@@ -38,3 +38,12 @@ def test_prefill_kernel_matches_step_kernel_bitwise(T):
     lib.check_err_word()
     assert torch.equal(oa, ob)
     assert torch.equal(Sa, Sb)
+    # column-split forms (2 and 4 CTAs per head + separate output norm): same bits
+    scratch = torch.zeros(T * nv * vd, device=dev)
+    for split in (2, 4):
+        Sc = S0.clone()
+        oc = torch.zeros_like(oa)
+        K.gdn_prefill(qkv, proj, conv_dim, conv_dim + value_dim, conv_dim + value_dim + nv, Sc, A_log, dt_bias, norm_w,
+                      0, T, in_slot, out_slot, oc, nk, nv, kd, vd, 1e-6, o_scratch=scratch, split=split)
+        torch.cuda.synchronize()
+        assert torch.equal(oa, oc) and torch.equal(Sa, Sc), split

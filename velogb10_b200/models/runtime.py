@@ -167,6 +167,7 @@ class GpuModel:
         self._prefill_ctx = None              # (slot, first position) while a prefill chunk is running
         self.kv_q4 = os.environ.get("VELO_KV_QUANT", "bf16").lower() == "q4"
         self._kv_scales = None                # (k scales, v scales) of the layer being run, 4-bit cache only
+        self._gdn_o = None                    # fp32 raw outputs of the column-split GDN prefill kernel
         self._k_rows = None                   # bf16 staging of a lane's keys for tensor-core prefill over a 4-bit cache
         # MoE decode: second stream for the shared expert (see moe_runtime.moe_forward)
         self.moe_side_stream = None
@@ -421,9 +422,13 @@ class GpuModel:
         if linear_chain and n > 16 and c.lin_k_dim == 128 and c.lin_v_dim == 128 and proj.stride(0) % 8 == 0 \
                 and conv_dim % 8 == 0:
             # prefill chunk: one chain through all n columns
+            need = ws.cap * value_dim
+            if self._gdn_o is None or self._gdn_o.numel() < need:
+                self._gdn_o = torch.zeros(need, dtype=torch.float32, device=self.dev)
             K.gdn_prefill(ws.conv_out, proj, conv_dim, conv_dim + value_dim, conv_dim + value_dim + Gd.nv, self.S[gi],
                           Gd.A_log, Gd.dt_bias, Gd.norm, 0, n, ws.st_in, ws.st_out, g16, Gd.nk, Gd.nv, c.lin_k_dim,
-                          c.lin_v_dim, c.rms_eps)
+                          c.lin_v_dim, c.rms_eps, o_scratch=self._gdn_o,
+                          split=int(os.environ.get("VELO_GDN_PREFILL_SPLIT", "0")))
         else:
             K.gdn_step(ws.conv_out, proj, conv_dim, conv_dim + value_dim, conv_dim + value_dim + Gd.nv, self.S[gi],
                        Gd.A_log, Gd.dt_bias, Gd.norm, ws.chain_start, ws.chain_len, n_chains, ws.st_in, ws.parent,

@@ -135,14 +135,16 @@ def gdn_step(qkv, proj, off_z, off_b, off_a, S, A_log, dt_bias, norm_w, chain_st
 
 
 def gdn_prefill(qkv, proj, off_z, off_b, off_a, S, A_log, dt_bias, norm_w, t0, tn, in_slot, out_slot, out16, nk, nv, kd, vd,
-                eps):
+                eps, o_scratch=None, split: int = 0):
     """One linear chain of ``tn`` columns (prefill): bit-identical to ``gdn_step`` on that chain, with the
-    per-token reductions batched so the critical path is the thread-local recurrence."""
+    per-token reductions batched so the critical path is the thread-local recurrence. With ``o_scratch``
+    (fp32, ``(t0 + tn) * nv * vd`` elements) each head is split over ``split`` CTAs (0 = automatic) and the
+    gated output norm runs as a second kernel."""
     rc = _lib.lib().vg_gdn_prefill(ptr(qkv), ptr(proj), c_int(proj.stride(0)), c_int(off_z), c_int(off_b), c_int(off_a),
                                    ptr(S), ptr(A_log), ptr(dt_bias), ptr(norm_w), c_int(t0), c_int(tn), ptr(in_slot),
                                    ptr(out_slot), ptr(out16), c_int(nk), c_int(nv), c_int(kd), c_int(vd), c_float(eps),
-                                   stream())
-    _lib.check(rc, "vg_gdn_prefill")
+                                   ptr(o_scratch), c_int(split), stream())
+    _lib.check(rc, "vg_gdn_prefill", 2 if o_scratch is not None else 1)
 
 
 def argmax(logits: torch.Tensor, n: int, out: torch.Tensor, out_val: Optional[torch.Tensor] = None,
