@@ -1,0 +1,69 @@
+"""The serving scheduler on the CUDA runtime: greedy output is identical however the work is batched or
+speculated (continuous batching, CUDA-graph decode, MTP chain / tree verification, prefix cache)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def weights():
+    from velogb10_b200.checkpoint.synthetic import SyntheticSource
+    from velogb10_b200.config import tiny_hybrid
+    from velogb10_b200.models.weights import ModelBuilder
+    cfg = tiny_hybrid(mtp=True)
+    return ModelBuilder(cfg, SyntheticSource(cfg, 0, "cuda", std=0.08), recipe="all", device="cuda").build()
+
+
+def _prompts(cfg, n, seed=1, lo=8, hi=40):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, cfg.vocab_size - 2, (int(torch.randint(lo, hi, (1,), generator=g)),), generator=g).tolist()
+            for _ in range(n)]
+
+
+def _run(model, prompts, max_new=14, max_batch=4, policy=None, **kw):
+    from velogb10_b200.engine.mtp import MtpPolicy
+    from velogb10_b200.engine.sampling import SamplingParams
+    from velogb10_b200.engine.scheduler import Request, Scheduler
+    sch = Scheduler(model, max_batch, 160, eos_ids=[model.cfg.vocab_size - 1],
+                    policy=policy or MtpPolicy("off", has_head=True), **kw)
+    outs = [[] for _ in prompts]
+    for i, p in enumerate(prompts):
+        sch.submit(Request(p, max_new, SamplingParams(temperature=0.0), on_token=outs[i].append))
+    sch.run_until_idle(10000)
+    torch.cuda.synchronize()
+    from velogb10_b200.ops import lib
+    lib.check_err_word()
+    return outs, sch
+
+
+def test_batching_speculation_and_prefix_cache_do_not_change_greedy_output(weights):
+    from velogb10_b200.engine.mtp import MtpPolicy
+    from velogb10_b200.models.runtime import GpuModel
+    gm = GpuModel(weights, keep_canonical=True)
+    prompts = _prompts(weights.cfg, 5)
+    solo = [_run(gm, [p], max_batch=1)[0][0] for p in prompts]
+    together, sch = _run(gm, prompts, max_batch=4)
+    assert together == solo
+    assert sch.stats["admitted"] == 5 and not sch.lanes
+    # bitwise-lossless speculation: the draft head proposes, a width-N verify decides
+    for depth in (2, 4):
+        spec, sch = _run(gm, prompts[:2], max_batch=1, policy=MtpPolicy("on", depth=depth))
+        assert spec == solo[:2], depth
+    tree, _ = _run(gm, prompts[:2], max_batch=1, policy=MtpPolicy("on", depth=3), tree_draft=True)
+    assert tree == solo[:2]
+    # a prompt that extends a served one re-uses the slot's state
+    again, sch = _run(gm, [prompts[0], prompts[0] + solo[0][:4]], max_batch=1)
+    assert again[0] == solo[0] and again[1] == solo[0][4:] + again[1][len(solo[0]) - 4:]
+
+
+def test_four_bit_cache_serving_is_self_consistent(weights, monkeypatch):
+    from velogb10_b200.engine.mtp import MtpPolicy
+    from velogb10_b200.models.runtime import GpuModel
+    monkeypatch.setenv("VELO_KV_QUANT", "q4")
+    gm = GpuModel(weights, keep_canonical=True)
+    prompts = _prompts(weights.cfg, 3, seed=5)
+    solo = [_run(gm, [p], max_batch=1)[0][0] for p in prompts]
+    together, _ = _run(gm, prompts, max_batch=4)
+    spec, _ = _run(gm, prompts[:2], max_batch=1, policy=MtpPolicy("on", depth=3))
+    assert together == solo and spec == solo[:2]
