@@ -147,6 +147,82 @@ __global__ void __launch_bounds__(256) allreduce_twoshot_kernel(VgCommCtx c, con
 }
 
 // All-gather of a small payload (<= slot_bytes) from every rank: out[q * bytes ...] = rank q's payload.
+// ------------------------------------------------------------------ fused GEMM + reduce-scatter: second half
+// Every rank's row-parallel GEMM pushed its fp32 partial tiles of this rank's token rows into this rank's slots and
+// published one epoch word per tile (csrc/gemm_tc.cu, rs epilogue). Here: wait for the tiles of every rank,
+// sum in rank order, push the bf16 result into every rank's result area, wait for the other segments, assemble
+// `out`. Same second flag round, completion counter and epoch update as the two-shot all-reduce.
+__global__ void __launch_bounds__(256) gemm_rs_finish_kernel(VgCommCtx c, __nv_bfloat16* __restrict__ out, int n, int M,
+                                                             int rs_rows, int m_tiles) {
+  __shared__ int failed;
+  const uint32_t e = *c.epoch + 1;
+  const int set = e & 1;
+  const int W = c.world, cta = blockIdx.x, nct = gridDim.x;
+  const int my0 = c.rank * rs_rows, my_rows = max(0, min(n, my0 + rs_rows) - my0);
+  const int my_tiles = ((my_rows + 127) / 128) * m_tiles;
+  if (threadIdx.x == 0) failed = 0;
+  __syncthreads();
+  // every tile of my rows from every rank
+  {
+    const uint32_t* fl = reinterpret_cast<const uint32_t*>(c.data[c.rank] + c.rsflags_off);
+    for (int i = threadIdx.x; i < W * my_tiles; i += blockDim.x) {
+      const int q = i / my_tiles, t = i % my_tiles;
+      if (!wait_flag(fl + ((size_t)(set * MAX_RANKS + q) * VG_RS_MAX_TILES + t), e, c.timeout_ns)) {
+        atomicCAS(c.status, 0, VG_ERR_PEER_WAIT);
+        failed = 1;
+      }
+    }
+  }
+  __syncthreads();
+  const size_t seg = (size_t)rs_rows * M;                          // elements per owner segment
+  const size_t mine = (size_t)my_rows * M;
+  const size_t per = ((mine + nct - 1) / nct + 7) & ~(size_t)7;
+  const size_t lo = min(mine, (size_t)cta * per), hi = min(mine, lo + per);
+  if (!failed) {
+    const float* base = reinterpret_cast<const float*>(c.data[c.rank] + c.slots_off + (size_t)set * MAX_RANKS * c.slot_bytes);
+    const size_t stride = c.slot_bytes / sizeof(float);
+    for (size_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      float s = 0.f;
+      for (int q = 0; q < W; ++q) s += __ldcg(&base[(size_t)q * stride + i]);
+      const __nv_bfloat16 v = __float2bfloat16_rn(s);
+      const size_t g = (size_t)c.rank * seg + i;
+      for (int k = 0; k < W; ++k) {
+        const int p = (c.rank + k) % W;
+        reinterpret_cast<__nv_bfloat16*>(c.data[p] + c.result_off + (size_t)set * c.result_bytes)[g] = v;
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < W)
+    st_release_sys(reinterpret_cast<uint32_t*>(c.data[threadIdx.x] + c.flags_off) + flag_index(2 + set, c.rank, cta), e);
+  if (threadIdx.x < W) {
+    const uint32_t* f = reinterpret_cast<const uint32_t*>(c.data[c.rank] + c.flags_off) + flag_index(2 + set, threadIdx.x, cta);
+    if (!wait_flag(f, e, c.timeout_ns)) { atomicCAS(c.status, 0, VG_ERR_PEER_WAIT); failed = 1; }
+  }
+  __syncthreads();
+  if (!failed) {
+    // CTA `cta` of every rank covered the same relative slice of its own segment: copy those slices
+    const __nv_bfloat16* res = reinterpret_cast<const __nv_bfloat16*>(c.data[c.rank] + c.result_off + (size_t)set * c.result_bytes);
+    const size_t total = (size_t)n * M;
+    for (int q = 0; q < W; ++q) {
+      const int q_rows = max(0, min(n, (q + 1) * rs_rows) - q * rs_rows);
+      const size_t qn = (size_t)q_rows * M;
+      const size_t qper = ((qn + nct - 1) / nct + 7) & ~(size_t)7;
+      const size_t qlo = min(qn, (size_t)cta * qper), qhi = min(qn, qlo + qper);
+      for (size_t i = qlo + threadIdx.x; i < qhi; i += blockDim.x) {
+        const size_t g = (size_t)q * seg + i;
+        if (g < total) out[g] = __ldcg(&res[g]);
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(c.done_ctr, 1u) == (unsigned)nct - 1) { *c.done_ctr = 0; *c.epoch = e; }
+  }
+}
+
 __global__ void __launch_bounds__(256) allgather_small_kernel(VgCommCtx c, const uint8_t* __restrict__ in,
                                                                uint8_t* __restrict__ out, int bytes) {
   __shared__ int failed;
@@ -256,6 +332,18 @@ extern "C" int vg_comm_allreduce(const VgCommCtx* ctx, const void* in, int in_is
     allreduce_twoshot_kernel<float><<<ctas, 256, 0, st>>>(c, static_cast<const float*>(in), static_cast<__nv_bfloat16*>(out_bf16), (int)n);
   else
     allreduce_twoshot_kernel<__nv_bfloat16><<<ctas, 256, 0, st>>>(c, static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out_bf16), (int)n);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int vg_comm_gemm_rs_finish(const VgCommCtx* ctx, void* out_bf16, int n, int M, int rs_rows, cudaStream_t st) {
+  if (!ctx || ctx->world < 2 || n <= 0 || M <= 0 || rs_rows <= 0 || (rs_rows % 128) != 0) return -2;
+  const int m_tiles = (M + 127) / 128;
+  if ((long long)(rs_rows / 128) * m_tiles > VG_RS_MAX_TILES || (unsigned long long)rs_rows * M * 4ull > ctx->slot_bytes ||
+      (unsigned long long)rs_rows * ctx->world * M * 2ull > ctx->result_bytes)
+    return -5;
+  int ctas = (int)(((long long)rs_rows * M + 256 * 32 - 1) / (256 * 32));
+  ctas = ctas < 1 ? 1 : (ctas > MAX_CTAS ? MAX_CTAS : ctas);
+  gemm_rs_finish_kernel<<<ctas, 256, 0, st>>>(*ctx, static_cast<__nv_bfloat16*>(out_bf16), n, M, rs_rows, m_tiles);
   return (int)cudaGetLastError();
 }
 

@@ -74,6 +74,7 @@ struct GemmParams {
   // partial tile into every rank's receive slot, raises a per-tile flag, waits for the other ranks' tiles
   // and stores the rank-order sum. ar == 0: plain store.
   int ar;
+  int rs_rows;           // > 0: fused reduce-scatter epilogue, token rows [r * rs_rows, (r + 1) * rs_rows) belong to rank r
   VgCommCtx comm;
 };
 
@@ -202,7 +203,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
   }
   const int x_row0 = p.grouped ? row0 / p.x_div : row0;
   // every CTA reads the collective epoch before any tile can publish the next one
-  const uint32_t ar_epoch = p.ar ? *p.comm.epoch + 1 : 0;
+  const uint32_t ar_epoch = (p.ar || p.rs_rows > 0) ? *p.comm.epoch + 1 : 0;
   const int ks0 = (int)(((long long)z * p.ks_total) / S);
   const int ks1 = (int)(((long long)(z + 1) * p.ks_total) / S);
   const int nks = ks1 - ks0;
@@ -450,6 +451,33 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
       __threadfence();
       if (atomicAdd(c.done_ctr, 1u) == gridDim.x * gridDim.y - 1) { *c.done_ctr = 0; *c.epoch = e; }
     }
+  } else if (epi && z == 0 && p.rs_rows > 0) {
+    // ---- fused reduce-scatter: this tile's token rows belong to one rank; its fp32 partial goes straight into
+    // that rank's receive slot over NVLink, then the tile's epoch is published there. No waiting here: the sum and
+    // the all-gather run in vg_comm_gemm_rs_finish while later tiles of this GEMM are still computing.
+    const VgCommCtx& c = p.comm;
+    const uint32_t e = ar_epoch;
+    const int set = e & 1;
+    const int et = threadIdx.x - 64;
+    const int m = (int)blockIdx.x * BM + m_local;
+    const int owner = row0 / p.rs_rows;
+    const int lrow0 = row0 - owner * p.rs_rows;
+    const float rsc = (p.row_scale && m < p.M) ? p.row_scale[m] : 1.0f;
+    if (have_acc && m < p.M) {
+      float* dst = reinterpret_cast<float*>(c.data[owner] + c.slots_off + (size_t)(set * MAX_RANKS + c.rank) * c.slot_bytes);
+#pragma unroll
+      for (int cc = 0; cc < CPW; ++cc) {
+        const int col = grp * CPW + cc;
+        if (col < rows_valid) dst[(size_t)(lrow0 + col) * p.M + m] = acc[cc] * rsc;
+      }
+    }
+    __threadfence_system();
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (et == 0) {
+      const int tile = (lrow0 / BN) * (int)gridDim.x + (int)blockIdx.x;
+      st_release_sys(reinterpret_cast<uint32_t*>(c.data[owner] + c.rsflags_off) +
+                         ((size_t)(set * MAX_RANKS + c.rank) * VG_RS_MAX_TILES + tile), e);
+    }
   } else if (epi && have_acc && z == 0) {
     const int m = (int)blockIdx.x * BM + m_local;       // row inside this (expert's) matrix
     if (m < p.M) {
@@ -593,7 +621,7 @@ int dispatch_bn(const GemmParams& p, const void* x, int ldx, int splitk, cudaStr
 
 extern "C" int vg_gemm_tc(const void* wt, const float* row_scale, const void* x_f16, int x_rows, int ldx, void* out,
                           int out_f32, int M, int K, int N, int ldo, int wfmt, int splitk, int* err,
-                          const VgCommCtx* ar_ctx, cudaStream_t stream) {
+                          const VgCommCtx* ar_ctx, int rs_rows, cudaStream_t stream) {
   if (M <= 0 || K <= 0 || N <= 0 || (K % 16) != 0 || splitk < 1 || splitk > 8 || x_rows < N) return -2;
   if (ldx < K || (ldx % 8) != 0 || (reinterpret_cast<uintptr_t>(x_f16) & 15) != 0) return -4;
   GemmParams p;
@@ -608,7 +636,16 @@ extern "C" int vg_gemm_tc(const void* wt, const float* row_scale, const void* x_
   p.trace = g_trace;
   p.grouped = 0;
   p.ar = 0;
-  if (ar_ctx && ar_ctx->world > 1) {
+  p.rs_rows = 0;
+  if (ar_ctx && ar_ctx->world > 1 && rs_rows > 0) {
+    // fused reduce-scatter (prefill widths): whole 128-token tiles per owner, every tile has a flag word
+    const long long tiles = (long long)((rs_rows + 127) / 128) * ((M + BM - 1) / BM);
+    if (N <= 64 || (rs_rows % 128) != 0 || out_f32 || tiles > VG_RS_MAX_TILES || splitk != 1 ||
+        (unsigned long long)rs_rows * M * 4ull > ar_ctx->slot_bytes || (long long)rs_rows * ar_ctx->world < N)
+      return -5;
+    p.rs_rows = rs_rows;
+    p.comm = *ar_ctx;
+  } else if (ar_ctx && ar_ctx->world > 1) {
     // fused reduction: decode widths only, one flag per row tile
     if (N > 16 || (M + BM - 1) / BM > MAX_CTAS || (unsigned long long)N * M * 4ull > ar_ctx->slot_bytes) return -5;
     p.ar = 1;
@@ -646,6 +683,7 @@ extern "C" int vg_gemm_tc_grouped(const void* wt, const float* row_scale, const 
   p.trace = nullptr;
   p.grouped = 1;
   p.ar = 0;
+  p.rs_rows = 0;
   p.g_exp = g_exp; p.g_off = g_off; p.g_cnt = g_cnt; p.tilemap = tilemap; p.n_items = n_items;
   p.tiles_per_expert = M / BM;
   p.x_div = x_div;

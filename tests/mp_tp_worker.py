@@ -37,6 +37,17 @@ def main():
     comm.check()
     rel = ((lt.float() - l1.float()).norm() / l1.float().norm()).item()
     assert lt.shape == l1.shape and rel < 0.05, rel
+    # prefill widths run the GEMM fused with the reduce-scatter; the unfused form (GEMM, then two-shot all-reduce)
+    # must agree to rounding, and the fused form must be deterministic
+    tp.fuse_allreduce = False
+    lu0, _ = tp.prefill(1, prompt)
+    tp.fuse_allreduce = True
+    lf0, _ = tp.prefill(1, prompt)
+    torch.cuda.synchronize()
+    comm.check()
+    assert torch.equal(lf0, lt)
+    relu = ((lu0.float() - lt.float()).norm() / lt.float().norm()).item()
+    assert relu < 0.02, relu
     # verify == sequential decodes at this world size, and run-to-run determinism
     S0, C0, K0, V0 = tp.S.clone(), tp.conv.clone(), tp.kc.clone(), tp.vc.clone()
     toks = [int(lt.argmax()), 5, 7, 11]

@@ -354,6 +354,15 @@ class GpuModel:
                 return
             self._linear(q, x16, n, out, act=act, comm=self.comm)
             return
+        if tp and n > 64 and not self.comm.use_nccl and self.fuse_allreduce and out.dtype == torch.bfloat16 \
+                and out.is_contiguous() and out.shape[1] == q.m:
+            # prefill widths: GEMM fused with the reduce-scatter (each partial tile goes to the rank owning its token
+            # rows as soon as it is computed), then the rank-order sum + all-gather
+            rs_rows = self.comm.rs_rows_for(n, q.m)
+            if rs_rows:
+                G.linear(q, x16, n, out=out, comm=self.comm, rs_rows=rs_rows)
+                self.comm.gemm_rs_finish(out, n, rs_rows)
+                return
         self._linear(q, x16, n, out, act=act)
         if tp:
             self._reduce(out, n)

@@ -27,7 +27,10 @@ class VgCommCtx(ctypes.Structure):
                 ("flags_off", ctypes.c_ulonglong), ("slots_off", ctypes.c_ulonglong), ("slot_bytes", ctypes.c_ulonglong),
                 ("result_off", ctypes.c_ulonglong), ("result_bytes", ctypes.c_ulonglong),
                 ("epoch", ctypes.c_void_p), ("done_ctr", ctypes.c_void_p), ("status", ctypes.c_void_p),
-                ("timeout_ns", ctypes.c_ulonglong)]
+                ("timeout_ns", ctypes.c_ulonglong), ("rsflags_off", ctypes.c_ulonglong)]
+
+
+RS_MAX_TILES = 4096                      # per-tile epoch words of the fused GEMM + reduce-scatter, per (set, rank)
 
 
 class CommError(RuntimeError):
@@ -48,7 +51,8 @@ class TpComm:
         self.flags_off = CTRL_BYTES
         self.slots_off = self.flags_off + FLAGS_BYTES
         self.result_off = self.slots_off + 2 * 8 * self.slot_bytes
-        self.total = self.result_off + 2 * self.result_bytes
+        self.rsflags_off = self.result_off + 2 * self.result_bytes
+        self.total = self.rsflags_off + 2 * 8 * RS_MAX_TILES * 4
         with torch.cuda.device(self.dev):
             base = ctypes.c_void_p()
             _lib.check(self.L.vg_comm_alloc(ctypes.byref(base), ctypes.c_ulonglong(self.total)), "vg_comm_alloc")
@@ -76,6 +80,7 @@ class TpComm:
         ctx.result_off, ctx.result_bytes = self.result_off, self.result_bytes
         ctx.epoch, ctx.done_ctr, ctx.status = self.base, self.base + 4, self.base + 8
         ctx.timeout_ns = int(timeout_s * 1e9)
+        ctx.rsflags_off = self.rsflags_off
         self.ctx = ctx
         self._status_view = self._view(8, 1, torch.int32)
         self._pairs = torch.zeros(2 * 64, dtype=torch.float32, device=self.dev)
@@ -107,6 +112,23 @@ class TpComm:
         rc = self.L.vg_comm_allreduce(ctypes.byref(self.ctx), ptr(t), c_int(1 if is32 else 0),
                                       ptr(None if is32 else t), ptr(t if is32 else None), c_ll(n), stream())
         _lib.check(rc, "vg_comm_allreduce")
+
+    def rs_rows_for(self, n_rows: int, m: int) -> int:
+        """Token rows per rank for the fused GEMM + reduce-scatter of an ``[n_rows, m]`` output (whole 128-token
+        tiles), or 0 when the shape does not fit the arena."""
+        rows = ((n_rows + self.world - 1) // self.world + 127) // 128 * 128
+        tiles = (rows // 128) * ((m + 127) // 128)
+        if tiles > RS_MAX_TILES or rows * m * 4 > self.slot_bytes or rows * self.world * m * 2 > self.result_bytes:
+            return 0
+        return rows
+
+    def gemm_rs_finish(self, out: torch.Tensor, n_rows: int, rs_rows: int):
+        """Second half of the fused GEMM + reduce-scatter: rank-order sum of the partial tiles every rank's GEMM
+        epilogue pushed here, all-gather of the bf16 result into ``out[:n_rows]`` on every rank."""
+        assert out.is_contiguous() and out.dtype == torch.bfloat16
+        rc = self.L.vg_comm_gemm_rs_finish(ctypes.byref(self.ctx), ptr(out), c_int(n_rows), c_int(out.shape[1]),
+                                           c_int(rs_rows), stream())
+        _lib.check(rc, "vg_comm_gemm_rs_finish")
 
     def all_gather_small(self, t: torch.Tensor) -> torch.Tensor:
         """[world, ...] stack of a small contiguous tensor from every rank."""
