@@ -104,6 +104,8 @@ __global__ void attn_prep_kernel(const __nv_bfloat16* qkv, int ld_qkv, const flo
                                  const int* pos, const int* slot, const int* kv_row, __nv_bfloat16* q_out,
                                  __nv_bfloat16* kc, __nv_bfloat16* vc, int nh, int nkv, int hd, int rdim, int max_seq,
                                  float eps, float log2_theta, int gated, __half* k_scale, __half* v_scale) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[32];
   extern __shared__ float xs[];
   const int n = blockIdx.x, hs = blockIdx.y, d = threadIdx.x;
