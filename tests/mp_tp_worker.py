@@ -42,6 +42,7 @@ def main():
     tp.fuse_allreduce = False
     lu0, _ = tp.prefill(1, prompt)
     tp.fuse_allreduce = True
+    tp.zero_slot(1)
     lf0, _ = tp.prefill(1, prompt)
     torch.cuda.synchronize()
     comm.check()
