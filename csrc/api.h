@@ -23,9 +23,12 @@ typedef struct VgCommCtx {
   unsigned int* done_ctr;    // CTA completion counter
   int* status;               // error status word (0 = ok)
   unsigned long long timeout_ns;
+  unsigned long long agbuf_off, agbuf_bytes;  // gather landing zone of the fused all-gather + GEMM (f16 rows)
+  unsigned long long agflags_off;  // [2 sets][VG_AG_MAX_TILES] epoch per 128-row tile of the landing zone
   unsigned long long rsflags_off;  // [2 sets][8 ranks][VG_RS_MAX_TILES] per-tile epochs of the fused GEMM + reduce-scatter
 } VgCommCtx;
 #define VG_RS_MAX_TILES 4096
+#define VG_AG_MAX_TILES 256
 
 // Optional epilogue of the decode-width GEMM that produces the GatedDeltaNet input projection: rows below
 // conv_dim are conv channels, and the thread that owns a row runs the depthwise causal conv + SiLU for every
@@ -42,13 +45,18 @@ typedef struct VgConvEpi {
 } VgConvEpi;
 
 int vg_gemm_tc(const void* wt, const float* row_scale, const void* x_f16, int x_rows, int ldx, void* out, int out_f32,
-               int M, int K, int N, int ldo, int wfmt, int splitk, int* err, const VgCommCtx* ar_ctx, int rs_rows,
+               int M, int K, int N, int ldo, int wfmt, int splitk, int* err, const VgCommCtx* ar_ctx, int rs_rows, int ag,
                cudaStream_t stream);
 // Second half of the fused GEMM + reduce-scatter (prefill widths): vg_gemm_tc(..., ar_ctx, rs_rows > 0) made every
 // rank push each partial output tile straight into the receive slot of the rank that owns the tile's token rows
 // (rows [p * rs_rows, (p + 1) * rs_rows) belong to rank p) and publish a per-tile epoch. This kernel waits for the
 // tiles of its own rows from every rank, sums them in rank order, broadcasts the bf16 result and assembles
 // out [n, M] on every rank.
+// Fused all-gather + GEMM (column-parallel layer whose input is sharded by token rows): every rank pushes its shard
+// (rows [row0, row0 + rows), whole 128-row tiles) into every rank's landing zone and publishes one epoch word per
+// tile; vg_gemm_tc(..., ag = 1) then reads the landing zone and holds the TMA loads of a token tile until that
+// tile's word has arrived, so the GEMM starts on the local rows while the others are still in flight.
+int vg_comm_ag_push(const VgCommCtx* ctx, const void* x_f16, int row0, int rows, int K, cudaStream_t stream);
 int vg_comm_gemm_rs_finish(const VgCommCtx* ctx, void* out_bf16, int n, int M, int rs_rows, cudaStream_t stream);
 int vg_act_quant_fp4(const void* x_f16, int ldx, int N, int K, void* bq, int ldb, void* sfb, float* g0, cudaStream_t stream);
 int vg_swiglu_fp4(const void* gu, int ld, int N, int I, void* bq, int ldb, void* sfb, float* g0, void* out16,

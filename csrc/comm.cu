@@ -147,6 +147,43 @@ __global__ void __launch_bounds__(256) allreduce_twoshot_kernel(VgCommCtx c, con
 }
 
 // All-gather of a small payload (<= slot_bytes) from every rank: out[q * bytes ...] = rank q's payload.
+// ------------------------------------------------------------------ fused all-gather + GEMM: the gather half
+// grid (tiles of 128 rows, column chunks). Each CTA copies its chunk of its tile into every rank's landing zone;
+// the last CTA of a tile (local counter) publishes the tile's epoch word on every rank.
+__global__ void __launch_bounds__(256) ag_push_kernel(VgCommCtx c, const __half* __restrict__ x, int row0, int rows, int K,
+                                                      unsigned int* __restrict__ tile_ctr) {
+  __shared__ int last;
+  const uint32_t e = *c.epoch + 1;
+  const int set = e & 1;
+  const int t = blockIdx.x, chunks = gridDim.y, ch = blockIdx.y;
+  const int r_lo = t * 128, r_hi = min(rows, r_lo + 128);
+  const int vec_per_row = K / 8;                                    // 16-byte vectors per row
+  const int v_lo = (int)((long long)vec_per_row * ch / chunks), v_hi = (int)((long long)vec_per_row * (ch + 1) / chunks);
+  const int vw = v_hi - v_lo;
+  // two landing zones, picked by the epoch's parity: a fast rank may push the next gather while a slow one still reads
+  const size_t cap_rows = (size_t)(c.agbuf_bytes / 2 / ((unsigned long long)K * 2ull)) / 128 * 128;
+  for (int k = 0; k < c.world; ++k) {
+    const int p = (c.rank + k) % c.world;
+    __half* dst = reinterpret_cast<__half*>(c.data[p] + c.agbuf_off) + (size_t)set * cap_rows * K;
+    for (int i = threadIdx.x; i < (r_hi - r_lo) * vw; i += blockDim.x) {
+      const int r = r_lo + i / vw, v = v_lo + i % vw;
+      const uint4 val = *reinterpret_cast<const uint4*>(x + (size_t)r * K + v * 8);
+      *reinterpret_cast<uint4*>(dst + (size_t)(row0 + r) * K + v * 8) = val;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) last = atomicAdd(&tile_ctr[t], 1u) == (unsigned)chunks - 1;
+  __syncthreads();
+  if (last) {
+    if (threadIdx.x == 0) tile_ctr[t] = 0;
+    __threadfence_system();
+    if (threadIdx.x < c.world)
+      st_release_sys(reinterpret_cast<uint32_t*>(c.data[threadIdx.x] + c.agflags_off) + (size_t)set * VG_AG_MAX_TILES +
+                         (row0 / 128 + t), e);
+  }
+}
+
 // ------------------------------------------------------------------ fused GEMM + reduce-scatter: second half
 // Every rank's row-parallel GEMM pushed its fp32 partial tiles of this rank's token rows into this rank's slots and
 // published one epoch word per tile (csrc/gemm_tc.cu, rs epilogue). Here: wait for the tiles of every rank,
@@ -332,6 +369,26 @@ extern "C" int vg_comm_allreduce(const VgCommCtx* ctx, const void* in, int in_is
     allreduce_twoshot_kernel<float><<<ctas, 256, 0, st>>>(c, static_cast<const float*>(in), static_cast<__nv_bfloat16*>(out_bf16), (int)n);
   else
     allreduce_twoshot_kernel<__nv_bfloat16><<<ctas, 256, 0, st>>>(c, static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out_bf16), (int)n);
+  return (int)cudaGetLastError();
+}
+
+namespace { unsigned int* g_ag_ctr[64] = {}; }
+extern "C" int vg_comm_ag_push(const VgCommCtx* ctx, const void* x_f16, int row0, int rows, int K, cudaStream_t st) {
+  if (!ctx || ctx->world < 2 || rows < 0 || (row0 % 128) != 0 || (K % 8) != 0) return -2;
+  const long long cap_rows = (long long)(ctx->agbuf_bytes / 2 / ((unsigned long long)K * 2ull)) / 128 * 128;
+  if ((row0 + rows + 127) / 128 > VG_AG_MAX_TILES || row0 + rows > cap_rows) return -5;
+  if (rows == 0) return 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return -2;
+  if (!g_ag_ctr[dev]) {                                   // per-tile arrival counters, allocated once per device
+    cudaError_t e = cudaMalloc(&g_ag_ctr[dev], VG_AG_MAX_TILES * sizeof(unsigned int));
+    if (e != cudaSuccess) return (int)e;
+    e = cudaMemset(g_ag_ctr[dev], 0, VG_AG_MAX_TILES * sizeof(unsigned int));
+    if (e != cudaSuccess) return (int)e;
+  }
+  dim3 grid((rows + 127) / 128, 8);
+  ag_push_kernel<<<grid, 256, 0, st>>>(*ctx, static_cast<const __half*>(x_f16), row0, rows, K, g_ag_ctr[dev]);
   return (int)cudaGetLastError();
 }
 

@@ -74,6 +74,8 @@ struct GemmParams {
   // partial tile into every rank's receive slot, raises a per-tile flag, waits for the other ranks' tiles
   // and stores the rank-order sum. ar == 0: plain store.
   int ar;
+  int ag;                // 1: X is the all-gather landing zone; a token tile is loaded once its epoch word has arrived
+  int ag_cap_rows;       // rows of one of the two landing-zone halves (the half is picked by the epoch's parity)
   int rs_rows;           // > 0: fused reduce-scatter epilogue, token rows [r * rs_rows, (r + 1) * rs_rows) belong to rank r
   VgCommCtx comm;
 };
@@ -203,7 +205,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
   }
   const int x_row0 = p.grouped ? row0 / p.x_div : row0;
   // every CTA reads the collective epoch before any tile can publish the next one
-  const uint32_t ar_epoch = (p.ar || p.rs_rows > 0) ? *p.comm.epoch + 1 : 0;
+  const uint32_t ar_epoch = (p.ar || p.rs_rows > 0 || p.ag) ? *p.comm.epoch + 1 : 0;
   const int ks0 = (int)(((long long)z * p.ks_total) / S);
   const int ks1 = (int)(((long long)(z + 1) * p.ks_total) / S);
   const int nks = ks1 - ks0;
@@ -246,6 +248,16 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
   } else if (warp == 10) {
     // ------------------------------------------------ activation producer
     if (lane == 0) {
+      if (p.ag) {
+        // fused all-gather: the 128-row tiles this CTA reads must have landed (pushed by their owner rank)
+        const uint32_t* fl = reinterpret_cast<const uint32_t*>(p.comm.data[p.comm.rank] + p.comm.agflags_off) +
+                             (size_t)(ar_epoch & 1) * VG_AG_MAX_TILES;
+        const int t_lo = x_row0 / 128, t_hi = (min(x_row0 + BN, p.N) - 1) / 128;
+        for (int t = t_lo; t <= t_hi; ++t)
+          if (!wait_flag(fl + t, ar_epoch, p.comm.timeout_ns)) { atomicCAS(p.comm.status, 0, VG_ERR_PEER_WAIT); *abort_flag = 1; }
+        asm volatile("fence.proxy.async;" ::: "memory");    // the rows were written through the generic proxy
+      }
+      const int x_row = x_row0 + (p.ag ? (int)(ar_epoch & 1) * p.ag_cap_rows : 0);
       for (int i = 0; i < nks && !*abort_flag; ++i) {
         const int b = i % NA;
         if (!mbar_wait(&ab_empty[b], ((i / NA) & 1) ^ 1)) { report(p.err, VG_ERR_EMPTY_WAIT, abort_flag); break; }
@@ -253,8 +265,8 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
         mbar_arrive_expect_tx(&b_full[b], C::b_bytes);
         uint8_t* bdst = sB + (size_t)b * C::b_bytes;
         const int ks = slab_of(i);
-        tma_tensor2d_g2s(bdst, &tmap_x, ks * BK, x_row0, &b_full[b]);
-        tma_tensor2d_g2s(bdst + BN * 128, &tmap_x, ks * BK + 64, x_row0, &b_full[b]);
+        tma_tensor2d_g2s(bdst, &tmap_x, ks * BK, x_row, &b_full[b]);
+        tma_tensor2d_g2s(bdst + BN * 128, &tmap_x, ks * BK + 64, x_row, &b_full[b]);
       }
     }
   } else if (warp == 1 || warp == 11) {
@@ -494,6 +506,11 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
       }
     }
   }
+  if (p.ag && threadIdx.x == 64) {
+    // the last CTA to finish publishes the epoch: the landing zone may be overwritten by the next gather
+    __threadfence();
+    if (atomicAdd(p.comm.done_ctr, 1u) == gridDim.x * gridDim.y * gridDim.z - 1) { *p.comm.done_ctr = 0; *p.comm.epoch = ar_epoch; }
+  }
   if (*abort_flag && threadIdx.x == 0) {
     // Give bulk copies that may still be in flight time to land before shared memory is released.
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
@@ -607,7 +624,7 @@ template <int WFMT>
 int dispatch_bn(const GemmParams& p, const void* x, int ldx, int splitk, cudaStream_t st) {
   CUtensorMap tm;
   int bn = p.N <= 16 ? 16 : (p.N <= 32 ? 32 : (p.N <= 64 ? 64 : 128));
-  int rc = get_tmap_x(x, p.N, p.K, bn, ldx, &tm);
+  int rc = get_tmap_x(x, p.ag ? 2 * p.ag_cap_rows : p.N, p.K, bn, ldx, &tm);
   if (rc) return rc;
   switch (bn) {
     case 16: return launch_bn<WFMT, 16>(p, tm, splitk, st);
@@ -621,7 +638,7 @@ int dispatch_bn(const GemmParams& p, const void* x, int ldx, int splitk, cudaStr
 
 extern "C" int vg_gemm_tc(const void* wt, const float* row_scale, const void* x_f16, int x_rows, int ldx, void* out,
                           int out_f32, int M, int K, int N, int ldo, int wfmt, int splitk, int* err,
-                          const VgCommCtx* ar_ctx, int rs_rows, cudaStream_t stream) {
+                          const VgCommCtx* ar_ctx, int rs_rows, int ag, cudaStream_t stream) {
   if (M <= 0 || K <= 0 || N <= 0 || (K % 16) != 0 || splitk < 1 || splitk > 8 || x_rows < N) return -2;
   if (ldx < K || (ldx % 8) != 0 || (reinterpret_cast<uintptr_t>(x_f16) & 15) != 0) return -4;
   GemmParams p;
@@ -637,7 +654,17 @@ extern "C" int vg_gemm_tc(const void* wt, const float* row_scale, const void* x_
   p.grouped = 0;
   p.ar = 0;
   p.rs_rows = 0;
-  if (ar_ctx && ar_ctx->world > 1 && rs_rows > 0) {
+  p.ag = 0;
+  if (ar_ctx && ar_ctx->world > 1 && ag) {
+    // fused all-gather: X must be this rank's landing zone, whole problem in one launch, plain epilogue
+    const long long cap_rows = (long long)(ar_ctx->agbuf_bytes / 2 / ((unsigned long long)K * 2ull)) / 128 * 128;
+    if (rs_rows > 0 || splitk != 1 || (N + 127) / 128 > VG_AG_MAX_TILES || ldx != K || N > cap_rows ||
+        x_f16 != (const void*)(ar_ctx->data[ar_ctx->rank] + ar_ctx->agbuf_off) || x_rows != 2 * cap_rows)
+      return -5;
+    p.ag = 1;
+    p.ag_cap_rows = (int)cap_rows;
+    p.comm = *ar_ctx;
+  } else if (ar_ctx && ar_ctx->world > 1 && rs_rows > 0) {
     // fused reduce-scatter (prefill widths): whole 128-token tiles per owner, every tile has a flag word
     const long long tiles = (long long)((rs_rows + 127) / 128) * ((M + BM - 1) / BM);
     if (N <= 64 || (rs_rows % 128) != 0 || out_f32 || tiles > VG_RS_MAX_TILES || splitk != 1 ||

@@ -15,7 +15,7 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     from velogb10_b200.parallel.comm import CommError, TpComm
-    comm = TpComm(rank, world, dev, max_elems=1 << 22, timeout_s=5.0)
+    comm = TpComm(rank, world, dev, max_elems=1 << 22, timeout_s=5.0, ag_bytes=2 * 1024 * 1024 * 2)
     g = torch.Generator(device=dev).manual_seed(100 + rank)
     for rows, h in ((1, 5120), (16, 5120), (3, 256), (700, 5120)):      # one-shot and two-shot sizes
         x = torch.randn(rows, h, generator=g, device=dev).to(torch.bfloat16)
@@ -78,6 +78,24 @@ def main():
     torch.cuda.synchronize()
     comm.check()
     assert torch.equal(y, want)
+    # fused all-gather + GEMM: token rows sharded over the ranks, every rank computes the full product
+    from velogb10_b200.models.weights import QLinear
+    n_total, K_, M_ = 300 + 128 * (world - 1), 1024, 384
+    gw = torch.Generator(device=dev).manual_seed(7)                       # same weights and inputs on every rank
+    w = (torch.randn(M_, K_, generator=gw, device=dev) * 0.05).to(torch.bfloat16)
+    xf = torch.randn(n_total, K_, generator=gw, device=dev).to(torch.float16)
+    q = QLinear.from_dense(w, "nvfp4")
+    rows_per = ((n_total + world - 1) // world + 127) // 128 * 128
+    r0, r1 = min(n_total, rank * rows_per), min(n_total, (rank + 1) * rows_per)
+    ref = (xf.float() @ q.dequant(torch.float32).t())
+    for rep in range(3):                                                   # both landing zones, repeated epochs
+        shard = (xf[r0:r1] * (rep + 1)).contiguous()
+        out = torch.zeros(n_total, M_, dtype=torch.bfloat16, device=dev)
+        comm.ag_gemm(q, shard, r0, n_total, out)
+        torch.cuda.synchronize()
+        comm.check()
+        rel = ((out.float() - ref * (rep + 1)).norm() / (ref * (rep + 1)).norm()).item()
+        assert rel < 1e-2, (rep, rel)
     dist.barrier()
     if rank == 0:
         print("COMM_OK")

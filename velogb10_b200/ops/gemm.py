@@ -118,11 +118,12 @@ def prepare(q: QLinear, keep_canonical: bool = True, splitk: Optional[int] = Non
 
 
 def linear(q: QLinear, x16: torch.Tensor, n: Optional[int] = None, out: Optional[torch.Tensor] = None,
-           out_f32: bool = False, comm=None, rs_rows: int = 0) -> torch.Tensor:
+           out_f32: bool = False, comm=None, rs_rows: int = 0, ag: bool = False) -> torch.Tensor:
     """``out[n, m] = sum_k W[m, k] x[n, k]`` on the tensor cores. ``x16`` is f16 ``[rows >= n, K]``.
     With ``comm`` (a ``TpComm``) the epilogue also sums the result over the tensor-parallel ranks (decode widths).
     With ``comm`` and ``rs_rows`` (prefill widths) the epilogue instead pushes every partial tile to the rank that
-    owns its token rows (``rs_rows`` per rank) and writes nothing to ``out``; ``comm.gemm_rs_finish`` completes it."""
+    owns its token rows (``rs_rows`` per rank) and writes nothing to ``out``; ``comm.gemm_rs_finish`` completes it.
+    With ``comm`` and ``ag`` the input is the all-gather landing zone (see ``TpComm.ag_gemm``)."""
     tw = prepare(q)
     assert x16.dtype == torch.float16 and x16.stride(1) == 1 and x16.shape[1] == tw.k
     n = x16.shape[0] if n is None else n
@@ -131,8 +132,9 @@ def linear(q: QLinear, x16: torch.Tensor, n: Optional[int] = None, out: Optional
     L = _lib.lib()
     rc = L.vg_gemm_tc(ptr(tw.wt), ptr(tw.row_scale), ptr(x16), c_int(x16.shape[0]), c_int(x16.stride(0)), ptr(out),
                       c_int(1 if out.dtype == torch.float32 else 0), c_int(tw.m), c_int(tw.k), c_int(n),
-                      c_int(out.stride(0)), c_int(tw.fmt), c_int(1 if rs_rows else tw.splitk), ptr(_lib.err_word(x16.device)),
-                      ctypes.byref(comm.ctx) if comm is not None else c_void_p(0), c_int(rs_rows), stream())
+                      c_int(out.stride(0)), c_int(tw.fmt), c_int(1 if (rs_rows or ag) else tw.splitk),
+                      ptr(_lib.err_word(x16.device)), ctypes.byref(comm.ctx) if comm is not None else c_void_p(0),
+                      c_int(rs_rows), c_int(1 if ag else 0), stream())
     _lib.check(rc, "vg_gemm_tc")
     return out
 

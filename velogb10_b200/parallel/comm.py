@@ -27,10 +27,12 @@ class VgCommCtx(ctypes.Structure):
                 ("flags_off", ctypes.c_ulonglong), ("slots_off", ctypes.c_ulonglong), ("slot_bytes", ctypes.c_ulonglong),
                 ("result_off", ctypes.c_ulonglong), ("result_bytes", ctypes.c_ulonglong),
                 ("epoch", ctypes.c_void_p), ("done_ctr", ctypes.c_void_p), ("status", ctypes.c_void_p),
-                ("timeout_ns", ctypes.c_ulonglong), ("rsflags_off", ctypes.c_ulonglong)]
+                ("timeout_ns", ctypes.c_ulonglong), ("agbuf_off", ctypes.c_ulonglong), ("agbuf_bytes", ctypes.c_ulonglong),
+                ("agflags_off", ctypes.c_ulonglong), ("rsflags_off", ctypes.c_ulonglong)]
 
 
 RS_MAX_TILES = 4096                      # per-tile epoch words of the fused GEMM + reduce-scatter, per (set, rank)
+AG_MAX_TILES = 256                       # per-tile epoch words of the fused all-gather + GEMM, per set
 
 
 class CommError(RuntimeError):
@@ -39,7 +41,7 @@ class CommError(RuntimeError):
 
 class TpComm:
     def __init__(self, rank: int, world: int, device: torch.device, max_elems: int = 4096 * 8192, use_nccl: bool = False,
-                 timeout_s: float = 5.0, group=None):
+                 timeout_s: float = 5.0, group=None, ag_bytes: int = 0):
         self.rank, self.world, self.dev = rank, world, torch.device(device)
         self.use_nccl = use_nccl
         self.group = group
@@ -52,7 +54,10 @@ class TpComm:
         self.slots_off = self.flags_off + FLAGS_BYTES
         self.result_off = self.slots_off + 2 * 8 * self.slot_bytes
         self.rsflags_off = self.result_off + 2 * self.result_bytes
-        self.total = self.rsflags_off + 2 * 8 * RS_MAX_TILES * 4
+        self.agflags_off = self.rsflags_off + 2 * 8 * RS_MAX_TILES * 4
+        self.agbuf_off = (self.agflags_off + 2 * AG_MAX_TILES * 4 + 1023) // 1024 * 1024
+        self.agbuf_bytes = (ag_bytes + 1023) // 1024 * 1024      # two landing zones of the fused all-gather + GEMM
+        self.total = self.agbuf_off + self.agbuf_bytes
         with torch.cuda.device(self.dev):
             base = ctypes.c_void_p()
             _lib.check(self.L.vg_comm_alloc(ctypes.byref(base), ctypes.c_ulonglong(self.total)), "vg_comm_alloc")
@@ -81,6 +86,7 @@ class TpComm:
         ctx.epoch, ctx.done_ctr, ctx.status = self.base, self.base + 4, self.base + 8
         ctx.timeout_ns = int(timeout_s * 1e9)
         ctx.rsflags_off = self.rsflags_off
+        ctx.agbuf_off, ctx.agbuf_bytes, ctx.agflags_off = self.agbuf_off, self.agbuf_bytes, self.agflags_off
         self.ctx = ctx
         self._status_view = self._view(8, 1, torch.int32)
         self._pairs = torch.zeros(2 * 64, dtype=torch.float32, device=self.dev)
@@ -96,7 +102,7 @@ class TpComm:
             pass
         a = _Arr()
         item = torch.tensor([], dtype=dtype).element_size()
-        typestr = {torch.int32: "<i4", torch.float32: "<f4", torch.uint8: "|u1"}[dtype]
+        typestr = {torch.int32: "<i4", torch.float32: "<f4", torch.uint8: "|u1", torch.float16: "<f2"}[dtype]
         a.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (self.base + offset, False), "version": 2}
         return torch.as_tensor(a, device=self.dev)
 
@@ -129,6 +135,20 @@ class TpComm:
         rc = self.L.vg_comm_gemm_rs_finish(ctypes.byref(self.ctx), ptr(out), c_int(n_rows), c_int(out.shape[1]),
                                            c_int(rs_rows), stream())
         _lib.check(rc, "vg_comm_gemm_rs_finish")
+
+    def ag_gemm(self, q, x_shard: torch.Tensor, row0: int, n_total: int, out: torch.Tensor) -> torch.Tensor:
+        """Fused all-gather + GEMM: ``x_shard`` (f16 ``[rows, K]``, this rank's token rows starting at the
+        128-aligned ``row0``) is pushed into every rank's landing zone; the GEMM over all ``n_total`` rows reads the
+        zone tile by tile as the tiles arrive. Needs ``ag_bytes`` >= 2 * n_total * K * 2 at construction."""
+        from ..ops import gemm as G
+        K_ = x_shard.shape[1]
+        assert x_shard.dtype == torch.float16 and x_shard.is_contiguous() and self.agbuf_bytes > 0
+        rc = self.L.vg_comm_ag_push(ctypes.byref(self.ctx), ptr(x_shard), c_int(row0), c_int(x_shard.shape[0]), c_int(K_),
+                                    stream())
+        _lib.check(rc, "vg_comm_ag_push")
+        cap_rows = (self.agbuf_bytes // 2 // (K_ * 2)) // 128 * 128
+        zone = self._view(self.agbuf_off, 2 * cap_rows * K_, torch.float16).view(2 * cap_rows, K_)
+        return G.linear(q, zone, n_total, out=out, comm=self, ag=True)
 
     def all_gather_small(self, t: torch.Tensor) -> torch.Tensor:
         """[world, ...] stack of a small contiguous tensor from every rank."""
