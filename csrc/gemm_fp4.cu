@@ -645,7 +645,7 @@ extern "C" int vg_gemm_fp4(const void* wt, const float* row_scale, const void* b
                            void* out, int out_f32, int M, int K, int N, int ldo, int splitk, int* err,
                            const VgCommCtx* ar_ctx, int ar_push_only, const VgConvEpi* conv, cudaStream_t stream) {
   if (M <= 0 || K <= 0 || N < 1 || N > 16 || splitk < 1 || splitk > 8 || (ldb % 128) != 0) return -2;
-  Fp4Params p;
+  Fp4Params p{};                  // every mode switch defaults to off
   p.wt = static_cast<const uint8_t*>(wt);
   p.row_scale = row_scale;
   p.sfb = static_cast<const uint8_t*>(sfb);
@@ -718,7 +718,7 @@ extern "C" int vg_gemm_fp4_grouped(const void* wt, const float* row_scale, const
                                    const float* g0, void* out, int out_f32, int M, int K, int ldo, int n_items, const int* g_exp,
                                    const int* g_off, int x_div, int* err, cudaStream_t stream) {
   if (M <= 0 || (M % BM) != 0 || K <= 0 || n_items < 1 || x_div < 1 || (ldb % 128) != 0 || (b_rows % NT) != 0) return -2;
-  Fp4Params p;
+  Fp4Params p{};                  // every mode switch defaults to off
   p.wt = static_cast<const uint8_t*>(wt);
   p.row_scale = row_scale;
   p.sfb = static_cast<const uint8_t*>(sfb);

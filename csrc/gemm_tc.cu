@@ -641,7 +641,7 @@ extern "C" int vg_gemm_tc(const void* wt, const float* row_scale, const void* x_
                           const VgCommCtx* ar_ctx, int rs_rows, int ag, cudaStream_t stream) {
   if (M <= 0 || K <= 0 || N <= 0 || (K % 16) != 0 || splitk < 1 || splitk > 8 || x_rows < N) return -2;
   if (ldx < K || (ldx % 8) != 0 || (reinterpret_cast<uintptr_t>(x_f16) & 15) != 0) return -4;
-  GemmParams p;
+  GemmParams p{};                 // every mode switch defaults to off
   p.wt = static_cast<const uint8_t*>(wt);
   p.row_scale = row_scale;
   p.out = out;
@@ -697,7 +697,7 @@ extern "C" int vg_gemm_tc_grouped(const void* wt, const float* row_scale, const 
                                   int* err, cudaStream_t stream) {
   if (M <= 0 || K <= 0 || max_items <= 0 || (K % 16) != 0 || (M % BM) != 0 || x_div < 1) return -2;
   if (ldx < K || (ldx % 8) != 0 || (reinterpret_cast<uintptr_t>(x_f16) & 15) != 0) return -4;
-  GemmParams p;
+  GemmParams p{};                 // every mode switch defaults to off
   p.wt = static_cast<const uint8_t*>(wt);
   p.row_scale = row_scale;
   p.out = out;
