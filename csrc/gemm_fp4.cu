@@ -64,7 +64,8 @@ struct Fp4Params {
   VgCommCtx comm;
 };
 
-constexpr int SMEM_TOTAL = NS * STAGE + (2 * NS + 1) * 8 + 16 + 1024;
+constexpr int smem_total(int ns) { return ns * STAGE + (2 * ns + 1) * 8 + 16 + 1024; }
+constexpr int SMEM_TOTAL = smem_total(NS);
 constexpr int CONV_MAX_CK = 4;            // taps the fused conv epilogue supports
 constexpr int CONV_SMEM = 16 * (CONV_MAX_CK - 1) * BM * 4;   // prefetched state samples, appended after SMEM_TOTAL
 
@@ -106,14 +107,17 @@ __device__ __forceinline__ void fail(int* err, int code, volatile int* abort_fla
   *abort_flag = 1;
 }
 
-__global__ void __launch_bounds__(THREADS, 1)
+// NSK: ring stages. Six for the dense layers (one CTA per SM, deep prefetch); two for the grouped MoE form, whose
+// work items are short (K / 256 slabs of one expert) and numerous, so two CTAs share an SM.
+template <int NSK>
+__global__ void __launch_bounds__(THREADS, NSK <= 2 ? 2 : 1)
 gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + NS * STAGE);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + NSK * STAGE);
   uint64_t* full = bars;                 // both producers arrive (count 2) + their bytes
-  uint64_t* empty = full + NS;           // MMA commit
-  uint64_t* acc_full = empty + NS;
+  uint64_t* empty = full + NSK;           // MMA commit
+  uint64_t* acc_full = empty + NSK;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -140,7 +144,7 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
   pdl_trigger();
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NS; ++i) { mbar_init(&full[i], 2); mbar_init(&empty[i], 1); }
+    for (int i = 0; i < NSK; ++i) { mbar_init(&full[i], 2); mbar_init(&empty[i], 1); }
     mbar_init(acc_full, 2);
     *abort_flag = 0;
     fence_mbar_init();
@@ -163,8 +167,8 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
       // bulk prefetches measured slower at every depth, so only the ring runs ahead.
       const uint8_t* wbase = p.wt + (size_t)mt * p.ks_total * (A_BYTES + SF_BYTES);
       for (int i = 0; i < nks && !*abort_flag; ++i) {
-        const int s = i % NS;
-        if (!mbar_wait(&empty[s], ((i / NS) & 1) ^ 1)) { fail(p.err, VG_ERR_EMPTY_WAIT, abort_flag); break; }
+        const int s = i % NSK;
+        if (!mbar_wait(&empty[s], ((i / NSK) & 1) ^ 1)) { fail(p.err, VG_ERR_EMPTY_WAIT, abort_flag); break; }
         uint8_t* st = smem + (size_t)s * STAGE;
         mbar_arrive_expect_tx(&full[s], A_BYTES + SF_BYTES);
         tma_bulk_g2s(st, wbase + (size_t)slab_of(i) * (A_BYTES + SF_BYTES), A_BYTES + SF_BYTES, &full[s]);
@@ -175,8 +179,8 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
       pdl_wait();                          // the activation series comes from the preceding kernel
       trace(4 * 16 + 1);
       for (int i = 0; i < nks && !*abort_flag; ++i) {
-        const int s = i % NS;
-        if (!mbar_wait(&empty[s], ((i / NS) & 1) ^ 1)) { fail(p.err, VG_ERR_EMPTY_WAIT, abort_flag); break; }
+        const int s = i % NSK;
+        if (!mbar_wait(&empty[s], ((i / NSK) & 1) ^ 1)) { fail(p.err, VG_ERR_EMPTY_WAIT, abort_flag); break; }
         uint8_t* st = smem + (size_t)s * STAGE + A_BYTES + SF_BYTES;
         const int ks = slab_of(i);
         mbar_arrive_expect_tx(&full[s], B_BYTES + SF_BYTES);
@@ -193,8 +197,8 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
       bool ok = true;
       int mine = 0;
       for (int i = me; i < nks && !*abort_flag; i += 2, ++mine) {
-        const int s = i % NS;
-        if (!mbar_wait(&full[s], (i / NS) & 1)) { fail(p.err, VG_ERR_TMA_WAIT, abort_flag); ok = false; break; }
+        const int s = i % NSK;
+        if (!mbar_wait(&full[s], (i / NSK) & 1)) { fail(p.err, VG_ERR_TMA_WAIT, abort_flag); ok = false; break; }
         if (i == 0) trace(4 * 16 + 3);
         tc_fence_after();
         const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE);
@@ -228,7 +232,7 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
   uint32_t ar_epoch = 0;
   // fused conv: state samples and taps of this thread's channel, fetched while the main loop runs
   const bool conv_row = epi && p.has_conv && mt * BM + m_local < p.conv.conv_dim && z == 0;
-  float* conv_pre = reinterpret_cast<float*>(smem + SMEM_TOTAL - 1024);      // [16][CONV_MAX_CK - 1][BM]
+  float* conv_pre = reinterpret_cast<float*>(smem + smem_total(NSK) - 1024);      // [16][CONV_MAX_CK - 1][BM]
   float wk[CONV_MAX_CK];
   uint32_t n_state = 0;                    // 2 bits per column: samples that come from the rolling state
   if (epi) {
@@ -690,7 +694,7 @@ extern "C" int vg_gemm_fp4(const void* wt, const float* row_scale, const void* b
   }
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_fp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL + CONV_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_fp4_kernel<NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL + CONV_SMEM);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -708,7 +712,7 @@ extern "C" int vg_gemm_fp4(const void* wt, const float* row_scale, const void* b
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_on() ? 2 : 1;
-  return (int)cudaLaunchKernelEx(&cfg, gemm_fp4_kernel, p, tm);
+  return (int)cudaLaunchKernelEx(&cfg, gemm_fp4_kernel<NS>, p, tm);
 }
 
 // MoE decode: `n_items` work items, item g = (expert g_exp[g] or -1, pair g_off[g]); the pair reads activation
@@ -735,13 +739,20 @@ extern "C" int vg_gemm_fp4_grouped(const void* wt, const float* row_scale, const
   CUtensorMap tm;
   int rc = get_tmap_b(bq, ldb, b_rows, &tm);
   if (rc) return rc;
+  // Few work items (a single stream): the deep ring, one CTA per SM, as for the dense layers. Many items (wide
+  // batches: hundreds of short K loops): the two-stage ring so that two CTAs share an SM.
+  constexpr int GNS = 2;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_fp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL + CONV_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_fp4_kernel<GNS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_total(GNS));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemm_fp4_kernel<NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL + CONV_SMEM);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return (int)launch_pdl(gemm_fp4_kernel, dim3(M / BM, n_items, 1), dim3(THREADS), SMEM_TOTAL, stream, p, tm);
+  if ((long long)(M / BM) * n_items > 2ll * sm_count())
+    return (int)launch_pdl(gemm_fp4_kernel<GNS>, dim3(M / BM, n_items, 1), dim3(THREADS), smem_total(GNS), stream, p, tm);
+  return (int)launch_pdl(gemm_fp4_kernel<NS>, dim3(M / BM, n_items, 1), dim3(THREADS), SMEM_TOTAL, stream, p, tm);
 }
 
 VG_TRACE_SETTER(vg_trace_set_gemm_fp4)
