@@ -75,6 +75,44 @@ def main():
     assert got == want, (got, want)
     torch.cuda.synchronize()
     comm.check()
+    # mixture-of-experts under tensor + expert parallelism (expert bands, forked shared expert, grouped FP4 GEMMs)
+    from velogb10_b200.config import tiny_moe
+    from velogb10_b200.ops import gemm as G
+    mcfg = tiny_moe(mtp=False)
+    m1 = GpuModel(ModelBuilder(mcfg, SyntheticSource(mcfg, 0, str(dev), std=0.05), recipe="all", device=str(dev)).build(),
+                  device=str(dev))
+    mt = GpuModel(ModelBuilder(mcfg, SyntheticSource(mcfg, 0, str(dev), std=0.05), recipe="all", device=str(dev),
+                               tp_rank=rank, tp_world=world).build(), device=str(dev), comm=comm)
+    m1.alloc_state(2, 2 + 17, 256)
+    mt.alloc_state(2, 2 + 17, 256)
+    # end to end (router near-ties may flip under the different summation order, so only sanity is asserted)
+    mp = torch.randint(0, mcfg.vocab_size, (90,), generator=g).tolist()
+    a1, _ = m1.prefill(0, mp)
+    at, _ = mt.prefill(0, mp)
+    print("moe prefill rel", ((at.float() - a1.float()).norm() / a1.float().norm()).item(), flush=True)
+    d1, _ = m1.decode([5, 7], [90, 3], [0, 1])
+    dt, _ = mt.decode([5, 7], [90, 3], [0, 1])
+    dt2 = dt.clone()
+    print("moe decode rel", ((dt.float() - d1.float()).norm() / d1.float().norm()).item(), flush=True)
+    assert torch.isfinite(dt.float()).all()
+    # layer level, identical inputs on both models (so the routing is identical and only the summation order of
+    # the expert-parallel reduction differs): per-pair decode path and sorted prefill path
+    for ws1, wst, n in ((m1.ws, mt.ws, 2), (m1.ws_prefill, mt.ws_prefill, 90)):
+        xin = (torch.randn((n, mcfg.hidden_size), generator=g) * 0.5).to(dev, torch.float16)
+        outs = []
+        for m, ws in ((m1, ws1), (mt, wst)):
+            ws.xn16[:n].copy_(xin)
+            moe = next(L.moe for L in m.w.layers if L.moe is not None)
+            act = G.quantize_act_fp4(ws.xn16, n, ((mcfg.hidden_size + 255) // 256) * 256) if (m.use_fp4 and n <= 16) else None
+            m._moe(ws, moe, n, act=act)
+            outs.append(ws.delta[:n].float().clone())
+        rel = ((outs[1] - outs[0]).norm() / outs[0].norm()).item()
+        assert rel < 0.02, ("moe layer", n, rel)
+    torch.cuda.synchronize()
+    comm.check()
+    both = comm.all_gather_small(dt2[:1, :64].contiguous())
+    torch.cuda.synchronize()
+    assert torch.equal(both[0], both[-1]), "ranks must hold identical logits"
     dist.barrier()
     if rank == 0:
         print("TP_OK")
