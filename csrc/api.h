@@ -135,6 +135,8 @@ int vg_moe_gather(const void* x_f16, int ldx, const int* perm, const int* total,
                   void* out_f16, cudaStream_t stream);
 int vg_moe_combine(const void* y, int ldy, const int* inv, const float* wts, int N, int topk, const void* shared,
                    const float* gate_logit, void* out, int h, cudaStream_t stream);
+int vg_moe_combine_push(const void* y, int ldy, const int* inv, const float* wts, int N, int topk, const void* shared,
+                        const float* gate_logit, int h, const VgCommCtx* ctx, cudaStream_t stream);
 int vg_moe_add_shared(void* out, const void* shared, const float* gate_logit, int N, int h, cudaStream_t stream);
 
 int vg_comm_alloc(void** ptr, unsigned long long bytes);

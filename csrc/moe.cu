@@ -149,11 +149,17 @@ __global__ void moe_total_kernel(const int* __restrict__ g_off, const int* __res
 //           (+ gate[t] * shared[t, :] when a shared expert is given)
 // out[t] = sum_s wts[t, s] * y[inv[t, s]] (slot order) + sigmoid(gate) * shared[t]; eight columns per thread,
 // all expert rows of a thread's columns are in flight before the first add.
+// PUSH (expert parallelism at decode widths): the row is this rank's partial sum over its resident experts. It is
+// not stored but sent, as fp32 (value, epoch) pairs, into the receive slot of every rank (this one included), where
+// the residual-add / RMSNorm kernel that follows polls its own memory and sums the ranks in order: combine and
+// all-reduce in one kernel, no barrier and no separate reduction launch. The caller passes the replicated shared
+// expert on one rank only.
+template <bool PUSH>
 __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* __restrict__ y, int ldy,
                                                            const int* __restrict__ inv, const float* __restrict__ wts, int topk,
                                                            const __nv_bfloat16* __restrict__ shared,
                                                            const float* __restrict__ gate_logit, __nv_bfloat16* __restrict__ out,
-                                                           int h) {
+                                                           int h, const VgCommCtx c) {
   __shared__ int spos[MAX_K];
   __shared__ float sw[MAX_K];
   pdl_trigger();
@@ -165,6 +171,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* _
   }
   __syncthreads();
   const float g = gate_logit ? sigmoidf(gate_logit[t]) : 1.0f;
+  const uint32_t e = PUSH ? *c.epoch + 1 : 0;   // (read after the wait: the preceding collective's consumer bumps it)
   for (int i = threadIdx.x * 8; i < h; i += blockDim.x * 8) {
     uint4 rows[MAX_K];
 #pragma unroll
@@ -191,7 +198,18 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* _
       if (shared) acc[k] += g * __bfloat162float(shb[k]);
       o[k] = __float2bfloat16_rn(acc[k]);
     }
-    *reinterpret_cast<uint4*>(out + (size_t)t * h + i) = o4;
+    if (PUSH) {
+      for (int q = 0; q < c.world; ++q) {
+        const int peer = (c.rank + q) % c.world;
+        uint2* dst = reinterpret_cast<uint2*>(c.data[peer] + c.slots_off + (size_t)((e & 1) * MAX_RANKS + c.rank) * c.slot_bytes) +
+                     ((size_t)t * h + i);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst + k), "r"(__float_as_uint(acc[k])), "r"(e) : "memory");
+      }
+    } else {
+      *reinterpret_cast<uint4*>(out + (size_t)t * h + i) = o4;
+    }
   }
 }
 
@@ -247,8 +265,20 @@ extern "C" int vg_moe_combine(const void* y, int ldy, const int* inv, const floa
                               const float* gate_logit, void* out, int h, cudaStream_t st) {
   if (N <= 0) return 0;
   if (topk > MAX_K || (h % 8) != 0 || (ldy % 8) != 0) return -2;
-  launch_pdl(moe_combine_kernel, dim3(N), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(y), ldy, inv, wts, topk,
-             static_cast<const __nv_bfloat16*>(shared), gate_logit, static_cast<__nv_bfloat16*>(out), h);
+  launch_pdl(moe_combine_kernel<false>, dim3(N), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(y), ldy, inv, wts, topk,
+             static_cast<const __nv_bfloat16*>(shared), gate_logit, static_cast<__nv_bfloat16*>(out), h, VgCommCtx{});
+  return (int)cudaGetLastError();
+}
+
+// Combine fused with the expert-parallel all-reduce (push half): see moe_combine_kernel<true>. The consumer is
+// vg_add_rmsnorm_fp4_ar on every rank; `shared` / `gate_logit` are passed on one rank only.
+extern "C" int vg_moe_combine_push(const void* y, int ldy, const int* inv, const float* wts, int N, int topk, const void* shared,
+                                   const float* gate_logit, int h, const VgCommCtx* ctx, cudaStream_t st) {
+  if (N <= 0) return 0;
+  if (!ctx || topk > MAX_K || (h % 16) != 0 || (ldy % 8) != 0) return -2;
+  if (ctx->world < 1 || ctx->world > MAX_RANKS || (unsigned long long)N * h * 8ull > ctx->slot_bytes) return -2;
+  launch_pdl(moe_combine_kernel<true>, dim3(N), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(y), ldy, inv, wts, topk,
+             static_cast<const __nv_bfloat16*>(shared), gate_logit, static_cast<__nv_bfloat16*>(nullptr), h, *ctx);
   return (int)cudaGetLastError();
 }
 

@@ -104,8 +104,14 @@ def main():
             ws.xn16[:n].copy_(xin)
             moe = next(L.moe for L in m.w.layers if L.moe is not None)
             act = G.quantize_act_fp4(ws.xn16, n, ((mcfg.hidden_size + 255) // 256) * 256) if (m.use_fp4 and n <= 16) else None
+            ws.x[:n].zero_()
             m._moe(ws, moe, n, act=act)
-            outs.append(ws.delta[:n].float().clone())
+            if m._pending_ar:
+                # the combine only pushed this rank's partial rows: the residual-add / RMSNorm kernel sums the ranks
+                m._norm(ws, None, m.w.final_norm, n)
+                outs.append(ws.x[:n].float().clone())
+            else:
+                outs.append(ws.delta[:n].float().clone())
         rel = ((outs[1] - outs[0]).norm() / outs[0].norm()).item()
         assert rel < 0.02, ("moe layer", n, rel)
     torch.cuda.synchronize()

@@ -11,6 +11,8 @@ the replicated shared expert is added.
 from __future__ import annotations
 
 import contextlib
+import ctypes
+import os
 
 from typing import Dict
 
@@ -158,11 +160,23 @@ def moe_forward(model, ws, M: MoeW, n: int, act=None):
     if joined is not None:
         torch.cuda.current_stream().wait_event(joined)
     ep = model.comm is not None and model.comm.world > 1 and M.n_local < E
+    comm = model.comm
+    if ep and decode and model.use_fp4 and model.split_allreduce and model.fuse_allreduce and not comm.use_nccl \
+            and h % 16 == 0 and n * h * 8 <= comm.slot_bytes and os.environ.get("VELO_NO_MOE_PUSH", "0") != "1":
+        # combine fused with the expert-parallel all-reduce: the partial rows go straight into every rank's receive
+        # slots and the next residual-add / RMSNorm kernel sums them (rank 0 contributes the replicated shared expert)
+        first = comm.rank == 0
+        rc = L.vg_moe_combine_push(ptr(b.y), c_int(b.y.stride(0)), ptr(inv), ptr(b.wts), c_int(n), c_int(topk),
+                                   ptr(shared if first else None), ptr(gate if first else None), c_int(h),
+                                   ctypes.byref(comm.ctx), stream())
+        _lib.check(rc, "vg_moe_combine_push")
+        model._pending_ar = True
+        return
     rc = L.vg_moe_combine(ptr(b.y), c_int(b.y.stride(0)), ptr(inv), ptr(b.wts), c_int(n), c_int(topk),
                           ptr(None if ep else shared), ptr(None if ep else gate), ptr(ws.delta), c_int(h), stream())
     _lib.check(rc, "vg_moe_combine")
     if ep:
-        model.comm.all_reduce_rows(ws.delta, n)
+        comm.all_reduce_rows(ws.delta, n)
         if shared is not None:
             rc = L.vg_moe_add_shared(ptr(ws.delta), ptr(shared), ptr(gate), c_int(n), c_int(h), stream())
             _lib.check(rc, "vg_moe_add_shared")
