@@ -111,6 +111,8 @@ long long vg_attn_scratch_floats(int N, int nh, int hd, int ns_grid);
 
 int vg_gdn_conv(const void* x, int ldx, float* state, const float* w, const int* in_slot, const int* parent,
                 const int* out_slot, float* out, int N, int conv_dim, int ck, int phase, cudaStream_t stream);
+int vg_gdn_conv_chain(const void* x, int ldx, float* state, const float* w, const int* in_slot, const int* parent,
+                      const int* out_slot, float* out, int N, int conv_dim, int ck, cudaStream_t stream);
 int vg_gdn_prefill(const float* qkv, const void* proj, int ldp, int off_z, int off_b, int off_a, float* S,
                    const float* A_log, const float* dt_bias, const float* norm_w, int t0, int tn, const int* in_slot,
                    const int* out_slot, void* out_f16, int nk, int nv, int kd, int vd, float eps, float* o_scratch,

@@ -27,14 +27,14 @@ constexpr int MAX_CK = 8;
 __global__ void gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, float* __restrict__ state,
                                 const float* __restrict__ w, const int* __restrict__ in_slot,
                                 const int* __restrict__ parent, const int* __restrict__ out_slot,
-                                float* __restrict__ out, int N, int conv_dim, int ck, int phase) {
+                                float* __restrict__ out, int N, int conv_dim, int ck, int phase, int t_first) {
   if (threadIdx.x == 0) trace(80);
   pdl_trigger();
   pdl_wait();
   if (threadIdx.x == 0) trace(81);
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (size_t)N * conv_dim) return;
-  const int t = (int)(idx / conv_dim), c = (int)(idx % conv_dim);
+  if (idx >= (size_t)(N - t_first) * conv_dim) return;
+  const int t = t_first + (int)(idx / conv_dim), c = (int)(idx % conv_dim);
   const int os = out_slot[t];
   if (!(phase & 1) && os < 0) return;
   float win[MAX_CK];
@@ -54,6 +54,68 @@ __global__ void gdn_conv_kernel(const __nv_bfloat16* __restrict__ x, int ldx, fl
   if ((phase & 2) && os >= 0) {
     float* dst = state + ((size_t)os * conv_dim + c) * ck;
     for (int i = 0; i < ck; ++i) dst[i] = win[i];
+  }
+}
+
+// Prefill form of the conv for one linear chain (parent[t] = t - 1, token 0 continues the state of in_slot[0]):
+// a thread owns eight adjacent channels and walks TS consecutive tokens with the window in registers, so every
+// input row is read once with 16-byte loads instead of ck times with 2-byte loads. Same taps in the same
+// ascending FMA order as gdn_conv_kernel. Conv + SiLU only: the state update of the chain's last token runs
+// afterwards as gdn_conv_kernel phase 2 over that token (it must not overlap the reads of the old state here).
+template <int CK, int TS>
+__global__ void __launch_bounds__(128) gdn_conv_chain_kernel(const __nv_bfloat16* __restrict__ x, int ldx,
+                                                             const float* __restrict__ state, const float* __restrict__ w,
+                                                             const int* __restrict__ in_slot, float* __restrict__ out, int N,
+                                                             int conv_dim) {
+  pdl_trigger();
+  // the taps do not depend on the preceding kernel
+  const int c = ((int)blockIdx.x * 128 + (int)threadIdx.x) * 8;
+  const bool live = c < conv_dim;
+  float wt[8][CK];
+  if (live) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+#pragma unroll
+      for (int i = 0; i < CK; ++i) wt[k][i] = w[(size_t)(c + k) * CK + i];
+  }
+  pdl_wait();
+  if (!live) return;
+  const int t_begin = (int)blockIdx.y * TS, t_end = min(t_begin + TS, N);
+  float win[8][CK];       // win[k][CK - 1] is the current token's sample
+  // history before t_begin: from the rows of earlier tokens, or from the carried state before token 0
+#pragma unroll
+  for (int i = 0; i < CK - 1; ++i) {
+    const int t = t_begin - (CK - 1) + i;
+    if (t >= 0) {
+      const uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)t * ldx + c);
+      const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) win[k][i + 1] = __bfloat162float(b[k]);
+    } else {
+      // the state holds the last CK samples; sample of (virtual) token t is its entry CK + t
+      const float* st = state + ((size_t)in_slot[0] * conv_dim + c) * CK;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) win[k][i + 1] = st[(size_t)k * CK + (CK + t)];
+    }
+  }
+#pragma unroll 4
+  for (int t = t_begin; t < t_end; ++t) {
+    const uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)t * ldx + c);
+    const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(&v);
+    float o[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+#pragma unroll
+      for (int i = 0; i < CK - 1; ++i) win[k][i] = win[k][i + 1];
+      win[k][CK - 1] = __bfloat162float(b[k]);
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < CK; ++i) acc = fmaf(wt[k][i], win[k][i], acc);
+      o[k] = silu(acc);
+    }
+    float4* dst = reinterpret_cast<float4*>(out + (size_t)t * conv_dim + c);
+    dst[0] = make_float4(o[0], o[1], o[2], o[3]);
+    dst[1] = make_float4(o[4], o[5], o[6], o[7]);
   }
 }
 
@@ -117,12 +179,13 @@ __global__ void __launch_bounds__(VD) gdn_step_kernel(
     const float beta = sigmoidf(bb);
     const float sp_ = aa > 20.f ? aa : log1pf(__expf(aa));
     const float g = __expf(a_coef * sp_);
-    // decay + kv_mem. Canonical summation order (shared with the prefill kernel, where two threads split a
-    // column): each half of the key range keeps four interleaved partial sums, halves are added last.
-    constexpr int HK = KD / 2;
-    float hsum[2];
+    // decay + kv_mem. Canonical summation order (shared with the prefill kernel, where four threads split a
+    // column): each quarter of the key range keeps four interleaved partial sums; the quarters are added
+    // pairwise, (q0 + q1) + (q2 + q3).
+    constexpr int HK = KD / 4;
+    float hsum[4];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
+    for (int h = 0; h < 4; ++h) {
       float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
 #pragma unroll
       for (int a = h * HK; a < (h + 1) * HK; a += 4) {
@@ -133,11 +196,11 @@ __global__ void __launch_bounds__(VD) gdn_step_kernel(
       }
       hsum[h] = (m0 + m1) + (m2 + m3);
     }
-    const float kv_mem = (hsum[0] + hsum[1]) * ksc;
+    const float kv_mem = ((hsum[0] + hsum[1]) + (hsum[2] + hsum[3])) * ksc;
     const float delta = (v - kv_mem) * beta;
     const float dk = delta * ksc;
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
+    for (int h = 0; h < 4; ++h) {
       float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
       for (int a = h * HK; a < (h + 1) * HK; a += 4) {
@@ -150,7 +213,7 @@ __global__ void __launch_bounds__(VD) gdn_step_kernel(
       }
       hsum[h] = (o0 + o1) + (o2 + o3);
     }
-    const float o = (hsum[0] + hsum[1]) * qsc;
+    const float o = ((hsum[0] + hsum[1]) + (hsum[2] + hsum[3])) * qsc;
     const float ss = block_sum(o * o, red);
     const float z = __bfloat162float(proj[(size_t)t * ldp + off_z + vh * VD + j]);
     out[((size_t)t * nv + vh) * VD + j] = f32_to_f16_sat(o * rsqrtf(ss / (float)VD + eps) * nw * silu(z));
@@ -220,7 +283,23 @@ extern "C" int vg_gdn_conv(const void* x, int ldx, float* state, const float* w,
   if (ck > MAX_CK) return -2;
   const size_t total = (size_t)N * conv_dim;
   launch_pdl(gdn_conv_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(x), ldx, state, w,
-                                                                   in_slot, parent, out_slot, out, N, conv_dim, ck, phase);
+                                                                   in_slot, parent, out_slot, out, N, conv_dim, ck, phase, 0);
+  return (int)cudaGetLastError();
+}
+
+// Conv + SiLU + state update of one linear chain of N tokens (parent[t] = t - 1; only the last token has an
+// output slot): the prefill form of vg_gdn_conv phases 1 + 2. Returns -2 for shapes it does not cover.
+extern "C" int vg_gdn_conv_chain(const void* x, int ldx, float* state, const float* w, const int* in_slot, const int* parent,
+                                 const int* out_slot, float* out, int N, int conv_dim, int ck, cudaStream_t st) {
+  if (N <= 0) return 0;
+  if (ck != 4 || (conv_dim % 8) != 0 || (ldx % 8) != 0 || ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) != 0)
+    return -2;
+  constexpr int TS = 16;
+  launch_pdl(gdn_conv_chain_kernel<4, TS>, dim3((unsigned)((conv_dim / 8 + 127) / 128), (unsigned)((N + TS - 1) / TS)), dim3(128), 0, st,
+             static_cast<const __nv_bfloat16*>(x), ldx, (const float*)state, w, in_slot, out, N, conv_dim);
+  // state of the last token (the only one with an output slot)
+  launch_pdl(gdn_conv_kernel, dim3((unsigned)((conv_dim + 255) / 256)), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(x), ldx, state, w,
+             in_slot, parent, out_slot, out, N, conv_dim, ck, 2, N - 1);
   return (int)cudaGetLastError();
 }
 
@@ -255,19 +334,25 @@ VG_DEVINL float block_sum_by_warp(const float* x, int lane) {
 // CS CTAs share one value head, each owning VD / CS state columns (the kernel stalls on shared-memory latency
 // with one CTA per head, and only nv SMs would be busy). With CS > 1 the gated output norm, the only step that
 // couples a head's columns, moves to gdn_out_norm_kernel: this kernel then stores the raw outputs (fp32).
-template <int KD, int VD, int TB, int CS>
-__global__ void __launch_bounds__(2 * VD / CS) gdn_prefill_kernel(
+template <int KD, int VD, int TB, int CS, int TPC>
+__global__ void __launch_bounds__(TPC * VD / CS) gdn_prefill_kernel(
     const float* __restrict__ qkv, const __nv_bfloat16* __restrict__ proj, int ldp, int off_z, int off_b, int off_a,
     float* __restrict__ S, const float* __restrict__ A_log, const float* __restrict__ dt_bias,
     const float* __restrict__ norm_w, int t0, int tn, const int* __restrict__ in_slot, const int* __restrict__ out_slot,
     __half* __restrict__ out, float* __restrict__ o_raw, int nk, int nv, float eps) {
   constexpr int VC = VD / CS;              // state columns of this CTA
-  constexpr int NT = 2 * VC, NWARP = NT / 32, HK = KD / 2;
-  static_assert(KD == VD && VD % 32 == 0 && VC % 32 == 0 && TB % NWARP == 0 && KD % 8 == 0, "layout");
+  // TPC threads share a state column, each owning QPT of the four quarters of the key range (the quarters are
+  // the unit of the canonical summation order). In shared memory every quarter of a q / k row is followed by a
+  // 16-byte pad, so the TPC different 16-byte reads of a warp's load instruction fall into different banks.
+  constexpr int QK = KD / 4, QPT = 4 / TPC;
+  constexpr int KDP = KD + 16;             // padded q / k row
+  constexpr int NT = TPC * VC, NWARP = NT / 32, HK = KD / TPC;
+  static_assert(KD == VD && VD % 32 == 0 && VC % 32 == 0 && TB % NWARP == 0 && KD % 16 == 0, "layout");
+  static_assert(TPC == 2 || TPC == 4, "threads per column");
   extern __shared__ __align__(16) float sm[];
-  float* qb = sm;                          // [2][TB][KD] raw q
-  float* kb = qb + 2 * TB * KD;            // [2][TB][KD] raw k
-  float* vb = kb + 2 * TB * KD;            // [2][TB][VC]
+  float* qb = sm;                          // [2][TB][KDP] raw q
+  float* kb = qb + 2 * TB * KDP;           // [2][TB][KDP] raw k
+  float* vb = kb + 2 * TB * KDP;           // [2][TB][VC]
   float* ob = vb + 2 * TB * VC;            // [TB][VC]    o before the output norm
   float* sq = ob + TB * VC;                // [TB][VC]    o^2 staging for the batched reductions
   float* sc = sq + TB * VC;                // [TB][4]     g, beta, ksc, qsc
@@ -279,7 +364,7 @@ __global__ void __launch_bounds__(2 * VD / CS) gdn_prefill_kernel(
   pdl_wait();
   const int vh = blockIdx.x / CS, part = blockIdx.x % CS;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int cl = tid >> 1, h = tid & 1;    // local column and which half of the key range
+  const int cl = tid / TPC, h = tid % TPC; // local column and which quarter of the key range
   const int c = part * VC + cl;            // column of the head's state
   const int kh = vh * nk / nv;
   const int key_dim = nk * KD, conv_dim = 2 * key_dim + nv * VD;
@@ -296,16 +381,17 @@ __global__ void __launch_bounds__(2 * VD / CS) gdn_prefill_kernel(
   }
   auto issue = [&](int b) {                // batch b -> buffer b & 1
     const int base = t0 + b * TB, cnt = min(TB, tn - b * TB);
-    float* q_ = qb + (b & 1) * TB * KD;
-    float* k_ = kb + (b & 1) * TB * KD;
+    float* q_ = qb + (b & 1) * TB * KDP;
+    float* k_ = kb + (b & 1) * TB * KDP;
     float* v_ = vb + (b & 1) * TB * VC;
     __nv_bfloat16* z_ = zb + (b & 1) * TB * VC;
     constexpr int CPT = KD / 4;            // 16-byte chunks per fp32 q / k row
     for (int i = tid; i < cnt * CPT; i += NT) {
       const int tt = i / CPT, o4 = (i % CPT) * 4;
       const float* row = qkv + (size_t)(base + tt) * conv_dim;
-      cp_async16(q_ + tt * KD + o4, row + kh * KD + o4);
-      cp_async16(k_ + tt * KD + o4, row + key_dim + kh * KD + o4);
+      const int po = o4 + (o4 / QK) * 4;   // padded offset
+      cp_async16(q_ + tt * KDP + po, row + kh * KD + o4);
+      cp_async16(k_ + tt * KDP + po, row + key_dim + kh * KD + o4);
     }
     constexpr int CPV = VC / 4;
     for (int i = tid; i < cnt * CPV; i += NT) {
@@ -337,8 +423,8 @@ __global__ void __launch_bounds__(2 * VD / CS) gdn_prefill_kernel(
   if (nb > 0) { issue(0); fetch_scalars(0); }
   for (int b = 0; b < nb; ++b) {
     const int base = t0 + b * TB, cnt = min(TB, tn - b * TB);
-    const float* q_ = qb + (b & 1) * TB * KD;
-    const float* k_ = kb + (b & 1) * TB * KD;
+    const float* q_ = qb + (b & 1) * TB * KDP;
+    const float* k_ = kb + (b & 1) * TB * KDP;
     const float* v_ = vb + (b & 1) * TB * VC;
     const __nv_bfloat16* z_ = zb + (b & 1) * TB * VC;
     if (tid < TB) { bab[tid * 2] = nb_b; bab[tid * 2 + 1] = nb_a; osl[tid] = nb_os; }
@@ -352,7 +438,8 @@ __global__ void __launch_bounds__(2 * VD / CS) gdn_prefill_kernel(
       float pq[VD / 32], pk[VD / 32];
 #pragma unroll
       for (int w = 0; w < VD / 32; ++w) {
-        const float x = q_[tt * KD + 32 * w + lane], y = k_[tt * KD + 32 * w + lane];
+        const int pi = 32 * w + lane + ((32 * w + lane) / QK) * 4;
+        const float x = q_[tt * KDP + pi], y = k_[tt * KDP + pi];
         pq[w] = warp_sum(x * x);
         pk[w] = warp_sum(y * y);
       }
@@ -374,35 +461,53 @@ __global__ void __launch_bounds__(2 * VD / CS) gdn_prefill_kernel(
     // ---- the recurrence: thread-local FMA chains, one shuffle per dot product
     for (int tt = 0; tt < cnt; ++tt) {
       const float g = sc[tt * 4 + 0], beta = sc[tt * 4 + 1], ksc = sc[tt * 4 + 2], qsc = sc[tt * 4 + 3];
-      const float* ks = k_ + tt * KD + h * HK;
-      const float* qs = q_ + tt * KD + h * HK;
+      const float* ks = k_ + tt * KDP + h * QPT * (QK + 4);
+      const float* qs = q_ + tt * KDP + h * QPT * (QK + 4);
       const float v = v_[tt * VC + cl];
-      float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
+      // this thread's part of k stays in registers for both passes over the state
+      float4 kr[HK / 4];
 #pragma unroll
-      for (int a = 0; a < HK; a += 4) {
-        const float4 k4 = *reinterpret_cast<const float4*>(&ks[a]);
-        s[a] *= g; s[a + 1] *= g; s[a + 2] *= g; s[a + 3] *= g;
-        m0 = fmaf(s[a], k4.x, m0); m1 = fmaf(s[a + 1], k4.y, m1);
-        m2 = fmaf(s[a + 2], k4.z, m2); m3 = fmaf(s[a + 3], k4.w, m3);
+      for (int qq = 0; qq < QPT; ++qq)
+#pragma unroll
+        for (int a = 0; a < QK; a += 4) kr[(qq * QK + a) / 4] = *reinterpret_cast<const float4*>(&ks[qq * (QK + 4) + a]);
+      float part[QPT];
+#pragma unroll
+      for (int qq = 0; qq < QPT; ++qq) {
+        float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
+#pragma unroll
+        for (int a = qq * QK; a < (qq + 1) * QK; a += 4) {
+          const float4 k4 = kr[a / 4];
+          s[a] *= g; s[a + 1] *= g; s[a + 2] *= g; s[a + 3] *= g;
+          m0 = fmaf(s[a], k4.x, m0); m1 = fmaf(s[a + 1], k4.y, m1);
+          m2 = fmaf(s[a + 2], k4.z, m2); m3 = fmaf(s[a + 3], k4.w, m3);
+        }
+        part[qq] = (m0 + m1) + (m2 + m3);
       }
-      float mine = (m0 + m1) + (m2 + m3);
-      float other = __shfl_xor_sync(0xffffffffu, mine, 1);
-      const float kv_mem = (h == 0 ? mine + other : other + mine) * ksc;
+      // quarters (q0 + q1) + (q2 + q3): IEEE addition commutes, so every thread of the column gets the same bits
+      float mine = QPT == 2 ? part[0] + part[QPT - 1] : part[0];
+      mine += __shfl_xor_sync(0xffffffffu, mine, 1);
+      if (TPC == 4) mine += __shfl_xor_sync(0xffffffffu, mine, 2);
+      const float kv_mem = mine * ksc;
       const float delta = (v - kv_mem) * beta;
       const float dk = delta * ksc;
-      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-      for (int a = 0; a < HK; a += 4) {
-        const float4 k4 = *reinterpret_cast<const float4*>(&ks[a]);
-        const float4 q4 = *reinterpret_cast<const float4*>(&qs[a]);
-        s[a] = fmaf(k4.x, dk, s[a]); s[a + 1] = fmaf(k4.y, dk, s[a + 1]);
-        s[a + 2] = fmaf(k4.z, dk, s[a + 2]); s[a + 3] = fmaf(k4.w, dk, s[a + 3]);
-        o0 = fmaf(s[a], q4.x, o0); o1 = fmaf(s[a + 1], q4.y, o1);
-        o2 = fmaf(s[a + 2], q4.z, o2); o3 = fmaf(s[a + 3], q4.w, o3);
+      for (int qq = 0; qq < QPT; ++qq) {
+        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+        for (int a = qq * QK; a < (qq + 1) * QK; a += 4) {
+          const float4 k4 = kr[a / 4];
+          const float4 q4 = *reinterpret_cast<const float4*>(&qs[qq * (QK + 4) + (a - qq * QK)]);
+          s[a] = fmaf(k4.x, dk, s[a]); s[a + 1] = fmaf(k4.y, dk, s[a + 1]);
+          s[a + 2] = fmaf(k4.z, dk, s[a + 2]); s[a + 3] = fmaf(k4.w, dk, s[a + 3]);
+          o0 = fmaf(s[a], q4.x, o0); o1 = fmaf(s[a + 1], q4.y, o1);
+          o2 = fmaf(s[a + 2], q4.z, o2); o3 = fmaf(s[a + 3], q4.w, o3);
+        }
+        part[qq] = (o0 + o1) + (o2 + o3);
       }
-      mine = (o0 + o1) + (o2 + o3);
-      other = __shfl_xor_sync(0xffffffffu, mine, 1);
-      const float o = (h == 0 ? mine + other : other + mine) * qsc;
+      mine = QPT == 2 ? part[0] + part[QPT - 1] : part[0];
+      mine += __shfl_xor_sync(0xffffffffu, mine, 1);
+      if (TPC == 4) mine += __shfl_xor_sync(0xffffffffu, mine, 2);
+      const float o = mine * qsc;
       if (h == 0) {
         ob[tt * VC + cl] = o;
         if (CS == 1) sq[tt * VC + cl] = o * o;
@@ -431,7 +536,7 @@ __global__ void __launch_bounds__(2 * VD / CS) gdn_prefill_kernel(
       if (lane == 0) ssb[tt] = ss;
     }
     __syncthreads();
-    for (int tt = h; tt < cnt; tt += 2) {
+    for (int tt = h; tt < cnt; tt += TPC) {
       const float z = __bfloat162float(z_[tt * VD + c]);
       out[((size_t)(base + tt) * nv + vh) * VD + c] =
           f32_to_f16_sat(ob[tt * VD + c] * rsqrtf(ssb[tt] / (float)VD + eps) * nw * silu(z));
@@ -439,19 +544,35 @@ __global__ void __launch_bounds__(2 * VD / CS) gdn_prefill_kernel(
   }
 }
 
-// Gated output norm of the column-split prefill: one CTA per (token, head), the same block_sum as the step kernel.
+// Gated output norm of the column-split prefill: one warp per (token, head), eight per CTA. The sum of squares
+// follows the step kernel's block_sum (per-warp butterflies over elements 32 w + lane, then a butterfly over the
+// VD / 32 partials), so the results are the same bits.
 template <int VD>
-__global__ void __launch_bounds__(VD) gdn_out_norm_kernel(const float* __restrict__ o_raw, const __nv_bfloat16* __restrict__ proj,
-                                                          int ldp, int off_z, const float* __restrict__ norm_w, int t0,
-                                                          __half* __restrict__ out, int nv, float eps) {
-  __shared__ float red[32];
+__global__ void __launch_bounds__(256) gdn_out_norm_kernel(const float* __restrict__ o_raw, const __nv_bfloat16* __restrict__ proj,
+                                                           int ldp, int off_z, const float* __restrict__ norm_w, int t0, int tn,
+                                                           __half* __restrict__ out, int nv, float eps) {
+  constexpr int NW = VD / 32;
   pdl_trigger();
   pdl_wait();
-  const int t = t0 + blockIdx.x, vh = blockIdx.y, j = threadIdx.x;
-  const float o = o_raw[((size_t)t * nv + vh) * VD + j];
-  const float ss = block_sum(o * o, red);
-  const float z = __bfloat162float(proj[(size_t)t * ldp + off_z + vh * VD + j]);
-  out[((size_t)t * nv + vh) * VD + j] = f32_to_f16_sat(o * rsqrtf(ss / (float)VD + eps) * norm_w[j] * silu(z));
+  const int lane = threadIdx.x & 31;
+  const size_t item = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);      // (token, head) pair
+  if (item >= (size_t)tn * nv) return;
+  const int t = t0 + (int)(item / nv), vh = (int)(item % nv);
+  const float* op = o_raw + ((size_t)t * nv + vh) * VD;
+  const __nv_bfloat16* zp = proj + (size_t)t * ldp + off_z + vh * VD;
+  float o[NW], z[NW], p[NW];
+#pragma unroll
+  for (int w = 0; w < NW; ++w) { o[w] = op[32 * w + lane]; z[w] = __bfloat162float(zp[32 * w + lane]); }
+#pragma unroll
+  for (int w = 0; w < NW; ++w) p[w] = warp_sum(o[w] * o[w]);
+  float r = 0.f;
+#pragma unroll
+  for (int w = 0; w < NW; ++w) r = lane == w ? p[w] : r;
+  const float ss = warp_sum(r);
+  const float inv = rsqrtf(ss / (float)VD + eps);
+  __half* dst = out + ((size_t)t * nv + vh) * VD;
+#pragma unroll
+  for (int w = 0; w < NW; ++w) dst[32 * w + lane] = f32_to_f16_sat(o[w] * inv * norm_w[32 * w + lane] * silu(z[w]));
 }
 
 }  // namespace
@@ -497,30 +618,37 @@ extern "C" int vg_gdn_prefill(const float* qkv, const void* proj, int ldp, int o
   if (split != 1 && (!o_scratch || (split != 2 && split != 4))) return -2;
   auto smem_for = [](int cs) {
     const int vc = 128 / cs;
-    return (size_t)(2 * TB * 128 * 2 + 2 * TB * vc + 2 * TB * vc + TB * 4 + TB + TB * 2) * sizeof(float) + TB * sizeof(int) +
+    return (size_t)(2 * TB * (128 + 16) * 2 + 2 * TB * vc + 2 * TB * vc + TB * 4 + TB + TB * 2) * sizeof(float) + TB * sizeof(int) +
            (size_t)2 * TB * vc * sizeof(__nv_bfloat16);
   };
   const __nv_bfloat16* pj = static_cast<const __nv_bfloat16*>(proj);
   __half* o16 = static_cast<__half*>(out_f16);
-#define VG_GDN_PF(CS)                                                                                                   \
+#define VG_GDN_PF(CS, TPC)                                                                                                 \
   {                                                                                                                     \
     static bool configured = false;                                                                                     \
     if (!configured) {                                                                                                  \
-      cudaError_t e = cudaFuncSetAttribute(gdn_prefill_kernel<128, 128, TB, CS>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+      cudaError_t e = cudaFuncSetAttribute(gdn_prefill_kernel<128, 128, TB, CS, TPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                            (int)smem_for(CS));                                                          \
       if (e != cudaSuccess) return (int)e;                                                                              \
       configured = true;                                                                                                \
     }                                                                                                                   \
-    launch_pdl(gdn_prefill_kernel<128, 128, TB, CS>, dim3(nv * CS), dim3(256 / CS), smem_for(CS), st, qkv, pj, ldp, off_z, off_b, \
+    launch_pdl(gdn_prefill_kernel<128, 128, TB, CS, TPC>, dim3(nv * CS), dim3(TPC * 128 / CS), smem_for(CS), st, qkv, pj, ldp, off_z, off_b, \
                off_a, S, A_log, dt_bias, norm_w, t0, tn, in_slot, out_slot, o16, o_scratch, nk, nv, eps);                 \
   }
-  if (split == 4) VG_GDN_PF(4)
-  else if (split == 2) VG_GDN_PF(2)
-  else VG_GDN_PF(1)
+  static const int tpc = [] { const char* e = getenv("VELO_GDN_PREFILL_TPC"); return e && e[0] == '4' ? 4 : 2; }();
+  if (tpc == 4) {
+    if (split == 4) VG_GDN_PF(4, 4)
+    else if (split == 2) VG_GDN_PF(2, 4)
+    else VG_GDN_PF(1, 4)
+  } else {
+    if (split == 4) VG_GDN_PF(4, 2)
+    else if (split == 2) VG_GDN_PF(2, 2)
+    else VG_GDN_PF(1, 2)
+  }
 #undef VG_GDN_PF
   if (split > 1)
-    launch_pdl(gdn_out_norm_kernel<128>, dim3(tn, nv), dim3(128), 0, st, (const float*)o_scratch, pj, ldp, off_z, norm_w, t0, o16, nv,
-               eps);
+    launch_pdl(gdn_out_norm_kernel<128>, dim3((unsigned)(((size_t)tn * nv + 7) / 8)), dim3(256), 0, st, (const float*)o_scratch, pj, ldp,
+               off_z, norm_w, t0, tn, o16, nv, eps);
   return (int)cudaGetLastError();
 }
 

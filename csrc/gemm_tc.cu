@@ -94,8 +94,9 @@ struct Cfg {
   static constexpr int bar_off = p_off + NP * pack;
   static constexpr int n_bars = 2 * NP + 3 * NA + 1;
   static constexpr int smem_total = bar_off + n_bars * 8 + 16 + 1024;
+  static constexpr bool dual = BN <= 128;                          // two accumulators, one per MMA issuer
   static constexpr uint32_t acc_w = BN;                            // columns of one accumulator
-  static constexpr uint32_t acc_cols = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators (one per MMA issuer)
+  static constexpr uint32_t acc_cols = dual ? (2 * BN < 32 ? 32 : 2 * BN) : BN;
   static constexpr uint32_t tmem_cols = pow2_cols(acc_cols + (quant ? NA * A_COLS : 0));
   static_assert(NP * pack >= BN * BM * 4 || BN > 64, "split-K staging must fit in the weight stages");
   static_assert(NP % 2 == 0 && NA % 2 == 0, "ring sizes must be even: one MMA issuer per stage");
@@ -219,7 +220,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
     // quantized: pack_empty is released by the 8 dequantizer warps; f16 tiles: by the MMA commit
     for (int i = 0; i < NP; ++i) { mbar_init(&pack_full[i], 1); mbar_init(&pack_empty[i], QUANT ? 8 : 1); }
     for (int i = 0; i < NA; ++i) { mbar_init(&a_full[i], 8); mbar_init(&b_full[i], 1); mbar_init(&ab_empty[i], 1); }
-    mbar_init(acc_full, 2);
+    mbar_init(acc_full, C::dual ? 2 : 1);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmap_x);
@@ -271,13 +272,15 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
     }
   } else if (warp == 1 || warp == 11) {
     // ------------------------------------------------ MMA issuers: even slabs -> accumulator 0 (warp 1),
-    // odd slabs -> accumulator 1 (warp 11). The epilogue adds the two in a fixed order.
-    if (lane == 0) {
+    // odd slabs -> accumulator 1 (warp 11). The epilogue adds the two in a fixed order. The 256-token tile has
+    // one accumulator (it fills half of TMEM by itself) and one issuer.
+    constexpr int STEP = C::dual ? 2 : 1;
+    if (lane == 0 && (C::dual || warp == 1)) {
       constexpr uint32_t idesc = umma_idesc_f16(BM, BN, 0, 0);
       const int me = warp == 1 ? 0 : 1;
       const uint32_t tmem_acc = tmem_base + (uint32_t)me * C::acc_w;
       bool ok = true;
-      for (int i = me; i < nks && !*abort_flag; i += 2) {
+      for (int i = me; i < nks && !*abort_flag; i += STEP) {
         const int a = i % NA;
         const int sp = i % NP;
         if (QUANT) {
@@ -294,7 +297,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
             const uint64_t bd = umma_desc_sw128(b_addr + (kk >> 2) * (BN * 128) + (kk & 3) * 32);
-            const uint32_t acc_flag = (i >= 2 || kk != 0) ? 1u : 0u;
+            const uint32_t acc_flag = (i >= STEP || kk != 0) ? 1u : 0u;
             if (QUANT) {
               umma_f16_ts(tmem_acc, tmem_a0 + (uint32_t)(a * A_COLS + kk * 8), bd, idesc, acc_flag);
             } else {
@@ -368,25 +371,30 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
   __syncwarp();
 
   // ---------------------------------------------------- epilogue (warps 2..9)
-  constexpr int CPW = BN / 2;            // accumulator columns handled by one warp
-  float acc[CPW];
-  bool have_acc = false;
+  // A pass covers 2 x CPW token columns (the two warp groups side by side); only the 256-token tile, which
+  // has neither split-K nor a fused reduction, takes two passes.
+  constexpr int CPW = BN >= 256 ? 64 : BN / 2;   // accumulator columns handled by one warp in one pass
+  constexpr int PASSES = BN / (2 * CPW);
   const int q = warp & 3;                // TMEM lane quarter this warp may read
-  const int grp = warp >= 6 ? 1 : 0;     // which half of the columns
+  const int grp = warp >= 6 ? 1 : 0;     // which half of the pass's columns
   const int m_local = q * 32 + lane;
   const bool epi = warp >= 2 && warp <= 9;
+  for (int ps = 0; ps < PASSES; ++ps) {
+  const int cb = ps * 2 * CPW + grp * CPW;       // first token column of this warp in this pass
+  float acc[CPW];
+  bool have_acc = false;
   if (epi) {
     if (mbar_wait(acc_full, 0)) {
       tc_fence_after();
 #pragma unroll
       for (int c = 0; c < CPW; c += 8) {
         uint32_t v0[8], v1[8];
-        tmem_ld8(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(grp * CPW + c), v0);
-        tmem_ld8(tmem_base + ((uint32_t)(q * 32) << 16) + C::acc_w + (uint32_t)(grp * CPW + c), v1);
+        tmem_ld8(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(cb + c), v0);
+        if (C::dual) tmem_ld8(tmem_base + ((uint32_t)(q * 32) << 16) + C::acc_w + (uint32_t)(cb + c), v1);
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-          acc[c + j] = nks >= 2 ? __uint_as_float(v0[j]) + __uint_as_float(v1[j]) : __uint_as_float(v0[j]);
+          acc[c + j] = (C::dual && nks >= 2) ? __uint_as_float(v0[j]) + __uint_as_float(v1[j]) : __uint_as_float(v0[j]);
       }
       have_acc = true;
     } else {
@@ -399,7 +407,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
     float* red = reinterpret_cast<float*>(sP);
     if (epi && have_acc) {
 #pragma unroll
-      for (int c = 0; c < CPW; ++c) red[(grp * CPW + c) * BM + m_local] = acc[c];
+      for (int c = 0; c < CPW; ++c) red[(cb + c) * BM + m_local] = acc[c];
     }
     cluster_sync_all();
     if (z == 0 && epi && have_acc) {
@@ -407,7 +415,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
       for (int s = 1; s < S; ++s) {
         const uint32_t remote = dsmem_map(red_addr, (uint32_t)s);
 #pragma unroll
-        for (int c = 0; c < CPW; ++c) acc[c] += dsmem_ld_f32(remote + (uint32_t)(((grp * CPW + c) * BM + m_local) * 4));
+        for (int c = 0; c < CPW; ++c) acc[c] += dsmem_ld_f32(remote + (uint32_t)(((cb + c) * BM + m_local) * 4));
       }
     }
     cluster_sync_all();
@@ -428,7 +436,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
         float* dst = reinterpret_cast<float*>(c.data[peer] + c.slots_off + (size_t)(set * MAX_RANKS + c.rank) * c.slot_bytes);
 #pragma unroll
         for (int cc = 0; cc < CPW; ++cc) {
-          const int col = grp * CPW + cc;
+          const int col = cb + cc;
           if (col < rows_valid) dst[(size_t)(row0 + col) * p.M + m] = acc[cc] * rsc;
         }
       }
@@ -447,7 +455,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
       const size_t stride = c.slot_bytes / sizeof(float);
 #pragma unroll
       for (int cc = 0; cc < CPW; ++cc) {
-        const int col = grp * CPW + cc;
+        const int col = cb + cc;
         if (col < rows_valid) {
           const size_t idx = (size_t)(row0 + col) * p.M + m;
           float sum = 0.f;
@@ -479,7 +487,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
       float* dst = reinterpret_cast<float*>(c.data[owner] + c.slots_off + (size_t)(set * MAX_RANKS + c.rank) * c.slot_bytes);
 #pragma unroll
       for (int cc = 0; cc < CPW; ++cc) {
-        const int col = grp * CPW + cc;
+        const int col = cb + cc;
         if (col < rows_valid) dst[(size_t)(lrow0 + col) * p.M + m] = acc[cc] * rsc;
       }
     }
@@ -496,7 +504,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
       const float rsc = p.row_scale ? p.row_scale[m_base + m] : 1.0f;
 #pragma unroll
       for (int c = 0; c < CPW; ++c) {
-        const int cc = grp * CPW + c;
+        const int cc = cb + c;
         const int n = row0 + cc;
         if (cc < rows_valid) {
           const float v = acc[c] * rsc;
@@ -506,6 +514,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
       }
     }
   }
+  }  // passes
   if (p.ag && threadIdx.x == 64) {
     // the last CTA to finish publishes the epoch: the landing zone may be overwritten by the next gather
     __threadfence();
@@ -612,7 +621,7 @@ int launch(const GemmParams& p, const CUtensorMap& tm, int splitk, cudaStream_t 
 template <int WFMT, int BN> struct Stages;
 template <int BN> struct Stages<VG_WF_NVFP4, BN> { static constexpr int np = BN <= 64 ? 8 : 6, na = 2; };
 template <int BN> struct Stages<VG_WF_FP8, BN> { static constexpr int np = 4, na = 2; };
-template <int BN> struct Stages<VG_WF_F16, BN> { static constexpr int np = 4, na = 2; };
+template <int BN> struct Stages<VG_WF_F16, BN> { static constexpr int np = BN >= 256 ? 2 : 4, na = 2; };
 
 template <int WFMT, int BN>
 int launch_bn(const GemmParams& p, const CUtensorMap& tm, int splitk, cudaStream_t st) {
@@ -620,16 +629,32 @@ int launch_bn(const GemmParams& p, const CUtensorMap& tm, int splitk, cudaStream
   return launch<WFMT, BN, S::np, S::na>(p, tm, splitk, st);
 }
 
+bool wide_tiles_on() {
+  static const bool on = [] { const char* e = getenv("VELO_NO_WIDE_TILES"); return !(e && e[0] == '1'); }();
+  return on;
+}
+int sm_count_tc() {
+  static const int n = [] { int dev = 0, sms = 148; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); return sms; }();
+  return n;
+}
+
 template <int WFMT>
 int dispatch_bn(const GemmParams& p, const void* x, int ldx, int splitk, cudaStream_t st) {
   CUtensorMap tm;
   int bn = p.N <= 16 ? 16 : (p.N <= 32 ? 32 : (p.N <= 64 ? 64 : 128));
+  // 256-token tiles for wide prefill GEMMs: every dequantised weight slab feeds twice the MMA work, which hides
+  // the dequantisers' latency (the 128-token tile leaves the tensor pipe idle more than half of the time). Only
+  // when the grid still fills the GPU twice over; the fused reduce-scatter keeps its 128-token flag granularity.
+  if (p.N > 128 && p.rs_rows == 0 && wide_tiles_on() &&
+      (long long)((p.M + BM - 1) / BM) * ((p.N + 255) / 256) >= 2ll * sm_count_tc())
+    bn = 256;
   int rc = get_tmap_x(x, p.ag ? 2 * p.ag_cap_rows : p.N, p.K, bn, ldx, &tm);
   if (rc) return rc;
   switch (bn) {
     case 16: return launch_bn<WFMT, 16>(p, tm, splitk, st);
     case 32: return launch_bn<WFMT, 32>(p, tm, splitk, st);
     case 64: return launch_bn<WFMT, 64>(p, tm, splitk, st);
+    case 256: return launch_bn<WFMT, 256>(p, tm, splitk, st);
     default: return launch_bn<WFMT, 128>(p, tm, splitk, st);
   }
 }

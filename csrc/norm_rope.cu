@@ -158,6 +158,24 @@ __global__ void swiglu_kernel(const __nv_bfloat16* gu, __half* out, int I, int l
   out[i] = f32_to_f16_sat(silu(g) * u);
 }
 
+// eight elements per thread (16-byte loads / stores): the form prefill widths use
+__global__ void swiglu_vec8_kernel(const __nv_bfloat16* __restrict__ gu, __half* __restrict__ out, int I8, int ld, size_t total8) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total8) return;
+  const size_t n = i / I8, c = (i % I8) * 8;
+  const uint4 g4 = *reinterpret_cast<const uint4*>(gu + n * ld + c);
+  const uint4 u4 = *reinterpret_cast<const uint4*>(gu + n * ld + (size_t)I8 * 8 + c);
+  const __nv_bfloat16* g = reinterpret_cast<const __nv_bfloat16*>(&g4);
+  const __nv_bfloat16* u = reinterpret_cast<const __nv_bfloat16*>(&u4);
+  uint4 o4;
+  __half* o = reinterpret_cast<__half*>(&o4);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) o[k] = f32_to_f16_sat(silu(__bfloat162float(g[k])) * __bfloat162float(u[k]));
+  *reinterpret_cast<uint4*>(out + n * (size_t)I8 * 8 + c) = o4;
+}
+
 template <typename T>
 __global__ void cast_f16_kernel(const T* in, __half* out, size_t total) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -225,6 +243,12 @@ extern "C" int vg_attn_prep(const void* qkv, int ld_qkv, const float* q_norm, co
 extern "C" int vg_swiglu(const void* gu, void* out_f16, int N, int I, int ld, cudaStream_t st) {
   const size_t total = (size_t)N * I;
   if (!total) return 0;
+  if (I % 8 == 0 && ld % 8 == 0 && ((reinterpret_cast<uintptr_t>(gu) | reinterpret_cast<uintptr_t>(out_f16)) & 15) == 0) {
+    const size_t total8 = total / 8;
+    launch_pdl(swiglu_vec8_kernel, dim3((unsigned)((total8 + 255) / 256)), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(gu),
+               static_cast<__half*>(out_f16), I / 8, ld, total8);
+    return (int)cudaGetLastError();
+  }
   launch_pdl(swiglu_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(gu),
                                                                  static_cast<__half*>(out_f16), I, ld, total);
   return (int)cudaGetLastError();

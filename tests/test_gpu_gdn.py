@@ -47,3 +47,35 @@ def test_prefill_kernel_matches_step_kernel_bitwise(T):
                       0, T, in_slot, out_slot, oc, nk, nv, kd, vd, 1e-6, o_scratch=scratch, split=split)
         torch.cuda.synchronize()
         assert torch.equal(oa, oc) and torch.equal(Sa, Sc), split
+
+
+@pytest.mark.parametrize("n", [1, 3, 50, 256])
+def test_conv_chain_matches_two_phase_conv_bitwise(n):
+    """The prefill conv (eight channels per thread, window in registers) against the generic per-element kernel:
+    same outputs and same carried state, bit for bit; and against a plain fp32 reference."""
+    from velogb10_b200.ops import kernels as K
+    dev = torch.device("cuda")
+    torch.manual_seed(3)
+    conv_dim, ck, ldx, slots = 1032, 4, 1048, 3
+    x = torch.randn(n, ldx, device=dev).to(torch.bfloat16)
+    w = torch.randn(conv_dim, ck, device=dev) * 0.5
+    state0 = torch.randn(slots, conv_dim, ck, device=dev)
+    in_slot = torch.full((n,), 1, dtype=torch.int32, device=dev)
+    parent = torch.arange(-1, n - 1, dtype=torch.int32, device=dev)
+    out_slot = torch.full((n,), -1, dtype=torch.int32, device=dev)
+    out_slot[-1] = 1
+    sa, sb = state0.clone(), state0.clone()
+    oa = torch.zeros(n, conv_dim, device=dev)
+    ob = torch.zeros(n, conv_dim, device=dev)
+    K.gdn_conv(x, sa, w, in_slot, parent, out_slot, oa, n, conv_dim, ck, phase=1)
+    K.gdn_conv(x, sa, w, in_slot, parent, out_slot, oa, n, conv_dim, ck, phase=2)
+    assert K.gdn_conv_chain(x, sb, w, in_slot, parent, out_slot, ob, n, conv_dim, ck)
+    torch.cuda.synchronize()
+    assert torch.equal(oa, ob)
+    assert torch.equal(sa, sb)
+    seq = torch.cat([state0[1].t(), x[:, :conv_dim].float()], 0)          # [ck + n, conv_dim]
+    win = torch.stack([seq[i + 1:i + 1 + n] for i in range(ck)], -1)       # [n, conv_dim, ck]
+    ref = torch.nn.functional.silu((win * w).sum(-1))
+    assert (ob - ref).abs().max().item() < 1e-4
+    assert torch.equal(sb[1], seq[-ck:].t())
+    assert torch.equal(sb[0], state0[0]) and torch.equal(sb[2], state0[2])

@@ -18,7 +18,8 @@ def _ref(q, x16):
 
 @pytest.mark.parametrize("fmt", ["nvfp4", "fp8", "bf16"])
 @pytest.mark.parametrize("m,k,n", [(128, 128, 1), (256, 256, 16), (384, 1024, 5), (1552, 256, 3),
-                                   (5120, 5120, 16), (640, 2048, 40), (512, 640, 100), (1024, 512, 300)])
+                                   (5120, 5120, 16), (640, 2048, 40), (512, 640, 100), (1024, 512, 300),
+                                   (19072, 640, 300), (38016, 384, 700)])   # the last two take the 256-token tile
 def test_gemm_tc_matches_reference(fmt, m, k, n):
     from velogb10_b200.ops import gemm as G, lib
     q = _mk(fmt, m, k)

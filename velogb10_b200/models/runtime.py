@@ -415,10 +415,12 @@ class GpuModel:
             G.linear_fp4(Gd.in_proj, ws.xn16, n, out=proj, act=act, conv=cv)
         elif seq_mode:
             self._linear(Gd.in_proj, ws.xn16, n, proj, act=act)
-            K.gdn_conv(proj, self.conv[gi], Gd.conv_w, ws.st_in, ws.parent, ws.st_out, ws.conv_out, n, conv_dim,
-                       c.conv_kernel, phase=1)
-            K.gdn_conv(proj, self.conv[gi], Gd.conv_w, ws.st_in, ws.parent, ws.st_out, ws.conv_out, n, conv_dim,
-                       c.conv_kernel, phase=2)
+            if not (linear_chain and K.gdn_conv_chain(proj, self.conv[gi], Gd.conv_w, ws.st_in, ws.parent, ws.st_out,
+                                                      ws.conv_out, n, conv_dim, c.conv_kernel)):
+                K.gdn_conv(proj, self.conv[gi], Gd.conv_w, ws.st_in, ws.parent, ws.st_out, ws.conv_out, n, conv_dim,
+                           c.conv_kernel, phase=1)
+                K.gdn_conv(proj, self.conv[gi], Gd.conv_w, ws.st_in, ws.parent, ws.st_out, ws.conv_out, n, conv_dim,
+                           c.conv_kernel, phase=2)
         else:
             self._linear(Gd.in_proj, ws.xn16, n, proj, act=act)
             K.gdn_conv(proj, self.conv[gi], Gd.conv_w, ws.st_in, ws.parent, ws.st_out, ws.conv_out, n, conv_dim,

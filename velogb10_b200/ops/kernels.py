@@ -121,6 +121,17 @@ def gdn_conv(x, state, w, in_slot, parent, out_slot, out, n, conv_dim, ck, phase
     _lib.check(rc, "vg_gdn_conv")
 
 
+def gdn_conv_chain(x, state, w, in_slot, parent, out_slot, out, n, conv_dim, ck) -> bool:
+    """Conv + SiLU + state update of one linear chain (prefill); False when the shape is not covered (the caller
+    then runs the generic two-phase form)."""
+    if ck != 4 or conv_dim % 8 or x.stride(0) % 8:
+        return False
+    rc = _lib.lib().vg_gdn_conv_chain(ptr(x), c_int(x.stride(0)), ptr(state), ptr(w), ptr(in_slot), ptr(parent),
+                                      ptr(out_slot), ptr(out), c_int(n), c_int(conv_dim), c_int(ck), stream())
+    _lib.check(rc, "vg_gdn_conv_chain")
+    return True
+
+
 def gdn_step(qkv, proj, off_z, off_b, off_a, S, A_log, dt_bias, norm_w, chain_start, chain_len, n_chains,
              in_slot, parent, out_slot, out16, nk, nv, kd, vd, eps, quant=None):
     """``quant = (bq, sfb, g0, col_ctr)`` makes the kernel also emit every output row as the FP4 activation

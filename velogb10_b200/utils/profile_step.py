@@ -27,6 +27,9 @@ def main():
     ap.add_argument("--ctx", type=int, default=512)
     ap.add_argument("--prompt", type=int, default=1024)
     ap.add_argument("--recipe", default="all")
+    ap.add_argument("--kernel-times", action="store_true",
+                    help="print the in-stream duration of every kernel of the timed steps (activity tracing, no "
+                         "replay: warm caches and real overlap, unlike a per-kernel profiler capture)")
     args = ap.parse_args()
 
     from ..config import preset
@@ -57,6 +60,24 @@ def main():
     torch.cuda.synchronize()
     n_launch = vlib.count_launches(lambda: step(1))
     torch.cuda.synchronize()
+    if args.kernel_times:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for i in range(args.steps):
+                step(2 + i)
+            torch.cuda.synchronize()
+        rows = []
+        for ev in prof.key_averages():
+            us = getattr(ev, "device_time_total", None)
+            if us is None:
+                us = getattr(ev, "cuda_time_total", 0.0)
+            if us > 0:
+                rows.append((us / args.steps, ev.count // args.steps, ev.key))
+        total = sum(r[0] for r in rows)
+        for us, cnt, name in sorted(rows, reverse=True)[:24]:
+            print(f"{us:10.1f} us {100 * us / total:5.1f}% x{cnt:<4d} {name[:110]}")
+        print(f"{total:10.1f} us total kernel time per step")
+        return
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.profiler.start()
     e0.record()
