@@ -26,6 +26,36 @@ template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
+// Rank-order sum of eight consecutive fp32 elements over the W receive slots (16-byte loads through L2).
+__device__ __forceinline__ void sum8_ranks(const float* base, size_t stride, size_t i, int W, float* s) {
+#pragma unroll
+  for (int k = 0; k < 8; ++k) s[k] = 0.f;
+  for (int q = 0; q < W; ++q) {
+    const float4 a = __ldcg(reinterpret_cast<const float4*>(base + (size_t)q * stride + i));
+    const float4 b = __ldcg(reinterpret_cast<const float4*>(base + (size_t)q * stride + i) + 1);
+    s[0] += a.x; s[1] += a.y; s[2] += a.z; s[3] += a.w;
+    s[4] += b.x; s[5] += b.y; s[6] += b.z; s[7] += b.w;
+  }
+}
+__device__ __forceinline__ uint4 pack_bf16x8(const float* s) {
+  uint4 o;
+  __nv_bfloat16* b = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) b[k] = __float2bfloat16_rn(s[k]);
+  return o;
+}
+template <typename T> __device__ __forceinline__ void load8_f32(const T* p, float* v);
+template <> __device__ __forceinline__ void load8_f32<float>(const float* p, float* v) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *(reinterpret_cast<const float4*>(p) + 1);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8_f32<__nv_bfloat16>(const __nv_bfloat16* p, float* v) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(&u);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) v[k] = __bfloat162float(b[k]);
+}
+
 // One-shot all-reduce: every rank pushes its whole vector (as fp32) into its slot on every rank, raises a
 // per-CTA flag there, waits for the W flags of its own chunk and sums the W slots in rank order.
 template <typename TIn>
@@ -86,15 +116,32 @@ __global__ void __launch_bounds__(256) allreduce_twoshot_kernel(VgCommCtx c, con
   const int seg = ((n + W - 1) / W + 7) & ~7;                    // elements per segment
   const int per = ((seg + nct - 1) / nct + 7) & ~7;              // elements per CTA within a segment
   const int lo = min(seg, cta * per), hi = min(seg, lo + per);
+  const bool vec = (n & 7) == 0 && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
   if (threadIdx.x == 0) failed = 0;
   // phase 1: push my partial of segment p to rank p
   for (int k = 0; k < W; ++k) {
     const int p = (c.rank + k) % W;
     float* dst = reinterpret_cast<float*>(c.data[p] + c.slots_off + (size_t)(set * MAX_RANKS + c.rank) * c.slot_bytes);
     const int g0 = p * seg;
-    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-      const int g = g0 + i;
-      dst[i] = g < n ? to_f32<TIn>(in[g]) : 0.f;
+    if (vec) {
+      // eight elements per thread, 16-byte stores over NVLink (n, seg, lo, hi are multiples of 8)
+      for (int i = lo + 8 * (int)threadIdx.x; i < hi; i += 8 * (int)blockDim.x) {
+        const int g = g0 + i;
+        float v[8];
+        if (g < n) {
+          load8_f32<TIn>(in + g, v);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) v[k] = 0.f;
+        }
+        reinterpret_cast<float4*>(dst + i)[0] = make_float4(v[0], v[1], v[2], v[3]);
+        reinterpret_cast<float4*>(dst + i)[1] = make_float4(v[4], v[5], v[6], v[7]);
+      }
+    } else {
+      for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const int g = g0 + i;
+        dst[i] = g < n ? to_f32<TIn>(in[g]) : 0.f;
+      }
     }
   }
   __threadfence_system();
@@ -110,14 +157,15 @@ __global__ void __launch_bounds__(256) allreduce_twoshot_kernel(VgCommCtx c, con
   if (!failed) {
     const float* base = reinterpret_cast<const float*>(c.data[c.rank] + c.slots_off + (size_t)set * MAX_RANKS * c.slot_bytes);
     const size_t stride = c.slot_bytes / sizeof(float);
-    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-      float s = 0.f;
-      for (int q = 0; q < W; ++q) s += __ldcg(&base[(size_t)q * stride + i]);
-      const __nv_bfloat16 v = __float2bfloat16_rn(s);
+    // (lo, hi and seg are multiples of 8: eight elements per thread, one 16-byte store per peer)
+    for (int i = lo + 8 * (int)threadIdx.x; i < hi; i += 8 * (int)blockDim.x) {
+      float s[8];
+      sum8_ranks(base, stride, (size_t)i, W, s);
+      const uint4 v = pack_bf16x8(s);
       const size_t g = (size_t)c.rank * seg + i;
       for (int k = 0; k < W; ++k) {
         const int p = (c.rank + k) % W;
-        reinterpret_cast<__nv_bfloat16*>(c.data[p] + c.result_off + (size_t)set * c.result_bytes)[g] = v;
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(c.data[p] + c.result_off + (size_t)set * c.result_bytes) + g) = v;
       }
     }
   }
@@ -133,11 +181,19 @@ __global__ void __launch_bounds__(256) allreduce_twoshot_kernel(VgCommCtx c, con
   __syncthreads();
   if (!failed) {
     const __nv_bfloat16* res = reinterpret_cast<const __nv_bfloat16*>(c.data[c.rank] + c.result_off + (size_t)set * c.result_bytes);
-    for (int q = 0; q < W; ++q)
-      for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-        const size_t g = (size_t)q * seg + i;
-        if (g < (size_t)n) out[g] = __ldcg(&res[g]);
+    for (int q = 0; q < W; ++q) {
+      if (vec) {
+        for (int i = lo + 8 * (int)threadIdx.x; i < hi; i += 8 * (int)blockDim.x) {
+          const size_t g = (size_t)q * seg + i;
+          if (g < (size_t)n) *reinterpret_cast<uint4*>(out + g) = __ldcg(reinterpret_cast<const uint4*>(res + g));
+        }
+      } else {
+        for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+          const size_t g = (size_t)q * seg + i;
+          if (g < (size_t)n) out[g] = __ldcg(&res[g]);
+        }
       }
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -218,14 +274,15 @@ __global__ void __launch_bounds__(256) gemm_rs_finish_kernel(VgCommCtx c, __nv_b
   if (!failed) {
     const float* base = reinterpret_cast<const float*>(c.data[c.rank] + c.slots_off + (size_t)set * MAX_RANKS * c.slot_bytes);
     const size_t stride = c.slot_bytes / sizeof(float);
-    for (size_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-      float s = 0.f;
-      for (int q = 0; q < W; ++q) s += __ldcg(&base[(size_t)q * stride + i]);
-      const __nv_bfloat16 v = __float2bfloat16_rn(s);
+    // (M is a multiple of 8, so are lo, hi and seg: eight elements per thread, one 16-byte store per peer)
+    for (size_t i = lo + 8 * (size_t)threadIdx.x; i < hi; i += 8 * (size_t)blockDim.x) {
+      float s[8];
+      sum8_ranks(base, stride, i, W, s);
+      const uint4 v = pack_bf16x8(s);
       const size_t g = (size_t)c.rank * seg + i;
       for (int k = 0; k < W; ++k) {
         const int p = (c.rank + k) % W;
-        reinterpret_cast<__nv_bfloat16*>(c.data[p] + c.result_off + (size_t)set * c.result_bytes)[g] = v;
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(c.data[p] + c.result_off + (size_t)set * c.result_bytes) + g) = v;
       }
     }
   }
@@ -247,9 +304,9 @@ __global__ void __launch_bounds__(256) gemm_rs_finish_kernel(VgCommCtx c, __nv_b
       const size_t qn = (size_t)q_rows * M;
       const size_t qper = ((qn + nct - 1) / nct + 7) & ~(size_t)7;
       const size_t qlo = min(qn, (size_t)cta * qper), qhi = min(qn, qlo + qper);
-      for (size_t i = qlo + threadIdx.x; i < qhi; i += blockDim.x) {
+      for (size_t i = qlo + 8 * (size_t)threadIdx.x; i < qhi; i += 8 * (size_t)blockDim.x) {
         const size_t g = (size_t)q * seg + i;
-        if (g < total) out[g] = __ldcg(&res[g]);
+        if (g < total) *reinterpret_cast<uint4*>(out + g) = __ldcg(reinterpret_cast<const uint4*>(res + g));
       }
     }
   }
@@ -394,6 +451,7 @@ extern "C" int vg_comm_ag_push(const VgCommCtx* ctx, const void* x_f16, int row0
 
 extern "C" int vg_comm_gemm_rs_finish(const VgCommCtx* ctx, void* out_bf16, int n, int M, int rs_rows, cudaStream_t st) {
   if (!ctx || ctx->world < 2 || n <= 0 || M <= 0 || rs_rows <= 0 || (rs_rows % 128) != 0) return -2;
+  if ((M % 8) != 0 || (reinterpret_cast<uintptr_t>(out_bf16) & 15) != 0) return -2;      // 16-byte accesses throughout
   const int m_tiles = (M + 127) / 128;
   if ((long long)(rs_rows / 128) * m_tiles > VG_RS_MAX_TILES || (unsigned long long)rs_rows * M * 4ull > ctx->slot_bytes ||
       (unsigned long long)rs_rows * ctx->world * M * 2ull > ctx->result_bytes)

@@ -124,6 +124,8 @@ class TpComm:
         tiles), or 0 when the shape does not fit the arena."""
         rows = ((n_rows + self.world - 1) // self.world + 127) // 128 * 128
         tiles = (rows // 128) * ((m + 127) // 128)
+        if m % 8:
+            return 0
         if tiles > RS_MAX_TILES or rows * m * 4 > self.slot_bytes or rows * self.world * m * 2 > self.result_bytes:
             return 0
         return rows

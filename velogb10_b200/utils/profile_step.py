@@ -27,6 +27,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=512)
     ap.add_argument("--prompt", type=int, default=1024)
     ap.add_argument("--recipe", default="all")
+    ap.add_argument("--tp", action="store_true", help="tensor parallel over the ranks of a torchrun job (rank 0 prints)")
     ap.add_argument("--kernel-times", action="store_true",
                     help="print the in-stream duration of every kernel of the timed steps (activity tracing, no "
                          "replay: warm caches and real overlap, unlike a per-kernel profiler capture)")
@@ -37,11 +38,22 @@ def main():
     from ..models.runtime import Plan
     from ..ops import lib as vlib
 
+    import os
+    rank, world, comm = 0, 1, None
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    if args.tp:
+        import torch.distributed as dist
+        from ..parallel.comm import TpComm
+        rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+        dist.init_process_group("nccl", device_id=dev)
+        comm = TpComm(rank, world, dev)
     cfg = preset(args.model, mtp=False)
     if args.layers and args.layers < cfg.num_layers:
         cfg.num_layers = args.layers
         cfg.layer_types = cfg.layer_types[:args.layers]
-    llm = LLM.synthetic(cfg, recipe=args.recipe, max_batch=max(4, args.batch), max_seq=max(args.ctx, args.prompt) + 64)
+    llm = LLM.synthetic(cfg, recipe=args.recipe, device=str(dev), max_batch=max(4, args.batch),
+                        max_seq=max(args.ctx, args.prompt) + 64, tp_rank=rank, tp_world=world, comm=comm)
     gm = llm.model
     g = torch.Generator().manual_seed(1)
     toks = torch.randint(0, cfg.vocab_size, (max(args.ctx, args.prompt),), generator=g).tolist()
@@ -74,9 +86,12 @@ def main():
             if us > 0:
                 rows.append((us / args.steps, ev.count // args.steps, ev.key))
         total = sum(r[0] for r in rows)
-        for us, cnt, name in sorted(rows, reverse=True)[:24]:
-            print(f"{us:10.1f} us {100 * us / total:5.1f}% x{cnt:<4d} {name[:110]}")
-        print(f"{total:10.1f} us total kernel time per step")
+        if rank == 0:
+            for us, cnt, name in sorted(rows, reverse=True)[:24]:
+                print(f"{us:10.1f} us {100 * us / total:5.1f}% x{cnt:<4d} {name[:110]}")
+            print(f"{total:10.1f} us total kernel time per step")
+        if args.tp:
+            dist.destroy_process_group()
         return
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.profiler.start()
@@ -87,8 +102,11 @@ def main():
     torch.cuda.synchronize()
     torch.cuda.profiler.stop()
     vlib.check_err_word()
-    print(json.dumps({"mode": args.mode, "layers": cfg.num_layers, "steps": args.steps,
-                      "ms_per_step_eager": e0.elapsed_time(e1) / args.steps, "launches_per_step": n_launch}))
+    if rank == 0:
+        print(json.dumps({"mode": args.mode, "layers": cfg.num_layers, "steps": args.steps,
+                          "ms_per_step_eager": e0.elapsed_time(e1) / args.steps, "launches_per_step": n_launch}))
+    if args.tp:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
