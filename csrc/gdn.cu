@@ -635,7 +635,10 @@ extern "C" int vg_gdn_prefill(const float* qkv, const void* proj, int ldp, int o
     launch_pdl(gdn_prefill_kernel<128, 128, TB, CS, TPC>, dim3(nv * CS), dim3(TPC * 128 / CS), smem_for(CS), st, qkv, pj, ldp, off_z, off_b, \
                off_a, S, A_log, dt_bias, norm_w, t0, tn, in_slot, out_slot, o16, o_scratch, nk, nv, eps);                 \
   }
-  static const int tpc = [] { const char* e = getenv("VELO_GDN_PREFILL_TPC"); return e && e[0] == '4' ? 4 : 2; }();
+  // threads per state column: two keep a 64-column CTA at 128 threads; with a head split four ways (32-column
+  // CTAs, the tensor-parallel case) four threads per column do the same (measured 1.26 -> 0.96 ms per layer)
+  static const int tpc_env = [] { const char* e = getenv("VELO_GDN_PREFILL_TPC"); return e ? (e[0] == '4' ? 4 : 2) : 0; }();
+  const int tpc = tpc_env ? tpc_env : (split == 4 ? 4 : 2);
   if (tpc == 4) {
     if (split == 4) VG_GDN_PF(4, 4)
     else if (split == 2) VG_GDN_PF(2, 4)

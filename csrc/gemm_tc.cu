@@ -494,7 +494,8 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
     __threadfence_system();
     asm volatile("bar.sync 1, 256;" ::: "memory");
     if (et == 0) {
-      const int tile = (lrow0 / BN) * (int)gridDim.x + (int)blockIdx.x;
+      // flags are per 128 token rows: a 256-token tile publishes one word per pass
+      const int tile = ((lrow0 + ps * 2 * CPW) / 128) * (int)gridDim.x + (int)blockIdx.x;
       st_release_sys(reinterpret_cast<uint32_t*>(c.data[owner] + c.rsflags_off) +
                          ((size_t)(set * MAX_RANKS + c.rank) * VG_RS_MAX_TILES + tile), e);
     }
@@ -644,8 +645,9 @@ int dispatch_bn(const GemmParams& p, const void* x, int ldx, int splitk, cudaStr
   int bn = p.N <= 16 ? 16 : (p.N <= 32 ? 32 : (p.N <= 64 ? 64 : 128));
   // 256-token tiles for wide prefill GEMMs: every dequantised weight slab feeds twice the MMA work, which hides
   // the dequantisers' latency (the 128-token tile leaves the tensor pipe idle more than half of the time). Only
-  // when the grid still fills the GPU twice over; the fused reduce-scatter keeps its 128-token flag granularity.
-  if (p.N > 128 && p.rs_rows == 0 && wide_tiles_on() &&
+  // when the grid still fills the GPU twice over, and with the fused reduce-scatter only when no tile straddles
+  // two owners (its flags stay per 128 token rows).
+  if (p.N > 128 && (p.rs_rows % 256) == 0 && wide_tiles_on() &&
       (long long)((p.M + BM - 1) / BM) * ((p.N + 255) / 256) >= 2ll * sm_count_tc())
     bn = 256;
   int rc = get_tmap_x(x, p.ag ? 2 * p.ag_cap_rows : p.N, p.K, bn, ldx, &tm);
