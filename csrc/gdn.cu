@@ -331,6 +331,21 @@ VG_DEVINL float block_sum_by_warp(const float* x, int lane) {
   return warp_sum(r);
 }
 
+// Packed pairs of fp32 (sm_100 f32x2 arithmetic): one instruction performs two IEEE fp32 operations, so the
+// results are the bits of the scalar form while the recurrence issues half as many FMA-pipe instructions.
+VG_DEVINL uint64_t pk2(float a, float b) { uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b)); return r; }
+VG_DEVINL void upk2(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+VG_DEVINL uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+VG_DEVINL uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
 // CS CTAs share one value head, each owning VD / CS state columns (the kernel stalls on shared-memory latency
 // with one CTA per head, and only nv SMs would be busy). With CS > 1 the gated output norm, the only step that
 // couples a head's columns, moves to gdn_out_norm_kernel: this kernel then stores the raw outputs (fp32).
@@ -373,11 +388,11 @@ __global__ void __launch_bounds__(TPC * VD / CS) gdn_prefill_kernel(
   const float nw = norm_w[c];
   constexpr int TPW = TB / NWARP;          // tokens per warp in the batched phases
 
-  float s[HK];
+  uint64_t s2[HK / 2];                     // state elements (2i, 2i + 1) of this thread's key range
   {
     const float* sp = S + (((size_t)in_slot[t0] * nv + vh) * KD + h * HK) * VD + c;
 #pragma unroll
-    for (int a = 0; a < HK; ++a) s[a] = sp[(size_t)a * VD];
+    for (int a = 0; a < HK; a += 2) s2[a / 2] = pk2(sp[(size_t)a * VD], sp[(size_t)(a + 1) * VD]);
   }
   auto issue = [&](int b) {                // batch b -> buffer b & 1
     const int base = t0 + b * TB, cnt = min(TB, tn - b * TB);
@@ -464,23 +479,31 @@ __global__ void __launch_bounds__(TPC * VD / CS) gdn_prefill_kernel(
       const float* ks = k_ + tt * KDP + h * QPT * (QK + 4);
       const float* qs = q_ + tt * KDP + h * QPT * (QK + 4);
       const float v = v_[tt * VC + cl];
-      // this thread's part of k stays in registers for both passes over the state
-      float4 kr[HK / 4];
+      // this thread's part of k stays in registers (as pairs) for both passes over the state
+      uint64_t kr[HK / 2];
 #pragma unroll
       for (int qq = 0; qq < QPT; ++qq)
 #pragma unroll
-        for (int a = 0; a < QK; a += 4) kr[(qq * QK + a) / 4] = *reinterpret_cast<const float4*>(&ks[qq * (QK + 4) + a]);
+        for (int a = 0; a < QK; a += 4) {
+          const float4 k4 = *reinterpret_cast<const float4*>(&ks[qq * (QK + 4) + a]);
+          kr[(qq * QK + a) / 2] = pk2(k4.x, k4.y);
+          kr[(qq * QK + a) / 2 + 1] = pk2(k4.z, k4.w);
+        }
+      const uint64_t g2 = pk2(g, g);
       float part[QPT];
 #pragma unroll
       for (int qq = 0; qq < QPT; ++qq) {
-        float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
+        uint64_t m01 = pk2(0.f, 0.f), m23 = pk2(0.f, 0.f);     // the four interleaved partial sums, as two pairs
 #pragma unroll
         for (int a = qq * QK; a < (qq + 1) * QK; a += 4) {
-          const float4 k4 = kr[a / 4];
-          s[a] *= g; s[a + 1] *= g; s[a + 2] *= g; s[a + 3] *= g;
-          m0 = fmaf(s[a], k4.x, m0); m1 = fmaf(s[a + 1], k4.y, m1);
-          m2 = fmaf(s[a + 2], k4.z, m2); m3 = fmaf(s[a + 3], k4.w, m3);
+          s2[a / 2] = mul2(s2[a / 2], g2);
+          s2[a / 2 + 1] = mul2(s2[a / 2 + 1], g2);
+          m01 = fma2(s2[a / 2], kr[a / 2], m01);
+          m23 = fma2(s2[a / 2 + 1], kr[a / 2 + 1], m23);
         }
+        float m0, m1, m2, m3;
+        upk2(m01, m0, m1);
+        upk2(m23, m2, m3);
         part[qq] = (m0 + m1) + (m2 + m3);
       }
       // quarters (q0 + q1) + (q2 + q3): IEEE addition commutes, so every thread of the column gets the same bits
@@ -490,18 +513,21 @@ __global__ void __launch_bounds__(TPC * VD / CS) gdn_prefill_kernel(
       const float kv_mem = mine * ksc;
       const float delta = (v - kv_mem) * beta;
       const float dk = delta * ksc;
+      const uint64_t dk2 = pk2(dk, dk);
 #pragma unroll
       for (int qq = 0; qq < QPT; ++qq) {
-        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+        uint64_t o01 = pk2(0.f, 0.f), o23 = pk2(0.f, 0.f);
 #pragma unroll
         for (int a = qq * QK; a < (qq + 1) * QK; a += 4) {
-          const float4 k4 = kr[a / 4];
           const float4 q4 = *reinterpret_cast<const float4*>(&qs[qq * (QK + 4) + (a - qq * QK)]);
-          s[a] = fmaf(k4.x, dk, s[a]); s[a + 1] = fmaf(k4.y, dk, s[a + 1]);
-          s[a + 2] = fmaf(k4.z, dk, s[a + 2]); s[a + 3] = fmaf(k4.w, dk, s[a + 3]);
-          o0 = fmaf(s[a], q4.x, o0); o1 = fmaf(s[a + 1], q4.y, o1);
-          o2 = fmaf(s[a + 2], q4.z, o2); o3 = fmaf(s[a + 3], q4.w, o3);
+          s2[a / 2] = fma2(kr[a / 2], dk2, s2[a / 2]);
+          s2[a / 2 + 1] = fma2(kr[a / 2 + 1], dk2, s2[a / 2 + 1]);
+          o01 = fma2(s2[a / 2], pk2(q4.x, q4.y), o01);
+          o23 = fma2(s2[a / 2 + 1], pk2(q4.z, q4.w), o23);
         }
+        float o0, o1, o2, o3;
+        upk2(o01, o0, o1);
+        upk2(o23, o2, o3);
         part[qq] = (o0 + o1) + (o2 + o3);
       }
       mine = QPT == 2 ? part[0] + part[QPT - 1] : part[0];
@@ -516,7 +542,12 @@ __global__ void __launch_bounds__(TPC * VD / CS) gdn_prefill_kernel(
       if (os >= 0) {
         float* dp = S + (((size_t)os * nv + vh) * KD + h * HK) * VD + c;
 #pragma unroll
-        for (int a = 0; a < HK; ++a) dp[(size_t)a * VD] = s[a];
+        for (int a = 0; a < HK; a += 2) {
+          float e0, e1;
+          upk2(s2[a / 2], e0, e1);
+          dp[(size_t)a * VD] = e0;
+          dp[(size_t)(a + 1) * VD] = e1;
+        }
       }
     }
     __syncthreads();
