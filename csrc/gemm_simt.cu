@@ -1,6 +1,6 @@
-// CUDA-core GEMV/GEMM over the canonical (checkpoint-order) weight layouts. One warp per output row,
-// K walked in a fixed lane-strided order and reduced with a fixed shuffle tree, one column at a time,
-// so each output column is bit-identical whatever the batch width (the property the reference's
+// CUDA-core GEMV/GEMM over the canonical (checkpoint-order) weight layouts. One warp per (output row,
+// column): K walked in a fixed lane-strided order and reduced with a fixed shuffle tree, every column by
+// its own warp (blockIdx.y), so each output column is bit-identical whatever the batch width (the property the reference's
 // `gemm_binv_b` provides, reference: kernels/gpu_batch.cu:2385-2403). It serves the tiny bf16 matrices
 // (MoE router, shared-expert gate), acts as the on-device cross-check for the tensor-core GEMM, and is
 // the fallback when a matrix is too small to tile.
@@ -54,8 +54,18 @@ __device__ __forceinline__ void load_w32(const void* wq, const uint8_t* scales, 
     }
   } else {
     const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(wq) + (size_t)m * K + k0;
+    if ((K & 7) == 0 && (reinterpret_cast<uintptr_t>(wq) & 15) == 0) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) w[i] = __bfloat162float(src[i]);
+      for (int i = 0; i < 4; ++i) {
+        const uint4 v = reinterpret_cast<const uint4*>(src)[i];
+        const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) w[i * 8 + j] = __bfloat162float(b[j]);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) w[i] = __bfloat162float(src[i]);
+    }
   }
 }
 
@@ -71,7 +81,8 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const void* wq, const ui
   const int m = warp;
   const int nchunks = K / 32;
   const int tail0 = nchunks * 32;       // K % 32 == 16 leaves one 16-wide tail (NVFP4 blocks are 16 wide)
-  for (int n = 0; n < N; ++n) {
+  {
+    const int n = blockIdx.y;
     float acc = 0.0f;
     const __half* xr = x + (size_t)n * ldx;
     for (int c = lane; c < nchunks; c += 32) {
@@ -126,13 +137,13 @@ extern "C" int vg_gemm_simt(const void* wq, const void* scales, const float* row
                             int out_f32, int M, int K, int N, int ldx, int ldo, int wfmt, cudaStream_t st) {
   if (M <= 0 || N <= 0 || K % 16 != 0) return -2;
   const int threads = 256;
-  const int blocks = (M * 32 + threads - 1) / threads;
+  const dim3 blocks((M * 32 + threads - 1) / threads, N);
   const __half* x = static_cast<const __half*>(x_f16);
   const uint8_t* sc = static_cast<const uint8_t*>(scales);
   switch (wfmt) {
-    case VG_WF_NVFP4: launch_pdl(gemm_simt_kernel<VG_WF_NVFP4>, dim3(blocks), dim3(threads), 0, st, wq, sc, row_scale, x, out, M, K, N, ldx, ldo, out_f32); break;
-    case VG_WF_FP8: launch_pdl(gemm_simt_kernel<VG_WF_FP8>, dim3(blocks), dim3(threads), 0, st, wq, sc, row_scale, x, out, M, K, N, ldx, ldo, out_f32); break;
-    case VG_WF_BF16: launch_pdl(gemm_simt_kernel<VG_WF_BF16>, dim3(blocks), dim3(threads), 0, st, wq, sc, row_scale, x, out, M, K, N, ldx, ldo, out_f32); break;
+    case VG_WF_NVFP4: launch_pdl(gemm_simt_kernel<VG_WF_NVFP4>, blocks, dim3(threads), 0, st, wq, sc, row_scale, x, out, M, K, N, ldx, ldo, out_f32); break;
+    case VG_WF_FP8: launch_pdl(gemm_simt_kernel<VG_WF_FP8>, blocks, dim3(threads), 0, st, wq, sc, row_scale, x, out, M, K, N, ldx, ldo, out_f32); break;
+    case VG_WF_BF16: launch_pdl(gemm_simt_kernel<VG_WF_BF16>, blocks, dim3(threads), 0, st, wq, sc, row_scale, x, out, M, K, N, ldx, ldo, out_f32); break;
     default: return -3;
   }
   return (int)cudaGetLastError();
