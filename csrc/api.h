@@ -29,6 +29,7 @@ typedef struct VgCommCtx {
 } VgCommCtx;
 #define VG_RS_MAX_TILES 4096
 #define VG_AG_MAX_TILES 256
+#define VG_ARGMAX_MAX_COLS 64     // columns vg_comm_argmax_merge accepts (size of the callers' pair buffers)
 
 // Optional epilogue of the decode-width GEMM that produces the GatedDeltaNet input projection: rows below
 // conv_dim are conv channels, and the thread that owns a row runs the depthwise causal conv + SiLU for every
@@ -78,8 +79,7 @@ int vg_gemm_tc_grouped(const void* wt, const float* row_scale, const void* x_f16
                        int M, int K, int ldo, int wfmt, int bn, int max_items, const int* g_exp, const int* g_off,
                        const int* g_cnt, const int* tilemap, const int* n_items, int x_div, int* err, cudaStream_t stream);
 int vg_gemm_tc_resident_ctas(int wfmt);
-void vg_gemm_tc_set_variant(int variant, int dbg);
-void vg_gemm_tc_set_trace(long long* buf);
+int vg_gemm_tc_set_debug(int dbg, long long* trace_buf);   // profiling builds only (-DVG_TRACE), else -1
 int vg_gemm_simt(const void* wq, const void* scales, const float* row_scale, const void* x_f16, void* out, int out_f32,
                  int M, int K, int N, int ldx, int ldo, int wfmt, cudaStream_t stream);
 

@@ -24,9 +24,12 @@ using namespace vg;
 
 constexpr int NW = 8;   // warps per CTA
 
-__device__ __forceinline__ int splits_for(int len) {
+// Splits of a column: one per 64 keys, at most 32 and never more than the launch grid (and the partial buffer)
+// provides, so a caller that passes a smaller `ns_grid` gets fewer, longer splits instead of dropped keys.
+__device__ __forceinline__ int splits_for(int len, int ns_grid) {
   int ns = len / 64;
-  return ns < 1 ? 1 : (ns > 32 ? 32 : ns);
+  ns = ns < 1 ? 1 : (ns > 32 ? 32 : ns);
+  return ns > ns_grid ? ns_grid : ns;
 }
 
 // One lane's DPL consecutive bf16 values of a cache row, fetched with a single vector load.
@@ -65,7 +68,7 @@ __global__ void __launch_bounds__(NW * 32) attn_split_kernel(
   const int kvh = blockIdx.y / nsub, sub = blockIdx.y % nsub;
   const int split = blockIdx.z;
   const int len = lens[col];
-  const int ns = direct ? 1 : splits_for(len);
+  const int ns = direct ? 1 : splits_for(len, ns_grid);
   if (split >= ns) return;
   const int chunk = (len + ns - 1) / ns;
   const int k0 = split * chunk;
@@ -198,7 +201,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part, const int* __r
   pdl_trigger();
   pdl_wait();
   const int col = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
-  const int ns = splits_for(lens[col]);
+  const int ns = splits_for(lens[col], ns_grid);
   const float* pp = part + ((size_t)col * nh + head) * ns_grid * (HD + 2);
   float M = -INFINITY;
   for (int s = 0; s < ns; ++s) M = fmaxf(M, pp[(size_t)s * (HD + 2)]);
@@ -262,7 +265,7 @@ int attn_decode_impl(const void* q, const void* kc, const void* vc, const void* 
                      const int* slots, const int* base, const int* path, int path_ld, float* part, int N, int nh, int nkv,
                      int hd, int max_seq, int ns_grid, int direct, const void* gate, int ld_gate, void* out, cudaStream_t st) {
   if (N <= 0) return 0;
-  if (nh % nkv) return -2;
+  if (nh % nkv || (!direct && ns_grid < 1)) return -2;
   const int G = nh / nkv;
   int rc;
   switch (hd) {

@@ -14,6 +14,9 @@
 // Rules of use:
 //  * Size limit: N * nh * ns_grid * (hd + 2) must not exceed VG_ATTN_STATIC_MAX_FLOATS. A larger request is
 //    refused with VG_ERR_STATIC_SCRATCH (-20) and a message on stderr; nothing is launched.
+//  * `ns_grid` is the largest number of key splits a column may use (the models pass 32). A column of `len`
+//    keys uses min(max(len / 64, 1), 32, ns_grid) splits, so a smaller `ns_grid` shrinks the buffer that is
+//    needed and makes every split longer; it never drops keys. ns_grid < 1 is refused (-2).
 //  * It calls no cudaMalloc / cudaFree and no allocating library routine.
 //  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with the
 //    stream's device current). Make that first call outside of any stream capture.

@@ -473,6 +473,7 @@ extern "C" int vg_comm_allgather_small(const VgCommCtx* ctx, const void* in, voi
 extern "C" int vg_comm_argmax_merge(const VgCommCtx* ctx, const float* val, const int* idx, int ncols, float* scratch_pairs,
                                     float* gathered, int* out, cudaStream_t st) {
   const VgCommCtx c = *ctx;
+  if (ncols < 1 || ncols > VG_ARGMAX_MAX_COLS) return -2;      // the wrappers' pair / gather buffers hold this many columns
   pack_pairs_kernel<<<(ncols + 127) / 128, 128, 0, st>>>(val, idx, ncols, scratch_pairs);
   int rc = vg_comm_allgather_small(ctx, scratch_pairs, gathered, ncols * 8, st);
   if (rc) return rc;

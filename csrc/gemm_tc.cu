@@ -10,7 +10,7 @@
 // dequantize-then-library-GEMM prefill path (reference: kernels/gpu_batch.cu:2846-2996,
 // src/gpu.rs:2080-2185).
 //
-// Pipeline per CTA (352 threads):
+// Pipeline per CTA (384 threads = 12 warps; warp 11 idles):
 //   warp 0      weight producer: 1-D bulk copies of pre-tiled packed weight slabs (128 rows x 128 k).
 //   warp 10     activation producer: tiled tensor copies of the X slab (128-byte swizzle), no multicast.
 //   warps 2-9   dequantizers: thread = weight row; e2m1 -> f16 with cvt, times the e4m3 block scale
@@ -59,8 +59,10 @@ struct GemmParams {
   int ks_total;
   int out_f32;
   int* err;
+#ifdef VG_TRACE      // profiling builds only
   int dbg;     // diagnostics: bit 0 skips the dequantisation math, bit 1 skips the MMA issue
   long long* trace;   // optional [9][64] cycle stamps of CTA (0,0,0): per-role pipeline events per slab
+#endif
   // grouped (mixture-of-experts) mode: blockIdx.y walks work items = (group, n-tile)
   int grouped;
   const int* g_exp;      // [groups] expert of the group, -1 = not resident here (skipped)
@@ -153,9 +155,15 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
 }
 
 enum { TR_PROD = 0, TR_PACK_FULL, TR_MATH, TR_A_EMPTY, TR_ST_DONE, TR_MMA_A, TR_MMA_B, TR_MMA_DONE, TR_BPROD };
+#ifdef VG_TRACE
 __device__ __forceinline__ void stamp(const GemmParams& p, int role, int slab) {
   if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && slab < 64) p.trace[role * 64 + slab] = clock64();
 }
+#define VG_DBG(p, bit) ((p).dbg & (bit))
+#else
+__device__ __forceinline__ void stamp(const GemmParams&, int, int) {}
+#define VG_DBG(p, bit) 0
+#endif
 
 __device__ __forceinline__ void report(int* err, int code, volatile int* abort_flag) {
   if (err) atomicCAS(err, 0, code);
@@ -293,7 +301,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
         stamp(p, TR_MMA_B, i);
         tc_fence_after();
         const uint32_t b_addr = smem_u32(sB + (size_t)a * C::b_bytes);
-        if (!(p.dbg & 2)) {
+        if (!VG_DBG(p, 2)) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
             const uint64_t bd = umma_desc_sw128(b_addr + (kk >> 2) * (BN * 128) + (kk & 3) * 32);
@@ -324,7 +332,7 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x) {
       if (warp == 2 && lane == 0) stamp(p, TR_PACK_FULL, i);
       const uint8_t* pk = sP + (size_t)s * PACK;
       uint32_t v[32];
-      if (p.dbg & 1) {
+      if (VG_DBG(p, 1)) {
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = 0;
       } else if (WFMT == VG_WF_NVFP4) {
@@ -555,9 +563,10 @@ struct TmapKey {
     return std::tie(ptr, rows, k, bn, ldx) < std::tie(o.ptr, o.rows, o.k, o.bn, o.ldx);
   }
 };
-int g_variant = 0;
+#ifdef VG_TRACE
 int g_dbg = 0;
 long long* g_trace = nullptr;
+#endif
 std::map<TmapKey, CUtensorMap> g_tmaps;
 std::mutex g_tmap_mu;
 
@@ -676,8 +685,10 @@ extern "C" int vg_gemm_tc(const void* wt, const float* row_scale, const void* x_
   p.ks_total = (K + BK - 1) / BK;
   p.out_f32 = out_f32;
   p.err = err;
+#ifdef VG_TRACE
   p.dbg = g_dbg;
   p.trace = g_trace;
+#endif
   p.grouped = 0;
   p.ar = 0;
   p.rs_rows = 0;
@@ -733,8 +744,6 @@ extern "C" int vg_gemm_tc_grouped(const void* wt, const float* row_scale, const 
   p.ks_total = (K + BK - 1) / BK;
   p.out_f32 = out_f32;
   p.err = err;
-  p.dbg = 0;
-  p.trace = nullptr;
   p.grouped = 1;
   p.ar = 0;
   p.rs_rows = 0;
@@ -755,10 +764,18 @@ extern "C" int vg_gemm_tc_grouped(const void* wt, const float* row_scale, const 
   return -3;
 }
 
-// Experiment hooks used by the micro-benchmark: diagnostic flags (see GemmParams::dbg).
-extern "C" void vg_gemm_tc_set_variant(int variant, int dbg) { g_variant = variant; g_dbg = dbg; }
-// Device buffer of 9 x 64 int64 that receives cycle stamps of CTA (0,0,0)'s pipeline events (null = off).
-extern "C" void vg_gemm_tc_set_trace(long long* buf) { g_trace = buf; }
+// Profiling builds (-DVG_TRACE) only: diagnostic flags (see GemmParams::dbg) and a device buffer of 9 x 64 int64
+// that receives cycle stamps of CTA (0,0,0)'s pipeline events (null = off). Returns -1 in a regular build.
+extern "C" int vg_gemm_tc_set_debug(int dbg, long long* trace_buf) {
+#ifdef VG_TRACE
+  g_dbg = dbg;
+  g_trace = trace_buf;
+  return 0;
+#else
+  (void)dbg; (void)trace_buf;
+  return -1;
+#endif
+}
 
 // Number of CTAs of the decode configuration that can be resident at once (used by the host
 // heuristic that picks the split-K factor).

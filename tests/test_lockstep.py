@@ -23,3 +23,19 @@ def test_divergence_drill_trips_the_guard():
     r = _run({"VELO_TP_AGREE_DRILL": "2"}, 29552)
     assert r.returncode != 0
     assert "DIVERGED" in r.stdout and "LOCKSTEP_OK" not in r.stdout
+
+
+def test_rank_leaving_between_steps_surfaces_as_divergence():
+    """A rank that stops answering (it exits between two steps, nothing of it in flight) must end the survivors
+    with DivergenceError through the control group's timeout, never hang them."""
+    r = _run({"LOCKSTEP_MODE": "leave"}, 29553)
+    assert r.returncode != 0
+    assert "DIVERGED rank 0" in r.stdout and "UNEXPECTED_END" not in r.stdout, (r.stdout[-2000:], r.stderr[-2000:])
+
+
+def test_device_failure_on_one_rank_stops_every_rank():
+    """One rank's health probe reports a kernel failure: the flag travels in the per-step agreement and both
+    ranks raise in the same step."""
+    r = _run({"LOCKSTEP_MODE": "fault"}, 29554)
+    assert r.returncode != 0
+    assert r.stdout.count("DIVERGED") == 2 and "device failure" in r.stdout, (r.stdout[-2000:], r.stderr[-2000:])

@@ -178,3 +178,29 @@ def test_draft_vocab_rows_rule():
     assert top == tail
     top, tail = draft_vocab_rows(200, 1024)
     assert tail == 1024 - 128 and (top + 128) % 128 == 0
+
+
+def test_per_expert_fuse_streams_one_layer_at_a_time():
+    """With the expert count known, a layer's stacked tensors come out as soon as its last per-expert tensor went
+    in (nothing of it stays stashed); a set that never completes is an error."""
+    from velogb10_b200.checkpoint import io
+    E, seen = 3, []
+
+    def feed():
+        for layer in range(2):
+            for e in range(E):
+                for kind in ("gate_proj", "up_proj", "down_proj"):
+                    seen.append((layer, e, kind))
+                    yield f"m.layers.{layer}.mlp.experts.{e}.{kind}.weight", torch.full((2, 4), float(e))
+            yield f"m.layers.{layer}.post.weight", torch.zeros(1)
+    order = []
+    for name, t in io._iter_fused(feed(), E):
+        order.append((name, len(seen)))
+    names = [n for n, _ in order]
+    assert names == ["m.layers.0.mlp.experts.gate_up_proj", "m.layers.0.mlp.experts.down_proj", "m.layers.0.post.weight",
+                     "m.layers.1.mlp.experts.gate_up_proj", "m.layers.1.mlp.experts.down_proj", "m.layers.1.post.weight"]
+    assert order[0][1] == 3 * E and order[3][1] == 6 * E          # fused before the next layer was read
+    gu = next(t for n, t in io._iter_fused(feed(), E) if n.endswith("0.mlp.experts.gate_up_proj"))
+    assert gu.shape == (E, 4, 4) and gu[2].eq(2).all()
+    with pytest.raises(ValueError):
+        list(io._iter_fused([("m.layers.0.mlp.experts.0.gate_proj.weight", torch.zeros(2, 4))], E))

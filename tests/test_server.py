@@ -173,3 +173,24 @@ def test_cli_arg_parsing_and_scripts(tmp_path):
     g = subprocess.run([sys.executable, "-m", "velogb10_b200", "--generate", "--cpu", "--model-dir", q, "--prompt", "hi",
                         "--max-new", "4"], capture_output=True, text=True, cwd=root)
     assert g.returncode == 0 and len(json.loads(g.stdout)["tokens"]) == 4, g.stderr
+
+
+def test_http_stop_string_that_matches_ends_both_modes(client):
+    """A stop string that does occur: the handler cancels the request, the scheduler must still deliver the final
+    event, and both the blocking reply and the stream (finish chunk + [DONE]) must arrive with the text cut."""
+    body = {"model": "tiny-test", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 16, "temperature": 0,
+            "seed": 7}
+    full = client.post("/v1/chat/completions", json=body).json()["choices"][0]["message"]["content"] or ""
+    assert len(full) >= 3, full
+    i = next(k for k in range(1, len(full)) if full[k] not in full[:k])
+    stop = full[i]
+    r = client.post("/v1/chat/completions", json={**body, "stop": [stop]})
+    assert r.status_code == 200
+    j = r.json()
+    assert (j["choices"][0]["message"]["content"] or "") == full[:i] and j["choices"][0]["finish_reason"] == "stop"
+    with client.stream("POST", "/v1/chat/completions", json={**body, "stop": stop, "stream": True}) as s:
+        lines = [l for l in s.iter_lines() if l.startswith("data: ")]
+    assert lines[-1] == "data: [DONE]"
+    chunks = [json.loads(l[6:]) for l in lines[:-1]]
+    assert chunks[-1]["choices"][0]["finish_reason"] == "stop"
+    assert "".join(c["choices"][0]["delta"].get("content", "") for c in chunks if c["choices"]) == full[:i]

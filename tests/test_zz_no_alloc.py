@@ -32,8 +32,10 @@ def test_static_scratch_entry_matches_regular_entry_twice():
     L.vg_attn_scratch_floats.restype = ctypes.c_longlong
     vp, ci = ctypes.c_void_p, ctypes.c_int
     st = vp(torch.cuda.current_stream().cuda_stream)
-    nh, nkv, hd, max_seq, ns = 8, 2, 128, 1024, 32
-    for seed, n, lens in ((1, 3, [5, 700, 1024]), (2, 5, [300, 1, 513, 256, 999])):
+    max_seq = 1024
+    # (the last case is the model shape, head_dim 256, with fewer splits than the columns' lengths ask for)
+    for seed, n, lens, nh, nkv, hd, ns in ((1, 3, [5, 700, 1024], 8, 2, 128, 32), (2, 5, [300, 1, 513, 256, 999], 8, 2, 128, 32),
+                                           (3, 2, [1024, 130], 6, 2, 256, 4)):
         q, kc, vc, lens_t, slot_t = _case(seed, n, lens, nh, nkv, hd, max_seq)
         part = torch.empty(int(L.vg_attn_scratch_floats(ci(n), ci(nh), ci(hd), ci(ns))), dtype=torch.float32, device="cuda")
         ref = torch.zeros(n, nh * hd, dtype=torch.float16, device="cuda")

@@ -147,12 +147,22 @@ def emit_tensor(w: ShardWriter, name: str, t: torch.Tensor, recipe: Optional[dic
         stats["fp8"] += 1
 
 
-_PER_EXPERT = re.compile(r"^(.*\.mlp\.experts)\.(\d+)\.(gate_proj|up_proj|down_proj)\.weight$")
+_PER_EXPERT = re.compile(r"^(.*\.experts)\.(\d+)\.(gate_proj|up_proj|down_proj)\.weight$")
+_EXPERT_KINDS = ("gate_proj", "up_proj", "down_proj")
 
 
-def _iter_fused(named: Iterable[Tuple[str, torch.Tensor]]):
-    """Pass tensors through, fusing per-expert 2-D tensors into stacked 3-D ones once a layer's set
-    is complete (gate‖up concatenated along rows; experts stacked in integer order)."""
+def _fuse_expert_set(base: str, d: Dict[Tuple[int, str], torch.Tensor], n: int):
+    gu = torch.stack([torch.cat([d[(e, "gate_proj")], d[(e, "up_proj")]], 0) for e in range(n)], 0)
+    dn = torch.stack([d[(e, "down_proj")] for e in range(n)], 0)
+    return [(base + ".gate_up_proj", gu), (base + ".down_proj", dn)]
+
+
+def _iter_fused(named: Iterable[Tuple[str, torch.Tensor]], n_experts: Optional[int] = None):
+    """Pass tensors through, fusing per-expert 2-D tensors into stacked 3-D ones (gate‖up concatenated along
+    rows; experts stacked in integer order). With ``n_experts`` known (from the checkpoint's config) a layer is
+    fused, yielded and dropped as soon as its last tensor arrives, so the stash holds about one layer of experts
+    (reference: src/main.rs ``run_quantize``); without it the count is only known once the input ends, and every
+    per-expert tensor is held until then. An incomplete set is an error either way."""
     stash: Dict[str, Dict[Tuple[int, str], torch.Tensor]] = {}
     for name, t in named:
         mt = _PER_EXPERT.match(name)
@@ -160,16 +170,17 @@ def _iter_fused(named: Iterable[Tuple[str, torch.Tensor]]):
             yield name, t
             continue
         base, e, kind = mt.group(1), int(mt.group(2)), mt.group(3)
-        stash.setdefault(base, {})[(e, kind)] = t
+        d = stash.setdefault(base, {})
+        d[(e, kind)] = t
+        if n_experts and len(d) == 3 * n_experts and all((x, k) in d for x in range(n_experts) for k in _EXPERT_KINDS):
+            yield from _fuse_expert_set(base, stash.pop(base), n_experts)
     for base, d in stash.items():
-        n = 1 + max(e for e, _ in d)
-        missing = [(e, k) for e in range(n) for k in ("gate_proj", "up_proj", "down_proj") if (e, k) not in d]
-        if missing:
-            raise ValueError(f"{base}: incomplete per-expert set, missing {missing[:3]}…")
-        gu = torch.stack([torch.cat([d[(e, "gate_proj")], d[(e, "up_proj")]], 0) for e in range(n)], 0)
-        dn = torch.stack([d[(e, "down_proj")] for e in range(n)], 0)
-        yield base + ".gate_up_proj", gu
-        yield base + ".down_proj", dn
+        n = n_experts or 1 + max(e for e, _ in d)
+        missing = [(e, k) for e in range(n) for k in _EXPERT_KINDS if (e, k) not in d]
+        if missing or len(d) != 3 * n:
+            raise ValueError(f"{base}: incomplete or inconsistent per-expert set ({len(d)} tensors for {n} experts), "
+                             f"missing {missing[:3]}")
+        yield from _fuse_expert_set(base, d, n)
 
 
 def write_checkpoint(out_dir: str, named: Iterable[Tuple[str, torch.Tensor]], config: dict,
@@ -179,7 +190,9 @@ def write_checkpoint(out_dir: str, named: Iterable[Tuple[str, torch.Tensor]], co
     rec = parse_recipe(recipe)
     w = ShardWriter(out_dir, recipe, max_shard_bytes)
     stats = {"nvfp4": 0, "fp8": 0, "copied": 0}
-    for name, t in _iter_fused(named):
+    tc = config.get("text_config", config)
+    n_experts = tc.get("num_experts") or tc.get("n_routed_experts") or tc.get("num_local_experts")
+    for name, t in _iter_fused(named, int(n_experts) if n_experts else None):
         emit_tensor(w, name, t, rec, stats)
     w.finish()
     cfg = dict(config)

@@ -16,10 +16,21 @@ import time
 from typing import Dict, List, Optional
 
 FLAG_ENV = {
-    "--kv-cache": "VELO_KV_QUANT", "--no-decode-graphs": "VELO_NO_DECODE_GRAPHS", "--fuse-residual": "VELO_FUSE_RESIDUAL",
-    "--cpu-sample": "VELO_CPU_SAMPLE", "--prefill-scalar": "VELO_PREFILL_SCALAR", "--zero-kv": "VELO_ZERO_KV",
-    "--draft-vocab": "VELO_DRAFT_VOCAB", "--tp-trace": "VELO_TP_TRACE", "--tp-fp32-partials": "VELO_TP_FP32_PARTIALS",
-    "--no-shard-mixers": "VELO_NO_SHARD_MIXERS", "--tp-nccl": "VELO_TP_NCCL", "--no-gqpack": "VELO_NO_GQPACK",
+    "--kv-cache": "VELO_KV_QUANT", "--no-decode-graphs": "VELO_NO_DECODE_GRAPHS",
+    "--cpu-sample": "VELO_CPU_SAMPLE",           # engine/scheduler.py: token selection on the host from copied logits
+    "--prefill-scalar": "VELO_PREFILL_SCALAR",   # models/runtime.py: exact per-token prefill kernels (no tensor-core
+                                                 # attention, no chunked GatedDeltaNet); bit-identical to stepping
+    "--zero-kv": "VELO_ZERO_KV", "--draft-vocab": "VELO_DRAFT_VOCAB",
+    "--tp-trace": "VELO_TP_TRACE",               # engine/scheduler.py: step-latency percentiles on stderr
+    "--tp-nccl": "VELO_TP_NCCL",
+}
+# Flags of the reference's command line that select between code paths this engine has only one of. They are
+# accepted so existing launch scripts keep working, and each use is reported on stderr with the reason.
+NO_EFFECT = {
+    "--fuse-residual": "the residual add is always fused into the RMSNorm kernel",
+    "--tp-fp32-partials": "tensor-parallel partial sums are always exchanged and added in fp32",
+    "--no-shard-mixers": "attention and GatedDeltaNet mixers are always head-sharded under --tp",
+    "--no-gqpack": "decode attention always serves a KV head's whole query group from one pass over its keys",
 }
 BOOL_FLAGS = {"--server", "--quantize", "--requant-gdn", "--generate", "--help", "-h", "--no-decode-graphs",
               "--fuse-residual", "--cpu-sample", "--prefill-scalar", "--zero-kv", "--tp-trace", "--tp-fp32-partials",
@@ -84,6 +95,9 @@ def env_bridge(args: Dict[str, str]):
     for flag, env in FLAG_ENV.items():
         if flag in args:
             os.environ[env] = args[flag]
+    for flag, why in NO_EFFECT.items():
+        if flag in args:
+            print(f"[cli] {flag} has no effect: {why}", file=sys.stderr)
 
 
 def on(v: Optional[str], default: bool) -> bool:

@@ -20,6 +20,8 @@ copy_state / zero_slot / compact_kv`` (the CUDA runtime or the fp32 CPU oracle).
 """
 from __future__ import annotations
 
+import os
+import sys
 import time
 from collections import deque
 from dataclasses import dataclass, field
@@ -48,7 +50,8 @@ class Request:
     on_token: Optional[Callable[[int], None]] = None
     on_finish: Optional[Callable[[str, dict], None]] = None
     id: int = 0
-    cancelled: bool = False
+    cancelled: bool = False                           # set by the owner of the request at any time (any thread)
+    cancel_applied: bool = False                      # set by the scheduler at a step boundary; the only flag it acts on
     # filled by the scheduler
     t_submit: float = 0.0
     t_first: float = 0.0
@@ -98,6 +101,15 @@ class Scheduler:
         self.stats = {"admitted": 0, "prefix_live": 0, "prefix_ckpt": 0, "prefix_miss": 0, "decode_steps": 0,
                       "mtp_steps": 0, "forest_steps": 0, "tree_steps": 0, "tokens": 0, "prefill_tokens": 0}
         self.log: List[str] = []
+        # True when something else (the lockstep driver) decides which cancellations a step sees, so that every
+        # rank of a tensor-parallel group applies the same ones in the same step
+        self.external_cancels = False
+        # optional health probe called once per step; raises when a kernel or a collective reported a failure
+        self.health_check: Optional[Callable[[], None]] = getattr(runner, "health_check", None)
+        # wall time of the most recent decode steps (ms), for per-token latency percentiles; --tp-trace prints them
+        self.step_ms: Deque[float] = deque(maxlen=4096)
+        self.trace_every = 256 if os.environ.get("VELO_TP_TRACE", "0") == "1" else 0
+        self.cpu_sample = os.environ.get("VELO_CPU_SAMPLE", "0") == "1"
 
     # ------------------------------------------------------------------ public
     def submit(self, req: Request) -> int:
@@ -116,14 +128,45 @@ class Scheduler:
             self.step()
             n += 1
 
+    def apply_cancels(self, ids: Optional[Set[int]] = None):
+        """Latch cancellations at a step boundary. ``ids=None`` snapshots the live ``cancelled`` flags of every
+        running and queued request; otherwise exactly the requests named are cancelled (lockstep: the head's
+        snapshot, replayed identically on every rank). The step acts on the latched flag only, so a flag that
+        flips while the step runs is seen by the next one."""
+        for req in [l.req for l in self.lanes] + list(self.queue):
+            if (req.cancelled if ids is None else req.id in ids):
+                req.cancel_applied = True
+
+    def pending_cancels(self) -> List[int]:
+        """Ids of running or queued requests whose owner cancelled them and that no step has acted on yet."""
+        return [r.id for r in [l.req for l in self.lanes] + list(self.queue) if r.cancelled and not r.cancel_applied]
+
     def step(self) -> bool:
         """Admit what fits, then run one decode step. Returns False when there was nothing to do."""
+        if not self.external_cancels:
+            self.apply_cancels(None)
+        if self.health_check is not None:
+            self.health_check()
         while self.queue and self.free_slots and len(self.lanes) < self.max_batch:
             self._admit(self.queue.popleft())
         if not self.lanes:
             return False
+        t0 = time.perf_counter()
         self._decode_step()
+        self.step_ms.append((time.perf_counter() - t0) * 1e3)
+        if self.trace_every and len(self.step_ms) % self.trace_every == 0:
+            print("[trace] step latency ms " + " ".join(f"{k}={v:.3f}" for k, v in self.latency_percentiles().items()),
+                  file=sys.stderr)
         return True
+
+    def latency_percentiles(self) -> Dict[str, float]:
+        """p50 / p90 / p99 / max of the recorded decode-step wall times (reference: src/gpu.rs:7296-7364 reports the
+        same percentiles per token)."""
+        v = sorted(self.step_ms)
+        if not v:
+            return {}
+        pick = lambda q: v[min(len(v) - 1, int(q * len(v)))]
+        return {"n": float(len(v)), "p50": pick(0.50), "p90": pick(0.90), "p99": pick(0.99), "max": v[-1]}
 
     # ------------------------------------------------------------------ admission
     def _pick_slot(self, prompt: List[int]) -> Tuple[int, int, str]:
@@ -151,7 +194,8 @@ class Scheduler:
     def _admit(self, req: Request):
         prompt = list(req.prompt)
         plen = len(prompt)
-        if req.cancelled:
+        if req.cancel_applied:
+            self._finish_req(req, "cancelled", plen, 0)
             return
         if plen == 0 or plen >= self.max_seq:
             self._finish_req(req, "context_length_exceeded", plen, 0)
@@ -256,12 +300,12 @@ class Scheduler:
     def _retire_finished(self):
         keep = []
         for lane in self.lanes:
-            if lane.req.cancelled and not lane.done:
+            if lane.req.cancel_applied and not lane.done:
                 lane.done = "cancelled"
             if lane.done:
                 self.free_slots.append(lane.slot)
-                if lane.done != "cancelled":
-                    self._finish_req(lane.req, lane.done, len(lane.req.prompt), lane.generated)
+                # a cancelled request still gets its final event: whoever waits on it must be released
+                self._finish_req(lane.req, lane.done, len(lane.req.prompt), lane.generated)
                 self.log.append(f"[req] {lane.req.id} done {lane.done} generated {lane.generated}")
             else:
                 keep.append(lane)
@@ -274,9 +318,6 @@ class Scheduler:
 
     # ------------------------------------------------------------------ decode step
     def _decode_step(self):
-        for lane in self.lanes:
-            if lane.req.cancelled:
-                lane.done = "cancelled"
         self._retire_finished()
         if not self.lanes:
             return

@@ -163,7 +163,9 @@ class GpuModel:
         # tensor-parallel decode: row-parallel GEMMs push partial rows, the following norm kernel sums them
         self.split_allreduce = os.environ.get("VELO_NO_SPLIT_ALLREDUCE", "0") != "1"
         self._pending_ar = False
-        self.tc_prefill_attn = os.environ.get("VELO_NO_TC_PREFILL_ATTN", "0") != "1"
+        # --prefill-scalar: exact per-token prefill kernels only (bit-identical to stepping the decode kernels)
+        self.prefill_exact = os.environ.get("VELO_PREFILL_SCALAR", "0") == "1"
+        self.tc_prefill_attn = os.environ.get("VELO_NO_TC_PREFILL_ATTN", "0") != "1" and not self.prefill_exact
         self._prefill_ctx = None              # (slot, first position) while a prefill chunk is running
         self.kv_q4 = os.environ.get("VELO_KV_QUANT", "bf16").lower() == "q4"
         self._kv_scales = None                # (k scales, v scales) of the layer being run, 4-bit cache only
@@ -288,6 +290,36 @@ class GpuModel:
     def _kv_tensors(self):
         """Main-model cache tensors, all shaped [attention layer, slot, kv head, position, ...]."""
         return [t for t in (self.kc, self.vc, self.ks, self.vs) if t is not None]
+
+    # ---------------------------------------------------------------- health
+    def health_check(self):
+        """Per-step failure probe without a synchronisation of its own: the kernels' bounded-wait status word and
+        the communicator's status word are copied to pinned host memory asynchronously; each call first reads the
+        copy the previous call enqueued (complete by now: the step's token read synchronised the stream in
+        between) and raises ``KernelError`` / ``CommError`` when either word is non-zero. Plays the role of the
+        reference's transport watchdog + abort word (reference: native/net_shim.c:471-507, src/main.rs:2825-2858)."""
+        if getattr(self, "_health_host", None) is None:
+            self._health_host = torch.zeros(2, dtype=torch.int32).pin_memory()
+            self._health_dev = torch.zeros(2, dtype=torch.int32, device=self.dev)
+            self._health_evt = None
+        if self._health_evt is not None and self._health_evt.query():
+            kerr, cerr = int(self._health_host[0]), int(self._health_host[1])
+            if kerr or cerr:
+                self._health_host.zero_()
+                _lib.err_word(self.dev).zero_()
+                if self.comm is not None and self.comm.world > 1:
+                    self.comm._status_view.zero_()
+                if cerr:
+                    from ..parallel.comm import CommError
+                    raise CommError(f"peer-memory collective reported error {cerr} (4 = a peer's flag did not arrive in time)")
+                raise _lib.KernelError(f"a kernel reported bounded-wait failure code {kerr}")
+        self._health_dev[0:1].copy_(_lib.err_word(self.dev))
+        if self.comm is not None and self.comm.world > 1:
+            self._health_dev[1:2].copy_(self.comm._status_view)
+        self._health_host.copy_(self._health_dev, non_blocking=True)
+        if self._health_evt is None:
+            self._health_evt = torch.cuda.Event()
+        self._health_evt.record()
 
     # ---------------------------------------------------------------- plan upload
     def _upload(self, ws: Workspace, p: Plan):

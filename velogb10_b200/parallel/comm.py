@@ -33,6 +33,7 @@ class VgCommCtx(ctypes.Structure):
 
 RS_MAX_TILES = 4096                      # per-tile epoch words of the fused GEMM + reduce-scatter, per (set, rank)
 AG_MAX_TILES = 256                       # per-tile epoch words of the fused all-gather + GEMM, per set
+ARGMAX_MAX_COLS = 64                     # columns the arg-max merge buffers hold (csrc/api.h VG_ARGMAX_MAX_COLS)
 
 
 class CommError(RuntimeError):
@@ -89,11 +90,11 @@ class TpComm:
         ctx.agbuf_off, ctx.agbuf_bytes, ctx.agflags_off = self.agbuf_off, self.agbuf_bytes, self.agflags_off
         self.ctx = ctx
         self._status_view = self._view(8, 1, torch.int32)
-        self._pairs = torch.zeros(2 * 64, dtype=torch.float32, device=self.dev)
-        self._gathered = torch.zeros(2 * 64 * world, dtype=torch.float32, device=self.dev)
-        self._out_tok = torch.zeros(64, dtype=torch.int32, device=self.dev)
-        self._val = torch.zeros(64, dtype=torch.float32, device=self.dev)
-        self._idx = torch.zeros(64, dtype=torch.int32, device=self.dev)
+        self._pairs = torch.zeros(2 * ARGMAX_MAX_COLS, dtype=torch.float32, device=self.dev)
+        self._gathered = torch.zeros(2 * ARGMAX_MAX_COLS * world, dtype=torch.float32, device=self.dev)
+        self._out_tok = torch.zeros(ARGMAX_MAX_COLS, dtype=torch.int32, device=self.dev)
+        self._val = torch.zeros(ARGMAX_MAX_COLS, dtype=torch.float32, device=self.dev)
+        self._idx = torch.zeros(ARGMAX_MAX_COLS, dtype=torch.int32, device=self.dev)
         dist.barrier(group=group)
 
     def _view(self, offset: int, n: int, dtype) -> torch.Tensor:
@@ -165,6 +166,7 @@ class TpComm:
 
     def argmax_merge(self, val: torch.Tensor, idx: torch.Tensor, n: int, out: torch.Tensor):
         """Global arg-max from per-rank (value, global index) pairs; enqueue-only (graph capturable)."""
+        assert 1 <= n <= ARGMAX_MAX_COLS, f"arg-max merge handles at most {ARGMAX_MAX_COLS} columns, got {n}"
         rc = self.L.vg_comm_argmax_merge(ctypes.byref(self.ctx), ptr(val), ptr(idx), c_int(n), ptr(self._pairs),
                                          ptr(self._gathered), ptr(out), stream())
         _lib.check(rc, "vg_comm_argmax_merge")
@@ -173,6 +175,7 @@ class TpComm:
         """Greedy token per row from vocabulary-sharded fp32 logits ``[n, V_local]``."""
         from ..ops import kernels as K
         n, vl = logits.shape
+        assert 1 <= n <= ARGMAX_MAX_COLS, f"arg-max merge handles at most {ARGMAX_MAX_COLS} columns, got {n}"
         lg = logits if logits.dtype == torch.float32 else logits.float()
         K.argmax(lg, n, self._idx, self._val, idx_offset=self.rank * vl)
         if self.use_nccl:

@@ -54,6 +54,8 @@ class Lockstep:
         self.step_no = 0
         self.drill = int(os.environ.get("VELO_TP_AGREE_DRILL", "-1"))
         self.mirror_reqs = {}
+        # every rank cancels exactly the ids the head broadcast for the step, never from a live flag
+        sched.external_cancels = True
 
     # ---- head side
     def head_step(self, admits: List[Request], cancels: List[int], stop: bool = False):
@@ -61,16 +63,16 @@ class Lockstep:
         for r in admits:
             self.s.submit(r)            # queues the request and assigns its id; nothing runs before the step
         msg = [{"admits": [wire_request(r) for r in admits], "cancels": list(cancels), "stop": stop}]
-        dist.broadcast_object_list(msg, src=0, group=self.group)
+        self._broadcast(msg)
         if stop:
             return
-        self.s.step()
-        self.agree()
+        self.s.apply_cancels(set(cancels))
+        self.agree(self._guarded_step())
 
     # ---- mirror side
     def mirror_step(self) -> bool:
         msg = [None]
-        dist.broadcast_object_list(msg, src=0, group=self.group)
+        self._broadcast(msg)
         ev = msg[0]
         if ev["stop"]:
             return False
@@ -79,26 +81,44 @@ class Lockstep:
             r = unwire_request(d, sink)
             self.s.submit(r)
             self.mirror_reqs[d["id"]] = (r, sink)
-        for rid in ev["cancels"]:
-            if rid in self.mirror_reqs:
-                self.mirror_reqs[rid][0].cancelled = True
-        self.s.step()
-        self.agree()
+        self.s.apply_cancels(set(ev["cancels"]))
+        self.agree(self._guarded_step())
         return True
 
     # ---- both
-    def agree(self):
+    def _broadcast(self, msg: list):
+        try:
+            dist.broadcast_object_list(msg, src=0, group=self.group)
+        except Exception as e:  # noqa: BLE001 - a peer that closed its connection or timed out ends the run
+            raise DivergenceError(f"step {self.step_no}: the step's events could not be exchanged ({e})") from e
+
+    def _guarded_step(self) -> Optional[str]:
+        """One scheduler step; a kernel or collective failure reported by the runner's health probe (a bounded
+        wait that ran out, a peer's flag that never came) is returned as text instead of raised, so this rank
+        still reaches ``agree`` and every rank leaves together."""
+        from ..ops.lib import KernelError
+        from .comm import CommError
+        try:
+            self.s.step()
+        except (KernelError, CommError) as e:
+            return f"rank {self.rank}: {e}"
+        return None
+
+    def agree(self, fault: Optional[str] = None):
         h = self.s.state_hash()
         if self.step_no == self.drill and self.rank == self.world - 1:
             h ^= 0xDEAD
-        mine = (self.step_no, len(self.s.lanes), h)
+        mine = (self.step_no, len(self.s.lanes), h, fault)
         allv = [None] * self.world
         try:
             dist.all_gather_object(allv, mine, group=self.group)
         except Exception as e:  # noqa: BLE001 - a silent or dead peer ends the run
             raise DivergenceError(f"step {self.step_no}: a rank did not answer ({e})") from e
         self.step_no += 1
-        if any(v != allv[0] for v in allv):
+        faults = [v[3] for v in allv if v[3]]
+        if faults:
+            raise DivergenceError(f"step {mine[0]}: device failure reported: {'; '.join(faults)}")
+        if any(v[:3] != allv[0][:3] for v in allv):
             raise DivergenceError(f"ranks diverged at step {mine[0]}: {allv}")
 
 

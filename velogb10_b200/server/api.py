@@ -43,7 +43,6 @@ class EngineLoop:
     def __init__(self, scheduler: Scheduler, lockstep=None):
         self.s = scheduler
         self.lockstep = lockstep          # parallel.lockstep.Lockstep on the head rank of a multi-process TP group
-        self._sent_cancels = set()
         self.inbox: "queue.Queue[Optional[Request]]" = queue.Queue()
         self.thread = threading.Thread(target=self._run, daemon=True, name="engine-loop")
         self.error: Optional[BaseException] = None
@@ -86,8 +85,9 @@ class EngineLoop:
                     item = self.inbox.get_nowait()
             except queue.Empty:
                 pass
-            cancels = [l.req.id for l in self.s.lanes if l.req.cancelled and l.req.id not in self._sent_cancels]
-            self._sent_cancels.update(cancels)
+            # one snapshot of the owners' flags per step, queued requests included; the scheduler on every rank
+            # acts on exactly this list (a flag that flips after this line belongs to the next step)
+            cancels = self.s.pending_cancels()
             if admits or not self.s.idle():
                 self.lockstep.head_step(admits, cancels)
         self.lockstep.head_step([], [], stop=True)
@@ -374,6 +374,8 @@ def create_app(state: AppState):
                                 reason = map_finish(r)
                     for k, seg in splitter.feed(tok.decode(out_ids), final=True):
                         yield chunk({"reasoning_content": seg} if k == "reasoning" else {"content": seg})
+                    if splitter.stopped:          # also when the match only completed in the final flush
+                        reason = "stop"
                     parsed = T.parse(splitter.content, tools) if T.has_tool_call(splitter.content) else None
                     if parsed and parsed.tool_calls:
                         yield chunk({"tool_calls": [c.to_openai(i) for i, c in enumerate(parsed.tool_calls)]})

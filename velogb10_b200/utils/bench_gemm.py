@@ -26,8 +26,6 @@ def main():
     ap.add_argument("--n", type=int, default=1)
     ap.add_argument("--fmt", default="nvfp4")
     ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--variants", default="0")
-    ap.add_argument("--dbg", default="0")
     ap.add_argument("--splitk", default="auto")
     ap.add_argument("--only", default="")
     ap.add_argument("--fp4", action="store_true", help="time the block-scaled FP4 path (nvfp4 weights, N <= 16)")
@@ -81,25 +79,21 @@ def main():
             continue
         out = torch.empty(max(16, args.n), m, dtype=torch.bfloat16, device="cuda")
         sks = [tws[0].kernel.splitk] if args.splitk == "auto" else [int(s) for s in args.splitk.split(",")]
-        for variant in [int(v) for v in args.variants.split(",")]:
-            for dbg in [int(d) for d in args.dbg.split(",")]:
-                for sk in sks:
-                    L.vg_gemm_tc_set_variant(variant, dbg)
-                    for qc in tws:
-                        qc.kernel.splitk = sk
-                    for i in range(3):
-                        G.linear(tws[i % copies], x, args.n, out=out)
-                    torch.cuda.synchronize()
-                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    e0.record()
-                    for i in range(args.iters):
-                        G.linear(tws[i % copies], x, args.n, out=out)
-                    e1.record()
-                    torch.cuda.synchronize()
-                    us = e0.elapsed_time(e1) * 1e3 / args.iters
-                    print(json.dumps({"shape": name, "m": m, "k": k, "n": args.n, "variant": variant, "dbg": dbg,
-                                      "splitk": sk, "us": round(us, 2), "GBs": round(bytes_w / us / 1e3, 1)}))
-        L.vg_gemm_tc_set_variant(0, 0)
+        for sk in sks:
+            for qc in tws:
+                qc.kernel.splitk = sk
+            for i in range(3):
+                G.linear(tws[i % copies], x, args.n, out=out)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(args.iters):
+                G.linear(tws[i % copies], x, args.n, out=out)
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / args.iters
+            print(json.dumps({"shape": name, "m": m, "k": k, "n": args.n, "splitk": sk, "us": round(us, 2),
+                              "GBs": round(bytes_w / us / 1e3, 1)}))
         vlib.check_err_word()
 
 
