@@ -124,7 +124,15 @@ int vg_gdn_step(const float* qkv, const void* proj, int ldp, int off_z, int off_
 
 int vg_argmax(const float* logits, int N, int V, int ld, int* out, float* out_val, int idx_offset, cudaStream_t stream);
 int vg_penalty(float* logits, int N, int V, int ld, const int* toks, const int* counts, const int* n_toks, int max_toks,
-               const float* rep, const float* pres, const float* freq, cudaStream_t stream);
+               const float* rep, const float* pres, const float* freq, int idx_offset, cudaStream_t stream);
+int vg_topk_chunks(int V);
+int vg_topk_local(const float* logits, int N, int V, int ld, const float* temp, const int* top_k, int idx_offset,
+                  void* cand_chunks, void* out_cand, cudaStream_t stream);
+int vg_nucleus_finish(const void* lists, int n_lists, int row_stride_pairs, int N, const float* temp, const int* top_k,
+                      const float* top_p, const float* u, int* out_tok, int* ids, float* probs, int* n_keep,
+                      cudaStream_t stream);
+int vg_spec_verify(const int* ids, const float* probs, const int* n_keep, const int* drafts, const float* u_acc,
+                   const float* u_ver, const int* col0, const int* nd, int n_lanes, int* result, cudaStream_t stream);
 int vg_nucleus(const float* logits, int N, int V, int ld, const float* temp, const int* top_k, const float* top_p,
                const unsigned* seed, int* out_tok, int* ids, float* probs, int* n_keep, cudaStream_t stream);
 int vg_nll(const float* logits, int N, int V, int ld, const int* target, float* out, cudaStream_t stream);

@@ -167,9 +167,8 @@ def argmax(logits: torch.Tensor, n: int, out: torch.Tensor, out_val: Optional[to
 
 
 def penalty(logits, n, toks, counts, n_toks, rep, pres, freq):
-    rc = _lib.lib().vg_penalty(ptr(logits), c_int(n), c_int(logits.shape[1]), c_int(logits.stride(0)), ptr(toks),
-                               ptr(counts), ptr(n_toks), c_int(toks.shape[1]), ptr(rep), ptr(pres), ptr(freq), stream())
-    _lib.check(rc, "vg_penalty")
+    """In-place repetition / presence / frequency penalties: row r's tokens ``toks[r, :n_toks[r]]`` with ``counts``."""
+    penalty_sharded(logits, n, toks, counts, n_toks, rep, pres, freq, 0)
 
 
 def nucleus(logits, n, temp, top_k, top_p, seed, out_tok=None, ids=None, probs=None, n_keep=None):
@@ -183,3 +182,35 @@ def nll(logits, n, target, out):
     rc = _lib.lib().vg_nll(ptr(logits), c_int(n), c_int(logits.shape[1]), c_int(logits.stride(0)), ptr(target),
                            ptr(out), stream())
     _lib.check(rc, "vg_nll")
+
+
+def penalty_sharded(logits, n, toks, counts, n_toks, rep, pres, freq, idx_offset: int = 0):
+    """``penalty`` over a vocabulary shard: token ids are global, ``idx_offset`` is the shard's first id."""
+    rc = _lib.lib().vg_penalty(ptr(logits), c_int(n), c_int(logits.shape[1]), c_int(logits.stride(0)), ptr(toks),
+                               ptr(counts), ptr(n_toks), c_int(toks.shape[1]), ptr(rep), ptr(pres), ptr(freq),
+                               c_int(idx_offset), stream())
+    _lib.check(rc, "vg_penalty")
+
+
+def topk_chunks(v: int) -> int:
+    return int(_lib.lib().vg_topk_chunks(c_int(v)))
+
+
+def topk_local(logits, n, temp, top_k, idx_offset, cand_chunks, out_cand):
+    """Per-row top-K (K = clamp(top_k, 1, 64); 1 for greedy rows) as (value, global index) pairs in selection order."""
+    rc = _lib.lib().vg_topk_local(ptr(logits), c_int(n), c_int(logits.shape[1]), c_int(logits.stride(0)), ptr(temp),
+                                  ptr(top_k), c_int(idx_offset), ptr(cand_chunks), ptr(out_cand), stream())
+    _lib.check(rc, "vg_topk_local", 2)
+
+
+def nucleus_finish(lists, n_lists, row_stride_pairs, n, temp, top_k, top_p, u, out_tok=None, ids=None, probs=None,
+                   n_keep=None):
+    rc = _lib.lib().vg_nucleus_finish(ptr(lists), c_int(n_lists), c_int(row_stride_pairs), c_int(n), ptr(temp), ptr(top_k),
+                                      ptr(top_p), ptr(u), ptr(out_tok), ptr(ids), ptr(probs), ptr(n_keep), stream())
+    _lib.check(rc, "vg_nucleus_finish")
+
+
+def spec_verify(ids, probs, n_keep, drafts, u_acc, u_ver, col0, nd, n_lanes, result):
+    rc = _lib.lib().vg_spec_verify(ptr(ids), ptr(probs), ptr(n_keep), ptr(drafts), ptr(u_acc), ptr(u_ver), ptr(col0),
+                                   ptr(nd), c_int(n_lanes), ptr(result), stream())
+    _lib.check(rc, "vg_spec_verify")
