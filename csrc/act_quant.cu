@@ -120,7 +120,8 @@ __global__ void __launch_bounds__(512) act_quant_kernel(const void* __restrict__
 // residual += delta; y = rmsnorm(residual) * (1 + w); emit y as FP4 terms (and optionally as f16).
 // AR: delta is not a tensor but the sum over ranks of the fp32 partial rows in this rank's receive slots
 // (pushed there by every rank's row-parallel GEMM); the kernel waits for the tile flags and sums in rank order.
-template <bool AR>
+// AR = 2: delta is the in-switch sum (multimem.ld_reduce) of the rows every rank's GEMM left in its own multimem slot.
+template <int AR>
 __global__ void __launch_bounds__(512) add_rmsnorm_fp4_kernel(__nv_bfloat16* res, const __nv_bfloat16* delta, const float* w,
                                                                 int h, float eps, int plus_one, int ld_res, int ld_delta,
                                                                 int Kpad, uint8_t* __restrict__ bq, int ldb,
@@ -149,6 +150,8 @@ __global__ void __launch_bounds__(512) add_rmsnorm_fp4_kernel(__nv_bfloat16* res
     ar_e = *c.epoch + 1;
     ar_set = ar_e & 1;
   }
+  const uint32_t* mm_flags = AR == 2 ? reinterpret_cast<const uint32_t*>(c.data[c.rank] + c.mmflags_off) + (size_t)ar_set * MAX_CTAS * MAX_RANKS
+                                       : nullptr;
   float r[MAXB][16];
   float ss = 0.f;
 #pragma unroll
@@ -162,7 +165,36 @@ __global__ void __launch_bounds__(512) add_rmsnorm_fp4_kernel(__nv_bfloat16* res
       const __nv_bfloat16* x1 = reinterpret_cast<const __nv_bfloat16*>(&a1);
       float dv[16];
       bool have_d = dp != nullptr;
-      if (AR) {
+      if (AR == 2) {
+        // the 128-row GEMM tile these 16 elements belong to: wait (bounded) until every rank's word for the tile
+        // carries this collective's epoch, then read the in-switch sum of the W copies
+        const uint32_t* f = mm_flags + (size_t)(b >> 3) * MAX_RANKS;
+        bool ok = false;
+        uint64_t t_start = 0;
+        for (int tries = 0;; ++tries) {
+          ok = true;
+          for (int q = 0; q < c.world; ++q) ok = ok && (int32_t)(ld_acquire_sys(f + q) - ar_e) >= 0;
+          if (ok) break;
+          if (tries == 64) t_start = global_ns();
+          if (tries > 64 && (tries & 63) == 0 && global_ns() - t_start > c.timeout_ns) {
+            atomicCAS(c.status, 0, VG_ERR_PEER_WAIT);
+            break;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) dv[i] = 0.f;
+        if (ok) {
+          const unsigned char* src = c.mc + c.mm_off + (size_t)ar_set * c.mm_slot_bytes + ((size_t)n * h + b * 16) * 4;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float4 v = multimem_ld_reduce_f32x4(src + 16 * i);
+            dv[4 * i] = v.x; dv[4 * i + 1] = v.y; dv[4 * i + 2] = v.z; dv[4 * i + 3] = v.w;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) dv[i] = __bfloat162float(__float2bfloat16_rn(dv[i]));
+        have_d = true;
+      } else if (AR == 1) {
         // Every rank stored its (value, epoch) pairs for these 16 elements into this rank's receive slots: poll
         // them (local memory) and take them once all 16 carry this collective's epoch; sum in rank order.
         // Bounded by the context's timeout.
@@ -303,20 +335,27 @@ extern "C" int vg_add_rmsnorm_fp4(void* res, const void* delta, const float* w, 
   if (N < 1 || N > 16 || (ldb % 128) != 0 || Kpad < h || (h % 16) != 0 || (ld_res % 8) != 0 || (ld_delta % 8) != 0 ||
       (Kpad >> 4) > MAX_THREADS * MAXB)
     return -2;
-  return (int)launch_pdl(add_rmsnorm_fp4_kernel<false>, dim3(N), dim3(threads_for(Kpad >> 4)), 0, st,
+  return (int)launch_pdl(add_rmsnorm_fp4_kernel<0>, dim3(N), dim3(threads_for(Kpad >> 4)), 0, st,
                          static_cast<__nv_bfloat16*>(res), static_cast<const __nv_bfloat16*>(delta), w, h, eps, plus_one,
                          ld_res, ld_delta, Kpad, static_cast<uint8_t*>(bq), ldb, static_cast<uint8_t*>(sfb), g0,
                          static_cast<__half*>(out16), VgCommCtx{});
 }
 
 extern "C" int vg_add_rmsnorm_fp4_ar(void* res, const float* w, int N, int h, float eps, int plus_one, int ld_res, void* bq,
-                                     int ldb, void* sfb, float* g0, void* out16, const VgCommCtx* ctx, cudaStream_t st) {
+                                     int ldb, void* sfb, float* g0, void* out16, const VgCommCtx* ctx, int mode,
+                                     cudaStream_t st) {
   const int Kpad = ldb * 2;
   if (!ctx || ctx->world < 2 || N < 1 || N > 16 || (ldb % 128) != 0 || Kpad < h || (h % 16) != 0 || (ld_res % 8) != 0 ||
       (Kpad >> 4) > MAX_THREADS * MAXB)
     return -2;
+  if (mode == 2) {
+    if (!ctx->mc || (unsigned long long)N * h * 4ull > ctx->mm_slot_bytes) return -5;
+    return (int)launch_pdl(add_rmsnorm_fp4_kernel<2>, dim3(N), dim3(threads_for(Kpad >> 4)), 0, st,
+                           static_cast<__nv_bfloat16*>(res), (const __nv_bfloat16*)nullptr, w, h, eps, plus_one, ld_res, 0, Kpad,
+                           static_cast<uint8_t*>(bq), ldb, static_cast<uint8_t*>(sfb), g0, static_cast<__half*>(out16), *ctx);
+  }
   if ((unsigned long long)N * h * 8ull > ctx->slot_bytes) return -5;
-  return (int)launch_pdl(add_rmsnorm_fp4_kernel<true>, dim3(N), dim3(threads_for(Kpad >> 4)), 0, st,
+  return (int)launch_pdl(add_rmsnorm_fp4_kernel<1>, dim3(N), dim3(threads_for(Kpad >> 4)), 0, st,
                          static_cast<__nv_bfloat16*>(res), (const __nv_bfloat16*)nullptr, w, h, eps, plus_one, ld_res, 0, Kpad,
                          static_cast<uint8_t*>(bq), ldb, static_cast<uint8_t*>(sfb), g0, static_cast<__half*>(out16), *ctx);
 }

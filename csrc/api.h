@@ -26,6 +26,13 @@ typedef struct VgCommCtx {
   unsigned long long agbuf_off, agbuf_bytes;  // gather landing zone of the fused all-gather + GEMM (f16 rows)
   unsigned long long agflags_off;  // [2 sets][VG_AG_MAX_TILES] epoch per 128-row tile of the landing zone
   unsigned long long rsflags_off;  // [2 sets][8 ranks][VG_RS_MAX_TILES] per-tile epochs of the fused GEMM + reduce-scatter
+  // NVLink-switch multicast (NVLS) view of the same arena: one address that reaches every rank's copy. Stores to it
+  // (multimem.st) land on all ranks; multimem.ld_reduce returns the sum of all ranks' copies, added inside the
+  // switch. Null when the arena has no multicast binding (then only the peer-pointer paths run).
+  unsigned char* mc;
+  unsigned long long mm_off, mm_slot_bytes;   // [2 sets][mm_slot_bytes] fp32 partial rows, written locally by their owner
+  unsigned long long mmflags_off;             // [2 sets][64 tiles][8 ranks] word = epoch of that rank's rows of the tile
+  unsigned int* mm_ctr;                       // (spare control word)
 } VgCommCtx;
 #define VG_RS_MAX_TILES 4096
 #define VG_AG_MAX_TILES 256
@@ -70,8 +77,11 @@ int vg_gemm_fp4(const void* wt, const float* row_scale, const void* bq, int ldb,
 // Residual add + RMSNorm + FP4 quantisation whose `delta` is the tensor-parallel sum of the partial rows a
 // preceding vg_gemm_fp4(..., ar_push_only = 1) pushed into every rank's receive slots: waits for each
 // rank's tile flags (bounded), adds the partials in rank order, then proceeds as vg_add_rmsnorm_fp4.
+// mode 1: (value, epoch) pairs in the per-rank receive slots (ar_push_only = 1). mode 2: in-switch reduction: the
+// partial rows were written by vg_gemm_fp4(..., ar_push_only = 2) into each rank's own multimem slot; the kernel waits
+// for every rank's epoch word and reads each element once with multimem.ld_reduce (needs ctx->mc).
 int vg_add_rmsnorm_fp4_ar(void* res, const float* w, int N, int h, float eps, int plus_one, int ld_res, void* bq, int ldb,
-                          void* sfb, float* g0, void* out16, const VgCommCtx* ctx, cudaStream_t stream);
+                          void* sfb, float* g0, void* out16, const VgCommCtx* ctx, int mode, cudaStream_t stream);
 int vg_gemm_fp4_grouped(const void* wt, const float* row_scale, const void* bq, int ldb, int b_rows, const void* sfb,
                         const float* g0, void* out, int out_f32, int M, int K, int ldo, int n_items, const int* g_exp,
                         const int* g_off, int x_div, int* err, cudaStream_t stream);
@@ -96,6 +106,12 @@ int vg_embed_gather(const void* table, const void* scales, const float* row_scal
 int vg_attn_decode(const void* q, const void* kc, const void* vc, const int* lens, const int* slots, const int* base,
                    const int* path, int path_ld, float* part, int N, int nh, int nkv, int hd, int max_seq, int ns_grid,
                    int direct, const void* gate, int ld_gate, void* out, cudaStream_t stream);
+// Tensor-core form of vg_attn_decode for head_dim 256, bf16 cache, no row indirection: one pass over the keys per KV
+// head (all of its query heads, at most 16, share the fetched tiles). `block_table` (optional) makes the cache a pool
+// of 128-key pages.
+int vg_attn_decode_tc(const void* q, const void* kc, const void* vc, long long cache_rows, const int* lens, const int* slots,
+                      const int* block_table, int bt_ld, float* part, int N, int nh, int nkv, int hd, int max_seq, int ns_grid,
+                      const void* gate, int ld_gate, void* out, int* err, cudaStream_t stream);
 int vg_attn_transpose_v(const void* vc, void* vT, int slot, int nkv, int hd, int max_seq, int len, int vt_cap,
                         cudaStream_t stream);
 int vg_attn_prefill_tc(const void* q, int q_cap, const void* kc, const void* vT, int vt_cap, int slot, int nkv, int nh,
@@ -117,6 +133,14 @@ int vg_gdn_prefill(const float* qkv, const void* proj, int ldp, int off_z, int o
                    const float* A_log, const float* dt_bias, const float* norm_w, int t0, int tn, const int* in_slot,
                    const int* out_slot, void* out_f16, int nk, int nv, int kd, int vd, float eps, float* o_scratch,
                    int split, cudaStream_t stream);
+// Chunked (tensor-core) form of vg_gdn_prefill: 64-token chunks, tf32 MMAs, fp32 state. `work` is 1024-byte aligned
+// scratch of vg_gdn_chunk_work_bytes(tn, nv) bytes, `o_raw` fp32 scratch of (t0 + tn) * nv * vd elements. The state is
+// read from slot in_slot[t0] and written to out_slot[t0 + tn - 1] when that is >= 0 (no other checkpoints).
+long long vg_gdn_chunk_work_bytes(int tn, int nv);
+int vg_gdn_chunk_prefill(const float* qkv, const void* proj, int ldp, int off_z, int off_b, int off_a, float* S,
+                         const float* A_log, const float* dt_bias, const float* norm_w, int t0, int tn, const int* in_slot,
+                         const int* out_slot, void* out_f16, int nk, int nv, int kd, int vd, float eps, void* work,
+                         float* o_raw, int* err, cudaStream_t stream);
 int vg_gdn_step(const float* qkv, const void* proj, int ldp, int off_z, int off_b, int off_a, float* S, const float* A_log,
                 const float* dt_bias, const float* norm_w, const int* chain_start, const int* chain_len, int n_chains,
                 const int* in_slot, const int* parent, const int* out_slot, void* out_f16, int nk, int nv, int kd, int vd,

@@ -285,6 +285,19 @@ int attn_decode_impl(const void* q, const void* kc, const void* vc, const void* 
 }
 }  // namespace
 
+// Merge of split partials (shared with the tensor-core split kernel in attention_decode_tc.cu).
+int vg_attn_merge_launch(const float* part, const int* lens, int N, int nh, int hd, int ns_grid, const void* gate, int ld_gate,
+                         void* out, cudaStream_t st) {
+  dim3 grid(N, nh);
+  switch (hd) {
+    case 64: launch_pdl(attn_merge_kernel<64>, dim3(grid), dim3(64), 0, st, part, lens, nh, ns_grid, static_cast<const __nv_bfloat16*>(gate), ld_gate, static_cast<__half*>(out)); break;
+    case 128: launch_pdl(attn_merge_kernel<128>, dim3(grid), dim3(128), 0, st, part, lens, nh, ns_grid, static_cast<const __nv_bfloat16*>(gate), ld_gate, static_cast<__half*>(out)); break;
+    case 256: launch_pdl(attn_merge_kernel<256>, dim3(grid), dim3(256), 0, st, part, lens, nh, ns_grid, static_cast<const __nv_bfloat16*>(gate), ld_gate, static_cast<__half*>(out)); break;
+    default: return -3;
+  }
+  return (int)cudaGetLastError();
+}
+
 // q [N, nh, hd] bf16; kc/vc [slots, nkv, max_seq, hd] bf16; lens[N] keys per column; slots[N];
 // base[N]/path[N, path_ld] optional row indirection; part: scratch of vg_attn_scratch_floats() floats;
 // gate: fused qkv buffer (bf16, row stride ld_gate) or null; out [N, nh*hd] f16.

@@ -198,6 +198,18 @@ VG_DEVINL bool wait_flag(const uint32_t* p, uint32_t e, uint64_t budget_ns) {
   }
 }
 
+// NVLS (NVLink-switch multicast) accesses on a multicast address: the store reaches every rank's copy of the word;
+// the load returns the sum over all ranks' copies of four consecutive fp32 values, added inside the switch.
+VG_DEVINL void multimem_st_u32(void* mc_addr, uint32_t v) {
+  asm volatile("multimem.st.relaxed.sys.global.u32 [%0], %1;" ::"l"(mc_addr), "r"(v) : "memory");
+}
+VG_DEVINL float4 multimem_ld_reduce_f32x4(const void* mc_addr) {
+  float4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "l"(mc_addr) : "memory");
+  return r;
+}
+
 VG_DEVINL size_t flag_index(int set, int src, int cta) {
   return ((size_t)(set * MAX_RANKS + src) * MAX_CTAS + cta) * FLAG_STRIDE;
 }

@@ -686,4 +686,12 @@ extern "C" int vg_gdn_prefill(const float* qkv, const void* proj, int ldp, int o
   return (int)cudaGetLastError();
 }
 
+// Gated output norm over fp32 raw outputs [t][nv][vd] (shared with the chunked prefill in gdn_chunk.cu).
+int vg_gdn_out_norm_launch(const float* o_raw, const void* proj, int ldp, int off_z, const float* norm_w, int t0, int tn,
+                           void* out_f16, int nv, int vd, float eps, cudaStream_t st) {
+  if (vd != 128) return -3;
+  return (int)launch_pdl(gdn_out_norm_kernel<128>, dim3((unsigned)(((size_t)tn * nv + 7) / 8)), dim3(256), 0, st, o_raw,
+                         static_cast<const __nv_bfloat16*>(proj), ldp, off_z, norm_w, t0, tn, static_cast<__half*>(out_f16), nv, eps);
+}
+
 VG_TRACE_SETTER(vg_trace_set_gdn)

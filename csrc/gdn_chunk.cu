@@ -1,0 +1,544 @@
+// GatedDeltaNet prefill in chunked (WY / UT-transform) form on the tensor cores (tcgen05.mma kind::tf32, fp32
+// accumulators in TMEM). The recurrence of one value head with state S [kd, vd],
+//     S_t = g_t S_{t-1} + k_t d_t^T,   d_t = beta_t (v_t - (g_t S_{t-1})^T k_t),   o_t = S_t^T q_t,
+// is evaluated 64 tokens at a time. With G_i = sum_{j<=i} log g_j inside a chunk, A_ij = beta_i e^{G_i-G_j} (k_i.k_j)
+// for j < i and T = (I + A)^-1 (unit lower triangular):
+//     W = T diag(beta e^G) K          U = T diag(beta) V          D = U - W S_0            (the chunk's deltas)
+//     O = diag(e^G) Q S_0 + (M o Q K^T) D,   M_ij = e^{G_i-G_j} [j <= i]
+//     S_C = e^{G_C} S_0 + (diag(e^{G_C-G}) K)^T D
+// Everything that does not involve S_0 is independent per chunk and runs first, for all chunks at once
+// (gdn_chunk_prep_kernel: grid = value heads x pairs of chunks); the part that carries the state runs as one CTA per
+// value head walking its chunks (gdn_chunk_scan_kernel), four small GEMMs per chunk. The reference evaluates the
+// same recurrence token by token on CUDA cores (reference: kernels/gpu_batch.cu:580 delta_step_prefill, :439-444);
+// the chunked form exists only for prefill. Decode and verify keep the exact step kernel, so the batch-invariance
+// contract (verify == sequential decode, bit for bit) is untouched; a prefill through this path agrees with the
+// step kernel to tf32 rounding (~1e-3 relative), not bit for bit.
+//
+// All operand tiles handed from the first kernel to the second are stored in global memory as ready-made images of
+// the shared-memory layout the MMA reads (K-major, 128-byte swizzle, 32-bit elements), so the second kernel's loads
+// are plain bulk copies. Every wait is bounded.
+#include "common.cuh"
+#include "api.h"
+
+namespace {
+using namespace vg;
+
+constexpr int CH = 64;                    // chunk length
+constexpr int KD = 128, VD = 128;
+constexpr uint32_t W_IMG = CH * KD * 4;   // 32 KB   [64 rows i][128 k]
+constexpr uint32_t Q_IMG = CH * KD * 4;   // 32 KB   [64 rows i][128 k]
+constexpr uint32_t P_IMG = CH * CH * 4;   // 16 KB   [64 rows i][64 j]
+constexpr uint32_t KT_IMG = KD * CH * 4;  // 32 KB   [128 rows d][64 j]
+constexpr uint32_t UT_BYTES = VD * CH * 4;  // 32 KB plain [128 v][64 i]
+constexpr uint32_t CHUNK_BYTES = W_IMG + Q_IMG + P_IMG + KT_IMG + UT_BYTES;   // 144 KB per (head, chunk)
+
+// Byte offset of element (r, k) in the image of a K-major tile of `rows` rows of 32-bit elements with the 128-byte
+// swizzle: 32 elements (128 bytes) of a row are contiguous, the 16-byte pieces of a row are XOR-ed with r & 7, and
+// successive groups of 32 k-values are whole [rows x 128 B] panels.
+__host__ __device__ __forceinline__ uint32_t img_off(int rows, int r, int k) {
+  const int panel = k >> 5, kk = k & 31;
+  return (uint32_t)(panel * rows * 128 + r * 128 + ((((kk >> 2) ^ (r & 7))) << 4) + (kk & 3) * 4);
+}
+__device__ __forceinline__ float to_tf32(float x) {
+  uint32_t u;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+  return __uint_as_float(u);
+}
+// kind::tf32 instruction descriptor: fp32 accumulate, both operands tf32 and K-major
+__device__ __forceinline__ constexpr uint32_t idesc_tf32(int m, int n) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[128 x n] (+)= A[128 x kdim] * B[n x kdim]^T over images at a_addr (128 rows) and b_addr (n rows); 8 k per MMA.
+__device__ __forceinline__ void mma_tile(uint32_t tmem_d, uint32_t a_addr, uint32_t b_addr, int n, int kdim, bool accumulate) {
+  const uint32_t idesc = idesc_tf32(128, n);
+  for (int ks = 0; ks < kdim / 8; ++ks) {
+    const uint32_t a = a_addr + (uint32_t)(ks >> 2) * (128 * 128) + (uint32_t)(ks & 3) * 32;
+    const uint32_t b = b_addr + (uint32_t)(ks >> 2) * ((uint32_t)n * 128) + (uint32_t)(ks & 3) * 32;
+    umma_tf32(tmem_d, umma_desc_sw128(a), umma_desc_sw128(b), idesc, (accumulate || ks > 0) ? 1u : 0u);
+  }
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fail(int* err, int code) {
+  if (err) atomicCAS(err, 0, code);
+}
+
+// ------------------------------------------------------------------------------------------------ chunk-local part
+// One CTA = one value head x 128 tokens (two chunks side by side; the cross-chunk blocks of the 128 x 128 products
+// are computed and ignored). 128 threads; thread i owns token i in the row-wise steps and TMEM lane i.
+constexpr int PREP_SMEM = 3 * 65536 + 32768 + 2048 + 1024;
+
+__global__ void __launch_bounds__(128, 1)
+gdn_chunk_prep_kernel(const float* __restrict__ qkv, const __nv_bfloat16* __restrict__ proj, int ldp, int off_b, int off_a,
+                      const float* __restrict__ A_log, const float* __restrict__ dt_bias, int t0, int tn, int nk, int nv,
+                      uint8_t* __restrict__ work, float* __restrict__ gc_out, int n_chunks, int* err) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* R0 = smem;                      // K image [128 i][128 d]  -> later T image [128 i][128 j]
+  uint8_t* R1 = smem + 65536;              // Q image [128 i][128 d]  -> later scaled K^T image [128 d][128 j]
+  uint8_t* R2 = smem + 2 * 65536;          // scaled V^T image [128 v][128 j]
+  float* R3 = reinterpret_cast<float*>(smem + 3 * 65536);     // V staging [64][128] (swizzled), then A^T [2][64 j][64 i]
+  float* Gs = reinterpret_cast<float*>(smem + 3 * 65536 + 32768);   // [128] cumulative log decay inside the chunk
+  float* betas = Gs + 128;                                          // [128]
+  float* lgs = betas + 128;                                         // [128] log g
+  uint64_t* bar = reinterpret_cast<uint64_t*>(lgs + 128);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 2);
+
+  // (no early launch_dependents here: the dependent scan kernel's CTAs need almost a whole SM each and would only
+  // sit on SMs this grid still has tiles for)
+  pdl_wait();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int pair = blockIdx.x, vh = blockIdx.y;
+  const int kh = vh * nk / nv;
+  const int key_dim = nk * KD, conv_dim = 2 * key_dim + nv * VD;
+  const int tok0 = pair * 128;             // first token of this tile, relative to t0
+
+  if (tid == 0) {
+    mbar_init(&bar[0], 1);
+    mbar_init(&bar[1], 1);
+    fence_mbar_init();
+  }
+  __syncwarp();
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  // ---- per-token gates
+  {
+    const int t = tok0 + tid;
+    float beta = 0.f, lg = 0.f;
+    if (t < tn) {
+      const size_t row = (size_t)(t0 + t) * ldp;
+      const float bb = __bfloat162float(proj[row + off_b + vh]);
+      const float aa = __bfloat162float(proj[row + off_a + vh]) + dt_bias[vh];
+      beta = 1.0f / (1.0f + expf(-bb));
+      const float sp = aa > 20.f ? aa : log1pf(expf(aa));
+      lg = -expf(A_log[vh]) * sp;
+    }
+    betas[tid] = beta;
+    lgs[tid] = lg;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  {
+    const int c0 = tid & ~63;
+    float g = 0.f;
+    for (int j = c0; j <= tid; ++j) g += lgs[j];
+    Gs[tid] = g;
+  }
+  // ---- q, k rows: l2-normalise (q also / sqrt(kd)), tf32, into the K-major images. A warp reads one row per step.
+  for (int i = warp; i < 128; i += 4) {
+    const int t = tok0 + i;
+    float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f), k4 = q4;
+    if (t < tn) {
+      const float* row = qkv + (size_t)(t0 + t) * conv_dim;
+      q4 = *reinterpret_cast<const float4*>(row + kh * KD + lane * 4);
+      k4 = *reinterpret_cast<const float4*>(row + key_dim + kh * KD + lane * 4);
+    }
+    const float qn = warp_sum(q4.x * q4.x + q4.y * q4.y + q4.z * q4.z + q4.w * q4.w);
+    const float kn = warp_sum(k4.x * k4.x + k4.y * k4.y + k4.z * k4.z + k4.w * k4.w);
+    const float qs = rsqrtf(qn + 1e-6f) * rsqrtf((float)KD), ks = rsqrtf(kn + 1e-6f);
+    const uint32_t off = img_off(128, i, lane * 4);
+    *reinterpret_cast<float4*>(R1 + off) = make_float4(to_tf32(q4.x * qs), to_tf32(q4.y * qs), to_tf32(q4.z * qs), to_tf32(q4.w * qs));
+    *reinterpret_cast<float4*>(R0 + off) = make_float4(to_tf32(k4.x * ks), to_tf32(k4.y * ks), to_tf32(k4.z * ks), to_tf32(k4.w * ks));
+  }
+  // ---- (beta V)^T image: rows of V are staged 64 tokens at a time (element (i, v) at [i][v ^ (i & 31)], so both the
+  // row-wise writes and the column-wise reads are free of bank conflicts) and re-read transposed
+  for (int half = 0; half < 2; ++half) {
+    __syncthreads();
+    for (int ii = warp; ii < 64; ii += 4) {
+      const int i = half * 64 + ii, t = tok0 + i;
+      float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (t < tn) v4 = *reinterpret_cast<const float4*>(qkv + (size_t)(t0 + t) * conv_dim + 2 * key_dim + vh * VD + lane * 4);
+      const int x = ii & 31;
+      R3[ii * 128 + ((lane * 4 + 0) ^ x)] = v4.x;
+      R3[ii * 128 + ((lane * 4 + 1) ^ x)] = v4.y;
+      R3[ii * 128 + ((lane * 4 + 2) ^ x)] = v4.z;
+      R3[ii * 128 + ((lane * 4 + 3) ^ x)] = v4.w;
+    }
+    __syncthreads();
+    for (int v = warp; v < 128; v += 4) {
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        const int ii = s * 32 + lane, i = half * 64 + ii;
+        const float val = R3[ii * 128 + (v ^ (ii & 31))] * betas[i];
+        *reinterpret_cast<float*>(R2 + img_off(128, v, i)) = to_tf32(val);
+      }
+    }
+  }
+  fence_proxy_async_smem();
+  __syncthreads();
+  // ---- K K^T and Q K^T (both 128 x 128 x 128)
+  if (tid == 0) {
+    tc_fence_after();
+    mma_tile(tmem_base, smem_u32(R0), smem_u32(R0), 128, 128, false);
+    mma_tile(tmem_base + 128, smem_u32(R1), smem_u32(R0), 128, 128, false);
+    umma_commit(&bar[0]);
+  }
+  const bool ok0 = mbar_wait(&bar[0], 0);
+  if (!ok0) fail(err, VG_ERR_MMA_WAIT);
+  tc_fence_after();
+  const int chn = tid >> 6, ii = tid & 63;             // this thread's chunk and row inside it
+  const int chunk_id = pair * 2 + chn;
+  const bool chunk_live = chunk_id < n_chunks;
+  uint8_t* wbase = work + ((size_t)vh * n_chunks + (chunk_live ? chunk_id : 0)) * CHUNK_BYTES;
+  const float Gi = Gs[tid], bi = betas[tid];
+  const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+  // A^T[chn][j][i] = beta_i e^{G_i - G_j} (k_i . k_j) for j < i
+  for (int cb = 0; cb < 4; ++cb) {
+    uint32_t r[16];
+    tmem_ld16(lane_addr + (uint32_t)(chn * 64 + cb * 16), r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int x = 0; x < 16; ++x) {
+      const int j = cb * 16 + x;
+      const float a = j < ii ? bi * expf(Gi - Gs[chn * 64 + j]) * __uint_as_float(r[x]) : 0.f;
+      R3[(chn * 64 + j) * 64 + ii] = a;
+    }
+  }
+  // P[i][j] = e^{G_i - G_j} (q_i . k_j) for j <= i  -> global image (row ii, k j)
+  for (int cb = 0; cb < 4; ++cb) {
+    uint32_t r[16];
+    tmem_ld16(lane_addr + (uint32_t)(128 + chn * 64 + cb * 16), r);
+    tmem_ld_wait();
+    if (chunk_live) {
+#pragma unroll
+      for (int x4 = 0; x4 < 4; ++x4) {
+        float o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = cb * 16 + x4 * 4 + e;
+          o[e] = j <= ii ? to_tf32(expf(Gi - Gs[chn * 64 + j]) * __uint_as_float(r[x4 * 4 + e])) : 0.f;
+        }
+        *reinterpret_cast<float4*>(wbase + W_IMG + Q_IMG + img_off(CH, ii, cb * 16 + x4 * 4)) = make_float4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  }
+  // e^{G_i} Q -> global image (row ii, k d), read back from this thread's row of the Q image
+  if (chunk_live) {
+    const float eg = expf(Gi);
+    for (int d = 0; d < 128; d += 4) {
+      const float4 q4 = *reinterpret_cast<const float4*>(R1 + img_off(128, tid, d));
+      *reinterpret_cast<float4*>(wbase + W_IMG + img_off(CH, ii, d)) =
+          make_float4(to_tf32(q4.x * eg), to_tf32(q4.y * eg), to_tf32(q4.z * eg), to_tf32(q4.w * eg));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();                          // R1 (Q image) and both accumulators are free now
+  // ---- scaled K^T: shared image (row d, k j) = beta_j e^{G_j} k_j[d]; global image (row d, k jj) = e^{G_C - G_j} k_j[d]
+  for (int d = warp; d < 128; d += 4) {
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      const int j = s * 32 + lane;
+      const float kv = *reinterpret_cast<const float*>(R0 + img_off(128, j, d));
+      const float gj = Gs[j];
+      *reinterpret_cast<float*>(R1 + img_off(128, d, j)) = to_tf32(betas[j] * expf(gj) * kv);
+      const int cj = j >> 6;
+      if (pair * 2 + cj < n_chunks) {
+        uint8_t* wb = work + ((size_t)vh * n_chunks + pair * 2 + cj) * CHUNK_BYTES;
+        *reinterpret_cast<float*>(wb + W_IMG + Q_IMG + P_IMG + img_off(KD, d, j & 63)) = to_tf32(expf(Gs[cj * 64 + 63] - gj) * kv);
+      }
+    }
+  }
+  __syncthreads();                          // the K image (R0) has been read for the last time
+  for (int x = tid; x < 65536 / 16; x += 128) reinterpret_cast<float4*>(R0)[x] = make_float4(0.f, 0.f, 0.f, 0.f);
+  __syncthreads();
+  // ---- T = (I + A)^-1: thread c solves column c of its chunk by forward substitution, x_i = [i == c] - sum_{j<i} A_ij x_j
+  {
+    float x[64];
+    const float* At = R3 + chn * 64 * 64;
+#pragma unroll
+    for (int i = 0; i < 64; ++i) {
+      float acc = (i == ii) ? 1.f : 0.f;
+#pragma unroll
+      for (int j = 0; j < i; ++j) acc = fmaf(-At[j * 64 + i], x[j], acc);
+      x[i] = acc;
+    }
+#pragma unroll
+    for (int i = 0; i < 64; ++i)
+      *reinterpret_cast<float*>(R0 + img_off(128, chn * 64 + i, tid)) = to_tf32(x[i]);
+  }
+  fence_proxy_async_smem();
+  __syncthreads();
+  // ---- W = T (beta e^G K)  [i][d]   and   U^T = (beta V)^T T^T  [v][i]
+  if (tid == 0) {
+    tc_fence_after();
+    mma_tile(tmem_base, smem_u32(R0), smem_u32(R1), 128, 128, false);
+    mma_tile(tmem_base + 128, smem_u32(R2), smem_u32(R0), 128, 128, false);
+    umma_commit(&bar[1]);
+  }
+  const bool ok1 = mbar_wait(&bar[1], 0);
+  if (!ok1) fail(err, VG_ERR_MMA_WAIT);
+  tc_fence_after();
+  if (chunk_live) {
+    for (int cb = 0; cb < 8; ++cb) {         // W row ii of this thread's chunk: 128 d values
+      uint32_t r[16];
+      tmem_ld16(lane_addr + (uint32_t)(cb * 16), r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int x4 = 0; x4 < 4; ++x4)
+        *reinterpret_cast<float4*>(wbase + img_off(CH, ii, cb * 16 + x4 * 4)) =
+            make_float4(to_tf32(__uint_as_float(r[x4 * 4])), to_tf32(__uint_as_float(r[x4 * 4 + 1])),
+                        to_tf32(__uint_as_float(r[x4 * 4 + 2])), to_tf32(__uint_as_float(r[x4 * 4 + 3])));
+    }
+  }
+  for (int cj = 0; cj < 2; ++cj) {           // U^T row v = tid, 64 tokens of chunk cj (plain fp32 [v][64])
+    const bool live = pair * 2 + cj < n_chunks;
+    float* ut = reinterpret_cast<float*>(work + ((size_t)vh * n_chunks + (live ? pair * 2 + cj : 0)) * CHUNK_BYTES + W_IMG + Q_IMG + P_IMG + KT_IMG) + tid * CH;
+    for (int cb = 0; cb < 4; ++cb) {
+      uint32_t r[16];
+      tmem_ld16(lane_addr + (uint32_t)(128 + cj * 64 + cb * 16), r);
+      tmem_ld_wait();
+      if (live) {
+#pragma unroll
+        for (int x4 = 0; x4 < 4; ++x4)
+          *reinterpret_cast<float4*>(ut + cb * 16 + x4 * 4) =
+              make_float4(__uint_as_float(r[x4 * 4]), __uint_as_float(r[x4 * 4 + 1]), __uint_as_float(r[x4 * 4 + 2]), __uint_as_float(r[x4 * 4 + 3]));
+      }
+    }
+  }
+  if (ii == 63 && chunk_live) gc_out[(size_t)vh * n_chunks + chunk_id] = expf(Gi);
+  tc_fence_before();
+  __syncthreads();
+  pdl_trigger();
+  if (warp == 0) tmem_dealloc(tmem_base, 256);
+}
+
+// ------------------------------------------------------------------------------------------------ state-carrying part
+// One CTA per value head. Warps 0-3: thread v owns row v of S^T (TMEM lane v). Warp 4 lane 0: bulk copies + MMA issue.
+constexpr int SCAN_SMEM = 65536 + 32768 + W_IMG + Q_IMG + P_IMG + KT_IMG + 256 + 1024;
+
+__global__ void __launch_bounds__(160, 1)
+gdn_chunk_scan_kernel(const uint8_t* __restrict__ work, const float* __restrict__ gc, float* __restrict__ S,
+                      const int* __restrict__ in_slot, const int* __restrict__ out_slot, float* __restrict__ o_raw, int t0, int tn,
+                      int nv, int n_chunks, int* err) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* S0 = smem;                       // S^T image [128 v][128 k]
+  uint8_t* DT = S0 + 65536;                 // D^T image [128 v][64 j]
+  uint8_t* Wb = DT + 32768;                 // W image   [64 i][128 k]
+  uint8_t* Qb = Wb + W_IMG;                 // e^G Q     [64 i][128 k]
+  uint8_t* Pb = Qb + Q_IMG;                 // P         [64 i][64 j]
+  uint8_t* Kb = Pb + P_IMG;                 // K~^T      [128 d][64 j]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Kb + KT_IMG);
+  uint64_t* ld_wq = bars, *ld_pk = bars + 1, *mma1 = bars + 2, *mma2 = bars + 3, *thr1 = bars + 4, *thr2 = bars + 5;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  pdl_trigger();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int vh = blockIdx.x;
+  if (tid == 0) {
+    mbar_init(ld_wq, 1); mbar_init(ld_pk, 1); mbar_init(mma1, 1); mbar_init(mma2, 1);
+    mbar_init(thr1, 128); mbar_init(thr2, 128);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 4) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t T_S = tmem_base, T_D = tmem_base + 128, T_O = tmem_base + 192;   // S^T [128 cols], D^T [64], O^T [64]
+  pdl_wait();                               // the images come from the preceding kernel, the state from earlier ones
+  const uint8_t* hbase = work + (size_t)vh * n_chunks * CHUNK_BYTES;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(ld_wq, W_IMG + Q_IMG);
+      tma_bulk_g2s(Wb, hbase, W_IMG + Q_IMG, ld_wq);                       // W and Q images are adjacent
+      mbar_arrive_expect_tx(ld_pk, P_IMG + KT_IMG);
+      tma_bulk_g2s(Pb, hbase + W_IMG + Q_IMG, P_IMG + KT_IMG, ld_pk);      // so are P and K~^T
+      for (int c = 0; c < n_chunks; ++c) {
+        const uint32_t ph = c & 1;
+        if (!mbar_wait(thr2, ph) || !mbar_wait(ld_wq, ph)) { fail(err, VG_ERR_TMA_WAIT); *abort_flag = 1; break; }
+        tc_fence_after();
+        mma_tile(T_D, smem_u32(S0), smem_u32(Wb), CH, KD, false);          // D^T  = S^T W^T
+        mma_tile(T_O, smem_u32(S0), smem_u32(Qb), CH, KD, false);          // O^T  = S^T (e^G Q)^T
+        umma_commit(mma1);
+        if (!mbar_wait(mma1, ph)) { fail(err, VG_ERR_MMA_WAIT); *abort_flag = 1; break; }
+        if (c + 1 < n_chunks) {
+          mbar_arrive_expect_tx(ld_wq, W_IMG + Q_IMG);
+          tma_bulk_g2s(Wb, hbase + (size_t)(c + 1) * CHUNK_BYTES, W_IMG + Q_IMG, ld_wq);
+        }
+        if (!mbar_wait(thr1, ph) || !mbar_wait(ld_pk, ph)) { fail(err, VG_ERR_TMA_WAIT); *abort_flag = 1; break; }
+        tc_fence_after();
+        mma_tile(T_O, smem_u32(DT), smem_u32(Pb), CH, CH, true);           // O^T += D^T P^T
+        mma_tile(T_S, smem_u32(DT), smem_u32(Kb), KD, CH, true);           // S^T  = e^{G_C} S^T + D^T K~
+        umma_commit(mma2);
+        if (!mbar_wait(mma2, ph)) { fail(err, VG_ERR_MMA_WAIT); *abort_flag = 1; break; }
+        if (c + 1 < n_chunks) {
+          mbar_arrive_expect_tx(ld_pk, P_IMG + KT_IMG);
+          tma_bulk_g2s(Pb, hbase + (size_t)(c + 1) * CHUNK_BYTES + W_IMG + Q_IMG, P_IMG + KT_IMG, ld_pk);
+        }
+      }
+    }
+  } else {
+    const int v = tid;                       // 0..127
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    // initial state: row v of S^T = column v of S[in_slot]
+    {
+      const float* sp = S + (((size_t)in_slot[t0] * nv + vh) * KD) * VD + v;
+      for (int cb = 0; cb < 8; ++cb) {
+        uint32_t r[16];
+#pragma unroll
+        for (int x = 0; x < 16; ++x) r[x] = __float_as_uint(sp[(size_t)(cb * 16 + x) * VD]);
+        tmem_st16(T_S + lane_addr + (uint32_t)(cb * 16), r);
+#pragma unroll
+        for (int x4 = 0; x4 < 4; ++x4)
+          *reinterpret_cast<float4*>(S0 + img_off(128, v, cb * 16 + x4 * 4)) =
+              make_float4(to_tf32(__uint_as_float(r[x4 * 4])), to_tf32(__uint_as_float(r[x4 * 4 + 1])),
+                          to_tf32(__uint_as_float(r[x4 * 4 + 2])), to_tf32(__uint_as_float(r[x4 * 4 + 3])));
+      }
+      tmem_st_wait();
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(thr2);
+    }
+    bool dead = false;
+    for (int c = 0; c < n_chunks && !dead; ++c) {
+      const uint32_t ph = c & 1;
+      const uint8_t* cbase = hbase + (size_t)c * CHUNK_BYTES;
+      const float4* ut = reinterpret_cast<const float4*>(cbase + W_IMG + Q_IMG + P_IMG + KT_IMG) + v * (CH / 4);
+      float4 u[16];
+#pragma unroll
+      for (int x = 0; x < 16; ++x) u[x] = __ldg(ut + x);
+      const float gcv = gc[(size_t)vh * n_chunks + c];
+      if (!mbar_wait(mma1, ph)) { fail(err, VG_ERR_MMA_WAIT); dead = true; break; }
+      tc_fence_after();
+      // D^T row v = U^T row - S^T W^T row  -> image (row v, k j)
+      for (int cb = 0; cb < 4; ++cb) {
+        uint32_t r[16];
+        tmem_ld16(T_D + lane_addr + (uint32_t)(cb * 16), r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int x4 = 0; x4 < 4; ++x4) {
+          const float4 uu = u[cb * 4 + x4];
+          *reinterpret_cast<float4*>(DT + img_off(128, v, cb * 16 + x4 * 4)) =
+              make_float4(to_tf32(uu.x - __uint_as_float(r[x4 * 4])), to_tf32(uu.y - __uint_as_float(r[x4 * 4 + 1])),
+                          to_tf32(uu.z - __uint_as_float(r[x4 * 4 + 2])), to_tf32(uu.w - __uint_as_float(r[x4 * 4 + 3])));
+        }
+      }
+      // decay the carried state before the chunk's outer products are accumulated onto it
+      for (int cb = 0; cb < 8; ++cb) {
+        uint32_t r[16];
+        tmem_ld16(T_S + lane_addr + (uint32_t)(cb * 16), r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int x = 0; x < 16; ++x) r[x] = __float_as_uint(__uint_as_float(r[x]) * gcv);
+        tmem_st16(T_S + lane_addr + (uint32_t)(cb * 16), r);
+      }
+      tmem_st_wait();
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(thr1);
+      if (!mbar_wait(mma2, ph)) { fail(err, VG_ERR_MMA_WAIT); dead = true; break; }
+      tc_fence_after();
+      // raw outputs o[token][vh * VD + v]
+      for (int cb = 0; cb < 4; ++cb) {
+        uint32_t r[16];
+        tmem_ld16(T_O + lane_addr + (uint32_t)(cb * 16), r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int x = 0; x < 16; ++x) {
+          const int t = c * CH + cb * 16 + x;
+          if (t < tn) o_raw[((size_t)(t0 + t) * nv + vh) * VD + v] = __uint_as_float(r[x]);
+        }
+      }
+      // the new state becomes the next chunk's operand image; after the last chunk it goes to the output slot
+      const bool last = c + 1 == n_chunks;
+      const int os = last ? out_slot[t0 + tn - 1] : -1;
+      float* dp = os >= 0 ? S + (((size_t)os * nv + vh) * KD) * VD + v : nullptr;
+      for (int cb = 0; cb < 8; ++cb) {
+        uint32_t r[16];
+        tmem_ld16(T_S + lane_addr + (uint32_t)(cb * 16), r);
+        tmem_ld_wait();
+        if (!last) {
+#pragma unroll
+          for (int x4 = 0; x4 < 4; ++x4)
+            *reinterpret_cast<float4*>(S0 + img_off(128, v, cb * 16 + x4 * 4)) =
+                make_float4(to_tf32(__uint_as_float(r[x4 * 4])), to_tf32(__uint_as_float(r[x4 * 4 + 1])),
+                            to_tf32(__uint_as_float(r[x4 * 4 + 2])), to_tf32(__uint_as_float(r[x4 * 4 + 3])));
+        } else if (dp) {
+#pragma unroll
+          for (int x = 0; x < 16; ++x) dp[(size_t)(cb * 16 + x) * VD] = __uint_as_float(r[x]);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(thr2);
+    }
+  }
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) tmem_dealloc(tmem_base, 256);
+}
+
+}  // namespace
+
+extern "C" long long vg_gdn_chunk_work_bytes(int tn, int nv) {
+  const long long n_chunks = (tn + CH - 1) / CH;
+  return n_chunks * nv * (long long)CHUNK_BYTES + n_chunks * nv * 4 + 1024;
+}
+
+int vg_gdn_out_norm_launch(const float* o_raw, const void* proj, int ldp, int off_z, const float* norm_w, int t0, int tn,
+                           void* out_f16, int nv, int vd, float eps, cudaStream_t st);
+
+// One linear chain of `tn` columns starting at column t0 (prefill) in chunked form: the carried state is read from
+// slot in_slot[t0] and, when out_slot[t0 + tn - 1] >= 0, written there after the last token. `work` is scratch of
+// vg_gdn_chunk_work_bytes(tn, nv) bytes (1024-byte aligned), `o_raw` fp32 scratch of (t0 + tn) * nv * vd elements.
+extern "C" int vg_gdn_chunk_prefill(const float* qkv, const void* proj, int ldp, int off_z, int off_b, int off_a, float* S,
+                                    const float* A_log, const float* dt_bias, const float* norm_w, int t0, int tn,
+                                    const int* in_slot, const int* out_slot, void* out_f16, int nk, int nv, int kd, int vd,
+                                    float eps, void* work, float* o_raw, int* err, cudaStream_t st) {
+  if (tn <= 0) return 0;
+  if (kd != KD || vd != VD) return -3;
+  const int key_dim = nk * KD, conv_dim = 2 * key_dim + nv * VD;
+  if ((reinterpret_cast<uintptr_t>(qkv) & 15) || (conv_dim % 4) != 0 || (reinterpret_cast<uintptr_t>(work) & 1023) || !o_raw) return -2;
+  const int n_chunks = (tn + CH - 1) / CH, n_pairs = (n_chunks + 1) / 2;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gdn_chunk_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PREP_SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gdn_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  uint8_t* wk = static_cast<uint8_t*>(work);
+  float* gc = reinterpret_cast<float*>(wk + (size_t)n_chunks * nv * CHUNK_BYTES);
+  cudaError_t e = launch_pdl(gdn_chunk_prep_kernel, dim3(n_pairs, nv), dim3(128), PREP_SMEM, st, qkv,
+                             static_cast<const __nv_bfloat16*>(proj), ldp, off_b, off_a, A_log, dt_bias, t0, tn, nk, nv, wk, gc,
+                             n_chunks, err);
+  if (e != cudaSuccess) return (int)e;
+  e = launch_pdl(gdn_chunk_scan_kernel, dim3(nv), dim3(160), SCAN_SMEM, st, (const uint8_t*)wk, (const float*)gc, S, in_slot,
+                 out_slot, o_raw, t0, tn, nv, n_chunks, err);
+  if (e != cudaSuccess) return (int)e;
+  return vg_gdn_out_norm_launch(o_raw, proj, ldp, off_z, norm_w, t0, tn, out_f16, nv, vd, eps, st);
+}

@@ -313,7 +313,24 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
           if (n < p.N) dst[(size_t)n * p.M + m] = y[n] * p.g0[n] * rsc;
       }
     }
-    if (p.ar == 2) {
+    if (p.ar == 3) {
+      // In-switch reduction: the partial rows stay in this rank's own copy of the multimem slot (plain local
+      // stores, nothing crosses NVLink here). Each CTA then publishes the epoch of its 128-row tile on every rank
+      // with one multicast store; the consumer (add_rmsnorm_fp4_kernel<2>) waits per tile for all W ranks' words and
+      // reads each element once with multimem.ld_reduce, the switch adding the W copies.
+      if (have && m < p.M) {
+        float* dst = reinterpret_cast<float*>(c.data[c.rank] + c.mm_off + (size_t)set * c.mm_slot_bytes);
+#pragma unroll
+        for (int n = 0; n < 16; ++n)
+          if (n < p.N) dst[(size_t)n * p.M + m] = y[n] * p.g0[n] * rsc;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (et == 0) {
+        __threadfence_system();                       // the tile's rows are visible system-wide before its word is
+        multimem_st_u32(c.mc + c.mmflags_off + ((size_t)(set * MAX_CTAS + (int)blockIdx.x) * MAX_RANKS + c.rank) * 4, e);
+        trace(4 * 16 + 6);
+      }
+    } else if (p.ar == 2) {
       // Publish only: every value goes to every rank's receive slot (this rank's own included) as an 8-byte
       // (value, epoch) pair: one store each, no fence and no flag lines. The residual-add / RMSNorm kernel that
       // follows polls its own memory, takes a pair once its epoch matches and sums in rank order.
@@ -670,7 +687,8 @@ extern "C" int vg_gemm_fp4(const void* wt, const float* row_scale, const void* b
   }
   if (ar_ctx && ar_ctx->world > 1) {
     if ((M + BM - 1) / BM > MAX_CTAS || (unsigned long long)N * M * 8ull > ar_ctx->slot_bytes) return -5;
-    p.ar = ar_push_only ? 2 : 1;
+    if (ar_push_only == 2 && (!ar_ctx->mc || (unsigned long long)N * M * 4ull > ar_ctx->mm_slot_bytes)) return -5;
+    p.ar = ar_push_only == 2 ? 3 : (ar_push_only ? 2 : 1);
     p.comm = *ar_ctx;
   }
   if (splitk > p.ks_total) splitk = p.ks_total;

@@ -96,8 +96,51 @@ def main():
         comm.check()
         rel = ((out.float() - ref * (rep + 1)).norm() / (ref * (rep + 1)).norm()).item()
         assert rel < 1e-2, (rep, rel)
+    # fused decode-width all-reduce: the row-parallel FP4 GEMM's epilogue publishes its partial rows and the
+    # residual-add / RMSNorm kernel sums the ranks (in the NVLink switch when the arena is multicast-bound, else
+    # from (value, epoch) pairs); same bits on every rank and on every repeat
+    from velogb10_b200.ops import gemm as G
+    h, kloc = 5120, 1024
+    wf = (torch.randn(h, kloc * world, generator=gw, device=dev) * 0.05).to(torch.bfloat16)
+    xa = torch.randn(16, kloc * world, generator=gw, device=dev).to(torch.float16)
+    qs = [QLinear.from_dense(wf[:, r * kloc:(r + 1) * kloc].contiguous(), "nvfp4") for r in range(world)]
+    ref = sum(xa[:, r * kloc:(r + 1) * kloc].float() @ qs[r].dequant(torch.float32).t() for r in range(world))
+    x_loc = xa[:, rank * kloc:(rank + 1) * kloc].contiguous()
+    ones = torch.zeros(h, device=dev)
+    x16 = torch.zeros(16, h, dtype=torch.float16, device=dev)
+    dummy = torch.zeros(16, h, dtype=torch.bfloat16, device=dev)
+    mode = 2 if comm.use_mm else 1
+    for n in (1, 5, 16):
+        for rep in range(4):
+            res = torch.zeros(16, h, dtype=torch.bfloat16, device=dev)
+            G.linear_fp4(qs[rank], x_loc, n, out=dummy, comm=comm, push_only=True)
+            G.add_rmsnorm_fp4_ar(res, ones, 1e-6, n, comm, out16=x16, mode=mode)
+            torch.cuda.synchronize()
+            comm.check()
+            rel = ((res[:n].float() - ref[:n]).norm() / ref[:n].norm()).item()
+            assert rel < 8e-3, ("fused all-reduce", n, rep, rel)
+            if rep == 0:
+                first = res.clone()
+            assert torch.equal(res, first), "fused all-reduce must be deterministic"
+        both = comm.all_gather_small(first[:1, :64].contiguous())
+        torch.cuda.synchronize()
+        assert torch.equal(both[0], both[-1]), "ranks must hold identical sums"
+    # device-side sampling over a vocabulary-sharded head: same token on every rank, equal to the full-logits result
+    from velogb10_b200.engine import sampling as S
+    from velogb10_b200.engine.device_sampler import DeviceSampler
+    vl = 3000
+    full_logits = (torch.randn(6, vl * world, generator=gw, device=dev) * 3 * 4).round() / 4
+    params = [S.SamplingParams(0.7, 0.8, 20), S.SamplingParams(0.0, 0.8, 20), S.SamplingParams(1.2, 0.95, 64)] * 2
+    sh = DeviceSampler(dev, vl, cap=16, comm=comm)
+    one = DeviceSampler(dev, vl * world, cap=16)
+    keys = [3, 5, 7, 11, 13, 17]
+    got = sh.pick(full_logits[:, rank * vl:(rank + 1) * vl].contiguous(), params, [[]] * 6, keys)
+    want = one.pick(full_logits.clone(), params, [[]] * 6, keys)
+    comm.check()
+    assert got == want, (got, want)
     dist.barrier()
     if rank == 0:
+        print("COMM_DESC", comm.describe())
         print("COMM_OK")
     dist.destroy_process_group()
 

@@ -20,7 +20,9 @@ def main():
     from velogb10_b200.models.weights import ModelBuilder
     from velogb10_b200.parallel.comm import TpComm
     cfg = tiny_hybrid(mtp=False)
-    cfg.num_heads, cfg.num_kv_heads = 4, 2
+    # enough heads to shard at this world size (KV heads are replicated when there are fewer of them than ranks)
+    cfg.num_heads, cfg.num_kv_heads = max(4, world), 2
+    cfg.lin_num_k_heads, cfg.lin_num_v_heads = max(4, world), 2 * max(4, world)
     comm = TpComm(rank, world, dev, max_elems=1 << 20)
     w1 = ModelBuilder(cfg, SyntheticSource(cfg, 0, str(dev), std=0.05), recipe="all", device=str(dev)).build()
     wt = ModelBuilder(cfg, SyntheticSource(cfg, 0, str(dev), std=0.05), recipe="all", device=str(dev), tp_rank=rank,
@@ -68,6 +70,10 @@ def main():
     tp.fuse_allreduce = True
     rel = ((lu.float() - lv.float()).norm() / lv.float().norm()).item()
     assert rel < 0.02 and lu.argmax(-1).tolist() == lv.argmax(-1).tolist(), rel
+    # every rank holds the same residual stream, bit for bit (the sums are order-fixed or made once in the switch)
+    hid = comm.all_gather_small(tp.ws.x[:1].contiguous().view(torch.int16))
+    torch.cuda.synchronize()
+    assert all(torch.equal(hid[0], hid[q]) for q in range(world)), "ranks diverged in the residual stream"
     # graph replay under tensor parallelism
     tp.S.copy_(S0); tp.conv.copy_(C0); tp.kc.copy_(K0); tp.vc.copy_(V0)
     want = int(lv[0].argmax())
@@ -79,6 +85,7 @@ def main():
     from velogb10_b200.config import tiny_moe
     from velogb10_b200.ops import gemm as G
     mcfg = tiny_moe(mtp=False)
+    mcfg.num_heads, mcfg.lin_num_k_heads, mcfg.lin_num_v_heads = max(4, world), max(4, world), 2 * max(4, world)
     m1 = GpuModel(ModelBuilder(mcfg, SyntheticSource(mcfg, 0, str(dev), std=0.05), recipe="all", device=str(dev)).build(),
                   device=str(dev))
     mt = GpuModel(ModelBuilder(mcfg, SyntheticSource(mcfg, 0, str(dev), std=0.05), recipe="all", device=str(dev),
@@ -121,6 +128,7 @@ def main():
     assert torch.equal(both[0], both[-1]), "ranks must hold identical logits"
     dist.barrier()
     if rank == 0:
+        print("TP_DESC", comm.describe())
         print("TP_OK")
     dist.destroy_process_group()
 

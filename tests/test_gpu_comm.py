@@ -1,5 +1,5 @@
-"""Peer-memory collectives and tensor-parallel inference on 2+ GPUs (spawned as one process per GPU).
-NVLS is switched off in the library used for bootstrap; the kernels under test use plain peer loads/stores."""
+"""Peer-memory collectives and tensor-parallel inference on 2, 4 and 8 GPUs (spawned as one process per GPU), with
+the arena on NVLink-switch multicast memory (in-switch reductions) and on plain CUDA-IPC memory (peer loads / stores)."""
 import os
 import subprocess
 import sys
@@ -11,10 +11,10 @@ pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _spawn(script: str, n: int, timeout: int = 300):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+def _spawn(script: str, n: int, timeout: int = 420, env_extra=None):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", **(env_extra or {}))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
-           "127.0.0.1", "--master-port", "29541", os.path.join(ROOT, "tests", script)]
+           "127.0.0.1", "--master-port", str(29541 + n), os.path.join(ROOT, "tests", script)]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
     assert r.returncode == 0, (r.stdout[-3000:], r.stderr[-3000:])
     return r.stdout
@@ -24,13 +24,19 @@ def _ngpu():
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
 
-@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-def test_collectives_two_ranks():
-    out = _spawn("mp_comm_worker.py", 2)
+WORLDS = [pytest.param(w, marks=pytest.mark.skipif(_ngpu() < w, reason=f"needs {w} GPUs")) for w in (2, 4, 8)]
+ARENAS = [pytest.param({}, id="multicast"), pytest.param({"VELO_NO_MULTIMEM": "1", "NCCL_NVLS_ENABLE": "0"}, id="ipc")]
+
+
+@pytest.mark.parametrize("world", WORLDS)
+@pytest.mark.parametrize("env", ARENAS)
+def test_collectives(world, env):
+    out = _spawn("mp_comm_worker.py", world, env_extra=env)
     assert "COMM_OK" in out
 
 
-@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-def test_tensor_parallel_model_matches_single_gpu():
-    out = _spawn("mp_tp_worker.py", 2)
+@pytest.mark.parametrize("world", WORLDS)
+@pytest.mark.parametrize("env", ARENAS)
+def test_tensor_parallel_model_matches_single_gpu(world, env):
+    out = _spawn("mp_tp_worker.py", world, env_extra=env)
     assert "TP_OK" in out

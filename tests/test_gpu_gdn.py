@@ -79,3 +79,62 @@ def test_conv_chain_matches_two_phase_conv_bitwise(n):
     assert (ob - ref).abs().max().item() < 1e-4
     assert torch.equal(sb[1], seq[-ck:].t())
     assert torch.equal(sb[0], state0[0]) and torch.equal(sb[2], state0[2])
+
+
+@pytest.mark.parametrize("T", [64, 333, 2048, 4096])
+def test_chunked_prefill_matches_exact_kernel(T):
+    """The tensor-core chunked form against the exact recurrence: outputs, the state at a mid-chain checkpoint and at
+    the end, and one decode step continued from either state, all to tf32 rounding."""
+    from velogb10_b200.ops import kernels as K, lib
+    torch.manual_seed(T)
+    dev = "cuda"
+    nk, nv, kd, vd = 2, 6, 128, 128
+    key_dim, value_dim = nk * kd, nv * vd
+    conv_dim = 2 * key_dim + value_dim
+    ldp = (conv_dim + value_dim + 2 * nv + 7) // 8 * 8
+    qkv = torch.randn(T + 1, conv_dim, device=dev)
+    proj = torch.randn(T + 1, ldp, device=dev).to(torch.bfloat16)
+    A_log = torch.randn(nv, device=dev) * 0.5
+    dt_bias = torch.randn(nv, device=dev) * 0.5
+    norm_w = torch.rand(vd, device=dev) + 0.5
+    S0 = torch.randn(4, nv, kd, vd, device=dev) * 0.1
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    mid = T // 2 + 5 if T > 64 else T        # a checkpoint that is not on a chunk boundary
+    off = (conv_dim, conv_dim + value_dim, conv_dim + value_dim + nv)
+
+    # exact: one chain, state checkpointed after token mid - 1 (slot 0) and after the last token (slot 2)
+    Sa = S0.clone()
+    oa = torch.zeros(T, value_dim, dtype=torch.float16, device=dev)
+    out_slot = [-1] * T
+    out_slot[mid - 1] = 0
+    out_slot[T - 1] = 2
+    K.gdn_prefill(qkv, proj, *off, Sa, A_log, dt_bias, norm_w, 0, T, i32([1] * T), i32(out_slot), oa, nk, nv, kd, vd, 1e-6)
+
+    # chunked: one call per segment between checkpoints; the second segment continues from the checkpoint slot
+    Sb = S0.clone()
+    ob = torch.zeros_like(oa)
+    work = torch.zeros(K.gdn_chunk_work_bytes(T, nv) + 1024, dtype=torch.uint8, device=dev)
+    work = work[(-work.data_ptr()) % 1024:]
+    o_raw = torch.zeros(T * value_dim, device=dev)
+    in_slot = i32([1] * mid + [0] * (T - mid))
+    out_t = i32(out_slot)
+    K.gdn_chunk_prefill(qkv, proj, *off, Sb, A_log, dt_bias, norm_w, 0, mid, in_slot, out_t, ob, nk, nv, kd, vd, 1e-6, work, o_raw)
+    if mid < T:
+        K.gdn_chunk_prefill(qkv, proj, *off, Sb, A_log, dt_bias, norm_w, mid, T - mid, in_slot, out_t, ob, nk, nv, kd, vd, 1e-6,
+                            work, o_raw)
+    torch.cuda.synchronize()
+    lib.check_err_word()
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()
+    assert rel(ob, oa) < 2e-3, ("outputs", rel(ob, oa))
+    assert rel(Sb[0], Sa[0]) < 1e-3, ("checkpoint state", rel(Sb[0], Sa[0]))
+    assert rel(Sb[2], Sa[2]) < 1e-3, ("final state", rel(Sb[2], Sa[2]))
+    assert torch.equal(Sb[1], S0[1]) and torch.equal(Sb[3], S0[3])          # untouched slots
+    # one decode step from each final state (the step kernel is exact): the outputs must agree as closely
+    outs = []
+    for Sx in (Sa, Sb):
+        o1 = torch.zeros(1, value_dim, dtype=torch.float16, device=dev)
+        K.gdn_step(qkv[T:], proj[T:], *off, Sx, A_log, dt_bias, norm_w, i32([0]), i32([1]), 1, i32([2]), i32([-1]), i32([3]), o1,
+                   nk, nv, kd, vd, 1e-6)
+        outs.append(o1)
+    torch.cuda.synchronize()
+    assert rel(outs[1], outs[0]) < 2e-3

@@ -46,6 +46,8 @@ def test_batching_speculation_and_prefix_cache_do_not_change_greedy_output(weigh
     together, sch = _run(gm, prompts, max_batch=4)
     assert together == solo
     assert sch.stats["admitted"] == 5 and not sch.lanes
+    # the model has a draft head and the decode steps still ran as CUDA-graph replays
+    assert sch.has_mtp and sch.stats.get("graph_steps", 0) > 0 and sch.stats["graph_steps"] == sch.stats["decode_steps"]
     # bitwise-lossless speculation: the draft head proposes, a width-N verify decides
     for depth in (2, 4):
         spec, sch = _run(gm, prompts[:2], max_batch=1, policy=MtpPolicy("on", depth=depth))
@@ -67,3 +69,47 @@ def test_four_bit_cache_serving_is_self_consistent(weights, monkeypatch):
     together, _ = _run(gm, prompts, max_batch=4)
     spec, _ = _run(gm, prompts[:2], max_batch=1, policy=MtpPolicy("on", depth=3))
     assert together == solo and spec == solo[:2]
+
+
+def _run_sampling(model, prompts, params, max_new=12, max_batch=4, policy=None, monkeypatch=None, cpu=False):
+    from velogb10_b200.engine.mtp import MtpPolicy
+    from velogb10_b200.engine.scheduler import Request, Scheduler
+    if monkeypatch is not None:
+        monkeypatch.setenv("VELO_CPU_SAMPLE", "1" if cpu else "0")
+    sch = Scheduler(model, max_batch, 160, eos_ids=[model.cfg.vocab_size - 1], policy=policy or MtpPolicy("off", has_head=True))
+    outs = [[] for _ in prompts]
+    for i, p in enumerate(prompts):
+        sch.submit(Request(p, max_new, params[i], on_token=outs[i].append))
+    sch.run_until_idle(10000)
+    torch.cuda.synchronize()
+    model.gather_logits = True
+    return outs, sch
+
+
+def test_device_sampling_graph_and_speculative_accept(weights, monkeypatch):
+    """Seeded sampling and penalised greedy run through the decode + sample graph on the device; the same seeds give
+    the same text again; penalised greedy equals the host path exactly; stochastic speculation runs its accept rule
+    on the device and stays seed-reproducible."""
+    from velogb10_b200.engine.mtp import MtpPolicy
+    from velogb10_b200.engine.sampling import SamplingParams
+    from velogb10_b200.models.runtime import GpuModel
+    gm = GpuModel(weights, keep_canonical=True)
+    prompts = _prompts(weights.cfg, 4, seed=9)
+    samp = [SamplingParams(0.8, 0.9, 20, seed=100 + i) for i in range(4)]
+    a, sch = _run_sampling(gm, prompts, samp, monkeypatch=monkeypatch)
+    assert sch.sampler is not None and sch.stats.get("graph_steps", 0) == sch.stats["decode_steps"] > 0
+    b, _ = _run_sampling(gm, prompts, samp, monkeypatch=monkeypatch)
+    assert a == b and all(len(x) >= 1 for x in a)
+    pen = [SamplingParams(0.0, 0.8, 20, 1.3, 0.7, 0.2) for _ in range(4)]
+    dev_out, _ = _run_sampling(gm, prompts, pen, monkeypatch=monkeypatch)
+    host_out, sch_h = _run_sampling(gm, prompts, pen, monkeypatch=monkeypatch, cpu=True)
+    assert sch_h.sampler is None and dev_out == host_out
+    # penalised greedy under speculation is still lossless (the verify columns are penalised with the growing history)
+    spec_out, _ = _run_sampling(gm, prompts[:2], pen[:2], max_batch=1, policy=MtpPolicy("on", depth=3), monkeypatch=monkeypatch)
+    solo_out = [_run_sampling(gm, [p], [pen[0]], max_batch=1, monkeypatch=monkeypatch)[0][0] for p in prompts[:2]]
+    assert spec_out == solo_out
+    s1, sch1 = _run_sampling(gm, prompts[:2], samp[:2], max_batch=1, policy=MtpPolicy("on", depth=3), monkeypatch=monkeypatch)
+    s2, _ = _run_sampling(gm, prompts[:2], samp[:2], max_batch=1, policy=MtpPolicy("on", depth=3), monkeypatch=monkeypatch)
+    assert s1 == s2 and sch1.stats["mtp_steps"] > 0 and all(len(x) >= 1 for x in s1)
+    from velogb10_b200.ops import lib
+    lib.check_err_word()

@@ -110,6 +110,11 @@ class Scheduler:
         self.step_ms: Deque[float] = deque(maxlen=4096)
         self.trace_every = 256 if os.environ.get("VELO_TP_TRACE", "0") == "1" else 0
         self.cpu_sample = os.environ.get("VELO_CPU_SAMPLE", "0") == "1"
+        # token selection on the device when the runner has a sampler (--cpu-sample forces the host path): forwards
+        # then return this rank's vocabulary shard and full logits never leave the GPU or cross ranks
+        self.sampler = None if self.cpu_sample else getattr(runner, "sampler", None)
+        if self.sampler is not None:
+            runner.gather_logits = False
 
     # ------------------------------------------------------------------ public
     def submit(self, req: Request) -> int:
@@ -269,6 +274,9 @@ class Scheduler:
                     keys: Sequence[int]) -> List[int]:
         """One token per row: penalties, then arg-max or a seeded nucleus draw."""
         n = logits.shape[0]
+        if self.sampler is not None and logits.is_cuda:
+            lg = logits if logits.dtype == torch.float32 else logits.float()
+            return self.sampler.pick(lg, list(params), [list(h) for h in histories], list(keys))
         if any(p.has_penalty and h for p, h in zip(params, histories)):
             logits = logits.clone() if logits.dtype == torch.float32 else logits.float()
             for i in range(n):
@@ -354,9 +362,20 @@ class Scheduler:
         pos = [l.pos for l in lanes]
         slots = [l.slot for l in lanes]
         plain = all(l.req.params.greedy and not l.req.params.has_penalty for l in lanes)
-        if plain and self.use_graphs and not self.has_mtp:
+        if plain and self.use_graphs:
+            # greedy graph; the hidden rows the draft head needs stay in the runner's fixed workspace buffer
             new = self.r.replay_decode(toks, pos, slots).tolist()
-            hidden = None
+            hidden = self.r.ws.x[:len(lanes)] if self.has_mtp else None
+            self.stats["graph_steps"] = self.stats.get("graph_steps", 0) + 1
+        elif self.use_graphs and self.sampler is not None and hasattr(self.r, "replay_decode_sample"):
+            # decode + sample graph: parameters, uniforms and penalty lists go up in one copy, one read comes back
+            self.r.ensure_sample_graph(len(lanes))
+            params = [l.req.params for l in lanes]
+            u = [S.rng_uniform(l.key, S.DOMAIN_SAMPLE, 0) for l in lanes]
+            self.sampler.upload(params, u=u, histories=[l.history for l in lanes])
+            new = self.r.replay_decode_sample(toks, pos, slots).tolist()
+            hidden = self.r.ws.x[:len(lanes)] if self.has_mtp else None
+            self.stats["graph_steps"] = self.stats.get("graph_steps", 0) + 1
         else:
             logits, hidden = self.r.decode(toks, pos, slots)
             new = self._pick_token(logits, [l.req.params for l in lanes], [l.history for l in lanes],
@@ -383,6 +402,18 @@ class Scheduler:
         h = lane.h_prev
         tok = lane.last_tok
         p = lane.pos - 1
+        if self.sampler is not None and self.ngram <= 0 and n_drafts > 0 and getattr(self.r, "tp", 1) == 1:
+            # the whole chain stays on the device: each step's arg-max feeds the next step's token slot directly and
+            # the draft ids come back in one read
+            from ..ops import kernels as K
+            outs = torch.empty(n_drafts, dtype=torch.int32, device=h.device)
+            tok_dev = None
+            for d in range(n_drafts):
+                logits, hh = self.r.mtp_forward(lane.slot, [tok if d == 0 else 0], h.reshape(1, -1), [p], tok_dev=tok_dev)
+                K.argmax(logits, 1, outs[d:d + 1])
+                tok_dev = outs[d:d + 1]
+                h, p = hh[0].clone(), p + 1
+            return outs.tolist(), h
         for d in range(n_drafts):
             if self.ngram > 0:
                 ng = self._ngram_lookup(lane, drafts)
@@ -393,7 +424,7 @@ class Scheduler:
                     h, tok, p = hh[0].clone(), ng, p + 1
                     continue
             logits, hh = self.r.mtp_forward(lane.slot, [tok], h.reshape(1, -1), [p])
-            nxt = S.argmax_rows(logits if logits.dtype == torch.float32 else logits.float())[0]
+            nxt = self._argmax(logits)[0]
             drafts.append(nxt)
             h, tok, p = hh[0].clone(), nxt, p + 1
         return drafts, h
@@ -441,14 +472,7 @@ class Scheduler:
         drafts, _ = self._draft_chain(lane, depth - 1)
         cols = [lane.last_tok] + drafts
         logits, hidden = self.r.verify(lane.slot, cols, lane.pos, self.ckpt_base)
-        if lane.req.params.has_penalty:
-            logits = logits.clone()
-            hist = list(lane.history)
-            for t in range(len(cols)):
-                logits[t] = S.apply_penalties(logits[t], hist, lane.req.params)
-                if t < len(drafts):
-                    hist.append(drafts[t])
-        preds = S.argmax_rows(logits if logits.dtype == torch.float32 else logits.float())
+        preds = self._greedy_preds(logits, lane, drafts)
         nacc = S.greedy_accept(preds, drafts)
         bonus = preds[nacc]
         pos0 = lane.pos
@@ -460,20 +484,54 @@ class Scheduler:
         self.policy.record_step(len(drafts), nacc, nacc + 1)
         self.stats["mtp_steps"] += 1
 
+    def _argmax(self, logits: torch.Tensor) -> List[int]:
+        """Greedy token per row (lowest index on ties), over the whole vocabulary even when ``logits`` is one rank's shard."""
+        if self.sampler is not None and logits.is_cuda:
+            n = logits.shape[0]
+            return self.sampler.pick(logits if logits.dtype == torch.float32 else logits.float(),
+                                     [SamplingParams(0.0, 1.0, 1)] * n, [[]] * n, [0] * n)
+        return S.argmax_rows(logits if logits.dtype == torch.float32 else logits.float())
+
+    def _greedy_preds(self, logits: torch.Tensor, lane: Lane, drafts: Sequence[int]) -> List[int]:
+        """Arg-max per verify column; column t is penalised with the history extended by the first t drafts."""
+        n = logits.shape[0]
+        if self.sampler is not None and logits.is_cuda:
+            hists, hist = [], list(lane.history)
+            for t in range(n):
+                hists.append(list(hist))
+                if t < len(drafts):
+                    hist.append(drafts[t])
+            greedy = SamplingParams(0.0, 1.0, 1, lane.req.params.repetition_penalty, lane.req.params.presence_penalty,
+                                    lane.req.params.frequency_penalty)
+            return self.sampler.pick(logits if logits.dtype == torch.float32 else logits.float(), [greedy] * n, hists, [0] * n)
+        if lane.req.params.has_penalty:
+            logits = logits.clone()
+            hist = list(lane.history)
+            for t in range(n):
+                logits[t] = S.apply_penalties(logits[t], hist, lane.req.params)
+                if t < len(drafts):
+                    hist.append(drafts[t])
+        return S.argmax_rows(logits if logits.dtype == torch.float32 else logits.float())
+
     def _mtp_sample_step(self, lane: Lane):
         depth = self._depth_for(lane)
         drafts, _ = self._draft_chain(lane, depth - 1)
         cols = [lane.last_tok] + drafts
         logits, hidden = self.r.verify(lane.slot, cols, lane.pos, self.ckpt_base)
-        logits = logits.clone() if logits.dtype == torch.float32 else logits.float()
-        if lane.req.params.has_penalty:
-            hist = list(lane.history)
-            for t in range(len(cols)):
-                logits[t] = S.apply_penalties(logits[t], hist, lane.req.params)
-                if t < len(drafts):
-                    hist.append(drafts[t])
-        nuclei = S.nucleus_rows(logits, [lane.req.params] * len(cols))
-        nacc, nxt = S.stochastic_accept(nuclei, drafts, lane.key)
+        if self.sampler is not None and logits.is_cuda:
+            # accept / residual resample / bonus on the device: one read of (accepted, next token) comes back
+            nacc, nxt = self.sampler.chain_accept(logits if logits.dtype == torch.float32 else logits.float(),
+                                                  lane.req.params, lane.history, drafts, lane.key)
+        else:
+            logits = logits.clone() if logits.dtype == torch.float32 else logits.float()
+            if lane.req.params.has_penalty:
+                hist = list(lane.history)
+                for t in range(len(cols)):
+                    logits[t] = S.apply_penalties(logits[t], hist, lane.req.params)
+                    if t < len(drafts):
+                        hist.append(drafts[t])
+            nuclei = S.nucleus_rows(logits, [lane.req.params] * len(cols))
+            nacc, nxt = S.stochastic_accept(nuclei, drafts, lane.key)
         pos0 = lane.pos
         self.r.copy_state(self.ckpt_base + nacc, lane.slot)
         fed = cols[:nacc + 1]
@@ -505,7 +563,7 @@ class Scheduler:
             logits, hidden = self.r.verify(lane.slot, tokens, lane.pos, self.ckpt_base)
         else:
             logits, hidden = self.r.verify(lane.slot, tokens, lane.pos, self.ckpt_base, parent=parent)
-        preds = S.argmax_rows(logits if logits.dtype == torch.float32 else logits.float())
+        preds = self._argmax(logits)
         path = S.tree_accept_walk(parent, tokens, preds)
         nacc = len(path) - 1
         last_col = path[-1]
@@ -536,7 +594,7 @@ class Scheduler:
             base += len(cols)
         outs = self.r.verify_forest([(lane.slot, cols, lane.pos, b) for lane, cols, _, b in plans])
         for (lane, cols, drafts, b), (logits, hidden) in zip(plans, outs):
-            preds = S.argmax_rows(logits if logits.dtype == torch.float32 else logits.float())
+            preds = self._argmax(logits)
             nacc = S.greedy_accept(preds, drafts)
             pos0 = lane.pos
             self.r.copy_state(b + nacc, lane.slot)

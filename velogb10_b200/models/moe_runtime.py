@@ -170,7 +170,7 @@ def moe_forward(model, ws, M: MoeW, n: int, act=None):
                                    ptr(shared if first else None), ptr(gate if first else None), c_int(h),
                                    ctypes.byref(comm.ctx), stream())
         _lib.check(rc, "vg_moe_combine_push")
-        model._pending_ar = True
+        model._pending_ar = 1
         return
     rc = L.vg_moe_combine(ptr(b.y), c_int(b.y.stride(0)), ptr(inv), ptr(b.wts), c_int(n), c_int(topk),
                           ptr(None if ep else shared), ptr(None if ep else gate), ptr(ws.delta), c_int(h), stream())

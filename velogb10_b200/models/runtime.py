@@ -162,14 +162,16 @@ class GpuModel:
         self.use_fp4 = os.environ.get("VELO_NO_FP4_MMA", "0") != "1"
         # tensor-parallel decode: row-parallel GEMMs push partial rows, the following norm kernel sums them
         self.split_allreduce = os.environ.get("VELO_NO_SPLIT_ALLREDUCE", "0") != "1"
-        self._pending_ar = False
+        self._pending_ar = 0                  # 0 none, 1 pair slots, 2 multimem slots hold the pending partial rows
         # --prefill-scalar: exact per-token prefill kernels only (bit-identical to stepping the decode kernels)
         self.prefill_exact = os.environ.get("VELO_PREFILL_SCALAR", "0") == "1"
         self.tc_prefill_attn = os.environ.get("VELO_NO_TC_PREFILL_ATTN", "0") != "1" and not self.prefill_exact
         self._prefill_ctx = None              # (slot, first position) while a prefill chunk is running
         self.kv_q4 = os.environ.get("VELO_KV_QUANT", "bf16").lower() == "q4"
         self._kv_scales = None                # (k scales, v scales) of the layer being run, 4-bit cache only
-        self._gdn_o = None                    # fp32 raw outputs of the column-split GDN prefill kernel
+        self._gdn_o = None                    # fp32 raw outputs of the column-split / chunked GDN prefill kernels
+        self._gdn_work = None                 # operand images handed between the two chunked GDN prefill kernels
+        self.gdn_chunk_min = int(os.environ.get("VELO_GDN_CHUNK_MIN", "128"))   # shorter prefill chunks run the exact kernel
         self._k_rows = None                   # bf16 staging of a lane's keys for tensor-core prefill over a 4-bit cache
         # MoE decode: second stream for the shared expert (see moe_runtime.moe_forward)
         self.moe_side_stream = None
@@ -216,6 +218,11 @@ class GpuModel:
                     G.prepare_fp4(q)
                 G.prepare(q, keep_canonical=keep_canonical)
         self.ws = Workspace(self.cfg, weights, max_cols, self.dev, max_cols)
+        # token selection on the device (penalties, top-k, nucleus, draw, speculative accept), vocabulary-shard aware
+        from ..engine.device_sampler import DeviceSampler
+        self.sampler = DeviceSampler(self.dev, weights.lm_head.m, cap=max(16, max_cols), comm=comm)
+        # False: forwards return this rank's vocabulary shard of the logits (the device sampler merges shards itself)
+        self.gather_logits = True
         self.col_ctr = torch.zeros(16, dtype=torch.int32, device=self.dev)     # per-column arrival counters
         self.ws_prefill: Optional[Workspace] = None
         self.state_ready = False
@@ -358,8 +365,8 @@ class GpuModel:
         linear only pushed its partial rows (``self._pending_ar``), the kernel also performs the
         tensor-parallel sum."""
         if self._pending_ar:
-            self._pending_ar = False
-            return G.add_rmsnorm_fp4_ar(ws.x, w, self.cfg.rms_eps, n, self.comm, out16=ws.xn16)
+            mode, self._pending_ar = self._pending_ar, 0
+            return G.add_rmsnorm_fp4_ar(ws.x, w, self.cfg.rms_eps, n, self.comm, out16=ws.xn16, mode=mode)
         if self.use_fp4 and n <= 16 and ws.x.shape[1] % 16 == 0:
             return G.add_rmsnorm_fp4(ws.x, delta, w, self.cfg.rms_eps, n, out16=ws.xn16)
         K.add_rmsnorm(ws.x, delta, w, self.cfg.rms_eps, n, out16=ws.xn16)
@@ -382,7 +389,7 @@ class GpuModel:
             if self.split_allreduce and self._fp4_ok(q, n) and q.m == self.cfg.hidden_size and q.m % 16 == 0:
                 # push the partial rows; the next residual-add / RMSNorm kernel sums them
                 G.linear_fp4(q, x16, n, out=out, comm=self.comm, act=act, push_only=True)
-                self._pending_ar = True
+                self._pending_ar = 2 if self.comm.use_mm else 1       # which form the consumer must read
                 return
             self._linear(q, x16, n, out, act=act, comm=self.comm)
             return
@@ -462,7 +469,22 @@ class GpuModel:
         if self._fp4_ok(Gd.out, n) and value_dim % 16 == 0:
             # the recurrence kernel quantises its own output rows for the output projection
             act_o = G.fp4_buffers(self.dev, Gd.out.kernel4.kp)
-        if linear_chain and n > 16 and c.lin_k_dim == 128 and c.lin_v_dim == 128 and proj.stride(0) % 8 == 0 \
+        if linear_chain and n >= self.gdn_chunk_min and c.lin_k_dim == 128 and c.lin_v_dim == 128 and conv_dim % 4 == 0 \
+                and not self.prefill_exact:
+            # long prefill chunk: the chunked (WY) form of the recurrence on the tensor cores; agrees with the exact
+            # kernels to tf32 rounding (decode and verify always run the exact step kernel)
+            need = ws.cap * value_dim
+            if self._gdn_o is None or self._gdn_o.numel() < need:
+                self._gdn_o = torch.zeros(need, dtype=torch.float32, device=self.dev)
+            wb = K.gdn_chunk_work_bytes(ws.cap, Gd.nv)
+            if self._gdn_work is None or self._gdn_work.numel() < wb + 1024:
+                self._gdn_work = torch.zeros(wb + 1024, dtype=torch.uint8, device=self.dev)
+            off = (-self._gdn_work.data_ptr()) % 1024
+            K.gdn_chunk_prefill(ws.conv_out, proj, conv_dim,
+                                conv_dim + value_dim, conv_dim + value_dim + Gd.nv, self.S[gi], Gd.A_log, Gd.dt_bias, Gd.norm,
+                                0, n, ws.st_in, ws.st_out, g16, Gd.nk, Gd.nv, c.lin_k_dim, c.lin_v_dim, c.rms_eps,
+                                self._gdn_work[off:], self._gdn_o)
+        elif linear_chain and n > 16 and c.lin_k_dim == 128 and c.lin_v_dim == 128 and proj.stride(0) % 8 == 0 \
                 and conv_dim % 8 == 0:
             # prefill chunk: one chain through all n columns
             need = ws.cap * value_dim
@@ -595,15 +617,19 @@ class GpuModel:
         return logits, (torch.cat(hs, 0) if want_hidden else None)
 
     # ---------------------------------------------------------------- MTP head
-    def mtp_forward(self, slot: int, tokens: Sequence[int], hidden: torch.Tensor, pos: Sequence[int]):
+    def mtp_forward(self, slot: int, tokens: Sequence[int], hidden: torch.Tensor, pos: Sequence[int],
+                    tok_dev: Optional[torch.Tensor] = None):
         """Draft head over N (hidden_t, token_{t+1}) pairs of one lane (replicated on every rank).
-        Returns (logits [N, V_local] fp32, head hidden [N, h] bf16)."""
+        Returns (logits [N, V_local] fp32, head hidden [N, h] bf16). ``tok_dev`` (int32 device tensor, N ids) replaces
+        ``tokens`` without a host round trip (a draft chain feeds each draft straight into the next step)."""
         m, c, ws = self.w.mtp, self.cfg, self.ws
         n = len(tokens)
         plan = Plan.chain(slot, tokens, 0, None)
         plan.pos = list(pos); plan.kv_row = list(pos)
         plan.lens = [p + 1 for p in pos]; plan.base = list(plan.lens)
         self._upload(ws, plan)
+        if tok_dev is not None:
+            ws.tok[:n].copy_(tok_dev[:n])
         h = c.hidden_size
         K.embed_gather(self.w.embed, ws.tok, ws.mtp_e, n)
         K.add_rmsnorm(ws.mtp_e, None, m.norm_embed, c.rms_eps, n, out_bf=ws.x)
@@ -639,7 +665,7 @@ class GpuModel:
 
     def _full_logits(self, local: torch.Tensor) -> torch.Tensor:
         """Under tensor parallelism the LM head is vocabulary-sharded: gather the shards (sampling paths)."""
-        if self.tp == 1:
+        if self.tp == 1 or not self.gather_logits:
             return local
         return self.comm.gather_logits(local)
 
@@ -684,6 +710,52 @@ class GpuModel:
                 t[:, :b].copy_(keep)
         self.graphs[("decode", b)] = g
         return g
+
+    def capture_decode_sample(self, b: int):
+        """Capture decode + token selection for batch size ``b`` (reference: src/gpu.rs:3987-4081
+        ``capture_decode_sample_graph``): backbone, then penalties / top-k / nucleus / draw from the parameter block the
+        sampler uploaded for this step; the chosen ids land in ``sampler.out_tok``."""
+        ws = self.ws
+        self._upload(ws, Plan.decode([0] * b, [0] * b, list(range(b))))
+        saved = [(t, t[:, :b].clone()) for t in (self.S, self.conv) if t is not None]
+        kv = self._kv_tensors()
+        saved += [(t, t[:, :b, :, :1].clone()) for t in kv]
+        from ..engine.sampling import SamplingParams
+        self.sampler.upload([SamplingParams()] * b, u=[0.5] * b)
+        torch.cuda.synchronize(self.dev)
+        s = torch.cuda.Stream(device=self.dev)
+        s.wait_stream(torch.cuda.current_stream(self.dev))
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                self._backbone(ws, b, b, False, False, False)
+                self.sampler.select(ws.logits, b, True)
+        torch.cuda.current_stream(self.dev).wait_stream(s)
+        torch.cuda.synchronize(self.dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._backbone(ws, b, b, False, False, False)
+            self.sampler.select(ws.logits, b, True)
+        for t, keep in saved:
+            if any(t is x for x in kv):
+                t[:, :b, :, :1].copy_(keep)
+            else:
+                t[:, :b].copy_(keep)
+        self.graphs[("sample", b)] = g
+        return g
+
+    def ensure_sample_graph(self, b: int):
+        """Capture the decode + sample graph for batch ``b`` if needed. Capturing stages placeholder sampling
+        parameters, so call this before ``sampler.upload`` for the step."""
+        if ("sample", b) not in self.graphs:
+            self.capture_decode_sample(b)
+
+    def replay_decode_sample(self, tokens, pos, slots) -> torch.Tensor:
+        """Graph replay of decode + sampling; the caller has staged this step's sampling parameters with
+        ``sampler.upload`` (after ``ensure_sample_graph``). Returns the device tensor of chosen ids."""
+        b = len(tokens)
+        self._upload(self.ws, Plan.decode(tokens, pos, slots))
+        self.graphs[("sample", b)].replay()
+        return self.sampler.out_tok[:b]
 
     def time_decode_steps(self, tok: int, pos: int, slot: int, steps: int) -> float:
         """Device time (ms) of ``steps`` consecutive batch-1 greedy decode steps with the sampled token fed

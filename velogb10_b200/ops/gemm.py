@@ -249,16 +249,17 @@ def swiglu_fp4(gu: torch.Tensor, n: int, inter: int, out16: Optional[torch.Tenso
 
 
 def add_rmsnorm_fp4_ar(res: torch.Tensor, w: torch.Tensor, eps: float, n: int, comm, out16: Optional[torch.Tensor] = None,
-                       plus_one: bool = True):
+                       plus_one: bool = True, mode: int = 1):
     """``add_rmsnorm_fp4`` whose delta is the tensor-parallel sum of the partial rows the preceding
-    ``linear_fp4(..., push_only=True)`` of every rank pushed into this rank's receive slots."""
+    ``linear_fp4(..., push_only=True)`` of every rank published: ``mode`` 1 = (value, epoch) pairs in this rank's
+    receive slots, 2 = fp32 rows in every rank's multimem slot, summed inside the NVLink switch."""
     h = res.shape[1]
     kp = ((h + 255) // 256) * 256
     bq, sfb, g0 = fp4_buffers(res.device, kp)
     rc = _lib.lib().vg_add_rmsnorm_fp4_ar(ptr(res), ptr(w), c_int(n), c_int(h), c_float(eps), c_int(1 if plus_one else 0),
                                           c_int(res.stride(0)), ptr(bq), c_int(bq.stride(0)), ptr(sfb), ptr(g0),
                                           ptr(out16) if out16 is not None else c_void_p(0), ctypes.byref(comm.ctx),
-                                          stream())
+                                          c_int(mode), stream())
     _lib.check(rc, "vg_add_rmsnorm_fp4_ar")
     return bq, sfb, g0
 
@@ -296,8 +297,9 @@ def linear_fp4(q: QLinear, x16: torch.Tensor, n: int, out: Optional[torch.Tensor
     """Decode-width linear on the block-scaled FP4 tensor-core path. ``act`` may carry an already quantised
     activation (several linears reading the same input share it). ``conv`` fuses the GatedDeltaNet causal
     conv of the leading ``conv_dim`` output rows into the epilogue. With ``comm`` the tensor-parallel sum is
-    fused into the epilogue; ``push_only`` stops after pushing the partial rows to every rank (nothing is written
-    to ``out``) and leaves the sum to ``add_rmsnorm_fp4_ar``."""
+    fused into the epilogue; ``push_only`` stops after publishing the partial rows (nothing is written to ``out``) and
+    leaves the sum to ``add_rmsnorm_fp4_ar``: rows are left in this rank's multimem slot for an in-switch reduction
+    when the communicator has a multicast address, else pushed to every rank as (value, epoch) pairs."""
     tw = prepare_fp4(q)
     assert n <= 16 and x16.shape[1] == tw.k
     bq, sfb, g0 = act if act is not None else quantize_act_fp4(x16, n, tw.kp)
@@ -307,7 +309,7 @@ def linear_fp4(q: QLinear, x16: torch.Tensor, n: int, out: Optional[torch.Tensor
                                 c_int(1 if out.dtype == torch.float32 else 0), c_int(tw.m), c_int(tw.k), c_int(n),
                                 c_int(out.stride(0)), c_int(tw.splitk), ptr(_lib.err_word(x16.device)),
                                 ctypes.byref(comm.ctx) if comm is not None else c_void_p(0),
-                                c_int(1 if push_only else 0),
+                                c_int((2 if comm.use_mm else 1) if (push_only and comm is not None) else 0),
                                 ctypes.byref(conv) if conv is not None else c_void_p(0), stream())
     _lib.check(rc, "vg_gemm_fp4")
     return out

@@ -214,3 +214,39 @@ def spec_verify(ids, probs, n_keep, drafts, u_acc, u_ver, col0, nd, n_lanes, res
     rc = _lib.lib().vg_spec_verify(ptr(ids), ptr(probs), ptr(n_keep), ptr(drafts), ptr(u_acc), ptr(u_ver), ptr(col0),
                                    ptr(nd), c_int(n_lanes), ptr(result), stream())
     _lib.check(rc, "vg_spec_verify")
+
+
+def gdn_chunk_work_bytes(tn: int, nv: int) -> int:
+    return int(_lib.lib().vg_gdn_chunk_work_bytes(c_int(tn), c_int(nv)))
+
+
+def gdn_chunk_prefill(qkv, proj, off_z, off_b, off_a, S, A_log, dt_bias, norm_w, t0, tn, in_slot, out_slot, out16, nk, nv, kd,
+                      vd, eps, work, o_raw):
+    """One linear chain of ``tn`` columns in chunked form on the tensor cores (64-token chunks, tf32 MMAs, fp32 state):
+    agrees with ``gdn_prefill`` / ``gdn_step`` to tf32 rounding. The carried state comes from slot ``in_slot[t0]`` and
+    is written to ``out_slot[t0 + tn - 1]`` when that is >= 0; there are no other checkpoints inside a call. ``work``:
+    uint8 scratch of ``gdn_chunk_work_bytes(tn, nv)`` bytes, 1024-byte aligned; ``o_raw``: fp32, ``(t0 + tn) * nv * vd``."""
+    L = _lib.lib()
+    L.vg_gdn_chunk_work_bytes.restype = c_ll
+    assert work.data_ptr() % 1024 == 0 and work.numel() >= gdn_chunk_work_bytes(tn, nv)
+    assert o_raw.numel() >= (t0 + tn) * nv * vd and qkv.is_contiguous()
+    rc = L.vg_gdn_chunk_prefill(ptr(qkv), ptr(proj), c_int(proj.stride(0)), c_int(off_z), c_int(off_b), c_int(off_a), ptr(S),
+                                ptr(A_log), ptr(dt_bias), ptr(norm_w), c_int(t0), c_int(tn), ptr(in_slot), ptr(out_slot),
+                                ptr(out16), c_int(nk), c_int(nv), c_int(kd), c_int(vd), c_float(eps), ptr(work), ptr(o_raw),
+                                ptr(_lib.err_word(qkv.device)), stream())
+    _lib.check(rc, "vg_gdn_chunk_prefill", 3)
+
+
+def attn_decode_tc(q, kc, vc, lens, slots, part, out16, n, nh, nkv, hd, gate=None, ns_grid: int = 32, block_table=None):
+    """Tensor-core split-K decode attention (head_dim 256, bf16 cache, query group <= 16). Slotted cache
+    ``[slots, nkv, max_seq, hd]``, or with ``block_table`` (int32 ``[n, pages]``) a pool ``[pages, nkv, 128, hd]`` of
+    128-key pages; column c's keys ``[128 p, 128 p + 128)`` live in page ``block_table[c, p]``."""
+    assert kc.dtype == torch.bfloat16 and kc.is_contiguous() and vc.is_contiguous() and hd == 256
+    rows = kc.numel() // hd
+    max_seq = kc.shape[2]
+    rc = _lib.lib().vg_attn_decode_tc(ptr(q), ptr(kc), ptr(vc), c_ll(rows), ptr(lens), ptr(slots), ptr(block_table),
+                                      c_int(block_table.stride(0) if block_table is not None else 0), ptr(part), c_int(n),
+                                      c_int(nh), c_int(nkv), c_int(hd), c_int(max_seq), c_int(ns_grid), ptr(gate),
+                                      c_int(gate.stride(0) if gate is not None else 0), ptr(out16),
+                                      ptr(_lib.err_word(q.device)), stream())
+    _lib.check(rc, "vg_attn_decode_tc", 2)

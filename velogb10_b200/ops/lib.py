@@ -39,6 +39,7 @@ def lib() -> ctypes.CDLL:
     L = ctypes.CDLL(path)
     L.vg_build_id.restype = ctypes.c_char_p
     L.vg_attn_scratch_floats.restype = c_ll
+    L.vg_gdn_chunk_work_bytes.restype = c_ll
     bid = L.vg_build_id().decode()
     if bid != _build.source_hash():
         raise KernelError(f"kernel library build id {bid} does not match sources {_build.source_hash()}")

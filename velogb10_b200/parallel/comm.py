@@ -10,6 +10,7 @@ It replaces the reference's two-node RDMA link (reference: src/net.rs:151-267, s
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import List, Optional
 
 import torch
@@ -28,11 +29,14 @@ class VgCommCtx(ctypes.Structure):
                 ("result_off", ctypes.c_ulonglong), ("result_bytes", ctypes.c_ulonglong),
                 ("epoch", ctypes.c_void_p), ("done_ctr", ctypes.c_void_p), ("status", ctypes.c_void_p),
                 ("timeout_ns", ctypes.c_ulonglong), ("agbuf_off", ctypes.c_ulonglong), ("agbuf_bytes", ctypes.c_ulonglong),
-                ("agflags_off", ctypes.c_ulonglong), ("rsflags_off", ctypes.c_ulonglong)]
+                ("agflags_off", ctypes.c_ulonglong), ("rsflags_off", ctypes.c_ulonglong),
+                ("mc", ctypes.c_void_p), ("mm_off", ctypes.c_ulonglong), ("mm_slot_bytes", ctypes.c_ulonglong),
+                ("mmflags_off", ctypes.c_ulonglong), ("mm_ctr", ctypes.c_void_p)]
 
 
 RS_MAX_TILES = 4096                      # per-tile epoch words of the fused GEMM + reduce-scatter, per (set, rank)
 AG_MAX_TILES = 256                       # per-tile epoch words of the fused all-gather + GEMM, per set
+MM_SLOT_BYTES = 1 << 20                  # fp32 partial rows of one decode-width collective (16 rows x 16384 columns)
 ARGMAX_MAX_COLS = 64                     # columns the arg-max merge buffers hold (csrc/api.h VG_ARGMAX_MAX_COLS)
 
 
@@ -58,26 +62,25 @@ class TpComm:
         self.agflags_off = self.rsflags_off + 2 * 8 * RS_MAX_TILES * 4
         self.agbuf_off = (self.agflags_off + 2 * AG_MAX_TILES * 4 + 1023) // 1024 * 1024
         self.agbuf_bytes = (ag_bytes + 1023) // 1024 * 1024      # two landing zones of the fused all-gather + GEMM
-        self.total = self.agbuf_off + self.agbuf_bytes
+        self.mmflags_off = (self.agbuf_off + self.agbuf_bytes + 1023) // 1024 * 1024
+        self.mm_off = self.mmflags_off + 4096          # flags: [2 sets][64 tiles][8 ranks] words
+        self.total = self.mm_off + 2 * MM_SLOT_BYTES
+        self.mc = 0                     # multicast (NVLS) address of the arena, 0 when it has none
+        self.arena_kind = "cuda-ipc"
+        self._symm = None
         with torch.cuda.device(self.dev):
-            base = ctypes.c_void_p()
-            _lib.check(self.L.vg_comm_alloc(ctypes.byref(base), ctypes.c_ulonglong(self.total)), "vg_comm_alloc")
-            self.base = base.value
-            hb = self.L.vg_comm_handle_bytes()
-            handle = (ctypes.c_ubyte * hb)()
-            _lib.check(self.L.vg_comm_export(base, handle), "vg_comm_export")
-            mine = bytes(handle)
-            handles: List[Optional[bytes]] = [None] * world
-            dist.all_gather_object(handles, mine, group=group)
-            self.peers: List[int] = []
-            for q in range(world):
-                if q == rank:
-                    self.peers.append(self.base)
-                    continue
-                p = ctypes.c_void_p()
-                buf = (ctypes.c_ubyte * hb).from_buffer_copy(handles[q])
-                _lib.check(self.L.vg_comm_import(buf, ctypes.byref(p)), "vg_comm_import")
-                self.peers.append(p.value)
+            # Preferred substrate: a symmetric allocation with an NVLink-switch multicast binding (torch's symmetric
+            # memory does the allocation and the handle exchange), which adds in-switch reductions to the peer
+            # pointers. VELO_NO_MULTIMEM=1 keeps the plain CUDA-IPC arena (peer loads / stores only): required for
+            # drills in which a rank may leave, since a dead rank must not hold memory bound to a multicast object.
+            if os.environ.get("VELO_NO_MULTIMEM", "0") != "1" and not use_nccl:
+                try:
+                    self._alloc_symmetric(group)
+                except Exception as e:  # noqa: BLE001 - any failure: the IPC arena serves every peer-pointer path
+                    self.arena_note = f"symmetric memory unavailable ({type(e).__name__}: {str(e)[:120]})"
+                    self._symm = None
+            if self._symm is None:
+                self._alloc_ipc(group)
         ctx = VgCommCtx()
         ctx.rank, ctx.world = rank, world
         for q in range(8):
@@ -88,7 +91,15 @@ class TpComm:
         ctx.timeout_ns = int(timeout_s * 1e9)
         ctx.rsflags_off = self.rsflags_off
         ctx.agbuf_off, ctx.agbuf_bytes, ctx.agflags_off = self.agbuf_off, self.agbuf_bytes, self.agflags_off
+        ctx.mc = self.mc or None
+        ctx.mm_off, ctx.mm_slot_bytes, ctx.mmflags_off = self.mm_off, MM_SLOT_BYTES, self.mmflags_off
+        ctx.mm_ctr = self.base + 12
         self.ctx = ctx
+        # decode-width all-reduce through the switch (multimem.ld_reduce) when the arena has a multicast address
+        # (measured on 2 GPUs the pair push is the faster of the two: one NVLink hop instead of flag + reduce round
+        # trip; its cost grows with the number of ranks, the in-switch form's does not)
+        mm_min = int(os.environ.get("VELO_MULTIMEM_MIN_WORLD", "4"))
+        self.use_mm = bool(self.mc) and world >= mm_min
         self._status_view = self._view(8, 1, torch.int32)
         self._pairs = torch.zeros(2 * ARGMAX_MAX_COLS, dtype=torch.float32, device=self.dev)
         self._gathered = torch.zeros(2 * ARGMAX_MAX_COLS * world, dtype=torch.float32, device=self.dev)
@@ -96,6 +107,50 @@ class TpComm:
         self._val = torch.zeros(ARGMAX_MAX_COLS, dtype=torch.float32, device=self.dev)
         self._idx = torch.zeros(ARGMAX_MAX_COLS, dtype=torch.int32, device=self.dev)
         dist.barrier(group=group)
+
+    def _alloc_ipc(self, group):
+        base = ctypes.c_void_p()
+        _lib.check(self.L.vg_comm_alloc(ctypes.byref(base), ctypes.c_ulonglong(self.total)), "vg_comm_alloc")
+        self.base = base.value
+        hb = self.L.vg_comm_handle_bytes()
+        handle = (ctypes.c_ubyte * hb)()
+        _lib.check(self.L.vg_comm_export(base, handle), "vg_comm_export")
+        mine = bytes(handle)
+        handles: List[Optional[bytes]] = [None] * self.world
+        dist.all_gather_object(handles, mine, group=group)
+        self.peers: List[int] = []
+        for q in range(self.world):
+            if q == self.rank:
+                self.peers.append(self.base)
+                continue
+            p = ctypes.c_void_p()
+            buf = (ctypes.c_ubyte * hb).from_buffer_copy(handles[q])
+            _lib.check(self.L.vg_comm_import(buf, ctypes.byref(p)), "vg_comm_import")
+            self.peers.append(p.value)
+
+    def _alloc_symmetric(self, group):
+        import torch.distributed._symmetric_memory as symm
+        t = symm.empty(self.total, dtype=torch.uint8, device=self.dev)
+        hdl = symm.rendezvous(t, group if group is not None else dist.group.WORLD)
+        off = int(getattr(hdl, "offset", 0) or 0)
+        peers = [int(p) + off for p in hdl.buffer_ptrs]
+        if len(peers) != self.world or peers[self.rank] != t.data_ptr():
+            raise RuntimeError("symmetric memory handle does not describe this allocation")
+        t.zero_()
+        torch.cuda.synchronize(self.dev)
+        self._symm = (t, hdl)
+        self.base, self.peers = t.data_ptr(), peers
+        mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
+        self.mc = mc + off if mc else 0
+        self.arena_kind = "symmetric+multicast" if self.mc else "symmetric"
+
+    def describe(self) -> dict:
+        """How this communicator moves data (recorded next to benchmark numbers)."""
+        return {"arena": self.arena_kind, "multicast": bool(self.mc), "note": getattr(self, "arena_note", ""),
+                "decode_allreduce": "nccl" if self.use_nccl else
+                ("in-switch multimem.ld_reduce of fp32 partials fused into GEMM epilogue + norm" if self.use_mm else
+                 "(value, epoch) pair push to every rank fused into GEMM epilogue + norm"),
+                "world": self.world}
 
     def _view(self, offset: int, n: int, dtype) -> torch.Tensor:
         """Torch view of a piece of this rank's arena."""
