@@ -166,6 +166,9 @@ class GpuModel:
         # --prefill-scalar: exact per-token prefill kernels only (bit-identical to stepping the decode kernels)
         self.prefill_exact = os.environ.get("VELO_PREFILL_SCALAR", "0") == "1"
         self.tc_prefill_attn = os.environ.get("VELO_NO_TC_PREFILL_ATTN", "0") != "1" and not self.prefill_exact
+        # decode / verify attention on the tensor cores (head_dim 256, bf16 cache, no tree paths); the CUDA-core
+        # split kernel serves every other case
+        self.tc_decode_attn = os.environ.get("VELO_TC_DECODE_ATTN", "1") == "1"
         self._prefill_ctx = None              # (slot, first position) while a prefill chunk is running
         self.kv_q4 = os.environ.get("VELO_KV_QUANT", "bf16").lower() == "q4"
         self._kv_scales = None                # (k scales, v scales) of the layer being run, 4-bit cache only
@@ -433,6 +436,10 @@ class GpuModel:
                 k_rows = self._k_rows
             K.attn_prefill_tc(ws.q, kc, vc, self._vt_scratch(A.nkv, kc.shape[2]), slot, pos0, n, A.nh, A.nkv, c.head_dim,
                               a16, gate=qkv if c.attn_out_gate else None, k_scale=ksc, v_scale=vsc, k_rows=k_rows)
+        elif (self.tc_decode_attn and not plan_direct and not use_path and ksc is None and c.head_dim == 256
+              and A.nh // A.nkv <= 16 and n <= 16):
+            K.attn_decode_tc(ws.q, kc, vc, ws.lens, ws.kv_slot, self.attn_part, a16, n, A.nh, A.nkv, c.head_dim,
+                             gate=qkv if c.attn_out_gate else None, ns_grid=self.ns_grid)
         else:
             K.attn_decode(ws.q, kc, vc, ws.lens, ws.kv_slot, self.attn_part, a16, n, A.nh, A.nkv, c.head_dim,
                           gate=qkv if c.attn_out_gate else None, base=ws.base if use_path else None,
