@@ -407,10 +407,14 @@ class Scheduler:
             # the draft ids come back in one read
             from ..ops import kernels as K
             outs = torch.empty(n_drafts, dtype=torch.int32, device=h.device)
+            ids = getattr(self.r, "draft_ids", None)            # draft-vocabulary head: row index -> token id
             tok_dev = None
             for d in range(n_drafts):
-                logits, hh = self.r.mtp_forward(lane.slot, [tok if d == 0 else 0], h.reshape(1, -1), [p], tok_dev=tok_dev)
+                logits, hh = self.r.mtp_forward(lane.slot, [tok if d == 0 else 0], h.reshape(1, -1), [p], tok_dev=tok_dev,
+                                                draft_only=True)
                 K.argmax(logits, 1, outs[d:d + 1])
+                if ids is not None and logits.shape[1] == ids.numel():
+                    outs[d:d + 1] = ids[outs[d:d + 1].long()].to(torch.int32)
                 tok_dev = outs[d:d + 1]
                 h, p = hh[0].clone(), p + 1
             return outs.tolist(), h

@@ -406,9 +406,22 @@ def profile_mtp(runner, cfg) -> int:
 
 
 def tp_barrier_bench(args) -> int:
-    """Adversarial all-reduce loop on the peer-memory transport: self-describing payloads, many epochs,
-    zero validation errors and zero timeouts required (run under torchrun)."""
+    """Adversarial loop over the peer-memory transport (run under torchrun): many epochs of every collective path with
+    payloads that name their epoch, checked ON THE DEVICE every epoch, random host-side stalls on one rank, and the
+    requirement of zero validation errors and zero timeouts (reference: src/tp_bench.rs:158-324). Paths (``--paths``):
+
+    * ``allreduce``  the stand-alone one-shot all-reduce kernel;
+    * ``fused``      the decode-width form used by the model: row-parallel FP4 GEMM whose epilogue publishes its partial
+                     rows + the residual-add / RMSNorm kernel that sums the ranks (pair push or in-switch reduction,
+                     whichever the communicator selected);
+    * ``gemm_rs``    prefill-width GEMM fused with the reduce-scatter + its finish kernel;
+    * ``ag_gemm``    all-gather pushes + flag-gated GEMM.
+
+    Inputs are scaled by 2^(epoch mod 8): every stage (FP4 series, GEMM, bf16 rounding) commutes exactly with a power
+    of two, so the expected output of epoch e is a precomputed reference times that factor and equality is exact. A
+    stale or torn read shows up as a mismatch because consecutive uses of a buffer set carry different factors."""
     import os
+    import random
     import torch.distributed as dist
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     if world < 2:
@@ -418,30 +431,135 @@ def tp_barrier_bench(args) -> int:
     dev = torch.device("cuda", local)
     if not dist.is_initialized():
         dist.init_process_group("nccl", device_id=dev)
+    from .models.weights import QLinear
+    from .ops import gemm as G
     from .parallel.comm import TpComm
-    comm = TpComm(rank, world, dev, max_elems=1 << 20)
-    epochs = int(args.get("--epochs", "2000"))
-    n = int(args.get("--elems", "5120"))
-    errors = 0
-    buf = torch.empty(1, n, dtype=torch.float32, device=dev)
-    t0 = time.time()
-    for e in range(epochs):
-        buf.fill_(float((e % 97) + rank))          # payload names its epoch and rank
-        comm.all_reduce_rows(buf, 1)
-        if e % 64 == 0:
-            want = float(world * (e % 97) + world * (world - 1) // 2)
-            errors += int((buf != want).any())
-    torch.cuda.synchronize()
-    dt = time.time() - t0
-    try:
-        comm.check()
+    comm = TpComm(rank, world, dev, max_elems=1 << 22, ag_bytes=2 * 512 * 1024 * 2 * 2)
+    paths = args.get("--paths", "allreduce,fused,gemm_rs,ag_gemm").split(",")
+    epochs = int(float(args.get("--epochs", "1000000")))
+    heavy_epochs = int(float(args.get("--heavy-epochs", str(max(1000, epochs // 50)))))
+    stall = rank == world - 1 and args.get("--stall", "on") != "off"
+    rnd = random.Random(1234)
+    gw = torch.Generator(device=dev).manual_seed(7)
+    h, kloc = 5120, 1024
+    results = {}
+    status_failed = False
+
+    def maybe_stall(e):
+        if stall and e % 997 == 0:
+            time.sleep(rnd.random() * (0.005 if e % 49850 == 0 else 0.0003))
+
+    def finish(name, n_ep, err_dev, t0):
+        nonlocal status_failed
+        torch.cuda.synchronize()
+        dt = time.time() - t0
         timeouts = 0
-    except Exception:  # noqa: BLE001
-        timeouts = 1
-    ok = errors == 0 and timeouts == 0
+        try:
+            comm.check()
+        except Exception:  # noqa: BLE001
+            timeouts = 1
+            status_failed = True
+        results[name] = {"epochs": n_ep, "validation_errors": int(err_dev.item()), "timeouts": timeouts,
+                         "us_per_epoch": dt / max(n_ep, 1) * 1e6}
+        dist.barrier()
+
+    scales = [float(2 ** i) for i in range(8)]
+    if "allreduce" in paths:
+        err = torch.zeros((), dtype=torch.int64, device=dev)
+        base = torch.arange(5120, device=dev, dtype=torch.float32).remainder(61).add_(rank + 1).reshape(1, -1)
+        want = sum((torch.arange(5120, device=dev, dtype=torch.float32).remainder(61) + q + 1) for q in range(world)).reshape(1, -1)
+        ins = [base * s_ for s_ in scales]
+        wants = [want * s_ for s_ in scales]
+        buf = torch.empty_like(base)
+        t0 = time.time()
+        for e in range(epochs):
+            maybe_stall(e)
+            buf.copy_(ins[e % 8])
+            comm.all_reduce_rows(buf, 1)
+            err += (buf != wants[e % 8]).any()
+        finish("allreduce", epochs, err, t0)
+    if "fused" in paths:
+        wf = (torch.randn(h, kloc * world, generator=gw, device=dev) * 0.05).to(torch.bfloat16)
+        xa = torch.randn(16, kloc * world, generator=gw, device=dev).to(torch.float16)
+        q = QLinear.from_dense(wf[:, rank * kloc:(rank + 1) * kloc].contiguous(), "nvfp4")
+        x_loc = [(xa[:, rank * kloc:(rank + 1) * kloc] * s_).contiguous() for s_ in scales]
+        acts = []
+        for xs in x_loc:                                  # private quantised copies: the loop then only runs the fused pair
+            bq, sfb, g0 = G.quantize_act_fp4(xs, 4, q.kernel4.kp if getattr(q, "kernel4", None) else G.prepare_fp4(q).kp)
+            acts.append((bq.clone(), sfb.clone(), g0.clone()))
+        ones = torch.zeros(h, device=dev)
+        x16 = torch.zeros(16, h, dtype=torch.float16, device=dev)
+        dummy = torch.zeros(16, h, dtype=torch.bfloat16, device=dev)
+        mode = 2 if comm.use_mm else 1
+        res = torch.zeros(16, h, dtype=torch.bfloat16, device=dev)
+        refs = []
+        for i in range(8):                                # reference = what the path itself produces once, then it must repeat
+            res.zero_()
+            G.linear_fp4(q, x_loc[i], 4, out=dummy, comm=comm, act=acts[i], push_only=True)
+            G.add_rmsnorm_fp4_ar(res, ones, 1e-6, 4, comm, out16=x16, mode=mode)
+            refs.append(res[:4].clone())
+        torch.cuda.synchronize()
+        exact_scaling = all(torch.equal(refs[i], refs[0] * scales[i]) for i in range(8))
+        err = torch.zeros((), dtype=torch.int64, device=dev)
+        t0 = time.time()
+        for e in range(epochs):
+            maybe_stall(e)
+            res.zero_()
+            G.linear_fp4(q, x_loc[e % 8], 4, out=dummy, comm=comm, act=acts[e % 8], push_only=True)
+            G.add_rmsnorm_fp4_ar(res, ones, 1e-6, 4, comm, out16=x16, mode=mode)
+            err += (res[:4] != refs[e % 8]).any()
+        finish("fused", epochs, err, t0)
+        results["fused"]["power_of_two_scaling_exact"] = bool(exact_scaling)
+        results["fused"]["form"] = "in-switch multimem.ld_reduce" if comm.use_mm else "(value, epoch) pair push"
+    if "gemm_rs" in paths:
+        n_tok, M_, K_ = 256 * world, 1024, 1024
+        w = (torch.randn(M_, K_ * world, generator=gw, device=dev) * 0.05).to(torch.bfloat16)
+        xf = torch.randn(n_tok, K_ * world, generator=gw, device=dev).to(torch.float16)
+        q = QLinear.from_dense(w[:, rank * K_:(rank + 1) * K_].contiguous(), "nvfp4")
+        G.prepare(q)
+        xs = [(xf[:, rank * K_:(rank + 1) * K_] * s_).contiguous() for s_ in scales]
+        out = torch.zeros(n_tok, M_, dtype=torch.bfloat16, device=dev)
+        rs_rows = comm.rs_rows_for(n_tok, M_)
+        refs = []
+        for i in range(8):
+            G.linear(q, xs[i], n_tok, out=out, comm=comm, rs_rows=rs_rows)
+            comm.gemm_rs_finish(out, n_tok, rs_rows)
+            refs.append(out.clone())
+        err = torch.zeros((), dtype=torch.int64, device=dev)
+        t0 = time.time()
+        for e in range(heavy_epochs):
+            maybe_stall(e * 50)
+            G.linear(q, xs[e % 8], n_tok, out=out, comm=comm, rs_rows=rs_rows)
+            comm.gemm_rs_finish(out, n_tok, rs_rows)
+            err += (out != refs[e % 8]).any()
+        finish("gemm_rs", heavy_epochs, err, t0)
+    if "ag_gemm" in paths:
+        rows_per, K_, M_ = 128, 1024, 512
+        n_total = rows_per * world
+        w = (torch.randn(M_, K_, generator=gw, device=dev) * 0.05).to(torch.bfloat16)
+        xf = torch.randn(n_total, K_, generator=gw, device=dev).to(torch.float16)
+        q = QLinear.from_dense(w, "nvfp4")
+        shards = [(xf[rank * rows_per:(rank + 1) * rows_per] * s_).contiguous() for s_ in scales]
+        out = torch.zeros(n_total, M_, dtype=torch.bfloat16, device=dev)
+        refs = []
+        for i in range(8):
+            comm.ag_gemm(q, shards[i], rank * rows_per, n_total, out)
+            refs.append(out.clone())
+        err = torch.zeros((), dtype=torch.int64, device=dev)
+        t0 = time.time()
+        for e in range(heavy_epochs):
+            maybe_stall(e * 50)
+            comm.ag_gemm(q, shards[e % 8], rank * rows_per, n_total, out)
+            err += (out != refs[e % 8]).any()
+        finish("ag_gemm", heavy_epochs, err, t0)
+    ok = all(r["validation_errors"] == 0 and r["timeouts"] == 0 for r in results.values()) and not status_failed
+    # every rank must have seen a clean run
+    flag = torch.tensor([0 if ok else 1], device=dev)
+    dist.all_reduce(flag)
+    ok = int(flag.item()) == 0
     if rank == 0:
-        _emit("tp-barrier-bench", ok, epochs=epochs, elems=n, validation_errors=errors, timeouts=timeouts,
-              us_per_allreduce=dt / epochs * 1e6)
+        _emit("tp-barrier-bench", ok, world=world, stalls_injected=bool(args.get("--stall", "on") != "off"),
+              arena=comm.describe()["arena"], **results)
     dist.barrier()
     return 0 if ok else 1
 

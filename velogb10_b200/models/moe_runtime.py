@@ -116,6 +116,11 @@ def moe_forward(model, ws, M: MoeW, n: int, act=None):
                 joined = model.moe_join_event
                 joined.record(model.moe_side_stream)
     _small_linear(M.router, ws.xn16, n, b.logits)
+    hook = getattr(model, "router_logits_hook", None)
+    if hook is not None:
+        # test / analysis hook: sees (and may overwrite) the fp32 router logits [n, E] before the top-k selection,
+        # e.g. to replay another run's routing so that two runs differ only in how the expert outputs are summed
+        hook(b.logits, n)
     P = n * topk
     decode = ws.cap <= DECODE_MAX
     rc = L.vg_moe_router(ptr(b.logits), c_int(n), c_int(E), c_int(topk), c_int(1 if cfg.router_sigmoid else 0),
@@ -165,18 +170,22 @@ def moe_forward(model, ws, M: MoeW, n: int, act=None):
             and h % 16 == 0 and n * h * 8 <= comm.slot_bytes and os.environ.get("VELO_NO_MOE_PUSH", "0") != "1":
         # combine fused with the expert-parallel all-reduce: the partial rows go straight into every rank's receive
         # slots and the next residual-add / RMSNorm kernel sums them (rank 0 contributes the replicated shared expert)
-        first = comm.rank == 0
+        # a sharded shared expert contributes a partial on every rank; a replicated one is added by rank 0 only
+        first = comm.rank == 0 or getattr(M.shared, "partial", False)
         rc = L.vg_moe_combine_push(ptr(b.y), c_int(b.y.stride(0)), ptr(inv), ptr(b.wts), c_int(n), c_int(topk),
                                    ptr(shared if first else None), ptr(gate if first else None), c_int(h),
                                    ctypes.byref(comm.ctx), stream())
         _lib.check(rc, "vg_moe_combine_push")
         model._pending_ar = 1
         return
+    sh_partial = ep and shared is not None and getattr(M.shared, "partial", False)
+    with_shared = (not ep) or sh_partial
     rc = L.vg_moe_combine(ptr(b.y), c_int(b.y.stride(0)), ptr(inv), ptr(b.wts), c_int(n), c_int(topk),
-                          ptr(None if ep else shared), ptr(None if ep else gate), ptr(ws.delta), c_int(h), stream())
+                          ptr(shared if with_shared else None), ptr(gate if with_shared else None), ptr(ws.delta), c_int(h),
+                          stream())
     _lib.check(rc, "vg_moe_combine")
     if ep:
         comm.all_reduce_rows(ws.delta, n)
-        if shared is not None:
+        if shared is not None and not sh_partial:
             rc = L.vg_moe_add_shared(ptr(ws.delta), ptr(shared), ptr(gate), c_int(n), c_int(h), stream())
             _lib.check(rc, "vg_moe_add_shared")

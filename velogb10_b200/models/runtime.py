@@ -625,10 +625,12 @@ class GpuModel:
 
     # ---------------------------------------------------------------- MTP head
     def mtp_forward(self, slot: int, tokens: Sequence[int], hidden: torch.Tensor, pos: Sequence[int],
-                    tok_dev: Optional[torch.Tensor] = None):
+                    tok_dev: Optional[torch.Tensor] = None, draft_only: bool = False):
         """Draft head over N (hidden_t, token_{t+1}) pairs of one lane (replicated on every rank).
         Returns (logits [N, V_local] fp32, head hidden [N, h] bf16). ``tok_dev`` (int32 device tensor, N ids) replaces
-        ``tokens`` without a host round trip (a draft chain feeds each draft straight into the next step)."""
+        ``tokens`` without a host round trip (a draft chain feeds each draft straight into the next step). With
+        ``draft_only`` and a draft-vocabulary head the logits returned are the ``[N, Vd]`` draft-vocabulary scores
+        (ids through ``self.draft_ids``) and the scatter into full-vocabulary rows is skipped."""
         m, c, ws = self.w.mtp, self.cfg, self.ws
         n = len(tokens)
         plan = Plan.chain(slot, tokens, 0, None)
@@ -659,6 +661,8 @@ class GpuModel:
                 self._draft_logits = torch.zeros((ws.logits.shape[0], self.draft_head.m), dtype=torch.float32, device=self.dev)
                 dl = self._draft_logits[:n]
             self._linear(self.draft_head, ws.xn16, n, self._draft_logits, act=act, out_f32=True)
+            if draft_only:
+                return dl, ws.x[:n]
             ws.logits[:n].fill_(float("-inf"))
             ws.logits[:n].index_copy_(1, self.draft_ids, dl)
             return ws.logits[:n], ws.x[:n]

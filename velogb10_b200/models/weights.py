@@ -451,7 +451,12 @@ class ModelBuilder:
         sg = None
         if c.shared_expert_intermediate_size > 0 and self._t(pre + "shared_expert.gate_proj.weight") is not None \
                 or self._t(pre + "shared_expert.gate_proj.weight_packed") is not None:
-            shared = self.mlp(pre + "shared_expert.", c.shared_expert_intermediate_size, shard=False)
+            # under expert parallelism the shared expert is split like a dense tensor-parallel MLP: every rank adds its
+            # partial (through the same gate) to its routed partial, and the one reduction of the layer sums both
+            si = c.shared_expert_intermediate_size
+            split = shard and self.world > 1 and self.ep and si % (16 * self.world) == 0
+            shared = self.mlp(pre + "shared_expert.", si, shard=split)
+            shared.partial = split
             sgl = self.linear(pre + "shared_expert_gate")
             sg = sgl if sgl.fmt == "bf16" else QLinear.from_dense(sgl.dequant(torch.bfloat16), "bf16")
         bias = self._t(pre + "expert_bias")
