@@ -201,20 +201,28 @@ __global__ void __launch_bounds__(512) add_rmsnorm_fp4_kernel(__nv_bfloat16* res
         const size_t stride = c.slot_bytes;
 #pragma unroll
         for (int i = 0; i < 16; ++i) dv[i] = 0.f;
-        for (int q = 0; q < c.world; ++q) {
-          const uint4* src = reinterpret_cast<const uint4*>(c.data[c.rank] + c.slots_off + (size_t)(ar_set * MAX_RANKS + q) * stride) +
-                             (((size_t)n * h + b * 16) >> 1);
-          uint4 v[8];
+        // Two ranks' pairs are fetched per poll round (sixteen independent 16-byte loads in flight), so the wait
+        // costs world / 2 round trips to L2 instead of world; the sums still run in rank order.
+        for (int q = 0; q < c.world; q += 2) {
+          const uint4* src0 = reinterpret_cast<const uint4*>(c.data[c.rank] + c.slots_off + (size_t)(ar_set * MAX_RANKS + q) * stride) +
+                              (((size_t)n * h + b * 16) >> 1);
+          const bool two = q + 1 < c.world;
+          const uint4* src1 = two ? reinterpret_cast<const uint4*>(c.data[c.rank] + c.slots_off + (size_t)(ar_set * MAX_RANKS + q + 1) * stride) +
+                                        (((size_t)n * h + b * 16) >> 1)
+                                  : src0;
+          uint4 v[8], w[8];
           uint64_t t_start = 0;
           for (int tries = 0;; ++tries) {
             bool ok = true;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                           : "=r"(v[i].x), "=r"(v[i].y), "=r"(v[i].z), "=r"(v[i].w) : "l"(src + i) : "memory");
+                           : "=r"(v[i].x), "=r"(v[i].y), "=r"(v[i].z), "=r"(v[i].w) : "l"(src0 + i) : "memory");
+              asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(w[i].x), "=r"(w[i].y), "=r"(w[i].z), "=r"(w[i].w) : "l"(src1 + i) : "memory");
             }
 #pragma unroll
-            for (int i = 0; i < 8; ++i) ok = ok && v[i].y == ar_e && v[i].w == ar_e;
+            for (int i = 0; i < 8; ++i) ok = ok && v[i].y == ar_e && v[i].w == ar_e && w[i].y == ar_e && w[i].w == ar_e;
             if (ok) break;
             if (tries == 64) t_start = global_ns();
             if (tries > 64 && (tries & 63) == 0 && global_ns() - t_start > c.timeout_ns) {
@@ -224,6 +232,10 @@ __global__ void __launch_bounds__(512) add_rmsnorm_fp4_kernel(__nv_bfloat16* res
           }
 #pragma unroll
           for (int i = 0; i < 8; ++i) { dv[2 * i] += __uint_as_float(v[i].x); dv[2 * i + 1] += __uint_as_float(v[i].z); }
+          if (two) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { dv[2 * i] += __uint_as_float(w[i].x); dv[2 * i + 1] += __uint_as_float(w[i].z); }
+          }
         }
         // the unfused path stores the sum as bf16 before the residual add: keep the same rounding
 #pragma unroll

@@ -181,6 +181,7 @@ int vg_comm_close(void* ptr);
 int vg_comm_handle_bytes(void);
 int vg_comm_allreduce(const VgCommCtx* ctx, const void* in, int in_is_f32, void* out_bf16, float* out_f32, long long n,
                       cudaStream_t stream);
+int vg_comm_allreduce_multimem(const VgCommCtx* ctx, void* mc_buf, long long n, cudaStream_t stream);
 int vg_comm_allgather_small(const VgCommCtx* ctx, const void* in, void* out, int bytes, cudaStream_t stream);
 int vg_comm_argmax_merge(const VgCommCtx* ctx, const float* val, const int* idx, int ncols, float* scratch_pairs,
                          float* gathered, int* out, cudaStream_t stream);

@@ -203,14 +203,27 @@ __global__ void attn_merge_kernel(const float* __restrict__ part, const int* __r
   const int col = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
   const int ns = splits_for(lens[col], ns_grid);
   const float* pp = part + ((size_t)col * nh + head) * ns_grid * (HD + 2);
+  // every split's three values are fetched before the first is used (the loads are independent: one L2 latency, not
+  // one per split); the sums still run over the splits in index order
+  float ms[32], ls[32], as[32];
+#pragma unroll
+  for (int s = 0; s < 32; ++s) {
+    const bool on = s < ns;
+    ms[s] = on ? pp[(size_t)s * (HD + 2)] : -INFINITY;
+    ls[s] = on ? pp[(size_t)s * (HD + 2) + 1] : 0.f;
+    as[s] = on ? pp[(size_t)s * (HD + 2) + 2 + d] : 0.f;
+  }
   float M = -INFINITY;
-  for (int s = 0; s < ns; ++s) M = fmaxf(M, pp[(size_t)s * (HD + 2)]);
+#pragma unroll
+  for (int s = 0; s < 32; ++s) M = fmaxf(M, ms[s]);
   float L = 0.f, A = 0.f;
-  for (int s = 0; s < ns; ++s) {
-    const float ms = pp[(size_t)s * (HD + 2)];
-    const float e = ms == -INFINITY ? 0.f : __expf(ms - M);
-    L += pp[(size_t)s * (HD + 2) + 1] * e;
-    A += pp[(size_t)s * (HD + 2) + 2 + d] * e;
+#pragma unroll
+  for (int s = 0; s < 32; ++s) {
+    if (s < ns) {
+      const float e = ms[s] == -INFINITY ? 0.f : __expf(ms[s] - M);
+      L += ls[s] * e;
+      A += as[s] * e;
+    }
   }
   float o = L > 0.f ? A / L : 0.f;
   // gate layout inside the fused qkv row: head h occupies [h*2hd, h*2hd+hd) = q, [.. + hd, .. + 2hd) = gate

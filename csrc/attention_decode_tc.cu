@@ -9,8 +9,9 @@
 //                   through shared memory), P written to shared memory as the bf16 B operand [head][key]
 //   O^T += V^T P^T  A = the V tile used MN-major (dim is the M index, keys the contraction index: the cache layout
 //                   [key][dim] is exactly that, so no transposed copy is needed), two M = 128 halves of the 256 dims
-// K and V tiles travel through a three-slot ring of 64 KB stages filled by TMA, so loads run ahead of the math and
-// the kernel is bound by HBM. The split rule (a pure function of the column's own length), the partial-buffer format
+// K tiles travel through a two-slot ring and V tiles through one slot (64 KB each), filled by TMA from their own
+// producer warps; S and P are double-buffered, and the issuer puts S(t+1) = K(t+1) Q^T ahead of O += V(t)^T P(t)^T, so
+// the softmax of the next tile runs while the tensor core finishes the current one and the loads stay ahead of both. The split rule (a pure function of the column's own length), the partial-buffer format
 // (max, sum, unnormalised accumulator per head and split) and the merge kernel are those of attention.cu, so a
 // column's result does not depend on what else is in the batch (reference: kernels/gpu_batch.cu:1968-1975, :2132
 // gqa_attn_splitk_gq reads each KV tile once per query group; this is the tensor-core form of that idea).
@@ -36,10 +37,10 @@ constexpr int SUB = 128 * 128;                // [128 rows x 64 bf16] swizzled s
 constexpr int TILE = 4 * SUB;                 // 64 KB: one K or V tile
 constexpr int NSLOT = 3;
 constexpr int Q_BYTES = 4 * 2048;             // [16 heads][256 dims]: four [16 rows x 128 B] panels
-constexpr int P_BYTES = 2 * 2048;             // [16 heads][128 keys]: two panels
-constexpr int SMEM_BYTES = NSLOT * TILE + Q_BYTES + P_BYTES + 1024 + 256 + 1024;
-constexpr int THREADS = 192;                  // warp 0 copies, warp 1 issues MMAs, warps 2..5 softmax / epilogue
-constexpr uint32_t TM_S = 0, TM_O = 16, TM_COLS = 64;
+constexpr int P_BYTES = 2 * 2048;             // [16 heads][128 keys]: two panels (two such buffers)
+constexpr int SMEM_BYTES = NSLOT * TILE + Q_BYTES + 2 * P_BYTES + 1024 + 256 + 1024;
+constexpr int THREADS = 224;                  // warp 0 K copies, warp 1 MMA issue, warps 2..5 softmax / epilogue, warp 6 V copies
+constexpr uint32_t TM_S = 0, TM_O = 32, TM_COLS = 64;     // S: two 16-column buffers; O^T: two 16-column halves
 
 VG_DEVINL void tmem_ld16(uint32_t taddr, uint32_t* r) {
   asm volatile(
@@ -94,15 +95,17 @@ attn_decode_tc_kernel(const DecParams p, const __grid_constant__ CUtensorMap tm_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* ring = smem;
   uint8_t* sQ = ring + NSLOT * TILE;
-  uint8_t* sP = sQ + Q_BYTES;
-  float* xch = reinterpret_cast<float*>(sP + P_BYTES);           // [4 warps][16 heads] tile maxima, then sums
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES + 1024);
-  uint64_t* full = bars;                  // [NSLOT]
-  uint64_t* empty = bars + NSLOT;         // [NSLOT]
-  uint64_t* s_full = bars + 2 * NSLOT;
-  uint64_t* p_ready = s_full + 1;
-  uint64_t* o_done = s_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 3);
+  uint8_t* sP = sQ + Q_BYTES;                                       // two P buffers
+  float* xch = reinterpret_cast<float*>(sP + 2 * P_BYTES);         // [4 warps][16 heads] tile maxima, then sums
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * P_BYTES + 1024);
+  uint64_t* k_full = bars;                // [2]
+  uint64_t* k_empty = bars + 2;           // [2]
+  uint64_t* v_full = bars + 4;
+  uint64_t* v_empty = bars + 5;
+  uint64_t* s_full = bars + 6;            // [2]
+  uint64_t* p_ready = bars + 8;           // [2]
+  uint64_t* pv_done = bars + 10;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -119,8 +122,8 @@ attn_decode_tc_kernel(const DecParams p, const __grid_constant__ CUtensorMap tm_
   const int G = p.nh / p.nkv, h0 = kvh * G;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NSLOT; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-    mbar_init(s_full, 1); mbar_init(p_ready, 128); mbar_init(o_done, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&s_full[i], 1); mbar_init(&p_ready[i], 128); }
+    mbar_init(v_full, 1); mbar_init(v_empty, 1); mbar_init(pv_done, 1);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
@@ -136,7 +139,7 @@ attn_decode_tc_kernel(const DecParams p, const __grid_constant__ CUtensorMap tm_
     if (row < G) v = *reinterpret_cast<const uint4*>(p.q + ((size_t)col * p.nh + h0 + row) * HD + c16 * 8);
     *reinterpret_cast<uint4*>(sQ + (c16 >> 3) * 2048 + row * 128 + (((c16 & 7) ^ (row & 7)) << 4)) = v;
   }
-  for (int c = threadIdx.x; c < P_BYTES / 16; c += THREADS) reinterpret_cast<uint4*>(sP)[c] = make_uint4(0, 0, 0, 0);
+  for (int c = threadIdx.x; c < 2 * P_BYTES / 16; c += THREADS) reinterpret_cast<uint4*>(sP)[c] = make_uint4(0, 0, 0, 0);
   fence_proxy_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -144,53 +147,69 @@ attn_decode_tc_kernel(const DecParams p, const __grid_constant__ CUtensorMap tm_
   const uint32_t tmem_base = *tmem_slot;
   auto fail = [&](int code) { if (p.err) atomicCAS(p.err, 0, code); *abort_flag = 1; };
 
+  auto tile_row = [&](int t) -> int {
+    const int page = page0 + t;
+    if (p.block_table) return (int)(((long long)p.block_table[(size_t)col * p.bt_ld + page] * p.nkv + kvh) * BK);
+    return (int)(((long long)p.slots[col] * p.nkv + kvh) * p.max_seq + (long long)page * BK);
+  };
   if (warp == 0) {
-    if (lane == 0) {
-      // ring order: K tile 0, V tile 0, K tile 1, V tile 1, ...
-      for (int i = 0; i < 2 * ntiles && !*abort_flag; ++i) {
-        const int s = i % NSLOT, t = i >> 1;
-        if (!mbar_wait(&empty[s], ((i / NSLOT) & 1) ^ 1)) { fail(VG_ERR_EMPTY_WAIT); break; }
-        const int page = page0 + t;
-        long long row0;
-        if (p.block_table) row0 = ((long long)p.block_table[(size_t)col * p.bt_ld + page] * p.nkv + kvh) * BK;
-        else row0 = ((long long)p.slots[col] * p.nkv + kvh) * p.max_seq + (long long)page * BK;
+    if (lane == 0) {                                         // K tiles: slots 0, 1 of the ring
+      for (int t = 0; t < ntiles && !*abort_flag; ++t) {
+        const int s = t & 1;
+        if (!mbar_wait(&k_empty[s], ((t >> 1) & 1) ^ 1)) { fail(VG_ERR_EMPTY_WAIT); break; }
         uint8_t* dst = ring + (size_t)s * TILE;
-        mbar_arrive_expect_tx(&full[s], TILE);
-        const CUtensorMap* tm = (i & 1) ? &tm_v : &tm_k;
+        const int row0 = tile_row(t);
+        mbar_arrive_expect_tx(&k_full[s], TILE);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) tma_tensor2d_g2s(dst + j * SUB, tm, 64 * j, (int)row0, &full[s]);
+        for (int j = 0; j < 4; ++j) tma_tensor2d_g2s(dst + j * SUB, &tm_k, 64 * j, row0, &k_full[s]);
+      }
+    }
+  } else if (warp == 6) {
+    if (lane == 0) {                                         // V tiles: slot 2
+      for (int t = 0; t < ntiles && !*abort_flag; ++t) {
+        if (!mbar_wait(v_empty, (t & 1) ^ 1)) { fail(VG_ERR_EMPTY_WAIT); break; }
+        uint8_t* dst = ring + (size_t)2 * TILE;
+        const int row0 = tile_row(t);
+        mbar_arrive_expect_tx(v_full, TILE);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) tma_tensor2d_g2s(dst + j * SUB, &tm_v, 64 * j, row0, v_full);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc_f16(128, 16, 1, 1);                  // bf16 x bf16 -> fp32, K-major both
       constexpr uint32_t idesc_o = umma_idesc_f16(128, 16, 1, 1) | (1u << 15);     // A (the V tile) MN-major
-      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      const uint64_t q_desc = umma_desc_sw128(smem_u32(sQ));
+      const uint64_t v_desc = umma_desc_mn_sw128(smem_u32(ring + (size_t)2 * TILE), SUB, 1024);
       bool ok = true;
-      for (int t = 0; t < ntiles && ok && !*abort_flag; ++t) {
-        const int ik = 2 * t, iv = 2 * t + 1;
-        const int sk = ik % NSLOT, sv = iv % NSLOT;
-        if (!mbar_wait(&full[sk], (ik / NSLOT) & 1)) { fail(VG_ERR_TMA_WAIT); ok = false; break; }
+      auto issue_qk = [&](int t) -> bool {
+        const int s = t & 1;
+        if (!mbar_wait(&k_full[s], (t >> 1) & 1)) { fail(VG_ERR_TMA_WAIT); return false; }
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(ring + (size_t)sk * TILE);
+        const uint64_t k_desc = umma_desc_sw128(smem_u32(ring + (size_t)s * TILE));
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          umma_f16(tmem_base + TM_S, umma_desc_sw128(k_addr + (kk >> 2) * SUB + (kk & 3) * 32),
-                   umma_desc_sw128(q_addr + (kk >> 2) * 2048 + (kk & 3) * 32), idesc_s, kk ? 1u : 0u);
-        umma_commit(&empty[sk]);
-        umma_commit(s_full);
-        if (!mbar_wait(p_ready, t & 1)) { fail(VG_ERR_MMA_WAIT); ok = false; break; }
-        if (!mbar_wait(&full[sv], (iv / NSLOT) & 1)) { fail(VG_ERR_TMA_WAIT); ok = false; break; }
+          umma_f16(tmem_base + TM_S + s * 16, k_desc + (uint64_t)(((kk >> 2) * SUB + (kk & 3) * 32) >> 4),
+                   q_desc + (uint64_t)(((kk >> 2) * 2048 + (kk & 3) * 32) >> 4), idesc_s, kk ? 1u : 0u);
+        umma_commit(&k_empty[s]);
+        umma_commit(&s_full[s]);
+        return true;
+      };
+      if (ntiles > 0) ok = issue_qk(0);
+      for (int t = 0; t < ntiles && ok && !*abort_flag; ++t) {
+        if (t + 1 < ntiles && !issue_qk(t + 1)) { ok = false; break; }            // S(t+1) ahead of O += V(t)^T P(t)^T
+        if (!mbar_wait(&p_ready[t & 1], (t >> 1) & 1)) { fail(VG_ERR_MMA_WAIT); ok = false; break; }
+        if (!mbar_wait(v_full, t & 1)) { fail(VG_ERR_TMA_WAIT); ok = false; break; }
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(ring + (size_t)sv * TILE);
+        const uint64_t p_desc = umma_desc_sw128(smem_u32(sP + (t & 1) * P_BYTES));
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
           for (int ks = 0; ks < BK / 16; ++ks)
-            umma_f16(tmem_base + TM_O + mt * 16, umma_desc_mn_sw128(v_addr + mt * 2 * SUB + ks * 2048, SUB, 1024),
-                     umma_desc_sw128(p_addr + (ks >> 2) * 2048 + (ks & 3) * 32), idesc_o, (t || ks) ? 1u : 0u);
-        umma_commit(&empty[sv]);
-        if (t == ntiles - 1) umma_commit(o_done);
+            umma_f16(tmem_base + TM_O + mt * 16, v_desc + (uint64_t)((mt * 2 * SUB + ks * 2048) >> 4),
+                     p_desc + (uint64_t)(((ks >> 2) * 2048 + (ks & 3) * 32) >> 4), idesc_o, (t || ks) ? 1u : 0u);
+        umma_commit(v_empty);
+        umma_commit(pv_done);
       }
     }
   } else {
@@ -203,12 +222,13 @@ attn_decode_tc_kernel(const DecParams p, const __grid_constant__ CUtensorMap tm_
     for (int h = 0; h < 16; ++h) { m_run[h] = -INFINITY; l_run[h] = 0.f; }
     bool ok = true;
     for (int t = 0; t < ntiles && ok && !*abort_flag; ++t) {
-      if (!mbar_wait(s_full, t & 1)) { fail(VG_ERR_MMA_WAIT); ok = false; break; }
+      if (!mbar_wait(&s_full[t & 1], (t >> 1) & 1)) { fail(VG_ERR_MMA_WAIT); ok = false; break; }
       tc_fence_after();
       const int key = (page0 + t) * BK + r;
       const bool valid = key >= k0 && key < k1;
+      uint8_t* sPt = sP + (t & 1) * P_BYTES;
       uint32_t sv[16];
-      tmem_ld16(lane_base + TM_S, sv);
+      tmem_ld16(lane_base + TM_S + (t & 1) * 16, sv);
       tmem_ld_wait();
       float s[16];
 #pragma unroll
@@ -235,10 +255,15 @@ attn_decode_tc_kernel(const DecParams p, const __grid_constant__ CUtensorMap tm_
         // the sum runs over the rounded values the tensor core will multiply with
         l_run[h] = l_run[h] * corr[h] + __bfloat162float(pb);
         m_run[h] = m_new;
-        *reinterpret_cast<__nv_bfloat16*>(sP + (r >> 6) * 2048 + h * 128 + ((((r & 63) >> 3) ^ (h & 7)) << 4) + (r & 7) * 2) = pb;
+        *reinterpret_cast<__nv_bfloat16*>(sPt + (r >> 6) * 2048 + h * 128 + ((((r & 63) >> 3) ^ (h & 7)) << 4) + (r & 7) * 2) = pb;
       }
-      // rescale O^T when some head's maximum moved (uniform: every thread sees the same maxima). The previous P V
-      // has completed: MMAs retire in order and this tile's S came after it.
+      // The previous tile's P V must have completed before O^T is rescaled (and it implies the one before, whose P
+      // buffer this tile has just rewritten, completed too: that was awaited one tile ago).
+      if (t > 0) {
+        if (!mbar_wait(pv_done, (t - 1) & 1)) { fail(VG_ERR_MMA_WAIT); ok = false; break; }
+        tc_fence_after();
+      }
+      // rescale O^T when some head's maximum moved (uniform: every thread sees the same maxima)
       if (t > 0 && moved) {
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt) {
@@ -253,11 +278,11 @@ attn_decode_tc_kernel(const DecParams p, const __grid_constant__ CUtensorMap tm_
       }
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(p_ready);
+      mbar_arrive(&p_ready[t & 1]);
       asm volatile("bar.sync 1, 128;" ::: "memory");          // xch is rewritten by the next tile
     }
     if (ok && !*abort_flag && ntiles > 0) {
-      if (!mbar_wait(o_done, 0)) { fail(VG_ERR_MMA_WAIT); ok = false; }
+      if (!mbar_wait(pv_done, (ntiles - 1) & 1)) { fail(VG_ERR_MMA_WAIT); ok = false; }
     }
     if (ok && !*abort_flag) {
       tc_fence_after();
@@ -370,5 +395,7 @@ extern "C" int vg_attn_decode_tc(const void* q, const void* kc, const void* vc, 
   }
   cudaError_t e = launch_pdl(attn_decode_tc_kernel, dim3(N, nkv, ns_grid), dim3(THREADS), SMEM_BYTES, st, p, tk, tv);
   if (e != cudaSuccess) return (int)e;
+  // (A merge by the last-arriving split inside this launch was measured and rejected: one CTA pulling a KV head's
+  // 6 x 32 partial rows through L2 takes longer (+37 us) than the separate, fully parallel merge launch costs.)
   return vg_attn_merge_launch(part, lens, N, nh, hd, ns_grid, gate, ld_gate, out, st);
 }

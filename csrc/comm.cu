@@ -202,6 +202,49 @@ __global__ void __launch_bounds__(256) allreduce_twoshot_kernel(VgCommCtx c, con
   }
 }
 
+// In-switch all-reduce of a bf16 buffer that lives in multicast-bound symmetric memory (same offset on every rank),
+// in place: after a flag round (every rank's producer has finished writing its copy), rank r reads the sum of all
+// ranks' copies of slice r with multimem.ld_reduce (fp32 accumulation inside the NVLink switch) and writes it to every
+// rank's copy with multimem.st; a second flag round makes the result complete everywhere. Every element crosses each
+// GPU's links once in and once out, and every rank ends with identical bits.
+__global__ void __launch_bounds__(256) allreduce_multimem_kernel(VgCommCtx c, unsigned char* mc_buf, long long n8) {
+  __shared__ int failed;
+  const uint32_t e = *c.epoch + 1;
+  const int set = e & 1;
+  const int W = c.world, cta = blockIdx.x, nct = gridDim.x;
+  if (threadIdx.x == 0) failed = 0;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < W)
+    st_release_sys(reinterpret_cast<uint32_t*>(c.data[threadIdx.x] + c.flags_off) + flag_index(set, c.rank, cta), e);
+  if (threadIdx.x < W) {
+    const uint32_t* f = reinterpret_cast<const uint32_t*>(c.data[c.rank] + c.flags_off) + flag_index(set, threadIdx.x, cta);
+    if (!wait_flag(f, e, c.timeout_ns)) { atomicCAS(c.status, 0, VG_ERR_PEER_WAIT); failed = 1; }
+  }
+  __syncthreads();
+  if (!failed) {
+    const long long seg = (n8 + W - 1) / W;                       // 16-byte vectors per rank
+    const long long lo = c.rank * seg, hi = min(n8, lo + seg);
+    for (long long i = lo + (long long)cta * blockDim.x + threadIdx.x; i < hi; i += (long long)nct * blockDim.x) {
+      const uint4 v = multimem_ld_reduce_bf16x8(mc_buf + i * 16);
+      multimem_st_bf16x8(mc_buf + i * 16, v);
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < W)
+    st_release_sys(reinterpret_cast<uint32_t*>(c.data[threadIdx.x] + c.flags_off) + flag_index(2 + set, c.rank, cta), e);
+  if (threadIdx.x < W) {
+    const uint32_t* f = reinterpret_cast<const uint32_t*>(c.data[c.rank] + c.flags_off) + flag_index(2 + set, threadIdx.x, cta);
+    if (!wait_flag(f, e, c.timeout_ns)) { atomicCAS(c.status, 0, VG_ERR_PEER_WAIT); failed = 1; }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(c.done_ctr, 1u) == (unsigned)nct - 1) { *c.done_ctr = 0; *c.epoch = e; }
+  }
+}
+
 // All-gather of a small payload (<= slot_bytes) from every rank: out[q * bytes ...] = rank q's payload.
 // ------------------------------------------------------------------ fused all-gather + GEMM: the gather half
 // grid (tiles of 128 rows, column chunks). Each CTA copies its chunk of its tile into every rank's landing zone;
@@ -426,6 +469,15 @@ extern "C" int vg_comm_allreduce(const VgCommCtx* ctx, const void* in, int in_is
     allreduce_twoshot_kernel<float><<<ctas, 256, 0, st>>>(c, static_cast<const float*>(in), static_cast<__nv_bfloat16*>(out_bf16), (int)n);
   else
     allreduce_twoshot_kernel<__nv_bfloat16><<<ctas, 256, 0, st>>>(c, static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out_bf16), (int)n);
+  return (int)cudaGetLastError();
+}
+
+// In-place in-switch all-reduce of `n` bf16 elements at the multicast address `mc_buf` (n a multiple of 8, buffer
+// 16-byte aligned and bound to the same multicast object on every rank).
+extern "C" int vg_comm_allreduce_multimem(const VgCommCtx* ctx, void* mc_buf, long long n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (!ctx || ctx->world < 2 || !mc_buf || (n % 8) != 0 || (reinterpret_cast<uintptr_t>(mc_buf) & 15) != 0) return -2;
+  allreduce_multimem_kernel<<<MAX_CTAS, 256, 0, st>>>(*ctx, static_cast<unsigned char*>(mc_buf), n / 8);
   return (int)cudaGetLastError();
 }
 

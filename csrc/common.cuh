@@ -210,6 +210,18 @@ VG_DEVINL float4 multimem_ld_reduce_f32x4(const void* mc_addr) {
   return r;
 }
 
+// Eight bf16 values: sum over all ranks' copies (fp32 accumulation inside the switch) / store to all ranks' copies.
+VG_DEVINL uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
+  uint4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc_addr) : "memory");
+  return r;
+}
+VG_DEVINL void multimem_st_bf16x8(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w) : "memory");
+}
+
 VG_DEVINL size_t flag_index(int set, int src, int cta) {
   return ((size_t)(set * MAX_RANKS + src) * MAX_CTAS + cta) * FLAG_STRIDE;
 }

@@ -25,12 +25,16 @@ using namespace vg;
 
 constexpr int CH = 64;                    // chunk length
 constexpr int KD = 128, VD = 128;
-constexpr uint32_t W_IMG = CH * KD * 4;   // 32 KB   [64 rows i][128 k]
-constexpr uint32_t Q_IMG = CH * KD * 4;   // 32 KB   [64 rows i][128 k]
-constexpr uint32_t P_IMG = CH * CH * 4;   // 16 KB   [64 rows i][64 j]
-constexpr uint32_t KT_IMG = KD * CH * 4;  // 32 KB   [128 rows d][64 j]
-constexpr uint32_t UT_BYTES = VD * CH * 4;  // 32 KB plain [128 v][64 i]
-constexpr uint32_t CHUNK_BYTES = W_IMG + Q_IMG + P_IMG + KT_IMG + UT_BYTES;   // 144 KB per (head, chunk)
+// Per (head, chunk) record in global memory. Operands that share an A operand in the state-carrying kernel are stacked
+// into ONE image, so one MMA sequence serves both (a kind::tf32 MMA covers only K = 8 and small MMAs retire at about
+// one per 100 cycles: the instruction count, not the FLOPs, is what the serial chain pays for):
+//   WQ   [128 rows][128 k]  rows 0..63 = W (row i), rows 64..127 = e^G Q (row i)
+//   PK   [192 rows][64 j]   rows 0..63 = P (row i), rows 64..191 = K~^T (row d)
+//   UT   plain fp32 [128 v][64 i]
+constexpr uint32_t WQ_IMG = 2 * CH * KD * 4;        // 64 KB
+constexpr uint32_t PK_IMG = (CH + KD) * CH * 4;     // 48 KB
+constexpr uint32_t UT_BYTES = VD * CH * 4;          // 32 KB
+constexpr uint32_t CHUNK_BYTES = WQ_IMG + PK_IMG + UT_BYTES;   // 144 KB per (head, chunk)
 
 // Byte offset of element (r, k) in the image of a K-major tile of `rows` rows of 32-bit elements with the 128-byte
 // swizzle: 32 elements (128 bytes) of a row are contiguous, the 16-byte pieces of a row are XOR-ed with r & 7, and
@@ -278,7 +282,7 @@ gdn_chunk_prep_kernel(const float* __restrict__ qkv, const __nv_bfloat16* __rest
           const int j = j0 + x4 * 4 + e;
           o[e] = j <= ii ? to_tf32(expf(Gi - Gs[chn * 64 + j]) * __uint_as_float(r[x4 * 4 + e])) : 0.f;
         }
-        *reinterpret_cast<float4*>(wbase + W_IMG + Q_IMG + img_off(CH, ii, j0 + x4 * 4)) = make_float4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<float4*>(wbase + WQ_IMG + img_off(CH + KD, ii, j0 + x4 * 4)) = make_float4(o[0], o[1], o[2], o[3]);
       }
     }
   }
@@ -288,7 +292,7 @@ gdn_chunk_prep_kernel(const float* __restrict__ qkv, const __nv_bfloat16* __rest
 #pragma unroll 4
     for (int d = hf * 64; d < hf * 64 + 64; d += 4) {
       const float4 q4 = *reinterpret_cast<const float4*>(R1 + img_off(128, row, d));
-      *reinterpret_cast<float4*>(wbase + W_IMG + img_off(CH, ii, d)) =
+      *reinterpret_cast<float4*>(wbase + img_off(2 * CH, CH + ii, d)) =
           make_float4(to_tf32(q4.x * eg), to_tf32(q4.y * eg), to_tf32(q4.z * eg), to_tf32(q4.w * eg));
     }
   }
@@ -312,7 +316,7 @@ gdn_chunk_prep_kernel(const float* __restrict__ qkv, const __nv_bfloat16* __rest
         const int cj = j >> 6;
         if (pair * 2 + cj < n_chunks) {
           uint8_t* wb = work + ((size_t)vh * n_chunks + pair * 2 + cj) * CHUNK_BYTES;
-          *reinterpret_cast<float*>(wb + W_IMG + Q_IMG + P_IMG + img_off(KD, d, j & 63)) = to_tf32(tj[s] * kv);
+          *reinterpret_cast<float*>(wb + WQ_IMG + img_off(CH + KD, CH + d, j & 63)) = to_tf32(tj[s] * kv);
         }
       }
     }
@@ -347,14 +351,14 @@ gdn_chunk_prep_kernel(const float* __restrict__ qkv, const __nv_bfloat16* __rest
       tmem_ld_wait();
 #pragma unroll
       for (int x4 = 0; x4 < 4; ++x4)
-        *reinterpret_cast<float4*>(wbase + img_off(CH, ii, d0 + x4 * 4)) =
+        *reinterpret_cast<float4*>(wbase + img_off(2 * CH, ii, d0 + x4 * 4)) =
             make_float4(to_tf32(__uint_as_float(r[x4 * 4])), to_tf32(__uint_as_float(r[x4 * 4 + 1])),
                         to_tf32(__uint_as_float(r[x4 * 4 + 2])), to_tf32(__uint_as_float(r[x4 * 4 + 3])));
     }
   }
   {                                          // U^T row v = row, the 64 tokens of chunk hf (plain fp32 [v][64])
     const bool live = pair * 2 + hf < n_chunks;
-    float* ut = reinterpret_cast<float*>(work + ((size_t)vh * n_chunks + (live ? pair * 2 + hf : 0)) * CHUNK_BYTES + W_IMG + Q_IMG + P_IMG + KT_IMG) + row * CH;
+    float* ut = reinterpret_cast<float*>(work + ((size_t)vh * n_chunks + (live ? pair * 2 + hf : 0)) * CHUNK_BYTES + WQ_IMG + PK_IMG) + row * CH;
 #pragma unroll
     for (int cb = 0; cb < 4; ++cb) {
       uint32_t r[16];
@@ -377,10 +381,10 @@ gdn_chunk_prep_kernel(const float* __restrict__ qkv, const __nv_bfloat16* __rest
 
 // ------------------------------------------------------------------------------------------------ state-carrying part
 // One CTA per value head. Warps 0-3: thread v owns row v of S^T (TMEM lane v). Warp 4 lane 0: bulk copies + MMA issue.
-// TMEM: S^T [128 columns] (kept pre-multiplied by the next chunk's total decay, so the chunk's outer products are
-// simply accumulated onto it), D^T [64], and two O^T buffers [64 each] so that a chunk's outputs are read out while
-// the next chunk's first products are already running.
-constexpr int SCAN_SMEM = 65536 + 32768 + W_IMG + Q_IMG + P_IMG + KT_IMG + 256 + 1024;
+// TMEM columns: [ D^T (64) | O^T (64) | S^T (128) ]. The first product of a chunk writes D^T and O^T together
+// (B = the stacked W / e^G Q image), the second accumulates onto O^T and S^T together (B = the stacked P / K~^T image);
+// S^T is kept pre-multiplied by the next chunk's total decay, so the chunk's outer products are simply accumulated.
+constexpr int SCAN_SMEM = 65536 + 32768 + WQ_IMG + PK_IMG + 256 + 1024;
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
   asm volatile(
@@ -412,11 +416,9 @@ gdn_chunk_scan_kernel(const uint8_t* __restrict__ work, const float* __restrict_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* S0 = smem;                       // S^T image [128 v][128 k]
   uint8_t* DT = S0 + 65536;                 // D^T image [128 v][64 j]
-  uint8_t* Wb = DT + 32768;                 // W image   [64 i][128 k]
-  uint8_t* Qb = Wb + W_IMG;                 // e^G Q     [64 i][128 k]
-  uint8_t* Pb = Qb + Q_IMG;                 // P         [64 i][64 j]
-  uint8_t* Kb = Pb + P_IMG;                 // K~^T      [128 d][64 j]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(Kb + KT_IMG);
+  uint8_t* WQb = DT + 32768;                // [W ; e^G Q] image [128 rows][128 k]
+  uint8_t* PKb = WQb + WQ_IMG;              // [P ; K~^T] image  [192 rows][64 j]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(PKb + PK_IMG);
   uint64_t* ld_wq = bars, *ld_pk = bars + 1, *mma1 = bars + 2, *mma2 = bars + 3, *thr1 = bars + 4, *thr2 = bars + 5;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -431,49 +433,45 @@ gdn_chunk_scan_kernel(const uint8_t* __restrict__ work, const float* __restrict_
     fence_mbar_init();
   }
   if (warp == 4) {
-    tmem_alloc(tmem_slot, 512);
+    tmem_alloc(tmem_slot, 256);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t T_S = tmem_base, T_D = tmem_base + 128, T_O = tmem_base + 192;   // S^T [128], D^T [64], O^T [2][64]
+  const uint32_t T_D = tmem_base, T_O = tmem_base + 64, T_S = tmem_base + 128;
   pdl_wait();                               // the images come from the preceding kernel, the state from earlier ones
   const uint8_t* hbase = work + (size_t)vh * n_chunks * CHUNK_BYTES;
 
   if (warp == 4) {
     if (lane == 0) {
-      mbar_arrive_expect_tx(ld_wq, W_IMG + Q_IMG);
-      tma_bulk_g2s(Wb, hbase, W_IMG + Q_IMG, ld_wq);                       // W and Q images are adjacent
-      mbar_arrive_expect_tx(ld_pk, P_IMG + KT_IMG);
-      tma_bulk_g2s(Pb, hbase + W_IMG + Q_IMG, P_IMG + KT_IMG, ld_pk);      // so are P and K~^T
-      const uint64_t d_s0 = img_desc(S0), d_dt = img_desc(DT), d_w = img_desc(Wb), d_q = img_desc(Qb), d_p = img_desc(Pb),
-                     d_k = img_desc(Kb);
+      mbar_arrive_expect_tx(ld_wq, WQ_IMG);
+      tma_bulk_g2s(WQb, hbase, WQ_IMG, ld_wq);
+      mbar_arrive_expect_tx(ld_pk, PK_IMG);
+      tma_bulk_g2s(PKb, hbase + WQ_IMG, PK_IMG, ld_pk);
+      const uint64_t d_s0 = img_desc(S0), d_dt = img_desc(DT), d_wq = img_desc(WQb), d_pk = img_desc(PKb);
       for (int c = 0; c < n_chunks; ++c) {
         const uint32_t ph = c & 1;
-        const uint32_t t_o = T_O + ph * 64;
         if (c + 2 < n_chunks)                                           // pull the chunk after next towards L2
           asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(hbase + (size_t)(c + 2) * CHUNK_BYTES), "r"(CHUNK_BYTES) : "memory");
         if (!mbar_wait(thr2, ph) || !mbar_wait(ld_wq, ph)) { fail(err, VG_ERR_TMA_WAIT); *abort_flag = 1; break; }
         tc_fence_after();
-        mma_tile<CH, KD>(T_D, d_s0, d_w, false);                           // D^T  = S^T W^T
-        mma_tile<CH, KD>(t_o, d_s0, d_q, false);                           // O^T  = S^T (e^G Q)^T
+        mma_tile<2 * CH, KD>(T_D, d_s0, d_wq, false);                      // [D^T | O^T] = S^T [W ; e^G Q]^T
         umma_commit(mma1);
         if (!mbar_wait(mma1, ph)) { fail(err, VG_ERR_MMA_WAIT); *abort_flag = 1; break; }
         if (c + 1 < n_chunks) {
-          mbar_arrive_expect_tx(ld_wq, W_IMG + Q_IMG);
-          tma_bulk_g2s(Wb, hbase + (size_t)(c + 1) * CHUNK_BYTES, W_IMG + Q_IMG, ld_wq);
+          mbar_arrive_expect_tx(ld_wq, WQ_IMG);
+          tma_bulk_g2s(WQb, hbase + (size_t)(c + 1) * CHUNK_BYTES, WQ_IMG, ld_wq);
         }
         if (!mbar_wait(thr1, ph) || !mbar_wait(ld_pk, ph)) { fail(err, VG_ERR_TMA_WAIT); *abort_flag = 1; break; }
         tc_fence_after();
-        mma_tile<CH, CH>(t_o, d_dt, d_p, true);                            // O^T += D^T P^T
-        mma_tile<KD, CH>(T_S, d_dt, d_k, true);                            // S^T (already decayed) += D^T K~
+        mma_tile<CH + KD, CH>(T_O, d_dt, d_pk, true);                      // [O^T | S^T] += D^T [P ; K~^T]^T
         umma_commit(mma2);
         if (!mbar_wait(mma2, ph)) { fail(err, VG_ERR_MMA_WAIT); *abort_flag = 1; break; }
         if (c + 1 < n_chunks) {
-          mbar_arrive_expect_tx(ld_pk, P_IMG + KT_IMG);
-          tma_bulk_g2s(Pb, hbase + (size_t)(c + 1) * CHUNK_BYTES + W_IMG + Q_IMG, P_IMG + KT_IMG, ld_pk);
+          mbar_arrive_expect_tx(ld_pk, PK_IMG);
+          tma_bulk_g2s(PKb, hbase + (size_t)(c + 1) * CHUNK_BYTES + WQ_IMG, PK_IMG, ld_pk);
         }
       }
     }
@@ -506,14 +504,13 @@ gdn_chunk_scan_kernel(const uint8_t* __restrict__ work, const float* __restrict_
     }
     bool dead = false;
     // U^T rows are fetched one chunk ahead (their DRAM latency would otherwise sit on the serial chain)
-    const size_t ut_off = (size_t)(W_IMG + Q_IMG + P_IMG + KT_IMG) + (size_t)v * CH * 4;
+    const size_t ut_off = (size_t)(WQ_IMG + PK_IMG) + (size_t)v * CH * 4;
     float4 u[16], un[16];
 #pragma unroll
     for (int x = 0; x < 16; ++x) un[x] = __ldg(reinterpret_cast<const float4*>(hbase + ut_off) + x);
     float g_n = n_chunks > 1 ? gcp[1] : 1.0f;
     for (int c = 0; c < n_chunks && !dead; ++c) {
       const uint32_t ph = c & 1;
-      const uint32_t t_o = T_O + ph * 64;
       const bool last = c + 1 == n_chunks;
       const float g_next = last ? 1.0f : g_n;
 #pragma unroll
@@ -545,6 +542,18 @@ gdn_chunk_scan_kernel(const uint8_t* __restrict__ work, const float* __restrict_
       mbar_arrive(thr1);
       if (!mbar_wait(mma2, ph)) { fail(err, VG_ERR_MMA_WAIT); dead = true; break; }
       tc_fence_after();
+      // raw outputs o[token][vh * VD + v] (the next chunk's first product overwrites O^T, so they are read out first)
+#pragma unroll
+      for (int cb = 0; cb < 2; ++cb) {
+        uint32_t r[32];
+        tmem_ld32(T_O + lane_addr + (uint32_t)(cb * 32), r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int x = 0; x < 32; ++x) {
+          const int t = c * CH + cb * 32 + x;
+          if (t < tn) o_raw[((size_t)(t0 + t) * nv + vh) * VD + v] = __uint_as_float(r[x]);
+        }
+      }
       // the new state: operand image for the next chunk, and back to TMEM times the next chunk's decay; after the
       // last chunk it goes to the output slot instead
       const int os = last ? out_slot[t0 + tn - 1] : -1;
@@ -560,38 +569,34 @@ gdn_chunk_scan_kernel(const uint8_t* __restrict__ work, const float* __restrict_
             *reinterpret_cast<float4*>(S0 + img_off(128, v, cb * 32 + x4 * 4)) =
                 make_float4(to_tf32(__uint_as_float(r[x4 * 4])), to_tf32(__uint_as_float(r[x4 * 4 + 1])),
                             to_tf32(__uint_as_float(r[x4 * 4 + 2])), to_tf32(__uint_as_float(r[x4 * 4 + 3])));
-#pragma unroll
-          for (int x = 0; x < 32; ++x) r[x] = __float_as_uint(__uint_as_float(r[x]) * g_next);
-          tmem_st32(T_S + lane_addr + (uint32_t)(cb * 32), r);
         } else if (dp) {
 #pragma unroll
           for (int x = 0; x < 32; ++x) dp[(size_t)(cb * 32 + x) * VD] = __uint_as_float(r[x]);
         }
       }
-      if (!last) tmem_st_wait();
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(thr2);
-      // raw outputs o[token][vh * VD + v], read out while the next chunk's first products run (they use the other
-      // O^T buffer)
-      tc_fence_after();
+      // off the serial chain (the next chunk's first products only read the image): the accumulator copy of the
+      // state times the next chunk's decay, needed by the next chunk's LAST product
+      if (!last) {
+#pragma unroll 1
+        for (int cb = 0; cb < 4; ++cb) {
+          uint32_t r[32];
+          tmem_ld32(T_S + lane_addr + (uint32_t)(cb * 32), r);
+          tmem_ld_wait();
 #pragma unroll
-      for (int cb = 0; cb < 2; ++cb) {
-        uint32_t r[32];
-        tmem_ld32(t_o + lane_addr + (uint32_t)(cb * 32), r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int x = 0; x < 32; ++x) {
-          const int t = c * CH + cb * 32 + x;
-          if (t < tn) o_raw[((size_t)(t0 + t) * nv + vh) * VD + v] = __uint_as_float(r[x]);
+          for (int x = 0; x < 32; ++x) r[x] = __float_as_uint(__uint_as_float(r[x]) * g_next);
+          tmem_st32(T_S + lane_addr + (uint32_t)(cb * 32), r);
         }
+        tmem_st_wait();
       }
     }
   }
   __syncwarp();
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem_base, 512);
+  if (warp == 4) tmem_dealloc(tmem_base, 256);
 }
 
 }  // namespace

@@ -716,6 +716,9 @@ extern "C" int vg_gemm_fp4(const void* wt, const float* row_scale, const void* b
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
+  // (Measured and rejected for 1 < tiles / SMs <= 2, the gate_up case: two CTAs per SM on the two-stage ring, so that
+  // every tile is resident at once. The shallow rings lose more bandwidth than the second wave's ramp costs:
+  // 173 -> 157 tok/s on the 27B shape.)
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((M + BM - 1) / BM, 1, splitk);
   cfg.blockDim = dim3(THREADS);

@@ -15,7 +15,7 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     from velogb10_b200.parallel.comm import CommError, TpComm
-    comm = TpComm(rank, world, dev, max_elems=1 << 22, timeout_s=5.0, ag_bytes=2 * 1024 * 1024 * 2)
+    comm = TpComm(rank, world, dev, max_elems=1 << 22, timeout_s=5.0, ag_bytes=2 * 256 * world * 1024 * 2)
     g = torch.Generator(device=dev).manual_seed(100 + rank)
     for rows, h in ((1, 5120), (16, 5120), (3, 256), (700, 5120)):      # one-shot and two-shot sizes
         x = torch.randn(rows, h, generator=g, device=dev).to(torch.bfloat16)
@@ -35,6 +35,28 @@ def main():
         both = comm.all_gather_small(first[:1, :64].contiguous())
         torch.cuda.synchronize()
         assert torch.equal(both[0], both[-1])
+    # in-switch all-reduce (multicast-bound symmetric buffer), in place: close to the fp32 reference, identical on
+    # every rank and on every repeat
+    sb = comm.symmetric_buffer(700 * 5120 * 2)
+    if sb is not None:
+        t = sb.view(torch.bfloat16).view(700, 5120)
+        x = torch.randn(700, 5120, generator=g, device=dev).to(torch.bfloat16)
+        ref = x.float().clone()
+        dist.all_reduce(ref)
+        for rep in range(3):
+            t.copy_(x)
+            dist.barrier()                      # no rank may still be reading the previous result
+            assert comm.all_reduce_multimem(t, 700)
+            torch.cuda.synchronize()
+            comm.check()
+            err = (t.float() - ref).abs().max().item()
+            assert err <= 0.02 * ref.abs().max().item() + 1e-3, ("multimem all-reduce", rep, err)
+            if rep == 0:
+                first = t.clone()
+            assert torch.equal(t, first)
+        both = comm.all_gather_small(first[:1, :64].contiguous())
+        torch.cuda.synchronize()
+        assert all(torch.equal(both[0], both[q]) for q in range(world))
     # graph replay advances the device-side epoch by itself
     x = torch.randn(4, 1024, generator=g, device=dev).to(torch.bfloat16)
     buf = x.clone()
@@ -80,7 +102,7 @@ def main():
     assert torch.equal(y, want)
     # fused all-gather + GEMM: token rows sharded over the ranks, every rank computes the full product
     from velogb10_b200.models.weights import QLinear
-    n_total, K_, M_ = 300 + 128 * (world - 1), 1024, 384
+    n_total, K_, M_ = 256 * world - 84, 1024, 384        # every rank's shard is non-empty, the last one ragged
     gw = torch.Generator(device=dev).manual_seed(7)                       # same weights and inputs on every rank
     w = (torch.randn(M_, K_, generator=gw, device=dev) * 0.05).to(torch.bfloat16)
     xf = torch.randn(n_total, K_, generator=gw, device=dev).to(torch.float16)
@@ -146,4 +168,9 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except BaseException:
+        import traceback
+        print(f"WORKER_FAILED rank {os.environ.get('RANK')}\n" + traceback.format_exc()[-1500:], flush=True)
+        raise

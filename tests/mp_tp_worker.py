@@ -167,4 +167,9 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except BaseException:
+        import traceback
+        print(f"WORKER_FAILED rank {os.environ.get('RANK')}\n" + traceback.format_exc()[-1500:], flush=True)
+        raise

@@ -16,7 +16,7 @@ def _spawn(script: str, n: int, timeout: int = 420, env_extra=None):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
            "127.0.0.1", "--master-port", str(29541 + n), os.path.join(ROOT, "tests", script)]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
-    assert r.returncode == 0, (r.stdout[-3000:], r.stderr[-3000:])
+    assert r.returncode == 0, (r.stdout[-6000:], r.stderr[-1500:])
     return r.stdout
 
 

@@ -122,7 +122,7 @@ class Workspace:
                 widths.append(L.mlp.gate_up.m)
             if L.moe and L.moe.shared:
                 widths.append(L.moe.shared.gate_up.m)
-        self.wide = bf(rows, max(widths))                 # qkv / in_proj / gate_up outputs
+        self.wide = bf(rows, (max(widths) + 63) // 64 * 64)                 # qkv / in_proj / gate_up outputs
         self._a16 = {}                                    # contiguous f16 GEMM-input buffers by width
         self._rows, self._dev = rows, dev
         nh_max = max([L.attn.nh for L in list(w.layers) + ([w.mtp.layer] if w.mtp else []) if L.attn] or [1])
@@ -396,6 +396,13 @@ class GpuModel:
                 return
             self._linear(q, x16, n, out, act=act, comm=self.comm)
             return
+        if tp and n > 64 and not self.comm.use_nccl and out.dtype == torch.bfloat16 and self.comm.multicast_address(out):
+            # prefill widths with a multicast-bound output buffer: plain GEMM, then the in-switch all-reduce in place
+            # (measured faster than pushing fp32 partial tiles from the GEMM epilogue: the switch adds the ranks'
+            # copies while each element crosses a GPU's links once)
+            self._linear(q, x16, n, out, act=act)
+            self.comm.all_reduce_rows(out, n)
+            return
         if tp and n > 64 and not self.comm.use_nccl and self.fuse_allreduce and out.dtype == torch.bfloat16 \
                 and out.is_contiguous() and out.shape[1] == q.m:
             # prefill widths: GEMM fused with the reduce-scatter (each partial tile goes to the rank owning its token
@@ -601,6 +608,15 @@ class GpuModel:
         chunk = min(self.prefill_chunk, max(N, 16))
         if self.ws_prefill is None or self.ws_prefill.cap < chunk:
             self.ws_prefill = Workspace(self.cfg, self.w, chunk, self.dev, 1)
+            if self.comm is not None and self.comm.world > 1 and self.comm.mc and not self.comm.use_nccl \
+                    and os.environ.get("VELO_NO_MULTIMEM_PREFILL", "0") != "1":
+                # the row-parallel outputs of a prefill chunk land in multicast-bound symmetric memory, where the
+                # tensor-parallel sum runs in place inside the NVLink switch (collective allocation: every rank
+                # creates its prefill workspace at the same point)
+                wsp = self.ws_prefill
+                buf = self.comm.symmetric_buffer(wsp.delta.numel() * 2)
+                if buf is not None:
+                    wsp.delta = buf.view(torch.bfloat16).view(wsp.delta.shape)
             need = K.attn_scratch_floats(16, 1, self.cfg.head_dim, 1)
             assert self.attn_part.numel() >= need
         ws = self.ws_prefill

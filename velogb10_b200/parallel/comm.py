@@ -68,6 +68,7 @@ class TpComm:
         self.mc = 0                     # multicast (NVLS) address of the arena, 0 when it has none
         self.arena_kind = "cuda-ipc"
         self._symm = None
+        self._symm_bufs = []
         with torch.cuda.device(self.dev):
             # Preferred substrate: a symmetric allocation with an NVLink-switch multicast binding (torch's symmetric
             # memory does the allocation and the handle exchange), which adds in-switch reductions to the peer
@@ -96,9 +97,10 @@ class TpComm:
         ctx.mm_ctr = self.base + 12
         self.ctx = ctx
         # decode-width all-reduce through the switch (multimem.ld_reduce) when the arena has a multicast address
-        # (measured on 2 GPUs the pair push is the faster of the two: one NVLink hop instead of flag + reduce round
-        # trip; its cost grows with the number of ranks, the in-switch form's does not)
-        mm_min = int(os.environ.get("VELO_MULTIMEM_MIN_WORLD", "4"))
+        # (measured on 2 and on 4 GPUs the pair push is the faster of the two: one NVLink hop instead of flag + reduce
+        # round trip, 198 vs 182 and 216 vs 206 tok/s; its cost grows with the number of ranks, the in-switch form's
+        # does not)
+        mm_min = int(os.environ.get("VELO_MULTIMEM_MIN_WORLD", "8"))
         self.use_mm = bool(self.mc) and world >= mm_min
         self._status_view = self._view(8, 1, torch.int32)
         self._pairs = torch.zeros(2 * ARGMAX_MAX_COLS, dtype=torch.float32, device=self.dev)
@@ -144,6 +146,45 @@ class TpComm:
         self.mc = mc + off if mc else 0
         self.arena_kind = "symmetric+multicast" if self.mc else "symmetric"
 
+    def symmetric_buffer(self, nbytes: int):
+        """A uint8 tensor in multicast-bound symmetric memory (collective: every rank calls it in the same order with the
+        same size), or None when the arena has no multicast binding. Buffers obtained here can be reduced in place with
+        ``all_reduce_multimem``."""
+        if not self.mc:
+            return None
+        import torch.distributed._symmetric_memory as symm
+        with torch.cuda.device(self.dev):
+            t = symm.empty(nbytes, dtype=torch.uint8, device=self.dev)
+            hdl = symm.rendezvous(t, self.group if self.group is not None else dist.group.WORLD)
+            mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
+            off = int(getattr(hdl, "offset", 0) or 0)
+            if not mc:
+                return None
+            t.zero_()
+            torch.cuda.synchronize(self.dev)
+        self._symm_bufs.append((t.data_ptr(), nbytes, mc + off, t, hdl))
+        dist.barrier(group=self.group)
+        return t
+
+    def multicast_address(self, t: torch.Tensor) -> int:
+        """Multicast address of a tensor that lives inside a ``symmetric_buffer`` (0 if it does not)."""
+        p = t.data_ptr()
+        for base, nbytes, mc, _, _ in self._symm_bufs:
+            if base <= p and p + t.numel() * t.element_size() <= base + nbytes:
+                return mc + (p - base)
+        return 0
+
+    def all_reduce_multimem(self, t: torch.Tensor, n_rows: int) -> bool:
+        """In-place sum over ranks of the first rows of a bf16 tensor inside a symmetric buffer, reduced inside the
+        NVLink switch. Returns False (nothing done) when the tensor is not multicast-addressable."""
+        mc = self.multicast_address(t)
+        n = n_rows * t.shape[1]
+        if not mc or t.dtype != torch.bfloat16 or not t.is_contiguous() or n % 8 or self.use_nccl:
+            return False
+        rc = self.L.vg_comm_allreduce_multimem(ctypes.byref(self.ctx), ctypes.c_void_p(mc), c_ll(n), stream())
+        _lib.check(rc, "vg_comm_allreduce_multimem")
+        return True
+
     def describe(self) -> dict:
         """How this communicator moves data (recorded next to benchmark numbers)."""
         return {"arena": self.arena_kind, "multicast": bool(self.mc), "note": getattr(self, "arena_note", ""),
@@ -166,6 +207,8 @@ class TpComm:
     def all_reduce_rows(self, t: torch.Tensor, n_rows: int):
         """In-place sum over ranks of the first ``n_rows`` rows of a contiguous bf16/f32 ``[rows, h]`` tensor."""
         n = n_rows * t.shape[1]
+        if n_rows > 64 and self._symm_bufs and self.all_reduce_multimem(t, n_rows):
+            return
         if self.use_nccl:
             dist.all_reduce(t[:n_rows], group=self.group)
             return

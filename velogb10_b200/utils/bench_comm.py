@@ -132,7 +132,16 @@ def main():
         flops = 2.0 * n_tok * h * kloc
         link_bytes = n_tok * h * 4 * (world - 1) / world + n_tok * h * 2 * (world - 1) / world     # fp32 partials out, bf16 result back
         floor_us = max(flops / tfl / 1e6, link_bytes / NVLINK_GBS / 1e3)
-        for name, fn in (("gemm + reduce-scatter fused, finish kernel", fused_rs), ("gemm + nccl_all_reduce", nccl_rs)):
+        forms = [("gemm + reduce-scatter fused, finish kernel", fused_rs), ("gemm + nccl_all_reduce", nccl_rs)]
+        sb = comm.symmetric_buffer(n_tok * h * 2)
+        if sb is not None:
+            o_mm = sb.view(torch.bfloat16).view(n_tok, h)
+
+            def mm_rs():
+                G.linear(q, xs, n_tok, out=o_mm)
+                comm.all_reduce_multimem(o_mm, n_tok)
+            forms.insert(0, ("gemm + in-switch multimem all-reduce (in place)", mm_rs))
+        for name, fn in forms:
             s_ = summary(timed(fn, max(20, args.iters // 5)), world)
             rows.append({"path": "gemm_rs", "form": name, "tokens": n_tok, "shape": [h, kloc], **s_, "roofline_us": round(floor_us, 1),
                          "fraction_of_roofline": round(floor_us / s_["p50_us"], 3)})
