@@ -169,6 +169,45 @@ def test_checkpoint_roundtrip_and_requant(tmp_path):
     assert l4.layers[0].mlp is None or l4.layers[0].mlp.down.fmt == "nvfp4"
 
 
+def test_read_ahead_loader_builds_the_same_model(tmp_path):
+    """The prefetching source hands the builder the same tensors as the plain lazy reader: through a window smaller
+    than one layer (eviction and direct-read fallbacks), and with tensors in the checkpoint that the builder never asks for."""
+    from velogb10_b200.checkpoint import io
+    from velogb10_b200.checkpoint.synthetic import synthetic_state_dict
+    from velogb10_b200.config import ModelConfig, tiny_hybrid
+    from velogb10_b200.models.weights import ModelBuilder
+    cfg = tiny_hybrid(mtp=True)
+    sd = synthetic_state_dict(cfg, seed=0)
+    sd["model.visual.blocks.0.unused.weight"] = torch.zeros(64, 64, dtype=torch.bfloat16)
+    sd["model.language_model.layers.0.unused_tail.weight"] = torch.zeros(64, 64, dtype=torch.bfloat16)
+    out = str(tmp_path / "ck")
+    io.write_checkpoint(out, sd.items(), cfg.to_hf_dict(), "all,gdn:fp8", max_shard_bytes=1 << 20)
+    cfg2 = ModelConfig.from_json(os.path.join(out, "config.json"))
+    plain = ModelBuilder(cfg2, io.SafetensorsSource(out)).build()
+    for workers, ahead in ((3, 2 << 30), (2, 4096)):
+        src = io.PrefetchSource(io.SafetensorsSource(out), "cpu", workers=workers, ahead_bytes=ahead)
+        try:
+            got = ModelBuilder(cfg2, src).build()
+        finally:
+            src.close()
+        st = src.summary()
+        assert st["hits"] > 0 and st["hits"] + st["misses"] >= len(list(plain.linears()))
+        for (na, a), (nb, b) in zip(got.linears(), plain.linears()):
+            assert na == nb and a.fmt == b.fmt and torch.equal(a.dequant(), b.dequant()), na
+        assert torch.equal(got.embed.dequant() if hasattr(got.embed, "dequant") else got.embed,
+                           plain.embed.dequant() if hasattr(plain.embed, "dequant") else plain.embed)
+    assert "read" in io.load_report(src, 1.0) and "no read-ahead" in io.load_report(io.SafetensorsSource(out), 1.0)
+    monkey = os.environ.get("VELO_LOAD_WORKERS")
+    os.environ["VELO_LOAD_WORKERS"] = "0"
+    try:
+        assert isinstance(io.open_checkpoint(out), io.SafetensorsSource)
+    finally:
+        if monkey is None:
+            del os.environ["VELO_LOAD_WORKERS"]
+        else:
+            os.environ["VELO_LOAD_WORKERS"] = monkey
+
+
 def test_draft_vocab_rows_rule():
     """FR-Spec row selection: the most frequent ids plus the special-token tail, padded with real rows."""
     from velogb10_b200.models.weights import draft_vocab_rows

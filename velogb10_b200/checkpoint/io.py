@@ -76,6 +76,187 @@ class SafetensorsSource(TensorSource):
         return f.get_tensor(name)
 
 
+class PrefetchSource(TensorSource):
+    """Read-ahead in front of a ``SafetensorsSource``: worker threads walk the checkpoint in the order a model builder
+    asks for it (embedding, layers by index, the rest), read each tensor into a pinned host buffer of their own and
+    start its host->device copy on a side stream, at most ``ahead_bytes`` ahead of the consumer. ``get`` hands out the
+    staged device tensor (the consumer's stream waits on the copy's event, the host does not) or reads directly for a
+    name outside the predicted order. Disk reads, the pinned memcpy and the uploads therefore overlap the builder's
+    GPU-side quantise / tile work; the counters split a load into read, wait and build time for the ``[load]`` line.
+    Plays the part of the reference's record / replay assembly pipeline with its worker pool and single uploader
+    (reference: src/gpu.rs:1304-1584), with the repack itself left to the GPU.
+
+    On a CPU device the workers only read ahead (no pinned staging)."""
+
+    _LAYER = re.compile(r"\.layers\.(\d+)\.")
+
+    def __init__(self, inner: "SafetensorsSource", device="cpu", workers: int = 4, ahead_bytes: int = 2 << 30,
+                 buf_bytes: int = 256 << 20):
+        import threading
+        self.inner, self.device = inner, torch.device(device)
+        self.metadata = inner.metadata
+        self.cuda = self.device.type == "cuda"
+        self.stats = {"bytes": 0, "read_s": 0.0, "wait_s": 0.0, "hits": 0, "misses": 0, "direct_bytes": 0}
+        self._order = sorted(inner.names(), key=self._rank)
+        self._idx = {n: i for i, n in enumerate(self._order)}
+        self._pending = set(self._order)
+        self._staged: Dict[str, Tuple[torch.Tensor, object]] = {}
+        self._cv = threading.Condition()
+        self._next, self._inflight, self._ahead, self._buf_bytes = 0, 0, ahead_bytes, buf_bytes
+        self._stop, self._failed = False, None
+        for shard in set(inner.where.values()):             # ask the page cache to start on every shard now
+            try:
+                fd = os.open(shard, os.O_RDONLY)
+                os.posix_fadvise(fd, 0, 0, os.POSIX_FADV_WILLNEED)
+                os.close(fd)
+            except (OSError, AttributeError):
+                pass
+        self._threads = [threading.Thread(target=self._work, daemon=True) for _ in range(max(1, workers))]
+        for t in self._threads:
+            t.start()
+
+    def _rank(self, name: str):
+        m = self._LAYER.search(name)
+        if m:
+            return (1 if ".mtp." not in name and not name.startswith("mtp.") else 3, int(m.group(1)), name)
+        return (0 if "embed" in name else 2, 0, name)
+
+    def _work(self):
+        import time
+        handles: Dict[str, object] = {}
+        pinned = torch.empty(self._buf_bytes, dtype=torch.uint8).pin_memory() if self.cuda else None
+        stream = torch.cuda.Stream(device=self.device) if self.cuda else None
+        busy = None                                          # event of the copy still reading this worker's buffer
+        try:
+            while True:
+                with self._cv:
+                    while not self._stop and self._next < len(self._order) and self._inflight >= self._ahead:
+                        self._cv.wait(0.5)
+                    if self._stop or self._next >= len(self._order):
+                        return
+                    name = self._order[self._next]
+                    self._next += 1
+                    if name not in self._pending:            # the consumer already read it directly
+                        continue
+                t0 = time.time()
+                shard = self.inner.where[name]
+                f = handles.get(shard)
+                if f is None:
+                    f = handles[shard] = safe_open(shard, framework="pt", device="cpu")
+                t = f.get_tensor(name)
+                nb = t.numel() * t.element_size()
+                ev = None
+                if self.cuda and 0 < nb <= self._buf_bytes:
+                    if busy is not None:
+                        busy.synchronize()
+                    host = pinned[:nb].view(t.dtype).view(t.shape) if t.dtype != torch.bool else None
+                    if host is not None:
+                        host.copy_(t)
+                        with torch.cuda.stream(stream):
+                            t = torch.empty(t.shape, dtype=t.dtype, device=self.device)
+                            t.copy_(host, non_blocking=True)
+                            ev = busy = torch.cuda.Event()
+                            ev.record(stream)
+                with self._cv:
+                    self.stats["read_s"] += time.time() - t0
+                    self.stats["bytes"] += nb
+                    if name in self._pending:
+                        self._staged[name] = (t, ev)
+                        self._inflight += nb
+                    self._cv.notify_all()
+        except Exception as e:  # noqa: BLE001 - reported to the consumer, which falls back to direct reads
+            with self._cv:
+                self._failed = e
+                self._cv.notify_all()
+
+    def names(self) -> List[str]:
+        return self.inner.names()
+
+    def has(self, name: str) -> bool:
+        return self.inner.has(name)
+
+    def get(self, name: str) -> Optional[torch.Tensor]:
+        import time
+        if not self.inner.has(name):
+            return None
+        t0 = time.time()
+        with self._cv:
+            if name in self._pending:
+                # wait only for a tensor a worker has already claimed or is about to (its rank is near the cursor)
+                while name not in self._staged and self._failed is None and not self._stop \
+                        and self._claimed_or_near(name):
+                    if self._inflight >= self._ahead and not self._drop_passed(name):
+                        break                                # the window is full of tensors still to come: read directly
+                    self._cv.wait(0.2)
+                self._pending.discard(name)
+                hit = self._staged.pop(name, None)
+                if hit is not None:
+                    t, ev = hit
+                    self._inflight -= t.numel() * t.element_size()
+                    self.stats["hits"] += 1
+                    self.stats["wait_s"] += time.time() - t0
+                    self._cv.notify_all()
+                    if ev is not None:
+                        cur = torch.cuda.current_stream(self.device)
+                        cur.wait_event(ev)
+                        t.record_stream(cur)                 # allocated on the worker's stream, used on this one
+                    return t
+            self.stats["misses"] += 1
+        t = self.inner.get(name)
+        self.stats["direct_bytes"] += t.numel() * t.element_size()
+        return t
+
+    def _claimed_or_near(self, name: str) -> bool:
+        """True while waiting for the workers beats reading ``name`` directly: it is among the next tensors they will
+        take (or one of them is reading it now)."""
+        return self._idx[name] < self._next + 64
+
+    def _drop_passed(self, name: str) -> bool:
+        """Free the read-ahead window of staged tensors that sort before ``name``: the consumer went past them without
+        asking (a tensor this model does not use). Called with the lock held; True if anything was freed."""
+        mine = self._idx[name]
+        gone = [n for n in self._staged if self._idx[n] < mine]
+        for n in gone:
+            t, _ = self._staged.pop(n)
+            self._inflight -= t.numel() * t.element_size()
+            self._pending.discard(n)
+        if gone:
+            self._cv.notify_all()
+        return bool(gone)
+
+    def close(self):
+        with self._cv:
+            self._stop = True
+            self._staged.clear()
+            self._cv.notify_all()
+        for t in self._threads:
+            t.join(timeout=5)
+
+    def summary(self) -> dict:
+        s = dict(self.stats)
+        s["read_gbs_per_worker"] = round(s["bytes"] / 1e9 / s["read_s"], 2) if s["read_s"] > 0 else None
+        return s
+
+
+def open_checkpoint(model_dir: str, device="cpu", workers: Optional[int] = None) -> TensorSource:
+    """The source a loader should build from: read-ahead workers in front of the lazy shard reader
+    (``VELO_LOAD_WORKERS`` / ``workers`` = 0 gives the plain reader)."""
+    n = int(os.environ.get("VELO_LOAD_WORKERS", "4")) if workers is None else workers
+    src = SafetensorsSource(model_dir)
+    return PrefetchSource(src, device, workers=n) if n > 0 else src
+
+
+def load_report(src: TensorSource, total_s: float) -> str:
+    """One ``[load]`` line splitting ``total_s`` into what the reader threads did and what the builder waited for."""
+    if not isinstance(src, PrefetchSource):
+        return f"[load] weights {total_s:.1f}s (no read-ahead)"
+    st = src.summary()
+    return (f"[load] weights {total_s:.1f}s: read {st['bytes'] / 1e9:.2f} GB by {len(src._threads)} workers "
+            f"({st['read_s']:.1f} worker-s, {st['read_gbs_per_worker']} GB/s each), builder waited {st['wait_s']:.1f}s for "
+            f"tensors, quantise / tile / upload of the rest {max(0.0, total_s - st['wait_s']):.1f}s; "
+            f"{st['hits']} staged, {st['misses']} direct ({st['direct_bytes'] / 1e9:.2f} GB)")
+
+
 # ------------------------------------------------------------------ writer
 
 class ShardWriter:

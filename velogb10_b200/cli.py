@@ -138,10 +138,10 @@ def load_runner(args: Dict[str, str], max_batch: int, max_seq: int):
             from .parallel.comm import TpComm
             comm = TpComm(rank, tp, torch.device(device), use_nccl="--tp-nccl" in args)
     if "--model-dir" in args:
-        from .checkpoint.io import SafetensorsSource
+        from .checkpoint.io import open_checkpoint
         d = args["--model-dir"]
         cfg = ModelConfig.from_json(os.path.join(d, "config.json"))
-        src = SafetensorsSource(d)
+        src = open_checkpoint(d, device)
         recipe = args.get("--recipe", "off")
         tok = ChatTokenizer.from_dir(d, args.get("--tokenizer"))
     else:
@@ -151,8 +151,16 @@ def load_runner(args: Dict[str, str], max_batch: int, max_seq: int):
         recipe = args.get("--recipe", "all")
         tok = ChatTokenizer(build_byte_tokenizer(), DEFAULT_TEMPLATE)
     max_seq = min(max_seq, cfg.max_position_embeddings)
+    t_build = time.time()
     w = ModelBuilder(cfg, src, recipe=recipe, device=device, tp_rank=rank if tp > 1 and not cpu else 0,
                      tp_world=tp if not cpu else 1).build()
+    if "--model-dir" in args:
+        from .checkpoint.io import load_report
+        if not cpu:
+            torch.cuda.synchronize()
+        print(load_report(src, time.time() - t_build), file=sys.stderr)
+        if hasattr(src, "close"):
+            src.close()
     if cpu:
         from .models.oracle import OracleModel
         runner = OracleModel(w)

@@ -38,12 +38,16 @@ class LLM:
     @classmethod
     def from_dir(cls, model_dir: str, device=None, max_batch: int = 8, max_seq: int = 4096, recipe: str = "off",
                  tp_rank: int = 0, tp_world: int = 1, comm=None, prefill_chunk: int = 4096) -> "LLM":
-        from ..checkpoint.io import SafetensorsSource
+        from ..checkpoint.io import open_checkpoint
         cfg = ModelConfig.from_json(os.path.join(model_dir, "config.json"))
         device = device or f"cuda:{torch.cuda.current_device()}"
         with torch.cuda.device(device):
-            w = ModelBuilder(cfg, SafetensorsSource(model_dir), recipe=recipe, device=device, tp_rank=tp_rank,
-                             tp_world=tp_world).build()
+            src = open_checkpoint(model_dir, device)
+            try:
+                w = ModelBuilder(cfg, src, recipe=recipe, device=device, tp_rank=tp_rank, tp_world=tp_world).build()
+            finally:
+                if hasattr(src, "close"):
+                    src.close()
             return cls.from_weights(w, device, max_batch, max_seq, comm, prefill_chunk)
 
     @classmethod

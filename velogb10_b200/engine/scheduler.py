@@ -84,6 +84,14 @@ class Scheduler:
         self.policy = policy or MtpPolicy("auto" if self.has_mtp else "off", has_head=self.has_mtp)
         self.prefix_cache = prefix_cache
         self.ngram, self.tree, self.mtp_lanes = ngram_draft, tree_draft, mtp_lanes
+        if hasattr(runner, "tc_decode_attn"):
+            # Tree verification needs the path-indirect attention kernel; a tree column equals the same column of a
+            # chain verify bit for bit only if chains and decodes take that kernel too, so tree drafting turns the
+            # tensor-core decode attention off for this runner (and a scheduler without it restores the default).
+            want = runner.tc_decode_attn_default and not (tree_draft and ngram_draft > 0)
+            if want != runner.tc_decode_attn:
+                runner.tc_decode_attn = want
+                runner.graphs.clear()                      # captured steps hold the other kernel
         self.window = prefill_window
         self.zero_kv = zero_kv
         self.use_graphs = use_graphs and hasattr(runner, "replay_decode")

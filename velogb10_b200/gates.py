@@ -199,7 +199,20 @@ def gate_mtp_lossless(runner, cfg, n_new: int = 48, depth: int = 4, **kw) -> int
 
 
 def gate_tree(runner, cfg) -> int:
-    """Twin-branch equality and random tree vs per-path chain oracle."""
+    """Twin-branch equality and random tree vs per-path chain oracle. Runs the runner as a tree-drafting scheduler
+    does: every attention call through the path-indirect kernel (the tensor-core decode kernel has no path form, and
+    two kernels do not round alike)."""
+    tc = getattr(runner, "tc_decode_attn", None)
+    if tc is not None:
+        runner.tc_decode_attn = False
+    try:
+        return _gate_tree(runner, cfg)
+    finally:
+        if tc is not None:
+            runner.tc_decode_attn = tc
+
+
+def _gate_tree(runner, cfg) -> int:
     ctx = 30
     toks = _rand_tokens(cfg, ctx, 11)
     runner.zero_slot(0)
@@ -583,6 +596,8 @@ def dispatch(args: Dict[str, str]) -> int:
     runner.alloc_state(4, 4 + 17 + 4, max_seq)
     rc = 0
     for m in modes:
+        if hasattr(runner, "n_slots") and (runner.n_slots != 4 or runner.max_seq != max_seq):
+            runner.alloc_state(4, 4 + 17 + 4, max_seq)     # a gate that ran a scheduler re-sized the state for itself
         if m == "--probe-binv":
             r = gate_binv(runner, cfg)
         elif m == "--bench-verify":

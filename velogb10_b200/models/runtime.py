@@ -168,7 +168,8 @@ class GpuModel:
         self.tc_prefill_attn = os.environ.get("VELO_NO_TC_PREFILL_ATTN", "0") != "1" and not self.prefill_exact
         # decode / verify attention on the tensor cores (head_dim 256, bf16 cache, no tree paths); the CUDA-core
         # split kernel serves every other case
-        self.tc_decode_attn = os.environ.get("VELO_TC_DECODE_ATTN", "1") == "1"
+        self.tc_decode_attn_default = os.environ.get("VELO_TC_DECODE_ATTN", "1") == "1"
+        self.tc_decode_attn = self.tc_decode_attn_default
         self._prefill_ctx = None              # (slot, first position) while a prefill chunk is running
         self.kv_q4 = os.environ.get("VELO_KV_QUANT", "bf16").lower() == "q4"
         self._kv_scales = None                # (k scales, v scales) of the layer being run, 4-bit cache only
@@ -335,6 +336,12 @@ class GpuModel:
     def _upload(self, ws: Workspace, p: Plan):
         n = p.n
         assert n <= ws.cap, (n, ws.cap)
+        # a plan that names a cache row, lane or state slot outside the allocated state would write through it
+        if max(p.kv_row) >= self.max_seq or max(p.lens) > self.max_seq or max(p.kv_slot) >= self.n_slots \
+                or max(max(p.st_in), max(p.st_out)) >= self.n_state_slots or min(p.kv_row) < 0 or min(p.kv_slot) < 0:
+            raise ValueError(f"plan outside the allocated state: rows <= {max(p.kv_row)} of {self.max_seq}, lanes <= "
+                             f"{max(p.kv_slot)} of {self.n_slots}, state slots <= {max(max(p.st_in), max(p.st_out))} of "
+                             f"{self.n_state_slots}")
         path = [row + [0] * (MAX_PATH - len(row)) for row in p.path]
         cs = [s for s, _ in p.chains] + [0] * (n - len(p.chains))
         cl = [l for _, l in p.chains] + [0] * (n - len(p.chains))

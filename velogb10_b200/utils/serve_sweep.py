@@ -3,7 +3,10 @@ with prompt lengths uniform in [512, 8192] and a fixed output length, greedy, fo
 1 / 2 / 4 forced on a random-weight draft head, followed by a second wave whose prompts extend the first wave's (the
 prefix-cache hit path). Reports per cell: aggregate generated tok/s, decode-step latency percentiles (the verify-step
 latency when speculating), prefill tokens computed vs reused, and whether the speculative output is bit-identical to
-the non-speculative one (it must be: a width-N verify equals N decodes).
+the non-speculative one. A width-N verify equals N decodes bit for bit while both run on the same GEMM path (steps of
+at most 16 columns take the FP4-series GEMM, wider steps the f16-activation tensor-core GEMM): cells whose plain decode
+step is wider than 16 lanes while the speculative forest verifies 16 columns at a time are marked
+``mixed_gemm_paths`` and their comparison is informational (near-tie arg-max flips between two roundings).
 
   python -m velogb10_b200.utils.serve_sweep --model 27b --requests 4,8,16 --widths 0,1,2,4 --out-len 256
   python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \\
@@ -99,7 +102,8 @@ def main():
                    "prefill_tokens_computed": sch.stats["prefill_tokens"], "step_latency_ms": {k: round(v, 3) for k, v in sch.latency_percentiles().items()},
                    "decode_steps": sch.stats["decode_steps"], "mtp_steps": sch.stats["mtp_steps"],
                    "forest_steps": sch.stats["forest_steps"], "graph_steps": sch.stats.get("graph_steps", 0),
-                   "bit_identical_to_plain_greedy": (outs == base) if (wd > 0 and base is not None) else None}
+                   "bit_identical_to_plain_greedy": (outs == base) if (wd > 0 and base is not None) else None,
+                   "mixed_gemm_paths": bool(wd > 0 and R > 16)}
             if wd == 0:
                 # prefix-cache hit path: every request again, extended by its own first 32 generated tokens
                 t_pref0 = sch.stats["prefill_tokens"]
