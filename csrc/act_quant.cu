@@ -29,11 +29,12 @@ __global__ void __launch_bounds__(512) act_quant_kernel(const void* __restrict__
                                                           float* __restrict__ g0, __half* __restrict__ out16) {
   __shared__ float red[32];
   if (threadIdx.x == 0) trace(32);
+  if (gridDim.x > 1) cluster_arrive_relaxed();
   pdl_trigger();
   pdl_wait();
   if (threadIdx.x == 0) trace(33);
   // a cluster of gridDim.x CTAs shares one row: CTA c owns blocks [c * bpc, (c + 1) * bpc)
-  __shared__ float cl_amax;
+  __shared__ float cl_amax[8];
   const int n = blockIdx.y, C = gridDim.x, c = blockIdx.x;
   const int nblk = Kpad >> 4;
   const int bpc = (nblk + C - 1) / C;
@@ -101,10 +102,12 @@ __global__ void __launch_bounds__(512) act_quant_kernel(const void* __restrict__
   }
   amax = block_max(amax, red);
   if (C > 1) {
-    if (threadIdx.x == 0) cl_amax = amax;
+    // every CTA stores its maximum into slot c of every CTA of the cluster (its own included); one cluster barrier
+    // orders the stores before the reads, which are local, so nobody touches a peer's memory after the barrier
+    cluster_wait();                                        // pairs with the arrive at entry: every peer has started
+    if (threadIdx.x < C) dsmem_st_f32(dsmem_map(smem_u32(&cl_amax[c]), threadIdx.x), amax);
     cluster_sync_all();
-    const uint32_t a = smem_u32(&cl_amax);
-    for (int q = 0; q < C; ++q) amax = fmaxf(amax, dsmem_ld_f32(dsmem_map(a, (uint32_t)q)));
+    for (int q = 0; q < C; ++q) amax = fmaxf(amax, cl_amax[q]);
   }
   const float g = amax > 0.f ? amax / (6.0f * 448.0f) : 1.0f;
   if (threadIdx.x == 0 && c == 0) g0[n] = g;
@@ -113,7 +116,6 @@ __global__ void __launch_bounds__(512) act_quant_kernel(const void* __restrict__
     const int b = c * bpc + threadIdx.x + j * blockDim.x;
     if (b < b_end) quant_block(r[j], g, n, b, bq, ldb, sfb);
   }
-  if (C > 1) cluster_sync_all();          // peers may still be reading cl_amax
   if (threadIdx.x == 0) trace(2 * 16 + 2);
 }
 

@@ -162,6 +162,10 @@ VG_DEVINL uint32_t cluster_ctarank() {
 VG_DEVINL void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// Split form for "every CTA of the cluster has started": arrive at kernel entry, wait just before the first store
+// into a peer's shared memory (by then the wait returns at once).
+VG_DEVINL void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
+VG_DEVINL void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 VG_DEVINL uint32_t dsmem_map(uint32_t local_addr, uint32_t cta_rank) {
   uint32_t r;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(cta_rank));
@@ -171,6 +175,10 @@ VG_DEVINL float dsmem_ld_f32(uint32_t addr) {
   float v;
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
   return v;
+}
+
+VG_DEVINL void dsmem_st_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
 // ------------------------------------------------------------------ peer-memory flags

@@ -119,6 +119,8 @@ __global__ void __launch_bounds__(128) gdn_conv_chain_kernel(const __nv_bfloat16
   }
 }
 
+constexpr int COL_AMAX = 16;     // col_ctr[t]: arrivals of column t; col_ctr[COL_AMAX + t]: running maximum of its outputs
+
 template <int KD, int VD>
 __global__ void __launch_bounds__(VD) gdn_step_kernel(
     const float* __restrict__ qkv, const __nv_bfloat16* __restrict__ proj, int ldp, int off_z, int off_b, int off_a,
@@ -216,7 +218,8 @@ __global__ void __launch_bounds__(VD) gdn_step_kernel(
     const float o = ((hsum[0] + hsum[1]) + (hsum[2] + hsum[3])) * qsc;
     const float ss = block_sum(o * o, red);
     const float z = __bfloat162float(proj[(size_t)t * ldp + off_z + vh * VD + j]);
-    out[((size_t)t * nv + vh) * VD + j] = f32_to_f16_sat(o * rsqrtf(ss / (float)VD + eps) * nw * silu(z));
+    const __half o16 = f32_to_f16_sat(o * rsqrtf(ss / (float)VD + eps) * nw * silu(z));
+    out[((size_t)t * nv + vh) * VD + j] = o16;
     const int os = out_slot[t];
     if (os >= 0) {
       float* dp = S + (((size_t)os * nv + vh) * KD) * VD + j;
@@ -224,53 +227,62 @@ __global__ void __launch_bounds__(VD) gdn_step_kernel(
       for (int a = 0; a < KD; ++a) dp[(size_t)a * VD] = s[a];
     }
     loaded_from = t;
+    bool tail = false;
     if (bq) {
       // The head that completes column t quantises the whole row for the output projection (FP4 series), so
-      // no separate quantiser kernel runs. Heads publish with a fence + counter; the last one reads through L2.
+      // no separate quantiser kernel runs. Every head first folds the maximum of its own outputs into the column's
+      // running maximum (non-negative floats order like their bit patterns), then publishes with a fence + counter;
+      // the last one finds the row maximum ready and reads the row through L2 once.
+      const float hmax = aq::block_max(fabsf(__half2float(o16)), red);
       __threadfence();
       __syncthreads();
-      if (j == 0) is_last = atomicAdd(&col_ctr[t], 1u) == (unsigned)nv - 1u;
+      if (j == 0) {
+        atomicMax(&col_ctr[COL_AMAX + t], __float_as_uint(hmax));
+        __threadfence();
+        is_last = atomicAdd(&col_ctr[t], 1u) == (unsigned)nv - 1u;
+      }
       __syncthreads();
-      if (is_last) {
+      tail = is_last != 0;
+      if (tail) {
         __threadfence();
         const int K = nv * VD, nblk = ldb >> 3;          // ldb bytes per row = Kpad / 2
         const __half* row16 = out + (size_t)t * K;
-        float amax = 0.f;
-        for (int b = j; b * 16 < K; b += VD) {
-          const uint4 u0 = __ldcg(reinterpret_cast<const uint4*>(row16 + b * 16));
-          const uint4 u1 = __ldcg(reinterpret_cast<const uint4*>(row16 + b * 16) + 1);
-          const __half2* h0 = reinterpret_cast<const __half2*>(&u0);
-          const __half2* h1 = reinterpret_cast<const __half2*>(&u1);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float2 a = __half22float2(h0[i]), c = __half22float2(h1[i]);
-            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(c.x), fabsf(c.y))));
-          }
-        }
-        amax = aq::block_max(amax, red);
+        const float amax = __uint_as_float(__ldcg(&col_ctr[COL_AMAX + t]));
         const float gq = amax > 0.f ? amax / (6.0f * 448.0f) : 1.0f;
-        if (j == 0) { g0[t] = gq; col_ctr[t] = 0; }
-        for (int b = j; b < nblk; b += VD) {
-          float r[16];
-          if (b * 16 < K) {
-            const uint4 u0 = __ldcg(reinterpret_cast<const uint4*>(row16 + b * 16));
-            const uint4 u1 = __ldcg(reinterpret_cast<const uint4*>(row16 + b * 16) + 1);
-            const __half2* h0 = reinterpret_cast<const __half2*>(&u0);
-            const __half2* h1 = reinterpret_cast<const __half2*>(&u1);
+        if (j == 0) g0[t] = gq;
+        constexpr int PF = 4;                            // blocks whose loads are in flight together
+        for (int b0 = j; b0 < nblk; b0 += PF * VD) {
+          uint4 u[PF][2];
+#pragma unroll
+          for (int q = 0; q < PF; ++q) {
+            const int b = b0 + q * VD;
+            if (b < nblk && b * 16 < K) {
+              u[q][0] = __ldcg(reinterpret_cast<const uint4*>(row16 + b * 16));
+              u[q][1] = __ldcg(reinterpret_cast<const uint4*>(row16 + b * 16) + 1);
+            } else {
+              u[q][0] = make_uint4(0, 0, 0, 0);
+              u[q][1] = make_uint4(0, 0, 0, 0);
+            }
+          }
+#pragma unroll
+          for (int q = 0; q < PF; ++q) {
+            const int b = b0 + q * VD;
+            if (b >= nblk) break;
+            float r[16];
+            const __half2* h0 = reinterpret_cast<const __half2*>(&u[q][0]);
+            const __half2* h1 = reinterpret_cast<const __half2*>(&u[q][1]);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               const float2 a = __half22float2(h0[i]), c = __half22float2(h1[i]);
               r[2 * i] = a.x; r[2 * i + 1] = a.y; r[8 + 2 * i] = c.x; r[8 + 2 * i + 1] = c.y;
             }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) r[i] = 0.f;
+            aq::quant_block(r, gq, t, b, bq, ldb, sfb);
           }
-          aq::quant_block(r, gq, t, b, bq, ldb, sfb);
         }
       }
     }
     __syncthreads();   // qs/ks are rewritten by the next column
+    if (tail && j == 0) { col_ctr[t] = 0; col_ctr[COL_AMAX + t] = 0; }   // every thread of the tail has read the maximum
   }
   if (threadIdx.x == 0) trace(6 * 16 + 2);
 }
@@ -609,7 +621,8 @@ __global__ void __launch_bounds__(256) gdn_out_norm_kernel(const float* __restri
 }  // namespace
 
 // bq / sfb / g0 / col_ctr (all or none): also emit each column's output row as the FP4 activation series for
-// the output projection; col_ctr is a zero-initialised counter per column that the kernel leaves zeroed.
+// the output projection (at most 16 columns); col_ctr is 32 zero-initialised words (an arrival counter and a running
+// maximum per column) that the kernel leaves zeroed.
 // Needs column index < 16, (nv * vd) % 16 == 0 and ldb * 2 >= nv * vd with ldb % 128 == 0.
 extern "C" int vg_gdn_step(const float* qkv, const void* proj, int ldp, int off_z, int off_b, int off_a, float* S,
                            const float* A_log, const float* dt_bias, const float* norm_w, const int* chain_start,

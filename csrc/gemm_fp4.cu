@@ -68,6 +68,7 @@ constexpr int smem_total(int ns) { return ns * STAGE + (2 * ns + 1) * 8 + 16 + 1
 constexpr int SMEM_TOTAL = smem_total(NS);
 constexpr int CONV_MAX_CK = 4;            // taps the fused conv epilogue supports
 constexpr int CONV_SMEM = 16 * (CONV_MAX_CK - 1) * BM * 4;   // prefetched state samples, appended after SMEM_TOTAL
+constexpr int SPLITK_PUSH_MAX = CONV_MAX_CK;                 // split-K widths whose partial slots fit the same region
 
 // instruction descriptor for kind::mxf4nvf4, e2m1 x e2m1, ue4m3 scales, K = 64, both operands K-major
 __device__ __forceinline__ constexpr uint32_t idesc_fp4(int m, int n) {
@@ -142,6 +143,8 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
   auto slab_of = [&](int i) { int k = i + rot; return ks0 + (k >= nks ? k - nks : k); };
   if (threadIdx.x == 0) trace(4 * 16);
   pdl_trigger();
+  const bool splitk_push = S > 1 && S <= SPLITK_PUSH_MAX && !p.has_conv;
+  if (splitk_push) cluster_arrive_relaxed();   // waited for just before the partial columns are pushed to the leader
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NSK; ++i) { mbar_init(&full[i], 2); mbar_init(&empty[i], 1); }
@@ -235,9 +238,18 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
   float* conv_pre = reinterpret_cast<float*>(smem + smem_total(NSK) - 1024);      // [16][CONV_MAX_CK - 1][BM]
   float wk[CONV_MAX_CK];
   uint32_t n_state = 0;                    // 2 bits per column: samples that come from the rolling state
+  // The per-row weight scale and the columns' global scales are fetched while the main loop runs (the row scale is
+  // a weight: before the dependency wait), so the epilogue's stores do not start with two global round trips.
+  __shared__ float g0s[16];
+  float rsc_pre = 1.0f;
+  if (epi && p.row_scale) {
+    const int m_pre = mt * BM + m_local;
+    if (p.grouped ? (int)blockIdx.x * BM + m_local < p.M : m_pre < p.M) rsc_pre = p.row_scale[m_pre];
+  }
   if (epi) {
     pdl_wait();                            // before g0 / epoch reads and every output write
     ar_epoch = p.ar ? *p.comm.epoch + 1 : 0;
+    if (threadIdx.x - 128 < 16) g0s[threadIdx.x - 128] = p.g0[b_tile * 16 + (threadIdx.x - 128)];
     if (conv_row) {
       const VgConvEpi& cv = p.conv;
       const int ck = cv.ck, ch = mt * BM + m_local;
@@ -252,6 +264,7 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
         n_state |= (uint32_t)(j + 1) << (2 * t);
       }
     }
+    asm volatile("bar.sync 1, 128;" ::: "memory");          // g0s visible to the four epilogue warps
     if (mbar_wait(acc_full, 0)) {
       if (threadIdx.x == 128) trace(4 * 16 + 4);
       tc_fence_after();
@@ -271,11 +284,35 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
         }
       }
       have = true;
+      if (threadIdx.x == 128) trace(4 * 16 + 8);
     } else {
       fail(p.err, VG_ERR_MMA_WAIT, abort_flag);
     }
   }
-  if (S > 1) {
+  if (splitk_push) {
+    // Split-K reduction, push form: the other CTAs of the cluster store their partial columns into slots of the
+    // leader's shared memory (a region no pipeline stage uses, so a fast peer cannot disturb the leader's running
+    // MMAs); one cluster barrier orders the stores before the leader's reads, which are local and in rank order.
+    float* slots = conv_pre;                               // [S - 1][16][BM] in the leader; conv launches never come here
+    cluster_wait();                                        // pairs with the arrive at entry: the leader has started
+    if (z != 0 && epi && have) {
+      const uint32_t dst = dsmem_map(smem_u32(slots + (size_t)(z - 1) * 16 * BM), 0u);
+#pragma unroll
+      for (int n = 0; n < 16; ++n)
+        if (n < p.N) dsmem_st_f32(dst + (uint32_t)((n * BM + m_local) * 4), y[n]);
+    }
+    cluster_sync_all();
+    if (threadIdx.x == 128) trace(4 * 16 + 9);
+    if (z == 0 && epi && have) {
+      for (int s2 = 1; s2 < S; ++s2) {
+        const float* sl = slots + (size_t)(s2 - 1) * 16 * BM;
+#pragma unroll
+        for (int n = 0; n < 16; ++n)
+          if (n < p.N) y[n] += sl[n * BM + m_local];
+      }
+    }
+    if (threadIdx.x == 128) trace(4 * 16 + 10);
+  } else if (S > 1) {
     float* red = reinterpret_cast<float*>(smem);          // stage 0 is idle once every MMA has completed
     if (epi && have) {
 #pragma unroll
@@ -283,6 +320,7 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
         if (n < p.N) red[n * BM + m_local] = y[n];
     }
     cluster_sync_all();
+    if (threadIdx.x == 128) trace(4 * 16 + 9);
     if (z == 0 && epi && have) {
       const uint32_t red_addr = smem_u32(red);
       for (int s = 1; s < S; ++s) {
@@ -293,6 +331,7 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
       }
     }
     cluster_sync_all();
+    if (threadIdx.x == 128) trace(4 * 16 + 10);
   }
   const int m = mt * BM + m_local;
   if (epi && z == 0 && p.ar) {
@@ -302,7 +341,7 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
     const uint32_t e = ar_epoch;
     const int set = e & 1;
     const int et = threadIdx.x - 128;
-    const float rsc = (p.row_scale && m < p.M) ? p.row_scale[m] : 1.0f;
+    const float rsc = rsc_pre;
     if (et == 0) ar_failed = 0;
     if (p.ar != 2 && have && m < p.M) {
       for (int k = 0; k < c.world; ++k) {
@@ -310,7 +349,7 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
         float* dst = reinterpret_cast<float*>(c.data[peer] + c.slots_off + (size_t)(set * MAX_RANKS + c.rank) * c.slot_bytes);
 #pragma unroll
         for (int n = 0; n < 16; ++n)
-          if (n < p.N) dst[(size_t)n * p.M + m] = y[n] * p.g0[n] * rsc;
+          if (n < p.N) dst[(size_t)n * p.M + m] = y[n] * g0s[n] * rsc;
       }
     }
     if (p.ar == 3) {
@@ -322,7 +361,7 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
         float* dst = reinterpret_cast<float*>(c.data[c.rank] + c.mm_off + (size_t)set * c.mm_slot_bytes);
 #pragma unroll
         for (int n = 0; n < 16; ++n)
-          if (n < p.N) dst[(size_t)n * p.M + m] = y[n] * p.g0[n] * rsc;
+          if (n < p.N) dst[(size_t)n * p.M + m] = y[n] * g0s[n] * rsc;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (et == 0) {
@@ -341,7 +380,7 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
 #pragma unroll
           for (int n = 0; n < 16; ++n)
             if (n < p.N) {
-              const uint32_t bits = __float_as_uint(y[n] * p.g0[n] * rsc);
+              const uint32_t bits = __float_as_uint(y[n] * g0s[n] * rsc);
               asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst + (size_t)n * p.M + m), "r"(bits), "r"(e) : "memory");
             }
         }
@@ -385,17 +424,17 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
       float yv = 0.f;
 #pragma unroll
       for (int n = 0; n < 16; ++n) yv = n == b_col ? y[n] : yv;
-      const float v = yv * p.g0[b_tile * 16 + b_col] * (p.row_scale ? p.row_scale[m] : 1.0f);
+      const float v = yv * g0s[b_col] * rsc_pre;
       if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)out_row * p.ldo + mi] = v;
       else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)out_row * p.ldo + mi] = __float2bfloat16_rn(v);
     }
   } else if (epi && have && z == 0 && m < p.M) {
-    const float rsc = p.row_scale ? p.row_scale[m] : 1.0f;
+    const float rsc = rsc_pre;
     float* xs = reinterpret_cast<float*>(smem) + 16 * BM;     // second half of idle stage 0: [n][row] samples
 #pragma unroll
     for (int n = 0; n < 16; ++n) {
       if (n < p.N) {
-        const float v = y[n] * p.g0[n] * rsc;
+        const float v = y[n] * g0s[n] * rsc;
         if (p.out_f32) reinterpret_cast<float*>(p.out)[(size_t)n * p.ldo + m] = v;
         else reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)n * p.ldo + m] = __float2bfloat16_rn(v);
         if (conv_row) xs[n * BM + m_local] = __bfloat162float(__float2bfloat16_rn(v));   // what a reader of `out` sees
@@ -430,6 +469,7 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
       }
     }
   }
+  if (threadIdx.x == 128) trace(4 * 16 + 11);
   if (*abort_flag && threadIdx.x == 0) {
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
@@ -722,7 +762,7 @@ extern "C" int vg_gemm_fp4(const void* wt, const float* row_scale, const void* b
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((M + BM - 1) / BM, 1, splitk);
   cfg.blockDim = dim3(THREADS);
-  cfg.dynamicSmemBytes = SMEM_TOTAL + (p.has_conv ? CONV_SMEM : 0);
+  cfg.dynamicSmemBytes = SMEM_TOTAL + ((p.has_conv || splitk > 1) ? CONV_SMEM : 0);
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;

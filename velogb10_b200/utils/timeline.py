@@ -10,7 +10,8 @@ the records of block 0 of every kernel in time order (microseconds from the firs
 
 Event codes: kernel * 16 + event; kernels 1 = residual/RMSNorm/quantise, 2 = quantiser (SwiGLU or plain), 4 = FP4
 GEMM, 5 = conv, 6 = GDN recurrence; events 0 = entry, 1 = dependency wait returned, 2 = end, 3 = first operands
-landed, 4 = accumulator complete, 5 = prologue done, 6 = all-reduce values published.
+landed, 4 = accumulator complete, 5 = prologue done, 6 = all-reduce values published, 8 = accumulators read out of
+TMEM, 9 / 10 = split-K partials visible across the cluster / reduced, 11 = outputs stored.
 """
 from __future__ import annotations
 
@@ -21,7 +22,8 @@ import os
 import torch
 
 KERNELS = {1: "norm_q", 2: "quant", 4: "gemm", 5: "conv", 6: "gdn"}
-EVENTS = {0: "entry", 1: "waited", 2: "end", 3: "first_full", 4: "acc_full", 5: "prologue_done", 6: "ar_published"}
+EVENTS = {0: "entry", 1: "waited", 2: "end", 3: "first_full", 4: "acc_full", 5: "prologue_done", 6: "ar_published",
+          7: "ar_flags_seen", 8: "acc_in_registers", 9: "splitk_partials_visible", 10: "splitk_reduced", 11: "outputs_stored"}
 SETTERS = ("vg_trace_set_act_quant", "vg_trace_set_gdn", "vg_trace_set_gemm_fp4")
 
 
