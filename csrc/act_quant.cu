@@ -101,6 +101,7 @@ __global__ void __launch_bounds__(512) act_quant_kernel(const void* __restrict__
     }
   }
   amax = block_max(amax, red);
+  if (threadIdx.x == 0) trace(2 * 16 + 3);
   if (C > 1) {
     // every CTA stores its maximum into slot c of every CTA of the cluster (its own included); one cluster barrier
     // orders the stores before the reads, which are local, so nobody touches a peer's memory after the barrier
@@ -109,6 +110,7 @@ __global__ void __launch_bounds__(512) act_quant_kernel(const void* __restrict__
     cluster_sync_all();
     for (int q = 0; q < C; ++q) amax = fmaxf(amax, cl_amax[q]);
   }
+  if (threadIdx.x == 0) trace(2 * 16 + 4);
   const float g = amax > 0.f ? amax / (6.0f * 448.0f) : 1.0f;
   if (threadIdx.x == 0 && c == 0) g0[n] = g;
 #pragma unroll
@@ -268,6 +270,7 @@ __global__ void __launch_bounds__(512) add_rmsnorm_fp4_kernel(__nv_bfloat16* res
     }
   }
   ss = block_sum(ss, red);
+  if (threadIdx.x == 0) trace(1 * 16 + 3);
   const float inv = rsqrtf(ss / (float)h + eps);
   float amax = 0.f;
 #pragma unroll
@@ -290,6 +293,7 @@ __global__ void __launch_bounds__(512) add_rmsnorm_fp4_kernel(__nv_bfloat16* res
     }
   }
   amax = block_max(amax, red);
+  if (threadIdx.x == 0) trace(1 * 16 + 4);
   const float g = amax > 0.f ? amax / (6.0f * 448.0f) : 1.0f;
   if (threadIdx.x == 0) g0[n] = g;
 #pragma unroll

@@ -43,9 +43,19 @@ __device__ __forceinline__ void e2m1x8_to_f32(uint32_t w, float* o) {
   }
 }
 
+__device__ __forceinline__ float rcp_approx(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
 // Quantise one 16-element block (values in r, consumed) of row n, block index b, into the four terms.
 // Rows are grouped sixteen to a 64-row B tile: row n lives in tile n / 16 as column n % 16 (tile T starts at
 // bq row 64 T and at scale chunk T * (ldb / 128)).
+// This routine sits on the serial path of every decode-width producer (a thread runs its four terms back to back),
+// so it is written for a short dependent chain: the block maximum as a tree, one true division per call (the
+// per-term scale factors are exact multiples of 8 of it), the hardware reciprocal for the element scaling (the
+// residual is formed from the codes actually stored, so the series stays exact whatever the rounding of a term).
 __device__ __forceinline__ void quant_block(float* r, float g, int n, int b, uint8_t* __restrict__ bq, int ldb,
                                             uint8_t* __restrict__ sfb) {
   const int slab = b >> 4, step = (b & 15) >> 2, kb = b & 3;
@@ -54,14 +64,16 @@ __device__ __forceinline__ void quant_block(float* r, float g, int n, int b, uin
   bq += (size_t)tile * 64 * ldb;
   sfb += (size_t)tile * (ldb >> 7) * SF_BYTES;
   float gt = g;
+  float q6 = 1.0f / (6.0f * g);            // block maximum -> scale code, term 0; times 8 per further term
 #pragma unroll
   for (int t = 0; t < TERMS; ++t) {
-    float bmax = 0.f;
+    float m[8];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(r[i]));
-    const uint8_t sc = f32_to_e4m3(bmax / (6.0f * gt));
+    for (int i = 0; i < 8; ++i) m[i] = fmaxf(fabsf(r[2 * i]), fabsf(r[2 * i + 1]));
+    const float bmax = fmaxf(fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3])), fmaxf(fmaxf(m[4], m[5]), fmaxf(m[6], m[7])));
+    const uint8_t sc = f32_to_e4m3(bmax * q6);
     const float s = e4m3_to_f32(sc) * gt;
-    const float inv = s > 0.f ? 1.0f / s : 0.f;
+    const float inv = s > 0.f ? rcp_approx(s) : 0.f;
     float v[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = r[i] * inv;
@@ -75,6 +87,7 @@ __device__ __forceinline__ void quant_block(float* r, float g, int n, int b, uin
     *reinterpret_cast<uint2*>(bq + (size_t)row * ldb + b * 8) = make_uint2(w0, w1);
     sfb[(size_t)slab * SF_BYTES + step * 512 + (row & 31) * 16 + (row >> 5) * 4 + kb] = sc;
     gt *= 0.125f;
+    q6 *= 8.0f;
   }
 }
 

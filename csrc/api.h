@@ -144,7 +144,7 @@ int vg_gdn_chunk_prefill(const float* qkv, const void* proj, int ldp, int off_z,
 int vg_gdn_step(const float* qkv, const void* proj, int ldp, int off_z, int off_b, int off_a, float* S, const float* A_log,
                 const float* dt_bias, const float* norm_w, const int* chain_start, const int* chain_len, int n_chains,
                 const int* in_slot, const int* parent, const int* out_slot, void* out_f16, int nk, int nv, int kd, int vd,
-                float eps, void* bq, int ldb, void* sfb, float* g0, unsigned int* col_ctr, cudaStream_t stream);
+                float eps, void* bq, int ldb, void* sfb, float* g0, unsigned int* col_ctr, int* err, cudaStream_t stream);
 
 int vg_argmax(const float* logits, int N, int V, int ld, int* out, float* out_val, int idx_offset, cudaStream_t stream);
 int vg_penalty(float* logits, int N, int V, int ld, const int* toks, const int* counts, const int* n_toks, int max_toks,

@@ -21,6 +21,7 @@ enum VgErr : int {
   VG_ERR_PEER_WAIT = 4,     // a peer rank's flag did not arrive in time
   VG_ERR_BAD_ARG = 5,
   VG_ERR_DEQ_WAIT = 6,
+  VG_ERR_GRID_WAIT = 7,     // CTAs of one grid waited too long for each other
 };
 
 namespace vg {
@@ -188,6 +189,11 @@ constexpr int FLAG_STRIDE = 32;      // uint32 per flag line (128 bytes)
 
 VG_DEVINL void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+VG_DEVINL uint32_t ld_acquire_gpu(const unsigned int* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
 }
 VG_DEVINL uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;

@@ -119,7 +119,9 @@ __global__ void __launch_bounds__(128) gdn_conv_chain_kernel(const __nv_bfloat16
   }
 }
 
-constexpr int COL_AMAX = 16;     // col_ctr[t]: arrivals of column t; col_ctr[COL_AMAX + t]: running maximum of its outputs
+// col_ctr[t]: heads of column t counted in; [COL_AMAX + t]: running maximum of its outputs; [COL_DONE + t]: heads that
+// have finished their share of the row (all-resident form)
+constexpr int COL_AMAX = 16, COL_DONE = 32;
 
 template <int KD, int VD>
 __global__ void __launch_bounds__(VD) gdn_step_kernel(
@@ -128,10 +130,11 @@ __global__ void __launch_bounds__(VD) gdn_step_kernel(
     const float* __restrict__ norm_w, const int* __restrict__ chain_start, const int* __restrict__ chain_len,
     const int* __restrict__ in_slot, const int* __restrict__ parent, const int* __restrict__ out_slot,
     __half* __restrict__ out, int nk, int nv, float eps, uint8_t* __restrict__ bq, int ldb, uint8_t* __restrict__ sfb,
-    float* __restrict__ g0, unsigned int* __restrict__ col_ctr) {
+    float* __restrict__ g0, unsigned int* __restrict__ col_ctr, int all_resident, int* __restrict__ err) {
   if (threadIdx.x == 0) trace(96);
   pdl_trigger();
   __shared__ float red[32];
+  __shared__ float hs[VD];                // this head's outputs of the current column (all-resident row quantisation)
   __shared__ __align__(16) float ks[KD];
   __shared__ __align__(16) float qs[KD];
   __shared__ int is_last;
@@ -227,13 +230,19 @@ __global__ void __launch_bounds__(VD) gdn_step_kernel(
       for (int a = 0; a < KD; ++a) dp[(size_t)a * VD] = s[a];
     }
     loaded_from = t;
+    if (threadIdx.x == 0) trace(6 * 16 + 3);
     bool tail = false;
     if (bq) {
-      // The head that completes column t quantises the whole row for the output projection (FP4 series), so
-      // no separate quantiser kernel runs. Every head first folds the maximum of its own outputs into the column's
-      // running maximum (non-negative floats order like their bit patterns), then publishes with a fence + counter;
-      // the last one finds the row maximum ready and reads the row through L2 once.
+      // The output projection reads this row as the FP4 series, which needs the row's maximum (over all heads)
+      // before any block can be quantised. Every head folds the maximum of its own outputs into the column's running
+      // maximum (non-negative floats order like their bit patterns) and then counts itself in.
+      //  * all_resident (the grid fits on the GPU at once, so no CTA waits for one that cannot start): every head
+      //    waits (bounded) until all heads of the column are counted, then quantises its own VD outputs, so the row
+      //    is quantised by nv CTAs side by side; the last head to finish zeroes the column's words.
+      //  * otherwise the head counted in last quantises the whole row, reading it back through L2.
+      // Both forms run the same arithmetic on the same values: the bits do not depend on the form.
       const float hmax = aq::block_max(fabsf(__half2float(o16)), red);
+      if (all_resident) hs[j] = __half2float(o16);
       __threadfence();
       __syncthreads();
       if (j == 0) {
@@ -241,11 +250,44 @@ __global__ void __launch_bounds__(VD) gdn_step_kernel(
         __threadfence();
         is_last = atomicAdd(&col_ctr[t], 1u) == (unsigned)nv - 1u;
       }
+      const int K = nv * VD, nblk = ldb >> 3;          // ldb bytes per row = Kpad / 2
+      if (all_resident) {
+        if (j == 0) {
+          uint64_t t_start = 0;
+          for (int tries = 0; ld_acquire_gpu(&col_ctr[t]) < (unsigned)nv; ++tries) {
+            if (tries == 256) t_start = global_ns();
+            if (tries > 256 && (tries & 63) == 0 && global_ns() - t_start > 2000000ull) {      // 2 ms
+              if (err) atomicCAS(err, 0, VG_ERR_GRID_WAIT);
+              break;
+            }
+          }
+        }
+        __syncthreads();
+        const float amax = __uint_as_float(__ldcg(&col_ctr[COL_AMAX + t]));
+        const float gq = amax > 0.f ? amax / (6.0f * 448.0f) : 1.0f;
+        if (vh == 0 && j == 0) g0[t] = gq;
+        // this head's VD / 16 blocks; head 0 also writes the zero blocks that pad the row to the GEMM's K
+        constexpr int HB = VD / 16;
+        const int pad0 = K >> 4;
+        int b = -1;
+        if (j < HB) b = vh * HB + j;
+        else if (vh == 0 && pad0 + (j - HB) < nblk) b = pad0 + (j - HB);
+        if (b >= 0) {
+          float r[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) r[i] = j < HB ? hs[j * 16 + i] : 0.f;
+          aq::quant_block(r, gq, t, b, bq, ldb, sfb);
+        }
+        __syncthreads();
+        if (j == 0 && atomicAdd(&col_ctr[COL_DONE + t], 1u) == (unsigned)nv - 1u) {
+          col_ctr[t] = 0; col_ctr[COL_AMAX + t] = 0; col_ctr[COL_DONE + t] = 0;     // every head has read the maximum
+        }
+      } else {
       __syncthreads();
       tail = is_last != 0;
       if (tail) {
+        if (threadIdx.x == 0) trace(6 * 16 + 4);
         __threadfence();
-        const int K = nv * VD, nblk = ldb >> 3;          // ldb bytes per row = Kpad / 2
         const __half* row16 = out + (size_t)t * K;
         const float amax = __uint_as_float(__ldcg(&col_ctr[COL_AMAX + t]));
         const float gq = amax > 0.f ? amax / (6.0f * 448.0f) : 1.0f;
@@ -280,8 +322,10 @@ __global__ void __launch_bounds__(VD) gdn_step_kernel(
           }
         }
       }
+      }
     }
     __syncthreads();   // qs/ks are rewritten by the next column
+    if (tail && j == 0) trace(6 * 16 + 5);
     if (tail && j == 0) { col_ctr[t] = 0; col_ctr[COL_AMAX + t] = 0; }   // every thread of the tail has read the maximum
   }
   if (threadIdx.x == 0) trace(6 * 16 + 2);
@@ -621,25 +665,36 @@ __global__ void __launch_bounds__(256) gdn_out_norm_kernel(const float* __restri
 }  // namespace
 
 // bq / sfb / g0 / col_ctr (all or none): also emit each column's output row as the FP4 activation series for
-// the output projection (at most 16 columns); col_ctr is 32 zero-initialised words (an arrival counter and a running
-// maximum per column) that the kernel leaves zeroed.
+// the output projection (at most 16 columns); col_ctr is 48 zero-initialised words (two counters and a running
+// maximum per column) that the kernel leaves zeroed. `err` (may be null) receives VG_ERR_GRID_WAIT if the heads of a
+// column waited too long for each other.
 // Needs column index < 16, (nv * vd) % 16 == 0 and ldb * 2 >= nv * vd with ldb % 128 == 0.
 extern "C" int vg_gdn_step(const float* qkv, const void* proj, int ldp, int off_z, int off_b, int off_a, float* S,
                            const float* A_log, const float* dt_bias, const float* norm_w, const int* chain_start,
                            const int* chain_len, int n_chains, const int* in_slot, const int* parent, const int* out_slot,
                            void* out_f16, int nk, int nv, int kd, int vd, float eps, void* bq, int ldb, void* sfb,
-                           float* g0, unsigned int* col_ctr, cudaStream_t st) {
+                           float* g0, unsigned int* col_ctr, int* err, cudaStream_t st) {
   if (n_chains <= 0) return 0;
   if (bq && (!sfb || !g0 || !col_ctr || (ldb % 128) != 0 || ldb * 2 < nv * vd || ((nv * vd) % 16) != 0)) return -2;
   dim3 grid(nv, n_chains);
+  // Row quantisation by all heads side by side needs every CTA of the grid on the GPU at once (they wait for each
+  // other): at most one CTA per SM is assumed, whatever else is resident. VELO_GDN_RESIDENT_QUANT=0 turns it off.
+  static const bool resident_on = [] { const char* e = getenv("VELO_GDN_RESIDENT_QUANT"); return !(e && e[0] == '0'); }();
+  static const int n_sm = [] {
+    int dev = 0, n = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n;
+  }();
+  const int all_resident = (bq && resident_on && (long long)nv * n_chains <= n_sm) ? 1 : 0;
   const __nv_bfloat16* pj = static_cast<const __nv_bfloat16*>(proj);
   __half* o = static_cast<__half*>(out_f16);
   uint8_t* bqp = static_cast<uint8_t*>(bq);
   uint8_t* sfp = static_cast<uint8_t*>(sfb);
   if (kd == 128 && vd == 128)
-    launch_pdl(gdn_step_kernel<128, 128>, dim3(grid), dim3(128), 0, st, qkv, pj, ldp, off_z, off_b, off_a, S, A_log, dt_bias, norm_w, chain_start, chain_len, in_slot, parent, out_slot, o, nk, nv, eps, bqp, ldb, sfp, g0, col_ctr);
+    launch_pdl(gdn_step_kernel<128, 128>, dim3(grid), dim3(128), 0, st, qkv, pj, ldp, off_z, off_b, off_a, S, A_log, dt_bias, norm_w, chain_start, chain_len, in_slot, parent, out_slot, o, nk, nv, eps, bqp, ldb, sfp, g0, col_ctr, all_resident, err);
   else if (kd == 64 && vd == 64)
-    launch_pdl(gdn_step_kernel<64, 64>, dim3(grid), dim3(64), 0, st, qkv, pj, ldp, off_z, off_b, off_a, S, A_log, dt_bias, norm_w, chain_start, chain_len, in_slot, parent, out_slot, o, nk, nv, eps, bqp, ldb, sfp, g0, col_ctr);
+    launch_pdl(gdn_step_kernel<64, 64>, dim3(grid), dim3(64), 0, st, qkv, pj, ldp, off_z, off_b, off_a, S, A_log, dt_bias, norm_w, chain_start, chain_len, in_slot, parent, out_slot, o, nk, nv, eps, bqp, ldb, sfp, g0, col_ctr, all_resident, err);
   else
     return -3;
   return (int)cudaGetLastError();

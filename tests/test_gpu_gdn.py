@@ -138,3 +138,57 @@ def test_chunked_prefill_matches_exact_kernel(T):
         outs.append(o1)
     torch.cuda.synchronize()
     assert rel(outs[1], outs[0]) < 2e-3
+
+
+def test_step_kernel_row_quantisation_forms_agree_and_match_the_standalone_quantiser():
+    """The step kernel's fused FP4-series output: the form in which every head quantises its own share (small grids,
+    all CTAs resident) and the form in which the last head quantises the row (large grids) write the same bytes,
+    and both equal the stand-alone quantiser run on the kernel's f16 output. Counters are left zeroed."""
+    from velogb10_b200.ops import gemm as G, kernels as K, lib
+    torch.manual_seed(11)
+    dev = "cuda"
+    nk, nv, kd, vd = 16, 48, 128, 128
+    key_dim, value_dim = nk * kd, nv * vd
+    conv_dim = 2 * key_dim + value_dim
+    ldp = (conv_dim + value_dim + 2 * nv + 7) // 8 * 8
+    n = 8                                                   # 8 chains x 48 heads > 148 CTAs: last-head form
+    qkv = torch.randn(n, conv_dim, device=dev)
+    proj = torch.randn(n, ldp, device=dev).to(torch.bfloat16)
+    A_log = torch.randn(nv, device=dev) * 0.5
+    dt_bias = torch.randn(nv, device=dev) * 0.5
+    norm_w = torch.rand(vd, device=dev) + 0.5
+    S0 = torch.randn(n + 1, nv, kd, vd, device=dev) * 0.1
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    kp = (value_dim + 255) // 256 * 256
+    off = (conv_dim, conv_dim + value_dim, conv_dim + value_dim + nv)
+
+    def run(cols):
+        S = S0.clone()
+        o = torch.zeros(n, value_dim, dtype=torch.float16, device=dev)
+        bq = torch.zeros(64, kp // 2, dtype=torch.uint8, device=dev)
+        sfb = torch.zeros(kp // 256 * 2048, dtype=torch.uint8, device=dev)
+        g0 = torch.zeros(16, device=dev)
+        ctr = torch.zeros(48, dtype=torch.int32, device=dev)
+        # every column its own chain, reading slot c and writing nothing; only the first `cols` columns are launched
+        K.gdn_step(qkv, proj, *off, S, A_log, dt_bias, norm_w, i32(list(range(cols))), i32([1] * cols), cols,
+                   i32(list(range(n))), i32([-1] * n), i32([-1] * n), o, nk, nv, kd, vd, 1e-6, quant=(bq, sfb, g0, ctr))
+        torch.cuda.synchronize()
+        lib.check_err_word()
+        assert int(ctr.abs().sum()) == 0
+        return o, bq, sfb, g0
+
+    o_big, bq_big, sf_big, g_big = run(n)                   # 384 CTAs
+    o_small, bq_small, sf_small, g_small = run(2)           # 96 CTAs: every head quantises its share
+    rows = [t * 16 + c for t in range(4) for c in range(2)]
+    assert torch.equal(o_big[:2], o_small[:2])
+    assert torch.equal(bq_big[rows], bq_small[rows])
+    assert torch.equal(g_big[:2], g_small[:2])
+    # scale bytes of columns 0..1: chunk layout [slab][step][(row & 31) * 16 + (row >> 5) * 4 + kb]
+    sfv_b, sfv_s = sf_big.view(-1, 4, 32, 4, 4), sf_small.view(-1, 4, 32, 4, 4)
+    for r in rows:
+        assert torch.equal(sfv_b[:, :, r & 31, r >> 5], sfv_s[:, :, r & 31, r >> 5])
+    # the stand-alone quantiser on the same f16 rows
+    ref_bq, ref_sf, ref_g = (t.clone() for t in G.quantize_act_fp4(o_big, n, kp))
+    torch.cuda.synchronize()
+    allrows = [t * 16 + c for t in range(4) for c in range(n)]
+    assert torch.equal(ref_bq[allrows], bq_big[allrows]) and torch.equal(ref_g[:n], g_big[:n])

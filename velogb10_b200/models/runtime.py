@@ -227,7 +227,7 @@ class GpuModel:
         self.sampler = DeviceSampler(self.dev, weights.lm_head.m, cap=max(16, max_cols), comm=comm)
         # False: forwards return this rank's vocabulary shard of the logits (the device sampler merges shards itself)
         self.gather_logits = True
-        self.col_ctr = torch.zeros(32, dtype=torch.int32, device=self.dev)     # per column: arrival counter, running maximum
+        self.col_ctr = torch.zeros(48, dtype=torch.int32, device=self.dev)     # per column: two counters, running maximum
         self.ws_prefill: Optional[Workspace] = None
         self.state_ready = False
         self.graphs: Dict[Tuple[str, int], torch.cuda.CUDAGraph] = {}

@@ -135,14 +135,15 @@ def gdn_conv_chain(x, state, w, in_slot, parent, out_slot, out, n, conv_dim, ck)
 def gdn_step(qkv, proj, off_z, off_b, off_a, S, A_log, dt_bias, norm_w, chain_start, chain_len, n_chains,
              in_slot, parent, out_slot, out16, nk, nv, kd, vd, eps, quant=None):
     """``quant = (bq, sfb, g0, col_ctr)`` makes the kernel also emit every output row as the FP4 activation
-    series (the head that finishes a column last quantises it); ``col_ctr`` is 32 zeroed int32 words."""
+    series (the head that finishes a column last quantises it); ``col_ctr`` is 48 zeroed int32 words."""
     bq, sfb, g0, ctr = quant if quant is not None else (None, None, None, None)
-    assert ctr is None or ctr.numel() >= 32
+    assert ctr is None or ctr.numel() >= 48
     rc = _lib.lib().vg_gdn_step(ptr(qkv), ptr(proj), c_int(proj.stride(0)), c_int(off_z), c_int(off_b), c_int(off_a),
                                 ptr(S), ptr(A_log), ptr(dt_bias), ptr(norm_w), ptr(chain_start), ptr(chain_len),
                                 c_int(n_chains), ptr(in_slot), ptr(parent), ptr(out_slot), ptr(out16), c_int(nk),
                                 c_int(nv), c_int(kd), c_int(vd), c_float(eps), ptr(bq),
-                                c_int(bq.stride(0) if bq is not None else 0), ptr(sfb), ptr(g0), ptr(ctr), stream())
+                                c_int(bq.stride(0) if bq is not None else 0), ptr(sfb), ptr(g0), ptr(ctr),
+                                ptr(_lib.err_word(qkv.device)), stream())
     _lib.check(rc, "vg_gdn_step")
 
 

@@ -91,5 +91,5 @@ def check_err_word(device=None):
     if v != 0:
         w.zero_()
         names = {1: "TMA stage wait", 2: "free-stage wait", 3: "accumulator wait", 4: "peer flag wait",
-                 5: "bad argument", 6: "dequant stage wait"}
+                 5: "bad argument", 6: "dequant stage wait", 7: "wait for the other CTAs of the grid"}
         raise KernelError(f"a kernel reported a bounded-wait failure: {names.get(v, v)}")

@@ -24,6 +24,12 @@ import torch
 KERNELS = {1: "norm_q", 2: "quant", 4: "gemm", 5: "conv", 6: "gdn"}
 EVENTS = {0: "entry", 1: "waited", 2: "end", 3: "first_full", 4: "acc_full", 5: "prologue_done", 6: "ar_published",
           7: "ar_flags_seen", 8: "acc_in_registers", 9: "splitk_partials_visible", 10: "splitk_reduced", 11: "outputs_stored"}
+# events whose meaning differs per kernel, and the ones printed from whichever block records them (the GDN row
+# quantisation runs in the last head to finish, not in block 0)
+PER_KERNEL = {1 * 16 + 3: "sum_of_squares_reduced", 1 * 16 + 4: "row_max_reduced", 2 * 16 + 3: "cta_max_reduced",
+              2 * 16 + 4: "cluster_max_known", 6 * 16 + 3: "head_outputs_stored", 6 * 16 + 4: "row_quantise_begins",
+              6 * 16 + 5: "row_quantise_done"}
+ANY_BLOCK = {6 * 16 + 4, 6 * 16 + 5}
 SETTERS = ("vg_trace_set_act_quant", "vg_trace_set_gdn", "vg_trace_set_gemm_fp4")
 
 
@@ -85,8 +91,9 @@ def main():
             us = (t - t0) / 1000.0
             if us > args.until_us:
                 break
-            if bx == 0 and bz == 0:
-                print(f"{us:9.2f} {KERNELS.get(code >> 4, code >> 4):7} {EVENTS.get(code & 15, code & 15)}")
+            name = PER_KERNEL.get(code, EVENTS.get(code & 15, code & 15))
+            if (bx == 0 and bz == 0) or code in ANY_BLOCK:
+                print(f"{us:9.2f} {KERNELS.get(code >> 4, code >> 4):7} {name}" + (f" (block {bx})" if bx else ""))
         print("records", n)
     if args.tp:
         dist.destroy_process_group()
