@@ -168,6 +168,11 @@ __global__ void __launch_bounds__(VD) gdn_step_kernel(
     // q, k of the key head: l2-normalise (eps 1e-6), q also scaled by 1/sqrt(kd)
     const float* row = qkv + (size_t)t * conv_dim;
     float qv = 0.f, kv = 0.f;
+    // every global read of the column is issued here, ahead of the first barrier, so their latencies overlap
+    const float v = row[2 * key_dim + vh * VD + j];
+    const float bb = __bfloat162float(proj[(size_t)t * ldp + off_b + vh]);
+    const float aa = __bfloat162float(proj[(size_t)t * ldp + off_a + vh]) + dtb;
+    const float z = __bfloat162float(proj[(size_t)t * ldp + off_z + vh * VD + j]);
     for (int i = j; i < KD; i += VD) {
       qs[i] = row[kh * KD + i];
       ks[i] = row[key_dim + kh * KD + i];
@@ -178,9 +183,6 @@ __global__ void __launch_bounds__(VD) gdn_step_kernel(
     const float kn = block_sum(kv, red);
     const float qsc = rsqrtf(qn + 1e-6f) * rsqrtf((float)KD);
     const float ksc = rsqrtf(kn + 1e-6f);
-    const float v = row[2 * key_dim + vh * VD + j];
-    const float bb = __bfloat162float(proj[(size_t)t * ldp + off_b + vh]);
-    const float aa = __bfloat162float(proj[(size_t)t * ldp + off_a + vh]) + dtb;
     const float beta = sigmoidf(bb);
     const float sp_ = aa > 20.f ? aa : log1pf(__expf(aa));
     const float g = __expf(a_coef * sp_);
@@ -220,7 +222,6 @@ __global__ void __launch_bounds__(VD) gdn_step_kernel(
     }
     const float o = ((hsum[0] + hsum[1]) + (hsum[2] + hsum[3])) * qsc;
     const float ss = block_sum(o * o, red);
-    const float z = __bfloat162float(proj[(size_t)t * ldp + off_z + vh * VD + j]);
     const __half o16 = f32_to_f16_sat(o * rsqrtf(ss / (float)VD + eps) * nw * silu(z));
     out[((size_t)t * nv + vh) * VD + j] = o16;
     const int os = out_slot[t];
