@@ -36,6 +36,25 @@ from .sampling import SamplingParams
 PREFILL_WINDOW = 8192
 MTP_PRIME_CHUNK = 2048
 VERIFY_CKPTS = 17            # 16 verify columns + 1 scratch (tree root)
+class _phase:
+    """NVTX range around a scheduler phase (``VELO_NVTX=1``), so a timeline profiler shows admission / prefill and
+    decode steps as named spans; a no-op otherwise."""
+
+    def __init__(self, name: str, on: bool):
+        self.name, self.on = name, on
+
+    def __enter__(self):
+        if self.on:
+            import torch
+            torch.cuda.nvtx.range_push(self.name)
+
+    def __exit__(self, *exc):
+        if self.on:
+            import torch
+            torch.cuda.nvtx.range_pop()
+        return False
+
+
 MAX_FOREST_LANES = 5
 MAX_VERIFY_COLS = 16
 
@@ -84,6 +103,7 @@ class Scheduler:
         self.policy = policy or MtpPolicy("auto" if self.has_mtp else "off", has_head=self.has_mtp)
         self.prefix_cache = prefix_cache
         self.ngram, self.tree, self.mtp_lanes = ngram_draft, tree_draft, mtp_lanes
+        self.nvtx = os.environ.get("VELO_NVTX", "0") == "1" and hasattr(runner, "dev")
         if hasattr(runner, "tc_decode_attn"):
             # Tree verification needs the path-indirect attention kernel; a tree column equals the same column of a
             # chain verify bit for bit only if chains and decodes take that kernel too, so tree drafting turns the
@@ -160,12 +180,14 @@ class Scheduler:
             self.apply_cancels(None)
         if self.health_check is not None:
             self.health_check()
-        while self.queue and self.free_slots and len(self.lanes) < self.max_batch:
-            self._admit(self.queue.popleft())
+        with _phase("admit + prefill", self.nvtx and bool(self.queue)):
+            while self.queue and self.free_slots and len(self.lanes) < self.max_batch:
+                self._admit(self.queue.popleft())
         if not self.lanes:
             return False
         t0 = time.perf_counter()
-        self._decode_step()
+        with _phase(f"decode step, {len(self.lanes)} lanes", self.nvtx):
+            self._decode_step()
         self.step_ms.append((time.perf_counter() - t0) * 1e3)
         if self.trace_every and len(self.step_ms) % self.trace_every == 0:
             print("[trace] step latency ms " + " ".join(f"{k}={v:.3f}" for k, v in self.latency_percentiles().items()),
