@@ -194,3 +194,31 @@ def test_four_bit_kv_cache(monkeypatch):
         t.copy_(k)
     ld2, _ = gm.decode([toks[0]], [150], [0])
     assert ((ld2.float() - ld1.float()).norm() / ld1.float().norm()).item() < 0.08
+
+
+def test_debug_probes_print_and_do_not_change_results(monkeypatch, capfd):
+    """VELO_DEBUG_HASH / VELO_CAP_DEBUG are host-side reads: the same prompt hashes the same twice, and logits are the
+    ones of a run without the probes."""
+    from velogb10_b200.checkpoint.synthetic import SyntheticSource
+    from velogb10_b200.config import tiny_hybrid
+    from velogb10_b200.models.runtime import GpuModel
+    from velogb10_b200.models.weights import ModelBuilder
+    cfg = tiny_hybrid(mtp=False)
+    w = ModelBuilder(cfg, SyntheticSource(cfg, 0, "cuda", std=0.08), recipe="all", device="cuda").build()
+    toks = torch.randint(0, cfg.vocab_size, (40,), generator=torch.Generator().manual_seed(2)).tolist()
+    ref = GpuModel(w)
+    ref.alloc_state(1, 20, 128)
+    base = ref.prefill(0, toks)[0].clone()
+    monkeypatch.setenv("VELO_DEBUG_HASH", "1")
+    monkeypatch.setenv("VELO_CAP_DEBUG", "1")
+    gm = GpuModel(w)
+    gm.alloc_state(1, 20, 128)
+    a = gm.prefill(0, toks)[0].clone()
+    e1 = capfd.readouterr().err
+    gm.zero_slot(0)
+    b = gm.prefill(0, toks)[0].clone()
+    e2 = capfd.readouterr().err
+    assert torch.equal(a, base) and torch.equal(a, b)
+    h1 = [l for l in e1.splitlines() if "[dbghash]" in l]
+    assert len(h1) >= 3 and h1 == [l for l in e2.splitlines() if "[dbghash]" in l]
+    assert "capdbg layer 0 normed" in e1 and "ffn out" in e1

@@ -243,3 +243,48 @@ def test_per_expert_fuse_streams_one_layer_at_a_time():
     assert gu.shape == (E, 4, 4) and gu[2].eq(2).all()
     with pytest.raises(ValueError):
         list(io._iter_fused([("m.layers.0.mlp.experts.0.gate_proj.weight", torch.zeros(2, 4))], E))
+
+
+def test_fake_quant_and_dequant_at_load(tmp_path, monkeypatch):
+    """VELO_FAKE_QUANT keeps bf16 kernels but feeds them weights that carry the codec's error: the model then behaves
+    like the really quantised one, not like the bf16 one. VELO_DEQUANT_AT_LOAD decodes a quantised checkpoint to bf16
+    at load: every linear is bf16 and the values are those of the quantised load."""
+    from velogb10_b200.checkpoint import io
+    from velogb10_b200.checkpoint.synthetic import SyntheticSource, synthetic_state_dict
+    from velogb10_b200.config import ModelConfig, tiny_hybrid
+    from velogb10_b200.models.oracle import OracleModel
+    from velogb10_b200.models.weights import ModelBuilder
+    cfg = tiny_hybrid(mtp=False)
+    toks = torch.randint(0, cfg.vocab_size, (24,), generator=torch.Generator().manual_seed(1)).tolist()
+
+    def logits(w):
+        m = OracleModel(w)
+        m.alloc_state(1, 2, 64)
+        return m.prefill(0, toks)[0].float()
+
+    plain = logits(ModelBuilder(cfg, SyntheticSource(cfg, 0, std=0.08)).build())
+    quant = logits(ModelBuilder(cfg, SyntheticSource(cfg, 0, std=0.08), recipe="all,gdn:fp8").build())
+    monkeypatch.setenv("VELO_FAKE_QUANT", "all,gdn:fp8")
+    b = ModelBuilder(cfg, SyntheticSource(cfg, 0, std=0.08))
+    wf = b.build()
+    assert all(q.fmt == "bf16" for _, q in wf.linears()) and b.fake_quant_stats
+    assert {f for _, f, _ in b.fake_quant_stats} == {"nvfp4", "fp8"} and all(0 < e < 0.2 for _, _, e in b.fake_quant_stats)
+    fake = logits(wf)
+    monkeypatch.delenv("VELO_FAKE_QUANT")
+    d_fq = float((fake - quant).norm() / quant.norm())
+    d_pl = float((plain - quant).norm() / quant.norm())
+    assert d_fq < 0.25 * d_pl, (d_fq, d_pl)
+    # dequantise-at-load from a checkpoint in the recipe layout
+    out = str(tmp_path / "ck")
+    io.write_checkpoint(out, synthetic_state_dict(cfg, seed=0).items(), cfg.to_hf_dict(), "all,gdn:fp8")
+    cfg2 = ModelConfig.from_json(os.path.join(out, "config.json"))
+    wq = ModelBuilder(cfg2, io.SafetensorsSource(out)).build()
+    monkeypatch.setenv("VELO_DEQUANT_AT_LOAD", "1")
+    wd = ModelBuilder(cfg2, io.SafetensorsSource(out)).build()
+    assert any(q.fmt != "bf16" for _, q in wq.linears()) and all(q.fmt == "bf16" for _, q in wd.linears())
+    for (na, a), (nb, bq) in zip(wq.linears(), wd.linears()):
+        # (rows fused from several checkpoint tensors are re-encoded to the group's common format in the quantised
+        # load, so those agree to one more rounding rather than exactly)
+        x, y = a.dequant(torch.float32), bq.dequant(torch.float32)
+        assert na == nb and float((x - y).norm() / x.norm()) < 0.03, na
+    assert float((logits(wd) - logits(wq)).norm() / logits(wq).norm()) < 0.05

@@ -178,3 +178,36 @@ def test_policy_tuning_and_accept_rules():
     assert S.nucleus_host(torch.tensor([1.0, 3.0, 3.0]), SamplingParams(temperature=0.0)).ids == [1]
     toks_, cnts = S.penalty_list([1, 2, 2, 3, 2])
     assert toks_ == [2, 3, 1] and cnts == [3, 1, 1]
+
+
+def test_log_lines_draft_log_and_accept_curve(weights, tmp_path, monkeypatch):
+    """The [req] / [mtp] lines reach the given stream, every chain step lands in the JSONL draft log with the fed
+    token, drafts, verify predictions and accepted count, and the accept-by-depth curve file follows the policy."""
+    import io
+    import json
+    from velogb10_b200.engine import scheduler as sched_mod
+    log_path, curve_path = tmp_path / "drafts.jsonl", tmp_path / "curve.json"
+    monkeypatch.setenv("VELO_MTP_DRAFT_LOG", str(log_path))
+    monkeypatch.setenv("VELO_MTP_CURVE_FILE", str(curve_path))
+    monkeypatch.setattr(sched_mod, "MTP_LOG_EVERY", 5)
+    stream = io.StringIO()
+    prompts = _prompts(weights.cfg, 1, seed=3)
+    base, _, _ = _run(weights, prompts, max_new=24, max_batch=1)
+    outs, fins, sch = _run(weights, prompts, max_new=24, max_batch=1, policy=MtpPolicy("on", depth=3), log_stream=stream)
+    assert outs == base
+    text = stream.getvalue()
+    assert "[req] 1 slot 0 prompt" in text and "prefix miss" in text and "temp 0.0" in text
+    assert "done length generated 24" in text and "tok/s" in text
+    assert "[mtp] steps 5 depth 3 acceptance" in text and "accept@k" in text
+    assert list(sch.log)[-1].startswith("[req]")
+    steps = [json.loads(l) for l in open(log_path)]
+    assert len(steps) == sch.stats["mtp_steps"] > 0
+    emitted = []
+    for i, st in enumerate(steps):
+        assert st["step"] == i + 1 and len(st["drafts"]) == 2 and len(st["preds"]) == 3 and 0 <= st["nacc"] <= 2
+        assert st["drafts"][:st["nacc"]] == st["preds"][:st["nacc"]]           # accepted drafts match the verify
+        emitted += st["preds"][:st["nacc"] + 1]
+    assert outs[0][1:1 + len(emitted)] == emitted[:len(outs[0]) - 1]            # the log reproduces the emitted text
+    curve = json.load(open(curve_path))
+    assert curve["depth"] == 3 and curve["accept_by_depth"][0]["offered"] >= 5
+    assert all(0.0 <= c["rate"] <= 1.0 and c["cond_chain"] <= c["rate"] + 1e-12 for c in curve["accept_by_depth"])

@@ -1,5 +1,6 @@
 """Tool parsing, chat template, stream splitting and the HTTP API (CPU oracle backend)."""
 import json
+import os
 
 import pytest
 
@@ -194,3 +195,19 @@ def test_http_stop_string_that_matches_ends_both_modes(client):
     chunks = [json.loads(l[6:]) for l in lines[:-1]]
     assert chunks[-1]["choices"][0]["finish_reason"] == "stop"
     assert "".join(c["choices"][0]["delta"].get("content", "") for c in chunks if c["choices"]) == full[:i]
+
+
+def test_prompt_and_raw_output_dumps(client, monkeypatch, tmp_path, capsys):
+    """VELO_DUMP_PROMPT writes the rendered prompt of each request to a numbered file; with tools offered and no call
+    parsed the raw model output is logged even without VELO_DUMP_TOOLS."""
+    import tempfile
+    monkeypatch.setenv("VELO_DUMP_PROMPT", "1")
+    monkeypatch.setattr(tempfile, "tempdir", str(tmp_path))
+    tools = [{"type": "function", "function": {"name": "f", "parameters": {"type": "object", "properties": {}}}}]
+    body = {"model": "tiny-test", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 4, "temperature": 0,
+            "tools": tools}
+    assert client.post("/v1/chat/completions", json=body).status_code == 200
+    files = sorted(os.listdir(tmp_path))
+    assert files and files[0].startswith("velo_prompt_") and "hi" in open(os.path.join(tmp_path, files[0])).read()
+    err = capsys.readouterr().err
+    assert "[req] dumped prompt" in err and "[req] raw model output" in err

@@ -200,7 +200,7 @@ def run_server(args: Dict[str, str]):
     sched = Scheduler(runner, max_batch, max_seq, eos_ids=sorted(eos), policy=policy,
                       prefix_cache=on(args.get("--prefix-cache"), True), ngram_draft=int(args.get("--ngram-draft", "0")),
                       tree_draft=on(args.get("--tree-draft"), False), mtp_lanes=on(args.get("--mtp-lanes"), False),
-                      zero_kv="--zero-kv" in args, use_graphs="--no-decode-graphs" not in args)
+                      zero_kv="--zero-kv" in args, use_graphs="--no-decode-graphs" not in args, log_stream=sys.stderr)
     if has_mtp and r_table is None and policy.mode == "auto" and hasattr(runner, "time_decode_steps"):
         from .gates import calibrate_mtp_r
         try:

@@ -109,5 +109,18 @@ class MtpPolicy:
     def acceptance(self) -> float:
         return self.total_accepted / self.total_drafts if self.total_drafts else 0.0
 
+    def accept_curve(self) -> List[dict]:
+        """Cumulative accept-by-depth curve: per draft position its accepted / offered counts, their ratio and the
+        chance that a draft chain reaches that depth (the product of the rates so far), which is what drives the
+        yield (reference: src/batch.rs:1717-1741 ``dump_accept_curve``)."""
+        out, chain = [], 1.0
+        for j in range(MAX_DEPTH):
+            if not self.tried[j]:
+                break
+            rate = self.acc[j] / self.tried[j]
+            chain *= rate
+            out.append({"pos": j + 1, "accepted": self.acc[j], "offered": self.tried[j], "rate": rate, "cond_chain": chain})
+        return out
+
     def curve(self) -> List[float]:
         return [self.acc[j] / self.tried[j] if self.tried[j] else 0.0 for j in range(8)]

@@ -20,6 +20,7 @@ copy_state / zero_slot / compact_kv`` (the CUDA runtime or the fp32 CPU oracle).
 """
 from __future__ import annotations
 
+import json
 import os
 import sys
 import time
@@ -55,6 +56,7 @@ class _phase:
         return False
 
 
+MTP_LOG_EVERY = 50
 MAX_FOREST_LANES = 5
 MAX_VERIFY_COLS = 16
 
@@ -95,8 +97,24 @@ class Scheduler:
     def __init__(self, runner, max_batch: int, max_seq: int, eos_ids: Sequence[int] = (), policy: Optional[MtpPolicy] = None,
                  prefix_cache: bool = True, ngram_draft: int = 0, tree_draft: bool = False, mtp_lanes: bool = False,
                  prefill_window: int = PREFILL_WINDOW, zero_kv: bool = False, use_graphs: bool = True,
-                 alloc: bool = True):
+                 alloc: bool = True, log_stream=None):
         self.r = runner
+        # Log lines ([req] admission / completion, [mtp] policy moves and the periodic acceptance line) are kept in a
+        # bounded ring and, when a stream is given (the server passes stderr), written as they happen
+        # (reference: src/batch.rs:1002-1005, :1059-1061, :294-315, :1936-1947).
+        self.log_stream = log_stream
+        self.log: Deque[str] = deque(maxlen=4096)
+        # VELO_MTP_DRAFT_LOG=path: one JSON object per chain-MTP step {step, lane, pos, committed, drafts, preds, nacc}
+        # (preds empty where the verify samples); VELO_MTP_CURVE_FILE=path: cumulative accept-by-depth curve,
+        # rewritten every MTP_LOG_EVERY speculative steps (reference: src/batch.rs:520-527, :1700-1741).
+        self._draft_log = None
+        path = os.environ.get("VELO_MTP_DRAFT_LOG")
+        if path:
+            try:
+                self._draft_log = open(path, "w")
+            except OSError as e:
+                print(f"[mtp] cannot open VELO_MTP_DRAFT_LOG {path}: {e}", file=sys.stderr)
+        self._curve_path = os.environ.get("VELO_MTP_CURVE_FILE")
         self.max_batch, self.max_seq = max_batch, max_seq
         self.eos = set(int(e) for e in eos_ids)
         self.has_mtp = getattr(runner, "w", None) is not None and runner.w.mtp is not None
@@ -128,7 +146,6 @@ class Scheduler:
         self.next_id = 1
         self.stats = {"admitted": 0, "prefix_live": 0, "prefix_ckpt": 0, "prefix_miss": 0, "decode_steps": 0,
                       "mtp_steps": 0, "forest_steps": 0, "tree_steps": 0, "tokens": 0, "prefill_tokens": 0}
-        self.log: List[str] = []
         # True when something else (the lockstep driver) decides which cancellations a step sees, so that every
         # rank of a tensor-parallel group applies the same ones in the same step
         self.external_cancels = False
@@ -173,6 +190,35 @@ class Scheduler:
     def pending_cancels(self) -> List[int]:
         """Ids of running or queued requests whose owner cancelled them and that no step has acted on yet."""
         return [r.id for r in [l.req for l in self.lanes] + list(self.queue) if r.cancelled and not r.cancel_applied]
+
+    def _log(self, line: str):
+        self.log.append(line)
+        if self.log_stream is not None:
+            print(line, file=self.log_stream, flush=True)
+
+    def _log_mtp_step(self, lane: "Lane", pos: int, committed: int, drafts: Sequence[int], preds: Sequence[int], nacc: int):
+        """Book-keeping after a speculative step of one lane: the draft log line, the policy's own messages, and every
+        MTP_LOG_EVERY steps the acceptance line with the accept-by-depth curve (also written to the curve file)."""
+        step = self.stats["mtp_steps"]
+        if self._draft_log is not None:
+            self._draft_log.write(json.dumps({"step": step, "lane": lane.slot, "pos": pos, "committed": int(committed),
+                                              "drafts": [int(x) for x in drafts], "preds": [int(x) for x in preds],
+                                              "nacc": int(nacc)}) + "\n")
+            self._draft_log.flush()
+        while self.policy.log:
+            self._log(self.policy.log.pop(0))
+        if step and step % MTP_LOG_EVERY == 0:
+            pol = self.policy
+            curve = pol.accept_curve()
+            self._log(f"[mtp] steps {step} depth {pol.depth} acceptance {pol.acceptance():.3f} tokens/step "
+                       f"{pol.total_emitted / max(1, pol.total_steps):.2f} accept@k "
+                       + " ".join(f"{c['rate']:.2f}" for c in curve[:pol.depth - 1]))
+            if self._curve_path:
+                try:
+                    with open(self._curve_path, "w") as f:
+                        json.dump({"depth": pol.depth, "steps": step, "accept_by_depth": curve}, f)
+                except OSError:
+                    pass
 
     def step(self) -> bool:
         """Admit what fits, then run one decode step. Returns False when there was nothing to do."""
@@ -249,7 +295,11 @@ class Scheduler:
             self.slot_ckpt_seq[slot] = []
             self.stats["prefix_miss"] += 1
         req.prefix_hit = reuse
-        self.log.append(f"[req] {req.id} slot {slot} prompt {plen} prefix {kind} {reuse}")
+        p_ = req.params
+        self._log(f"[req] {req.id} slot {slot} prompt {plen} prefix {kind} {reuse} max_new {max_new}"
+                   + (f" (clamped from {req.max_new_tokens})" if max_new != req.max_new_tokens else "")
+                   + f" temp {p_.temperature} top_p {p_.top_p} top_k {p_.top_k} rep {p_.repetition_penalty} "
+                     f"pres {p_.presence_penalty} freq {p_.frequency_penalty}")
         # prefill the suffix in windows; force a window boundary at the checkpoint position
         ckpt_at = req.ckpt_at if (req.ckpt_at is not None and reuse < req.ckpt_at < plen) else None
         pos = reuse
@@ -344,7 +394,9 @@ class Scheduler:
                 self.free_slots.append(lane.slot)
                 # a cancelled request still gets its final event: whoever waits on it must be released
                 self._finish_req(lane.req, lane.done, len(lane.req.prompt), lane.generated)
-                self.log.append(f"[req] {lane.req.id} done {lane.done} generated {lane.generated}")
+                dt = time.time() - lane.req.t_first if lane.req.t_first else 0.0
+                self._log(f"[req] {lane.req.id} done {lane.done} generated {lane.generated}"
+                           + (f" in {dt:.2f}s ({lane.generated / dt:.1f} tok/s)" if dt > 0 else ""))
             else:
                 keep.append(lane)
         self.lanes = keep
@@ -517,6 +569,7 @@ class Scheduler:
         self._commit(lane, fed, bonus, drafts[:nacc] + [bonus], hid[nacc])
         self.policy.record_step(len(drafts), nacc, nacc + 1)
         self.stats["mtp_steps"] += 1
+        self._log_mtp_step(lane, pos0, cols[0], drafts, preds, nacc)
 
     def _argmax(self, logits: torch.Tensor) -> List[int]:
         """Greedy token per row (lowest index on ties), over the whole vocabulary even when ``logits`` is one rank's shard."""
@@ -574,6 +627,7 @@ class Scheduler:
         self._commit(lane, fed, nxt, drafts[:nacc] + [nxt], hid[nacc])
         self.policy.record_step(len(drafts), nacc, nacc + 1)
         self.stats["mtp_steps"] += 1
+        self._log_mtp_step(lane, pos0, cols[0], drafts, [], nacc)
 
     def _mtp_tree_step(self, lane: Lane):
         """Fork drafting: branch A is the head's greedy chain, branch B a pure n-gram continuation; the fork

@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import math
 import os
+import sys
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -168,6 +169,8 @@ class GpuModel:
         self.tc_prefill_attn = os.environ.get("VELO_NO_TC_PREFILL_ATTN", "0") != "1" and not self.prefill_exact
         # decode / verify attention on the tensor cores (head_dim 256, bf16 cache, no tree paths); the CUDA-core
         # split kernel serves every other case
+        self.debug_hash = os.environ.get("VELO_DEBUG_HASH", "0") == "1"
+        self.cap_debug = os.environ.get("VELO_CAP_DEBUG", "0") == "1"
         self.tc_decode_attn_default = os.environ.get("VELO_TC_DECODE_ATTN", "1") == "1"
         self.tc_decode_attn = self.tc_decode_attn_default
         self._prefill_ctx = None              # (slot, first position) while a prefill chunk is running
@@ -543,15 +546,21 @@ class GpuModel:
     def _layer(self, ws, L: LayerW, li, n, n_chains, seq_mode, direct, use_path, kc, vc, first_delta):
         c = self.cfg
         act = self._norm(ws, first_delta, L.input_norm, n)
+        if self.cap_debug:
+            self._cap_debug(f"layer {li} normed", ws.xn16, n)
         if L.attn is not None:
             self._attn(ws, L, n, kc, vc, direct, use_path, act=act)
         else:
             self._gdn(ws, L, li, n, n_chains, seq_mode, act=act)
+        if self.cap_debug and not self._pending_ar:
+            self._cap_debug(f"layer {li} mixer out", ws.delta, n)
         act = self._norm(ws, ws.delta, L.post_norm, n)
         if L.moe is not None:
             self._moe(ws, L.moe, n, act=act)
         else:
             self._mlp(ws, L.mlp, n, ws.delta, act=act)
+        if self.cap_debug and not self._pending_ar:
+            self._cap_debug(f"layer {li} ffn out", ws.delta, n)
 
     def _backbone(self, ws: Workspace, n: int, n_chains: int, seq_mode: bool, direct: bool, use_path: bool,
                   logits_rows: Optional[Tuple[int, int]] = None):
@@ -644,7 +653,39 @@ class GpuModel:
                 hs.append(ws.x[:n].clone())
             if last:
                 logits = self._full_logits(ws.logits[:1])[0]
+        if self.debug_hash:
+            self._dbg_probe_prefill(f"prefill.slot{slot}", slot, pos_start + N, ws.x[n - 1:n])
         return logits, (torch.cat(hs, 0) if want_hidden else None)
+
+    # ---------------------------------------------------------------- debugging probes (host side, env-gated)
+    def dbg_hash(self, tag: str, t: torch.Tensor):
+        """VELO_DEBUG_HASH=1: FNV-1a over the raw bytes of a tensor plus its first values, on stderr. Two runs (or two
+        ranks, or two code paths) that should agree bit for bit are compared by diffing these lines; synchronises, so
+        it is for hunting a divergence, not for production (reference: src/gpu.rs:6787-6837)."""
+        raw = t.detach().contiguous().view(torch.uint8).cpu().numpy().tobytes()
+        h = 0xCBF29CE484222325
+        for b in raw:
+            h = ((h ^ b) * 0x100000001B3) & 0xFFFFFFFFFFFFFFFF
+        first = [round(float(v), 6) for v in t.detach().reshape(-1)[:4].float().cpu()]
+        print(f"  [dbghash] {tag} n={t.numel()} fnv={h:016x} first={first}", file=sys.stderr, flush=True)
+
+    def _dbg_probe_prefill(self, tag: str, slot: int, plen: int, last_hidden: torch.Tensor):
+        self.dbg_hash(f"{tag}.hidden_last", last_hidden)
+        if self.kc is not None and self.kc.numel() and not self.kv_q4:
+            # only the rows the prompt wrote: the rest of a lane's cache holds whatever an earlier request left
+            self.dbg_hash(f"{tag}.k.L0[:{plen}]", self.kc[0, slot, :, :plen])
+            self.dbg_hash(f"{tag}.v.L0[:{plen}]", self.vc[0, slot, :, :plen])
+        if self.S is not None and self.S.numel():
+            self.dbg_hash(f"{tag}.gdn_state.L0", self.S[0, slot])
+
+    def _cap_debug(self, tag: str, t: torch.Tensor, n: int):
+        """VELO_CAP_DEBUG=1: absolute maximum and rms of an activation, to localise a numeric blow-up layer by layer
+        (eager steps only; reference: src/gpu.rs:3496-3502, :5899-5926)."""
+        if torch.cuda.is_current_stream_capturing():
+            return
+        v = t[:n].float()
+        print(f"  capdbg {tag}: absmax={float(v.abs().max()):.4f} rms={float(v.pow(2).mean().sqrt()):.6f}",
+              file=sys.stderr, flush=True)
 
     # ---------------------------------------------------------------- MTP head
     def mtp_forward(self, slot: int, tokens: Sequence[int], hidden: torch.Tensor, pos: Sequence[int],

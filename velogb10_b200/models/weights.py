@@ -15,8 +15,10 @@ The kernel-side tile-major layout is derived from this form by ``velogb10_b200.o
 """
 from __future__ import annotations
 
+import os
+import sys
 from dataclasses import dataclass, field
-from typing import Callable, Dict, List, Optional
+from typing import Callable, Dict, List, Optional, Tuple
 
 import torch
 
@@ -282,6 +284,15 @@ class ModelBuilder:
         self.recipe = parse_recipe(recipe)
         self.rank, self.world = tp_rank, tp_world
         self.ep = ep
+        # Debug loads (reference: src/gpu.rs:766-802, src/quant.rs:364-376):
+        #  VELO_FAKE_QUANT=<recipe>   bf16 weights of the named groups are round-tripped through the 4- / 8-bit codec and
+        #                             kept as bf16: the engine runs its bf16 path on values that carry the quantisation
+        #                             error, which tells whether a group needs precision before committing a checkpoint;
+        #  VELO_DEQUANT_AT_LOAD=1     quantised checkpoint tensors are decoded to bf16 at load: same numbers through the
+        #                             bf16 kernels, to prove the quantised kernels against.
+        self.fake_quant = parse_recipe(os.environ.get("VELO_FAKE_QUANT", "off"))
+        self.dequant_at_load = os.environ.get("VELO_DEQUANT_AT_LOAD", "0") not in ("", "0")
+        self.fake_quant_stats: List[Tuple[str, str, float]] = []       # (tensor, format, relative rms error)
 
     # -- raw access
     def _t(self, name: str) -> Optional[torch.Tensor]:
@@ -311,8 +322,9 @@ class ModelBuilder:
                 sc2 = sc2.view(torch.uint8)
             m, k = p2.shape[0], p2.shape[1] * 2
             rs = torch.full((m,), 1.0, dtype=torch.float32, device=self.device) / float(gs)
-            return QLinear("nvfp4", m, k, packed=p2.contiguous(), scales=sc2.to(self.device).contiguous(),
-                           row_scale=rs, experts=experts)
+            q = QLinear("nvfp4", m, k, packed=p2.contiguous(), scales=sc2.to(self.device).contiguous(),
+                        row_scale=rs, experts=experts)
+            return self._maybe_dequant(q)
         w = self._t(stem + suffix)
         if w is None and suffix:
             w = self._t(stem)
@@ -322,9 +334,27 @@ class ModelBuilder:
             rs = self._t(stem + ".weight_scale").float().reshape(-1).to(self.device)
             experts = int(w.shape[0]) if w.dim() == 3 else 1
             c = w.view(torch.uint8).reshape(-1, w.shape[-1]).to(self.device)
-            return QLinear("fp8", c.shape[0], c.shape[1], codes=c.contiguous(), row_scale=rs, experts=experts)
+            return self._maybe_dequant(QLinear("fp8", c.shape[0], c.shape[1], codes=c.contiguous(), row_scale=rs,
+                                               experts=experts))
         fmt = fmt_for(self.recipe, stem + suffix)
-        return QLinear.from_dense(w.to(self.device), fmt)
+        w = w.to(self.device)
+        fq = fmt_for(self.fake_quant, stem + suffix) if self.fake_quant is not None else "bf16"
+        if fq != "bf16" and w.dtype == torch.bfloat16:
+            rt = QLinear.from_dense(w, fq)
+            if rt.fmt == fq:
+                back = rt.dequant(torch.float32).reshape(w.shape)
+                err = float((back - w.float()).norm() / w.float().norm().clamp(min=1e-20))
+                self.fake_quant_stats.append((stem + suffix, fq, err))
+                return QLinear.from_dense(back.to(torch.bfloat16), "bf16")
+        return QLinear.from_dense(w, fmt)
+
+    def _maybe_dequant(self, q: QLinear) -> QLinear:
+        if not self.dequant_at_load:
+            return q
+        w = q.dequant(torch.bfloat16)
+        if q.experts > 1:
+            w = w.reshape(q.experts, q.m // q.experts, q.k)
+        return QLinear.from_dense(w, "bf16")
 
     # -- TP helpers
     def _shard_rows(self, q: QLinear, n_units: int, unit_rows: int) -> QLinear:
@@ -499,6 +529,13 @@ class ModelBuilder:
             mtp = MtpW(self.linear("mtp.fc"), self._f32("mtp.pre_fc_norm_hidden.weight"),
                        self._f32("mtp.pre_fc_norm_embedding.weight"),
                        self.layer("mtp.layers.0.", -1, True, shard=False), self._f32("mtp.norm.weight"))
+        if self.fake_quant_stats and self.rank == 0:
+            by_fmt: Dict[str, List[float]] = {}
+            for _, f, e in self.fake_quant_stats:
+                by_fmt.setdefault(f, []).append(e)
+            print("[load] fake-quant: " + ", ".join(f"{len(v)} tensors through {f} (relative rms error mean "
+                                                    f"{sum(v) / len(v):.4f}, max {max(v):.4f})" for f, v in by_fmt.items()),
+                  file=sys.stderr)
         return ModelWeights(c, embed, layers, final_norm, lm_head, mtp, self.rank, self.world,
                             self.recipe_str)
 

@@ -14,8 +14,12 @@ inbox and receive token events on asyncio queues.
 from __future__ import annotations
 
 import asyncio
+import itertools
 import json
+import os
 import queue
+import sys
+import tempfile
 import threading
 import time
 import uuid
@@ -276,6 +280,29 @@ def create_app(state: AppState):
     app = FastAPI(title="velogb10_b200")
     app.add_middleware(CORSMiddleware, allow_origins=["*"], allow_methods=["*"], allow_headers=["*"])
 
+    dump_counter = itertools.count()
+
+    def dump_prompt(prompt_text: str):
+        """VELO_DUMP_PROMPT=1: the exact rendered prompt of every request goes to a numbered file under the
+        temporary directory, so the bytes a model sees can be inspected or diffed across turns
+        (reference: src/server.rs:299-309)."""
+        if os.environ.get("VELO_DUMP_PROMPT"):
+            path = os.path.join(tempfile.gettempdir(), f"velo_prompt_{next(dump_counter)}.txt")
+            try:
+                with open(path, "w", encoding="utf-8") as f:
+                    f.write(prompt_text)
+                print(f"[req] dumped prompt ({len(prompt_text)} chars) -> {path}", file=sys.stderr, flush=True)
+            except OSError:
+                pass
+
+    def log_raw_output(content: str, tools, parsed):
+        """With tools offered, the model's literal output is what settles a "the tool ran but nothing happened"
+        report: logged on request (VELO_DUMP_TOOLS=1) and always when tools were offered and no call was parsed
+        (the model declined, or emitted a call the parser did not understand) (reference: src/server.rs:509-516,
+        :587-599)."""
+        if tools and (os.environ.get("VELO_DUMP_TOOLS") or not (parsed and parsed.tool_calls)):
+            print(f"[req] raw model output ({len(content)} chars): {content[:1200]!r}", file=sys.stderr, flush=True)
+
     @app.get("/health")
     async def health():
         return {"status": "ok"}
@@ -306,6 +333,7 @@ def create_app(state: AppState):
             prompt_text, ids = tok.apply_chat_template(messages, tools, enable_thinking, effort)
         except Exception as e:  # noqa: BLE001 - template failure is a 500 text body
             return PlainTextResponse(f"chat template error: {e}", status_code=500)
+        dump_prompt(prompt_text)
         if len(ids) >= state.max_seq_len:
             return JSONResponse(context_error(len(ids), state.max_seq_len), status_code=400)
         ckpt_at = tok.checkpoint_position(messages, tools, enable_thinking, effort, ids)
@@ -377,6 +405,7 @@ def create_app(state: AppState):
                     if splitter.stopped:          # also when the match only completed in the final flush
                         reason = "stop"
                     parsed = T.parse(splitter.content, tools) if T.has_tool_call(splitter.content) else None
+                    log_raw_output(splitter.content, tools, parsed)
                     if parsed and parsed.tool_calls:
                         yield chunk({"tool_calls": [c.to_openai(i) for i, c in enumerate(parsed.tool_calls)]})
                         reason = "tool_calls"
@@ -415,6 +444,7 @@ def create_app(state: AppState):
                 reason = "stop"
         reasoning, content = split_think(text, think_open, think_close, start_in_think)
         parsed = T.parse(content, tools)
+        log_raw_output(content, tools, parsed)
         msg: Dict[str, Any] = {"role": "assistant", "content": parsed.content or None}
         if reasoning:
             msg["reasoning_content"] = reasoning
