@@ -42,6 +42,10 @@ class DeviceSampler:
         self.h_f = self.h_rows.view(torch.float32)
         self.h_toks = self.host[N_ROWS * cap:N_ROWS * cap + cap * 64].view(cap, 64)
         self.h_cnts = self.host[N_ROWS * cap + cap * 64:].view(cap, 64)
+        # numpy views of the same pinned block: element writes through tensor indexing cost microseconds each, and a
+        # step writes a dozen per lane
+        self.h_rows, self.h_f = self.h_rows.numpy(), self.h_f.numpy()
+        self.h_toks, self.h_cnts = self.h_toks.numpy(), self.h_cnts.numpy()
         d_rows = self.devbuf[:N_ROWS * cap].view(N_ROWS, cap)
         d_f = d_rows.view(torch.float32)
         self.temp, self.top_p, self.u, self.u_acc, self.u_ver = d_f[R_TEMP], d_f[R_TOPP], d_f[R_U], d_f[R_UACC], d_f[R_UVER]
@@ -86,8 +90,8 @@ class DeviceSampler:
             if histories is not None and p.has_penalty and histories[r]:
                 toks, cnts = S.penalty_list(histories[r])
                 nt = len(toks)
-                self.h_toks[r, :nt] = torch.tensor(toks, dtype=torch.int32)
-                self.h_cnts[r, :nt] = torch.tensor(cnts, dtype=torch.int32)
+                self.h_toks[r, :nt] = toks
+                self.h_cnts[r, :nt] = cnts
                 any_pen = True
             hi[R_NTOK, r] = nt
         if lanes is not None:

@@ -15,6 +15,7 @@ import sys
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..config import ModelConfig
@@ -106,6 +107,7 @@ class Workspace:
         # all per-column int32 metadata lives in one buffer so a step needs a single host->device copy
         self.meta = i32(11, rows)
         self.meta_host = torch.zeros((11, rows), dtype=torch.int32).pin_memory()
+        self.meta_host_np = self.meta_host.numpy()        # same pinned memory, written without tensor constructors
         (self.tok, self.pos, self.kv_slot, self.kv_row, self.lens, self.base, self.st_in, self.parent, self.st_out,
          self.chain_start, self.chain_len) = [self.meta[i] for i in range(11)]
         self.path = i32(rows, MAX_PATH)
@@ -339,25 +341,27 @@ class GpuModel:
     def _upload(self, ws: Workspace, p: Plan):
         n = p.n
         assert n <= ws.cap, (n, ws.cap)
-        # a plan that names a cache row, lane or state slot outside the allocated state would write through it
-        if max(p.kv_row) >= self.max_seq or max(p.lens) > self.max_seq or max(p.kv_slot) >= self.n_slots \
-                or max(max(p.st_in), max(p.st_out)) >= self.n_state_slots or min(p.kv_row) < 0 or min(p.kv_slot) < 0:
-            raise ValueError(f"plan outside the allocated state: rows <= {max(p.kv_row)} of {self.max_seq}, lanes <= "
-                             f"{max(p.kv_slot)} of {self.n_slots}, state slots <= {max(max(p.st_in), max(p.st_out))} of "
-                             f"{self.n_state_slots}")
-        path = [row + [0] * (MAX_PATH - len(row)) for row in p.path]
         cs = [s for s, _ in p.chains] + [0] * (n - len(p.chains))
         cl = [l for _, l in p.chains] + [0] * (n - len(p.chains))
-        mh = ws.meta_host
+        # one numpy conversion for the eleven per-column rows (a tensor constructor per row costs tens of microseconds
+        # of host time on every step)
+        rows = np.asarray((p.tok, p.pos, p.kv_slot, p.kv_row, p.lens, p.base, p.st_in, p.parent, p.st_out, cs, cl), dtype=np.int32)
+        # a plan that names a cache row, lane or state slot outside the allocated state would write through it
+        if rows[3].max() >= self.max_seq or rows[4].max() > self.max_seq or rows[2].max() >= self.n_slots \
+                or max(rows[6].max(), rows[8].max()) >= self.n_state_slots or rows[3].min() < 0 or rows[2].min() < 0:
+            raise ValueError(f"plan outside the allocated state: rows <= {rows[3].max()} of {self.max_seq}, lanes <= "
+                             f"{rows[2].max()} of {self.n_slots}, state slots <= {max(rows[6].max(), rows[8].max())} of "
+                             f"{self.n_state_slots}")
         if ws.upload_done is not None:
             ws.upload_done.synchronize()        # the previous copy must have left the pinned buffer
-        for i, row in enumerate((p.tok, p.pos, p.kv_slot, p.kv_row, p.lens, p.base, p.st_in, p.parent, p.st_out, cs, cl)):
-            mh[i, :n] = torch.tensor(row, dtype=torch.int32)
+        ws.meta_host_np[:, :n] = rows
+        mh = ws.meta_host
         if mh.shape[1] <= 64:
             ws.meta.copy_(mh, non_blocking=True)
         else:
             ws.meta[:, :n].copy_(mh[:, :n], non_blocking=True)
         if any(p.path):
+            path = [row + [0] * (MAX_PATH - len(row)) for row in p.path]
             ws.path[:n].copy_(torch.tensor(path, dtype=torch.int32), non_blocking=True)
         if ws.upload_done is None:
             ws.upload_done = torch.cuda.Event()
