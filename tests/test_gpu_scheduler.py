@@ -52,6 +52,10 @@ def test_batching_speculation_and_prefix_cache_do_not_change_greedy_output(weigh
     for depth in (2, 4):
         spec, sch = _run(gm, prompts[:2], max_batch=1, policy=MtpPolicy("on", depth=depth))
         assert spec == solo[:2], depth
+        # the verifies ran as graph replays of that width, and without graphs the text is the same
+        assert sch.stats.get("verify_graph_steps", 0) == sch.stats["mtp_steps"] > 0
+        eager, sch_e = _run(gm, prompts[:2], max_batch=1, policy=MtpPolicy("on", depth=depth), use_graphs=False)
+        assert eager == solo[:2] and sch_e.stats.get("verify_graph_steps", 0) == 0
     tree, _ = _run(gm, prompts[:2], max_batch=1, policy=MtpPolicy("on", depth=3), tree_draft=True)
     assert tree == solo[:2]
     # a prompt that extends a served one re-uses the slot's state

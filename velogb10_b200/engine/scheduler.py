@@ -553,11 +553,18 @@ class Scheduler:
         room = self.max_seq - lane.pos - 1
         return max(1, min(self.policy.depth, cap, room))
 
+    def _verify_chain(self, lane: Lane, cols: Sequence[int]):
+        """Chain verify of one lane: a graph replay per width when the runner has one (same kernels, same bits)."""
+        if self.use_graphs and hasattr(self.r, "replay_verify") and 1 < len(cols) <= MAX_VERIFY_COLS:
+            self.stats["verify_graph_steps"] = self.stats.get("verify_graph_steps", 0) + 1
+            return self.r.replay_verify(lane.slot, cols, lane.pos, self.ckpt_base)
+        return self.r.verify(lane.slot, cols, lane.pos, self.ckpt_base)
+
     def _mtp_chain_step(self, lane: Lane):
         depth = self._depth_for(lane)
         drafts, _ = self._draft_chain(lane, depth - 1)
         cols = [lane.last_tok] + drafts
-        logits, hidden = self.r.verify(lane.slot, cols, lane.pos, self.ckpt_base)
+        logits, hidden = self._verify_chain(lane, cols)
         preds = self._greedy_preds(logits, lane, drafts)
         nacc = S.greedy_accept(preds, drafts)
         bonus = preds[nacc]
@@ -604,7 +611,7 @@ class Scheduler:
         depth = self._depth_for(lane)
         drafts, _ = self._draft_chain(lane, depth - 1)
         cols = [lane.last_tok] + drafts
-        logits, hidden = self.r.verify(lane.slot, cols, lane.pos, self.ckpt_base)
+        logits, hidden = self._verify_chain(lane, cols)
         if self.sampler is not None and logits.is_cuda:
             # accept / residual resample / bonus on the device: one read of (accepted, next token) comes back
             nacc, nxt = self.sampler.chain_accept(logits if logits.dtype == torch.float32 else logits.float(),

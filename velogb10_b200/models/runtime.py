@@ -790,6 +790,45 @@ class GpuModel:
         self.graphs[("decode", b)] = g
         return g
 
+    def capture_verify(self, n: int, ckpt_base: int):
+        """Capture a chain verify of ``n`` columns of one lane (reference: the verify-width graphs of
+        src/batch.rs:566-633). Lane, positions, tokens and checkpoint slots are read from the workspace's device arrays
+        at replay; only the width is fixed. Warm-up and capture run real steps on lane 0 at positions 0..n-1 writing the
+        checkpoint slots ``ckpt_base ..``: what they touch is saved and put back."""
+        ws = self.ws
+        self._upload(ws, Plan.chain(0, [0] * n, 0, ckpt_base))
+        touched = [0] + list(range(ckpt_base, ckpt_base + n))
+        saved = [(t, t[:, touched].clone()) for t in (self.S, self.conv) if t is not None]
+        kv = self._kv_tensors()
+        saved_kv = [(t, t[:, :1, :, :n].clone()) for t in kv]
+        torch.cuda.synchronize(self.dev)
+        s = torch.cuda.Stream(device=self.dev)
+        s.wait_stream(torch.cuda.current_stream(self.dev))
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                self._backbone(ws, n, 1, True, False, False)
+        torch.cuda.current_stream(self.dev).wait_stream(s)
+        torch.cuda.synchronize(self.dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._backbone(ws, n, 1, True, False, False)
+        for t, keep in saved:
+            t[:, touched] = keep
+        for t, keep in saved_kv:
+            t[:, :1, :, :n].copy_(keep)
+        self.graphs[("verify", n)] = g
+        return g
+
+    def replay_verify(self, slot: int, tokens: Sequence[int], pos_start: int, ckpt_base: int):
+        """``verify`` of a linear chain as a graph replay: same kernels, same bits, one launch."""
+        n = len(tokens)
+        g = self.graphs.get(("verify", n))
+        if g is None:
+            g = self.capture_verify(n, ckpt_base)
+        self._upload(self.ws, Plan.chain(slot, tokens, pos_start, ckpt_base))
+        g.replay()
+        return self._full_logits(self.ws.logits[:n]), self.ws.x[:n]
+
     def capture_decode_sample(self, b: int):
         """Capture decode + token selection for batch size ``b`` (reference: src/gpu.rs:3987-4081
         ``capture_decode_sample_graph``): backbone, then penalties / top-k / nucleus / draw from the parameter block the
