@@ -365,7 +365,7 @@ gemm_fp4_kernel(const Fp4Params p, const __grid_constant__ CUtensorMap tmap_b) {
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (et == 0) {
-        __threadfence_system();                       // the tile's rows are visible system-wide before its word is
+        asm volatile("fence.acq_rel.sys;" ::: "memory");   // release: the tile's rows are visible system-wide before its word is
         multimem_st_u32(c.mc + c.mmflags_off + ((size_t)(set * MAX_CTAS + (int)blockIdx.x) * MAX_RANKS + c.rank) * 4, e);
         trace(4 * 16 + 6);
       }
