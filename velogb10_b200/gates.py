@@ -285,14 +285,22 @@ def calibrate_mtp_r(runner, sched: Optional[Scheduler] = None, steps: int = 8) -
         _sync(runner)
         return (time.perf_counter() - t0) / steps
 
-    base = timed(lambda: runner.decode([toks[ctx]], [ctx], [0]))
+    # what the scheduler runs: graph replays of the decode step and of the chain verify where the runner has them
+    graphs = hasattr(runner, "replay_decode") and hasattr(runner, "replay_verify") and (sched is None or sched.use_graphs)
+    if graphs:
+        base = timed(lambda: runner.replay_decode([toks[ctx]], [ctx], [0]))
+    else:
+        base = timed(lambda: runner.decode([toks[ctx]], [ctx], [0]))
     table = {}
     h = hidden[-1:].clone()
     for d in AUTO_DEPTHS:
         def step():
             for j in range(d - 1):
                 runner.mtp_forward(0, [toks[ctx + j]], h, [ctx - 1 + j])
-            _, hid = runner.verify(0, toks[ctx:ctx + d], ctx, ckpt_base=1)
+            if graphs:
+                _, hid = runner.replay_verify(0, toks[ctx:ctx + d], ctx, 1)
+            else:
+                _, hid = runner.verify(0, toks[ctx:ctx + d], ctx, ckpt_base=1)
             hid = hid.clone()
             runner.copy_state(1, 0)
             runner.mtp_forward(0, toks[ctx + 1:ctx + d], hid[:d - 1], list(range(ctx, ctx + d - 1)))

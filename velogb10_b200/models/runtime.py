@@ -24,6 +24,7 @@ from ..ops import kernels as K
 from ..ops import lib as _lib
 from .weights import LayerW, ModelWeights, MoeW, MtpW, QLinear
 
+MTP_GRAPH_MAX_COLS = 8        # draft-head calls of at most this many columns are captured (one graph per width)
 MAX_PATH = 16
 
 
@@ -171,6 +172,7 @@ class GpuModel:
         self.tc_prefill_attn = os.environ.get("VELO_NO_TC_PREFILL_ATTN", "0") != "1" and not self.prefill_exact
         # decode / verify attention on the tensor cores (head_dim 256, bf16 cache, no tree paths); the CUDA-core
         # split kernel serves every other case
+        self.mtp_graphs = os.environ.get("VELO_NO_DECODE_GRAPHS", "0") != "1"    # draft-head steps as graph replays
         self.debug_hash = os.environ.get("VELO_DEBUG_HASH", "0") == "1"
         self.cap_debug = os.environ.get("VELO_CAP_DEBUG", "0") == "1"
         self.tc_decode_attn_default = os.environ.get("VELO_TC_DECODE_ATTN", "1") == "1"
@@ -707,11 +709,40 @@ class GpuModel:
         self._upload(ws, plan)
         if tok_dev is not None:
             ws.tok[:n].copy_(tok_dev[:n])
+        ws.hidden_keep[:n].copy_(hidden[:n])
+        # The device work below reads only workspace buffers (token ids, hidden rows, the uploaded plan) and is
+        # idempotent (the head's layer is an attention layer: re-running a column rewrites the same cache row), so
+        # small widths, the draft step and the re-prime after a verify, run as graph replays.
+        if self.mtp_graphs and n <= MTP_GRAPH_MAX_COLS and not torch.cuda.is_current_stream_capturing():
+            key = ("mtp", n, bool(draft_only))
+            g = self.graphs.get(key)
+            if g is None:
+                torch.cuda.synchronize(self.dev)
+                side = torch.cuda.Stream(device=self.dev)
+                side.wait_stream(torch.cuda.current_stream(self.dev))
+                with torch.cuda.stream(side):
+                    for _ in range(2):
+                        self._mtp_body(ws, n, draft_only)
+                torch.cuda.current_stream(self.dev).wait_stream(side)
+                torch.cuda.synchronize(self.dev)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self._mtp_body(ws, n, draft_only)
+                self.graphs[key] = g
+            g.replay()
+        else:
+            self._mtp_body(ws, n, draft_only)
+        if self.draft_head is not None:
+            return (self._draft_logits[:n] if draft_only else ws.logits[:n]), ws.x[:n]
+        return self._full_logits(ws.logits[:n]), ws.x[:n]
+
+    def _mtp_body(self, ws: Workspace, n: int, draft_only: bool):
+        """Device part of the draft head over the ``n`` columns staged in the workspace."""
+        m, c = self.w.mtp, self.cfg
         h = c.hidden_size
         K.embed_gather(self.w.embed, ws.tok, ws.mtp_e, n)
         K.add_rmsnorm(ws.mtp_e, None, m.norm_embed, c.rms_eps, n, out_bf=ws.x)
         ws.cat16[:n, :h].copy_(ws.x[:n])
-        ws.hidden_keep[:n].copy_(hidden[:n])
         K.add_rmsnorm(ws.hidden_keep, None, m.norm_hidden, c.rms_eps, n, out_bf=ws.x)
         ws.cat16[:n, h:].copy_(ws.x[:n])
         self._linear(m.fc, ws.cat16, n, ws.x)
@@ -724,18 +755,14 @@ class GpuModel:
         act = self._norm(ws, ws.delta, m.norm, n)
         if self.draft_head is not None:
             # score the draft vocabulary only; every other token gets -inf so arg-max / sampling stay inside it
-            dl = self._draft_logits[:n] if getattr(self, "_draft_logits", None) is not None else None
-            if dl is None:
+            if getattr(self, "_draft_logits", None) is None:
                 self._draft_logits = torch.zeros((ws.logits.shape[0], self.draft_head.m), dtype=torch.float32, device=self.dev)
-                dl = self._draft_logits[:n]
             self._linear(self.draft_head, ws.xn16, n, self._draft_logits, act=act, out_f32=True)
-            if draft_only:
-                return dl, ws.x[:n]
-            ws.logits[:n].fill_(float("-inf"))
-            ws.logits[:n].index_copy_(1, self.draft_ids, dl)
-            return ws.logits[:n], ws.x[:n]
+            if not draft_only:
+                ws.logits[:n].fill_(float("-inf"))
+                ws.logits[:n].index_copy_(1, self.draft_ids, self._draft_logits[:n])
+            return
         self._linear(self.w.lm_head, ws.xn16, n, ws.logits, act=act, out_f32=True)
-        return self._full_logits(ws.logits[:n]), ws.x[:n]
 
     # ---------------------------------------------------------------- vocabulary-parallel head
     @property
