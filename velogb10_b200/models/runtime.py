@@ -244,6 +244,16 @@ class GpuModel:
     def alloc_state(self, n_slots: int, n_state_slots: int, max_seq: int):
         c = self.cfg
         dev = self.dev
+        if getattr(self, "state_ready", False) and (self.n_slots, self.n_state_slots, self.max_seq) == (n_slots, n_state_slots, max_seq) \
+                and self._state_kv_q4 == self.kv_q4:
+            # the same shape again (a new scheduler over this runner): clear the state in place and keep the buffers, so
+            # the captured graphs, which hold their addresses, stay valid
+            for t in [self.S, self.conv, getattr(self, "mtp_kc", None), getattr(self, "mtp_vc", None), self.mtp_ks,
+                      self.mtp_vs] + self._kv_tensors():
+                if t is not None:
+                    t.zero_()
+            return
+        self._state_kv_q4 = self.kv_q4
         self.n_slots, self.n_state_slots, self.max_seq = n_slots, n_state_slots, max_seq
         attn_layers = [i for i, L in enumerate(self.w.layers) if L.attn]
         gdn_layers = [i for i, L in enumerate(self.w.layers) if L.gdn]
