@@ -56,6 +56,10 @@ def test_batching_speculation_and_prefix_cache_do_not_change_greedy_output(weigh
         assert sch.stats.get("verify_graph_steps", 0) == sch.stats["mtp_steps"] > 0
         eager, sch_e = _run(gm, prompts[:2], max_batch=1, policy=MtpPolicy("on", depth=depth), use_graphs=False)
         assert eager == solo[:2] and sch_e.stats.get("verify_graph_steps", 0) == 0
+    # several greedy lanes speculate together: their chains are packed into one forest verify (a graph per shape)
+    forest, sch_f = _run(gm, prompts, max_batch=4, policy=MtpPolicy("on", depth=3), mtp_lanes=True)
+    assert forest == solo and sch_f.stats["forest_steps"] > 0
+    assert any(k[0] == "forest" for k in gm.graphs)
     tree, _ = _run(gm, prompts[:2], max_batch=1, policy=MtpPolicy("on", depth=3), tree_draft=True)
     assert tree == solo[:2]
     # a prompt that extends a served one re-uses the slot's state

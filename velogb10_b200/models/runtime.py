@@ -626,7 +626,13 @@ class GpuModel:
         """Several lanes' chain verifies packed into one forward of at most ``max_cols`` columns:
         list of (slot, tokens, pos_start, ckpt_base) -> list of (logits, hidden) clones per lane."""
         plans = [Plan.chain(slot, toks, pos, ck) for slot, toks, pos, ck in lanes]
-        logits, hidden = self.forward(Plan.concat(plans))
+        widths = {pl.n for pl in plans}
+        if self.mtp_graphs and len(widths) == 1 and len(plans) * plans[0].n <= self.ws.cap \
+                and all(ck is not None for _, _, _, ck in lanes):
+            # equal chain widths (what the scheduler packs): one graph per (lanes, width)
+            logits, hidden = self._replay_forest(plans, min(ck for _, _, _, ck in lanes))
+        else:
+            logits, hidden = self.forward(Plan.concat(plans))
         outs, o = [], 0
         for pl in plans:
             outs.append((logits[o:o + pl.n].clone(), hidden[o:o + pl.n].clone()))
@@ -865,6 +871,41 @@ class GpuModel:
         self._upload(self.ws, Plan.chain(slot, tokens, pos_start, ckpt_base))
         g.replay()
         return self._full_logits(self.ws.logits[:n]), self.ws.x[:n]
+
+    def _replay_forest(self, plans: Sequence[Plan], ckpt_base: int):
+        """Several lanes' equal-width chain verifies packed into one forward, as a graph replay. Capture runs real steps
+        on lanes 0..p-1 at positions 0..w-1 with checkpoints from ``ckpt_base``: what they touch is saved and put back."""
+        ws = self.ws
+        p, w = len(plans), plans[0].n
+        n = p * w
+        key = ("forest", p, w)
+        g = self.graphs.get(key)
+        if g is None:
+            cap_plan = Plan.concat([Plan.chain(l, [0] * w, 0, ckpt_base + l * w) for l in range(p)])
+            self._upload(ws, cap_plan)
+            touched = list(range(p)) + list(range(ckpt_base, ckpt_base + n))
+            saved = [(t, t[:, touched].clone()) for t in (self.S, self.conv) if t is not None]
+            kv = self._kv_tensors()
+            saved_kv = [(t, t[:, :p, :, :w].clone()) for t in kv]
+            torch.cuda.synchronize(self.dev)
+            side = torch.cuda.Stream(device=self.dev)
+            side.wait_stream(torch.cuda.current_stream(self.dev))
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    self._backbone(ws, n, p, True, False, False)
+            torch.cuda.current_stream(self.dev).wait_stream(side)
+            torch.cuda.synchronize(self.dev)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._backbone(ws, n, p, True, False, False)
+            for t, keep in saved:
+                t[:, touched] = keep
+            for t, keep in saved_kv:
+                t[:, :p, :, :w].copy_(keep)
+            self.graphs[key] = g
+        self._upload(ws, Plan.concat(plans))
+        g.replay()
+        return self._full_logits(ws.logits[:n]), ws.x[:n]
 
     def capture_decode_sample(self, b: int):
         """Capture decode + token selection for batch size ``b`` (reference: src/gpu.rs:3987-4081
