@@ -222,3 +222,57 @@ def test_debug_probes_print_and_do_not_change_results(monkeypatch, capfd):
     h1 = [l for l in e1.splitlines() if "[dbghash]" in l]
     assert len(h1) >= 3 and h1 == [l for l in e2.splitlines() if "[dbghash]" in l]
     assert "capdbg layer 0 normed" in e1 and "ffn out" in e1
+
+
+def test_hy3_family_matches_oracle_and_verify_is_bitwise_sequential():
+    """The attention-only ``hy_v3`` family on the CUDA runtime: sigmoid + bias router, ungated shared expert, plain
+    norm weights, full-head rotary, bare q_proj, dense first layer, draft block: prefill / decode against the oracle,
+    a chain verify equal to sequential decodes bit for bit, and lossless speculation through the scheduler."""
+    from velogb10_b200.checkpoint.synthetic import SyntheticSource
+    from velogb10_b200.config import tiny_hy3
+    from velogb10_b200.engine.mtp import MtpPolicy
+    from velogb10_b200.engine.sampling import SamplingParams
+    from velogb10_b200.engine.scheduler import Request, Scheduler
+    from velogb10_b200.models.oracle import OracleModel
+    from velogb10_b200.models.runtime import GpuModel
+    from velogb10_b200.models.weights import ModelBuilder
+    from velogb10_b200.ops import lib
+    cfg = tiny_hy3(mtp=True)
+    recipe = "all,-router,-embed,-lmhead"
+    w = ModelBuilder(cfg, SyntheticSource(cfg, 0, "cuda", std=0.08), recipe=recipe, device="cuda").build()
+    orc = OracleModel(ModelBuilder(cfg, SyntheticSource(cfg, 0, "cuda", std=0.08), recipe=recipe, device="cuda").build())
+    gm = GpuModel(w, keep_canonical=True)
+    gm.alloc_state(2, 2 + 17, 256)
+    orc.alloc_state(2, 2 + 17, 256)
+    g = torch.Generator().manual_seed(6)
+    prompt = torch.randint(0, cfg.vocab_size, (40,), generator=g).tolist()
+    lg, _ = gm.prefill(0, prompt)
+    lo, _ = orc.prefill(0, prompt)
+    assert ((lg.float().cpu() - lo).norm() / lo.norm()) < 0.06
+    toks = [int(lo.argmax()), 3, 9, 27]
+    K0, V0 = gm.kc.clone(), gm.vc.clone()
+    lv, _ = gm.verify(0, toks, 40, ckpt_base=2)
+    lv = lv.clone()
+    lov, _ = orc.verify(0, toks, 40, ckpt_base=2)
+    assert ((lv.float().cpu() - lov).norm() / lov.norm()) < 0.06
+    gm.kc.copy_(K0); gm.vc.copy_(V0)
+    for t in range(4):
+        ld, _ = gm.decode([toks[t]], [40 + t], [0])
+        assert torch.equal(ld[0], lv[t]), t
+
+    def run(prompts, policy, max_batch):
+        sch = Scheduler(gm, max_batch, 160, eos_ids=[cfg.vocab_size - 1], policy=policy)
+        outs = [[] for _ in prompts]
+        for i, p in enumerate(prompts):
+            sch.submit(Request(p, 12, SamplingParams(temperature=0.0), on_token=outs[i].append))
+        sch.run_until_idle(10000)
+        torch.cuda.synchronize()
+        lib.check_err_word()
+        return outs, sch
+
+    prompts = [torch.randint(0, cfg.vocab_size - 2, (int(n),), generator=g).tolist() for n in (9, 21, 14)]
+    solo = [run([p], MtpPolicy("off", has_head=True), 1)[0][0] for p in prompts]
+    together, sch = run(prompts, MtpPolicy("off", has_head=True), 4)
+    assert together == solo and sch.stats.get("graph_steps", 0) > 0
+    spec, sch = run(prompts[:2], MtpPolicy("on", depth=3), 1)
+    assert spec == solo[:2] and sch.stats["mtp_steps"] > 0

@@ -51,15 +51,22 @@ def tensor_shapes(cfg: ModelConfig) -> Dict[str, Tuple[int, ...]]:
         m = pre + "mlp."
         if c.is_moe_layer(i):
             E, I = c.num_experts, c.moe_intermediate_size
-            s[m + "gate.weight"] = (E, h)
+            hy3 = c.family == "hy_v3"
+            # hy_v3 names the router and the (ungated) shared expert differently and adds a selection bias
+            # (reference: src/gpu.rs:1151-1197)
+            s[m + ("router.gate.weight" if hy3 else "gate.weight")] = (E, h)
+            if hy3 and c.router_expert_bias:
+                s[m + "expert_bias"] = (E,)
             s[m + "experts.gate_up_proj"] = (E, 2 * I, h)
             s[m + "experts.down_proj"] = (E, h, I)
             if c.shared_expert_intermediate_size > 0:
                 si = c.shared_expert_intermediate_size
-                s[m + "shared_expert.gate_proj.weight"] = (si, h)
-                s[m + "shared_expert.up_proj.weight"] = (si, h)
-                s[m + "shared_expert.down_proj.weight"] = (h, si)
-                s[m + "shared_expert_gate.weight"] = (1, h)
+                sh = m + ("shared_mlp." if hy3 else "shared_expert.")
+                s[sh + "gate_proj.weight"] = (si, h)
+                s[sh + "up_proj.weight"] = (si, h)
+                s[sh + "down_proj.weight"] = (h, si)
+                if not hy3:
+                    s[m + "shared_expert_gate.weight"] = (1, h)
         else:
             I = c.intermediate_size
             s[m + "gate_proj.weight"] = (I, h)
@@ -68,7 +75,15 @@ def tensor_shapes(cfg: ModelConfig) -> Dict[str, Tuple[int, ...]]:
 
     for i in range(c.num_layers):
         layer(f"layers.{i}.", i, c.is_full_attn(i))
-    if c.mtp_layers > 0:
+    if c.mtp_layers > 0 and c.family == "hy_v3":
+        # the draft block is one more decoder layer after the last (reference: src/gpu.rs:1262-1283)
+        mp = f"layers.{c.num_layers}."
+        s[mp + "eh_proj.weight"] = (h, 2 * h)
+        s[mp + "hnorm.weight"] = (h,)
+        s[mp + "enorm.weight"] = (h,)
+        s[mp + "final_layernorm.weight"] = (h,)
+        layer(mp, -1, True)
+    elif c.mtp_layers > 0:
         s["mtp.fc.weight"] = (h, 2 * h)
         s["mtp.pre_fc_norm_hidden.weight"] = (h,)
         s["mtp.pre_fc_norm_embedding.weight"] = (h,)
@@ -112,6 +127,8 @@ class SyntheticSource(TensorSource):
             e = min(n, o + step)
             out[o:e] = (torch.randn(e - o, generator=g, device=self.device, dtype=torch.float32) * self.std
                         ).to(torch.bfloat16)
+        if self.cfg.family == "hy_v3" and "norm" in key and key.endswith(".weight"):
+            out = (out.float() + 1.0).to(torch.bfloat16)     # plain (not zero-centred) RMSNorm weights in this family
         return out.reshape(shape)
 
 
@@ -119,4 +136,5 @@ def synthetic_state_dict(cfg: ModelConfig, seed: int = 0, device="cpu") -> Dict[
     """The full bf16 model as a prefixed state dict (small configs only)."""
     src = SyntheticSource(cfg, seed, device)
     # MTP tensors are stored unprefixed (``mtp.fc.weight``), everything else under the language-model prefix
-    return {(n if n.startswith("mtp.") else PREFIX + n): src.get(n) for n in src.names()}
+    pre = "model." if cfg.family == "hy_v3" else PREFIX
+    return {(n if n.startswith("mtp.") else pre + n): src.get(n) for n in src.names()}

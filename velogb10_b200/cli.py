@@ -55,7 +55,7 @@ modes
 
 model selection
   --model-dir DIR         checkpoint directory (config.json, safetensors, tokenizer files)
-  --synthetic NAME        seeded random-init model: tiny | tiny-moe | 27b | 35b-a3b | 122b-a10b
+  --synthetic NAME        seeded random-init model: tiny | tiny-moe | tiny-hy3 | 27b | 35b-a3b | 122b-a10b
   --recipe SPEC           load-time quantization for bf16 checkpoints / synthetic models (default all)
   --model-name NAME       id reported by /v1/models (default: derived from the directory)
   --tokenizer PATH        tokenizer.json (default: MODEL_DIR/tokenizer.json)

@@ -308,6 +308,13 @@ class ModelBuilder:
             raise KeyError(name)
         return t.to(self.device).float().contiguous()
 
+    def _norm_w(self, name: str) -> torch.Tensor:
+        """An RMSNorm weight in the zero-centred convention every norm kernel uses, ``y = x_hat * (1 + w)``. The
+        ``hy_v3`` family stores plain weights (``y = x_hat * w``): they are held as ``w - 1`` (reference:
+        src/gpu.rs:926-934), so kernels and oracle need no second flavour."""
+        w = self._f32(name)
+        return w - 1.0 if self.cfg.family == "hy_v3" else w
+
     def linear(self, stem: str, suffix: str = ".weight") -> QLinear:
         """Load one linear named ``stem`` (+``.weight`` for 2-D tensors; stacked experts have no
         suffix when unquantized)."""
@@ -400,8 +407,10 @@ class ModelBuilder:
             k = k.rows(k0 * hd, (k0 + nkv_l) * hd)
             v = v.rows(k0 * hd, (k0 + nkv_l) * hd)
             nh, nkv = nh_l, nkv_l
-        return AttnW(fuse_rows([q, k, v]), self._f32(pre + "q_norm.weight"),
-                     self._f32(pre + "k_norm.weight"), o, nh, nkv)
+        if not c.qk_norm:
+            raise NotImplementedError("attention without per-head q / k RMSNorm is not supported")
+        return AttnW(fuse_rows([q, k, v]), self._norm_w(pre + "q_norm.weight"),
+                     self._norm_w(pre + "k_norm.weight"), o, nh, nkv)
 
     def gdn(self, pre: str) -> GdnW:
         c = self.cfg
@@ -464,7 +473,8 @@ class ModelBuilder:
     def moe(self, pre: str, shard: bool = True) -> MoeW:
         c = self.cfg
         E, I, h = c.num_experts, c.moe_intermediate_size, c.hidden_size
-        router = self.linear(pre + "gate")
+        hy3 = c.family == "hy_v3"
+        router = self.linear(pre + ("router.gate" if hy3 else "gate"))
         if router.fmt != "bf16":
             router = QLinear.from_dense(router.dequant(torch.bfloat16), "bf16")
         gu = self.linear(pre + "experts.gate_up_proj", suffix="")
@@ -479,24 +489,26 @@ class ModelBuilder:
         gu.experts = dn.experts = n_local
         shared = None
         sg = None
-        if c.shared_expert_intermediate_size > 0 and self._t(pre + "shared_expert.gate_proj.weight") is not None \
-                or self._t(pre + "shared_expert.gate_proj.weight_packed") is not None:
+        sh = pre + ("shared_mlp." if hy3 else "shared_expert.")
+        if c.shared_expert_intermediate_size > 0 and self._t(sh + "gate_proj.weight") is not None \
+                or self._t(sh + "gate_proj.weight_packed") is not None:
             # under expert parallelism the shared expert is split like a dense tensor-parallel MLP: every rank adds its
             # partial (through the same gate) to its routed partial, and the one reduction of the layer sums both
             si = c.shared_expert_intermediate_size
             split = shard and self.world > 1 and self.ep and si % (16 * self.world) == 0
-            shared = self.mlp(pre + "shared_expert.", si, shard=split)
+            shared = self.mlp(sh, si, shard=split)
             shared.partial = split
-            sgl = self.linear(pre + "shared_expert_gate")
-            sg = sgl if sgl.fmt == "bf16" else QLinear.from_dense(sgl.dequant(torch.bfloat16), "bf16")
+            if not hy3:                     # hy_v3 adds its shared expert ungated
+                sgl = self.linear(pre + "shared_expert_gate")
+                sg = sgl if sgl.fmt == "bf16" else QLinear.from_dense(sgl.dequant(torch.bfloat16), "bf16")
         bias = self._t(pre + "expert_bias")
         return MoeW(router, gu, dn, shared, sg, None if bias is None else bias.float().to(self.device),
                     n_local, e_base)
 
     def layer(self, pre: str, i: int, full: bool, shard: bool = True) -> LayerW:
         c = self.cfg
-        lw = LayerW(self._f32(pre + "input_layernorm.weight"),
-                    self._f32(pre + "post_attention_layernorm.weight"))
+        lw = LayerW(self._norm_w(pre + "input_layernorm.weight"),
+                    self._norm_w(pre + "post_attention_layernorm.weight"))
         if full:
             lw.attn = self.attn(pre + "self_attn.", shard)
         else:
@@ -511,7 +523,7 @@ class ModelBuilder:
         c = self.cfg
         embed = self.linear("embed_tokens")
         layers = [self.layer(f"layers.{i}.", i, c.is_full_attn(i)) for i in range(c.num_layers)]
-        final_norm = self._f32("norm.weight")
+        final_norm = self._norm_w("norm.weight")
         if c.tie_word_embeddings or (self._t("lm_head.weight") is None
                                      and self._t("lm_head.weight_packed") is None):
             lm_head = embed
@@ -523,8 +535,16 @@ class ModelBuilder:
             assert per * self.world == V
             lm_head = lm_head.rows(self.rank * per, (self.rank + 1) * per)
         mtp = None
-        if c.mtp_layers > 0 and (self._t("mtp.fc.weight") is not None
-                                 or self._t("mtp.fc.weight_packed") is not None):
+        hy3_mtp = f"layers.{c.num_layers}."
+        if c.family == "hy_v3" and c.mtp_layers > 0 and (self._t(hy3_mtp + "eh_proj.weight") is not None
+                                                          or self._t(hy3_mtp + "eh_proj.weight_packed") is not None):
+            # hy_v3 keeps its draft block as decoder layer number num_layers: eh_proj = fc, hnorm / enorm = the two
+            # input norms, final_layernorm = the head's norm (reference: src/gpu.rs:1262-1283); replicated on every rank
+            mtp = MtpW(self.linear(hy3_mtp + "eh_proj"), self._norm_w(hy3_mtp + "hnorm.weight"),
+                       self._norm_w(hy3_mtp + "enorm.weight"), self.layer(hy3_mtp, -1, True, shard=False),
+                       self._norm_w(hy3_mtp + "final_layernorm.weight"))
+        elif c.mtp_layers > 0 and (self._t("mtp.fc.weight") is not None
+                                   or self._t("mtp.fc.weight_packed") is not None):
             # The draft head is replicated on every rank (reference: src/gpu.rs:2545-2547).
             mtp = MtpW(self.linear("mtp.fc"), self._f32("mtp.pre_fc_norm_hidden.weight"),
                        self._f32("mtp.pre_fc_norm_embedding.weight"),
