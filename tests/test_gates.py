@@ -1,8 +1,5 @@
 """Gate functions on the CPU oracle and the statistics of the gate runner."""
 import json
-import math
-
-import torch
 
 from velogb10_b200 import gate, gates
 from velogb10_b200.checkpoint.synthetic import SyntheticSource

@@ -8,7 +8,7 @@ holding the bf16 model in memory.
 from __future__ import annotations
 
 import zlib
-from typing import Dict, Iterator, List, Optional, Tuple
+from typing import Dict, List, Optional, Tuple
 
 import torch
 

@@ -9,7 +9,7 @@ when no depth beats plain decoding and probes again after ``RETRY`` plain steps
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional
 
 AUTO_DEPTHS = (2, 3, 4, 5, 6, 8)

@@ -19,7 +19,7 @@ Works on CPU tensors (oracle backend) and on CUDA tensors (device kernels build 
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch

@@ -13,7 +13,7 @@ import json
 import math
 import random
 import time
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Tuple
 
 import torch
 

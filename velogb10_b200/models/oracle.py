@@ -14,7 +14,7 @@ exact equality to check the state plumbing (slots, positions, checkpoints) of th
 from __future__ import annotations
 
 import math
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch

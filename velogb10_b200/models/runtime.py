@@ -9,10 +9,9 @@ decode, chain, tree and forest verify and prefill.
 """
 from __future__ import annotations
 
-import math
 import os
 import sys
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -22,7 +21,7 @@ from ..config import ModelConfig
 from ..ops import gemm as G
 from ..ops import kernels as K
 from ..ops import lib as _lib
-from .weights import LayerW, ModelWeights, MoeW, MtpW, QLinear
+from .weights import LayerW, ModelWeights, MoeW, QLinear
 
 MTP_GRAPH_MAX_COLS = 8        # draft-head calls of at most this many columns are captured (one graph per width)
 MAX_PATH = 16

@@ -35,7 +35,7 @@ def main():
 
     from ..config import preset
     from ..engine.llm import LLM
-    from ..models.runtime import Plan
+
     from ..ops import lib as vlib
 
     import os
