@@ -608,26 +608,26 @@ __global__ void __launch_bounds__(TPC * VD / CS) gdn_prefill_kernel(
       }
     }
     __syncthreads();
-    if (CS > 1) {
+    if constexpr (CS > 1) {
       // raw outputs of the batch, coalesced; the norm over the whole head runs in gdn_out_norm_kernel
       for (int i = tid; i < cnt * VC; i += NT) {
         const int tt = i / VC, cc = i % VC;
         o_raw[((size_t)(base + tt) * nv + vh) * VD + part * VC + cc] = ob[tt * VC + cc];
       }
-      continue;
-    }
-    // ---- output norm of the batch
-    for (int u = 0; u < TPW; ++u) {
-      const int tt = warp * TPW + u;
-      if (tt >= cnt) break;
-      const float ss = block_sum_by_warp<VD>(sq + tt * VD, lane);
-      if (lane == 0) ssb[tt] = ss;
-    }
-    __syncthreads();
-    for (int tt = h; tt < cnt; tt += TPC) {
-      const float z = __bfloat162float(z_[tt * VD + c]);
-      out[((size_t)(base + tt) * nv + vh) * VD + c] =
-          f32_to_f16_sat(ob[tt * VD + c] * rsqrtf(ssb[tt] / (float)VD + eps) * nw * silu(z));
+    } else {
+      // ---- output norm of the batch
+      for (int u = 0; u < TPW; ++u) {
+        const int tt = warp * TPW + u;
+        if (tt >= cnt) break;
+        const float ss = block_sum_by_warp<VD>(sq + tt * VD, lane);
+        if (lane == 0) ssb[tt] = ss;
+      }
+      __syncthreads();
+      for (int tt = h; tt < cnt; tt += TPC) {
+        const float z = __bfloat162float(z_[tt * VD + c]);
+        out[((size_t)(base + tt) * nv + vh) * VD + c] =
+            f32_to_f16_sat(ob[tt * VD + c] * rsqrtf(ssb[tt] / (float)VD + eps) * nw * silu(z));
+      }
     }
   }
 }
