@@ -93,7 +93,7 @@ def _serve_and_generate(backend_args, extra_env, boot_timeout):
 
 
 def test_two_rank_server_and_generate_cpu():
-    _serve_and_generate(["--cpu"], {}, 180)
+    _serve_and_generate(["--cpu"], {}, 420)
 
 
 @pytest.mark.gpu
