@@ -20,7 +20,9 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="27b")
     ap.add_argument("--layers", type=int, default=8)
-    ap.add_argument("--mode", default="decode", choices=["decode", "verify", "prefill"])
+    ap.add_argument("--mode", default="decode", choices=["decode", "verify", "prefill", "spec"],
+                    help="spec: one sampled decode (device penalties / top-k / nucleus draw), one draft-head step and one "
+                         "stochastic chain verify with the device accept kernel: the kernels of the speculative serving path")
     ap.add_argument("--steps", type=int, default=1)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--width", type=int, default=4)
@@ -48,7 +50,7 @@ def main():
         rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
         dist.init_process_group("nccl", device_id=dev)
         comm = TpComm(rank, world, dev)
-    cfg = preset(args.model, mtp=False)
+    cfg = preset(args.model, mtp=args.mode == "spec")
     if args.layers and args.layers < cfg.num_layers:
         cfg.num_layers = args.layers
         cfg.layer_types = cfg.layer_types[:args.layers]
@@ -65,6 +67,16 @@ def main():
             gm.decode([1 + i] * args.batch, [args.ctx + i] * args.batch, list(range(args.batch)))
         elif args.mode == "verify":
             gm.verify(0, list(range(1, 1 + args.width)), args.ctx, ckpt_base=args.batch)
+        elif args.mode == "spec":
+            from ..engine.sampling import SamplingParams
+            sp = SamplingParams(0.8, 0.9, 20, 1.1, 0.5, 0.1, seed=1)
+            logits, hidden = gm.decode([1 + i], [args.ctx], [0])
+            gm.sampler.pick(logits.float(), [sp], [[1, 2, 3, 2]], [7 + i])                     # sampled decode
+            h = hidden[:1].clone()
+            gm.mtp_forward(0, [2 + i], h, [args.ctx - 1])                                       # draft-head step
+            drafts = list(range(2, 1 + args.width))
+            lv, _ = gm.verify(0, [1 + i] + drafts, args.ctx, ckpt_base=args.batch)            # chain verify
+            gm.sampler.chain_accept(lv.float(), sp, [1, 2, 3, 2], drafts, 11 + i)               # accept / resample
         else:
             gm.prefill(1 % max(args.batch, 2), toks[:args.prompt], 0, want_hidden=False)
 
